@@ -1,0 +1,237 @@
+/*
+ * paged_attn_b200 — C ABI of the B200 (sm_100a) paged-attention library.
+ *
+ * Two tiers.
+ *
+ * Tier 1 keeps the seven entry points of the reference's own FFI for this
+ * path, with the same names, argument order and ownership rules
+ * (crates/mlx-sys/src/lib.rs:689-803, implemented by
+ * crates/mlx-sys/src/mlx.cpp:3796-4258).  The opaque `mlx_array` the reference
+ * passes across that boundary is, in this library, a small descriptor of a
+ * tensor in device memory (pa_array_* below build and inspect one).
+ *
+ * Tier 2 (`pa_*`) is what tier 1 is built on: plain device pointers, explicit
+ * sizes and strides, an explicit cudaStream_t (passed as void*), a status code
+ * from every call.  It is what a CUDA port of the crate's `metal` module
+ * (crates/mlx-paged-attn/src/metal/mod.rs:29-44) binds.
+ *
+ * All tensors are bf16 (dtype code 1) on the tuned path.  Pool layout is the
+ * reference's (crates/mlx-paged-attn/src/cache_engine.rs:58-106):
+ *   key   [num_blocks, num_kv_heads, head_size/8, block_size, 8]
+ *   value [num_blocks, num_kv_heads, head_size, block_size]
+ *
+ * Threading: the library keeps no global mutable state except a per-thread
+ * error string and a per-thread current device/stream for tier 1.  One cache
+ * handle is used by one stream at a time; different handles may be used
+ * concurrently.  Every launch is asynchronous on the given stream.
+ * No entry point aborts, traps or throws across the boundary.
+ */
+#ifndef PAGED_ATTN_B200_H_
+#define PAGED_ATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ------------------------------------------------------------- */
+typedef int32_t pa_status;
+enum {
+  PA_OK = 0,
+  PA_ERR_INVALID_ARG = 1,  /* null pointer, bad size/stride/alignment          */
+  PA_ERR_UNSUPPORTED = 2,  /* dtype / head size / block size not built         */
+  PA_ERR_OOM = 3,          /* device allocation failed                         */
+  PA_ERR_OUT_OF_RANGE = 4, /* a block id or slot outside the pool was seen     */
+  PA_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out               */
+  PA_ERR_CUDA = 6,         /* a CUDA runtime call failed                       */
+  PA_ERR_NCCL = 7
+};
+/* Text of the last error raised on the calling thread ("" if none).  The
+ * reference reports errors as Result<_, String> (crate) or null / silent
+ * return (crates/mlx-sys/src/mlx.cpp:3824, 3907-3908, 4051-4053).             */
+const char *pa_last_error_string(void);
+/* Library version: major*10000 + minor*100 + patch. */
+int32_t pa_version(void);
+
+/* ---- configuration and cache handle -------------------------------------- */
+/* Same six u32 fields as the reference (crates/mlx-sys/src/lib.rs:690-705,
+ * crates/mlx-sys/src/mlx.cpp:3796-3803). dtype: 0 f16, 1 bf16, 2 f32.         */
+typedef struct PagedAttnConfig {
+  uint32_t block_size;
+  uint32_t num_blocks;
+  uint32_t head_size;
+  uint32_t num_kv_heads;
+  uint32_t num_layers;
+  uint32_t dtype;
+} PagedAttnConfig;
+
+typedef struct PagedAttnCache PagedAttnCache; /* opaque */
+typedef struct mlx_array mlx_array;           /* opaque device-tensor view */
+
+/* ---- tier 1: the reference's FFI names ----------------------------------- */
+/* crates/mlx-sys/src/lib.rs:721, mlx.cpp:3823-3867.  Allocates zero-filled
+ * per-layer K and V pools on the calling thread's current device
+ * (pa_set_device).  Null on failure (see pa_last_error_string).              */
+PagedAttnCache *mlx_paged_attn_create_cache(const PagedAttnConfig *config);
+/* crates/mlx-sys/src/lib.rs:724, mlx.cpp:3870-3872. */
+void mlx_paged_attn_free_cache(PagedAttnCache *cache);
+/* crates/mlx-sys/src/lib.rs:734-750, mlx.cpp:3875-3884.  Returns a NEW handle
+ * that views the layer's pool; the caller deletes it with mlx_array_delete
+ * (as crates/mlx-core/src/transformer/paged_attention.rs:182-186 does).       */
+mlx_array *mlx_paged_attn_get_key_cache(PagedAttnCache *cache, uint32_t layer_idx);
+mlx_array *mlx_paged_attn_get_value_cache(PagedAttnCache *cache, uint32_t layer_idx);
+/* crates/mlx-sys/src/lib.rs:760-766, mlx.cpp:3900-4012.
+ * keys/values [num_tokens, num_kv_heads, head_size] bf16, slot_mapping
+ * [num_tokens] int64 (a negative slot is skipped).  Silent no-op on null or
+ * bad layer, like the reference; the reason is left in the error string.      */
+void mlx_paged_attn_reshape_and_cache(PagedAttnCache *cache, uint32_t layer_idx,
+                                      mlx_array *keys, mlx_array *values,
+                                      mlx_array *slot_mapping);
+/* crates/mlx-sys/src/lib.rs:782-791, mlx.cpp:4041-4162.
+ * queries [num_seqs, num_heads, head_size]; block_tables int32
+ * [num_seqs, max_blocks]; context_lens int32 [num_seqs].  Returns a new
+ * [num_seqs, num_heads, head_size] array that owns its device memory, or null. */
+mlx_array *mlx_paged_attn_forward(mlx_array *queries, mlx_array *key_cache,
+                                  mlx_array *value_cache, mlx_array *block_tables,
+                                  mlx_array *context_lens, float scale,
+                                  uint32_t block_size, uint32_t max_context_len);
+/* crates/mlx-sys/src/lib.rs:799-803, mlx.cpp:4170-4258.  block_mapping int64,
+ * [num_pairs, 2] or flat [2*num_pairs], pairs are (src, dst).                 */
+void mlx_paged_attn_copy_blocks(PagedAttnCache *cache, uint32_t layer_idx,
+                                mlx_array *block_mapping);
+
+/* The array shim standing in for the reference's mlx_array on this path.
+ * dtype codes: 0 f16, 1 bf16, 2 f32, 3 int32, 4 int64, 5 uint32.
+ * (crates/mlx-sys/src/lib.rs:332-355 declares the shape/dtype/delete calls.)  */
+mlx_array *pa_array_from_device(void *device_ptr, int32_t dtype, const int64_t *shape,
+                                size_t ndim);
+/* Copies host data into a new device array the handle owns
+ * (the role of crates/mlx-sys/src/lib.rs:19-28 mlx_array_from_int32/int64/...). */
+mlx_array *pa_array_from_host(const void *host_ptr, int32_t dtype, const int64_t *shape,
+                              size_t ndim);
+void *pa_array_data(mlx_array *a);
+size_t mlx_array_ndim(mlx_array *handle);
+void mlx_array_shape(mlx_array *handle, int64_t *out);
+int32_t mlx_array_dtype(mlx_array *handle);
+void mlx_array_delete(mlx_array *arr);
+/* Device and stream tier 1 runs on, per calling thread (default: device 0,
+ * the legacy default stream).                                                 */
+pa_status pa_set_device(int32_t device);
+pa_status pa_set_stream(void *cuda_stream);
+
+/* ---- tier 2: raw device pointers ------------------------------------------ */
+/* Allocate (and zero) the pools on `device`.  Replaces
+ * CacheEngine::initialize (crates/mlx-paged-attn/src/cache_engine.rs:58-106). */
+pa_status pa_cache_create(const PagedAttnConfig *config, int32_t device,
+                          PagedAttnCache **out_cache);
+/* Wrap pools the caller owns: key_ptrs/value_ptrs are num_layers device
+ * pointers, each 128-byte aligned, laid out as above.  Nothing is copied or
+ * freed by the library.                                                       */
+pa_status pa_cache_wrap(const PagedAttnConfig *config, int32_t device,
+                        void *const *key_ptrs, void *const *value_ptrs,
+                        PagedAttnCache **out_cache);
+pa_status pa_cache_free(PagedAttnCache *cache);
+/* Borrowed pointers into the pools (crates/mlx-paged-attn/src/cache_engine.rs
+ * key_cache()/value_cache() accessors). Null on bad arguments.                */
+void *pa_cache_key_ptr(PagedAttnCache *cache, uint32_t layer_idx);
+void *pa_cache_value_ptr(PagedAttnCache *cache, uint32_t layer_idx);
+pa_status pa_cache_get_config(const PagedAttnCache *cache, PagedAttnConfig *out);
+/* Synchronises `stream` and reports, then clears, the error word the kernels
+ * of this cache write instead of trapping (out-of-range block id or slot,
+ * a bounded wait that ran out).                                               */
+pa_status pa_cache_check_errors(PagedAttnCache *cache, void *cuda_stream);
+
+/* KV block write.  dispatch_reshape_and_cache_raw
+ * (crates/mlx-paged-attn/src/metal/reshape_and_cache.rs:177-270) over the
+ * kernel crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:33-98.
+ * key/value: bf16 [num_tokens, num_kv_heads, head_size] with row strides
+ * key_stride/value_stride in elements; slot_mapping: int64 [num_tokens] on
+ * the device, slot < 0 skipped, slot >= num_blocks*block_size skipped and
+ * reported through pa_cache_check_errors.                                     */
+pa_status pa_reshape_and_cache(PagedAttnCache *cache, uint32_t layer_idx,
+                               const void *key, const void *value,
+                               const int64_t *slot_mapping, int64_t num_tokens,
+                               int64_t key_stride, int64_t value_stride,
+                               void *cuda_stream);
+
+/* Copy-on-write block copy.  dispatch_copy_blocks_raw
+ * (crates/mlx-paged-attn/src/metal/copy_blocks.rs:96-99) over
+ * crates/mlx-paged-attn/metal/cache/copy_blocks.metal:6-36.
+ * block_mapping: int64 [num_pairs, 2] (src, dst) on the device.               */
+pa_status pa_copy_blocks(PagedAttnCache *cache, uint32_t layer_idx,
+                         const int64_t *block_mapping, int64_t num_pairs,
+                         void *cuda_stream);
+
+/* Scratch the attention calls need, for any batch on this cache's device
+ * (it depends only on the device's SM count and the head size).               */
+size_t pa_attention_workspace_bytes(const PagedAttnCache *cache);
+
+/* Single-token decode attention: one query per sequence, all query heads of a
+ * GQA group served from one read of the KV blocks.  Replaces
+ * dispatch_paged_attention_auto (crates/mlx-paged-attn/src/metal/
+ * paged_attention.rs:954-991; kernels crates/mlx-paged-attn/metal/attention/
+ * paged_attention.metal:760-1260) and mlx_paged_attn_forward
+ * (crates/mlx-sys/src/mlx.cpp:4041-4162).
+ *   out, q        bf16 [num_seqs, num_q_heads, head_size]; row strides
+ *                 q_stride / out_stride in elements
+ *   block_tables  int32 [num_seqs, max_blocks_per_seq], device
+ *   context_lens  int32 [num_seqs], device; counts the token written this step
+ *   softcap       1.0f = off (crates/.../paged_attention.metal:937-940)
+ *   workspace     >= pa_attention_workspace_bytes(), 256-byte aligned, device
+ * context_len 0 gives a zero row (mlx.cpp:4084-4088).                         */
+pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
+                                    void *out, const void *q,
+                                    const int32_t *block_tables,
+                                    const int32_t *context_lens, int32_t num_seqs,
+                                    int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                    int64_t q_stride, int64_t out_stride, float scale,
+                                    float softcap, void *workspace,
+                                    size_t workspace_bytes, void *cuda_stream);
+
+/* Variable-length paged attention: decode, speculative-verify and
+ * chunked-prefill sequences mixed in one call.  The reference has no such
+ * entry (its scheduler says so, crates/mlx-paged-attn/src/scheduler.rs:237-242);
+ * the semantics extend its decode (above) and its dense causal prefill
+ * (crates/mlx-core/src/transformer/block.rs:279-317):
+ * sequence s has context_lens[s] tokens in the pool after this step's write
+ * and q_len_s = cu_q_lens[s+1]-cu_q_lens[s] >= 0 queries that occupy the last
+ * q_len_s positions; query j attends keys [0, context_lens[s]-q_len_s+j].
+ *   out, q        bf16 [total_q, num_q_heads, head_size], packed by sequence
+ *   cu_q_lens     int32 [num_seqs+1] in HOST memory (the scheduler has it);
+ *                 the library uploads what its kernels need
+ *   max_context_len  upper bound of context_lens (0 = unknown)                */
+pa_status pa_paged_attention_varlen(PagedAttnCache *cache, uint32_t layer_idx,
+                                    void *out, const void *q,
+                                    const int32_t *block_tables,
+                                    const int32_t *context_lens,
+                                    const int32_t *cu_q_lens_host, int32_t num_seqs,
+                                    int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                    int64_t q_stride, int64_t out_stride, float scale,
+                                    float softcap, int32_t max_context_len,
+                                    void *workspace, size_t workspace_bytes,
+                                    void *cuda_stream);
+
+/* One decode step of one layer from HOST buffers, the order
+ * TransformerBlock::forward_paged keeps (crates/mlx-core/src/transformer/
+ * block.rs:223-232): write the new tokens' K/V, then attend with context
+ * lengths that already count them.  Copies q/k/v/slots/tables/lens to the
+ * device, launches both kernels, copies `out` back and synchronises.  Staging
+ * buffers are kept in the cache handle and grow on demand.                    */
+pa_status pa_decode_step_host(PagedAttnCache *cache, uint32_t layer_idx,
+                              void *out_host, const void *q_host, const void *k_host,
+                              const void *v_host, const int64_t *slot_mapping_host,
+                              const int32_t *block_tables_host,
+                              const int32_t *context_lens_host, int32_t num_seqs,
+                              int32_t num_q_heads, int32_t max_blocks_per_seq,
+                              float scale, float softcap);
+
+/* Number of kernels this library has launched from the calling process
+ * (all threads), for launch accounting in benchmarks.                         */
+uint64_t pa_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAGED_ATTN_B200_H_ */

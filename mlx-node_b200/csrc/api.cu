@@ -1,0 +1,658 @@
+// C ABI of the library (declared in include/paged_attn_b200.h): cache handle,
+// argument validation, launch orchestration, the reference-named tier-1 entry
+// points and the host-buffer decode step.  No tensor-library types cross this
+// boundary and there is no CPU fallback: without a CUDA device every compute
+// entry fails with PA_ERR_CUDA.
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/paged_attn_b200.h"
+#include "pa_common.cuh"
+
+namespace {
+
+thread_local std::string t_err;
+thread_local int t_device = 0;
+thread_local cudaStream_t t_stream = nullptr;
+
+pa_status fail(pa_status code, const std::string &msg) {
+  t_err = msg;
+  return code;
+}
+pa_status cuda_fail(cudaError_t e, const char *what) {
+  return fail(e == cudaErrorMemoryAllocation ? PA_ERR_OOM : PA_ERR_CUDA,
+              std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define PA_CUDA(call)                                        \
+  do {                                                       \
+    cudaError_t e_ = (call);                                 \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call);      \
+  } while (0)
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    ok = prev == dev || cudaSetDevice(dev) == cudaSuccess;
+    if (prev == dev) prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace
+
+struct PagedAttnCache {
+  PagedAttnConfig cfg{};
+  int device = 0;
+  bool owns = false;
+  int num_sms = 0;
+  std::vector<void *> k, v;
+  unsigned *err_dev = nullptr;
+  // scratch owned by the handle: attention workspace for tier 1 / the host step,
+  // per-call metadata (cu_q_lens copy, tile work list), host-step staging
+  void *ws = nullptr;
+  size_t ws_bytes = 0;
+  void *meta = nullptr;
+  size_t meta_bytes = 0;
+  void *stage = nullptr;
+  size_t stage_bytes = 0;
+  cudaStream_t step_stream = nullptr;
+};
+
+struct mlx_array {
+  void *data = nullptr;
+  int32_t dtype = 1;
+  int32_t device = 0;
+  size_t ndim = 0;
+  int64_t shape[8] = {0};
+  bool owns = false;
+};
+
+namespace {
+
+size_t dtype_size(int32_t d) {
+  switch (d) {
+    case 0: case 1: return 2;
+    case 2: case 3: case 5: return 4;
+    case 4: return 8;
+    default: return 0;
+  }
+}
+
+pa_status validate_config(const PagedAttnConfig *c) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "config is null");
+  // Same acceptance rules as PagedAttentionConfig::validate
+  // (crates/mlx-paged-attn/src/config.rs:36-75) before the narrower "built" test.
+  static const uint32_t heads[] = {32, 64, 80, 96, 112, 120, 128, 192, 256};
+  bool head_ok = false;
+  for (uint32_t hs : heads) head_ok |= hs == c->head_size;
+  if (c->block_size != 8 && c->block_size != 16 && c->block_size != 32)
+    return fail(PA_ERR_INVALID_ARG, "block_size must be 8, 16, or 32");
+  if (!head_ok) return fail(PA_ERR_INVALID_ARG, "unsupported head_size");
+  if (c->num_blocks == 0 || c->num_kv_heads == 0 || c->num_layers == 0)
+    return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
+  if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
+  if (c->dtype != 1) return fail(PA_ERR_UNSUPPORTED, "only dtype 1 (bf16) is built");
+  if (c->head_size != pa::kHeadSize || c->block_size != pa::kBlockSize)
+    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 with block_size 16 is built");
+  return PA_OK;
+}
+
+size_t layer_bytes(const PagedAttnConfig &c) {
+  return (size_t)c.num_blocks * c.num_kv_heads * c.head_size * c.block_size * 2;
+}
+
+pa_status finish_create(PagedAttnCache *c) {
+  int sms = 0;
+  PA_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device));
+  int major = 0;
+  PA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, c->device));
+  if (major != 10) return fail(PA_ERR_UNSUPPORTED, "this library is built for sm_100a only");
+  c->num_sms = sms;
+  PA_CUDA(cudaMalloc(&c->err_dev, 256));
+  PA_CUDA(cudaMemset(c->err_dev, 0, 256));
+  PA_CUDA(pa::splitkv_configure());
+  PA_CUDA(pa::tile_configure());
+  PA_CUDA(cudaStreamCreateWithFlags(&c->step_stream, cudaStreamNonBlocking));
+  return PA_OK;
+}
+
+pa_status grow(void **buf, size_t *have, size_t need) {
+  if (*have >= need) return PA_OK;
+  if (*buf) PA_CUDA(cudaFree(*buf));
+  *buf = nullptr;
+  *have = 0;
+  const size_t sz = (need + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+  PA_CUDA(cudaMalloc(buf, sz));
+  *have = sz;
+  return PA_OK;
+}
+
+pa_status check_layer(const PagedAttnCache *c, uint32_t layer) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  if (layer >= c->cfg.num_layers) return fail(PA_ERR_INVALID_ARG, "layer_idx out of range");
+  return PA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *pa_last_error_string(void) { return t_err.c_str(); }
+int32_t pa_version(void) { return 100; }
+uint64_t pa_kernel_launch_count(void) {
+  return __atomic_load_n(&pa::g_launch_count, __ATOMIC_RELAXED);
+}
+
+pa_status pa_set_device(int32_t device) {
+  int n = 0;
+  PA_CUDA(cudaGetDeviceCount(&n));
+  if (device < 0 || device >= n) return fail(PA_ERR_INVALID_ARG, "no such device");
+  t_device = device;
+  return PA_OK;
+}
+pa_status pa_set_stream(void *cuda_stream) {
+  t_stream = static_cast<cudaStream_t>(cuda_stream);
+  return PA_OK;
+}
+
+pa_status pa_cache_create(const PagedAttnConfig *config, int32_t device, PagedAttnCache **out) {
+  if (!out) return fail(PA_ERR_INVALID_ARG, "out_cache is null");
+  *out = nullptr;
+  pa_status st = validate_config(config);
+  if (st != PA_OK) return st;
+  DeviceGuard g(device);
+  if (!g.ok) return fail(PA_ERR_CUDA, "cannot select device");
+  PagedAttnCache *c = new (std::nothrow) PagedAttnCache();
+  if (!c) return fail(PA_ERR_OOM, "host allocation failed");
+  c->cfg = *config;
+  c->device = device;
+  c->owns = true;
+  const size_t bytes = layer_bytes(*config);
+  for (uint32_t i = 0; i < config->num_layers; i++) {
+    void *kp = nullptr, *vp = nullptr;
+    cudaError_t e = cudaMalloc(&kp, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&vp, bytes);
+    // zero-filled, as the reference's create_cache (crates/mlx-sys/src/mlx.cpp:3847-3863)
+    if (e == cudaSuccess) e = cudaMemset(kp, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(vp, 0, bytes);
+    if (kp) c->k.push_back(kp);
+    if (vp) c->v.push_back(vp);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "pool allocation");
+      cudaGetLastError();
+      std::string keep = t_err;
+      pa_cache_free(c);
+      return fail(e == cudaErrorMemoryAllocation ? PA_ERR_OOM : PA_ERR_CUDA, keep);
+    }
+  }
+  st = finish_create(c);
+  if (st != PA_OK) {
+    std::string keep = t_err;
+    pa_cache_free(c);
+    return fail(st, keep);
+  }
+  *out = c;
+  return PA_OK;
+}
+
+pa_status pa_cache_wrap(const PagedAttnConfig *config, int32_t device, void *const *key_ptrs,
+                        void *const *value_ptrs, PagedAttnCache **out) {
+  if (!out) return fail(PA_ERR_INVALID_ARG, "out_cache is null");
+  *out = nullptr;
+  pa_status st = validate_config(config);
+  if (st != PA_OK) return st;
+  if (!key_ptrs || !value_ptrs) return fail(PA_ERR_INVALID_ARG, "pool pointer arrays are null");
+  for (uint32_t i = 0; i < config->num_layers; i++) {
+    if (!key_ptrs[i] || !value_ptrs[i]) return fail(PA_ERR_INVALID_ARG, "a pool pointer is null");
+    if ((reinterpret_cast<uintptr_t>(key_ptrs[i]) | reinterpret_cast<uintptr_t>(value_ptrs[i])) & 127u)
+      return fail(PA_ERR_INVALID_ARG, "pool pointers must be 128-byte aligned");
+  }
+  DeviceGuard g(device);
+  if (!g.ok) return fail(PA_ERR_CUDA, "cannot select device");
+  PagedAttnCache *c = new (std::nothrow) PagedAttnCache();
+  if (!c) return fail(PA_ERR_OOM, "host allocation failed");
+  c->cfg = *config;
+  c->device = device;
+  c->owns = false;
+  c->k.assign(key_ptrs, key_ptrs + config->num_layers);
+  c->v.assign(value_ptrs, value_ptrs + config->num_layers);
+  st = finish_create(c);
+  if (st != PA_OK) {
+    std::string keep = t_err;
+    pa_cache_free(c);
+    return fail(st, keep);
+  }
+  *out = c;
+  return PA_OK;
+}
+
+pa_status pa_cache_free(PagedAttnCache *c) {
+  if (!c) return PA_OK;
+  DeviceGuard g(c->device);
+  if (c->owns) {
+    for (void *p : c->k) cudaFree(p);
+    for (void *p : c->v) cudaFree(p);
+  }
+  if (c->err_dev) cudaFree(c->err_dev);
+  if (c->ws) cudaFree(c->ws);
+  if (c->meta) cudaFree(c->meta);
+  if (c->stage) cudaFree(c->stage);
+  if (c->step_stream) cudaStreamDestroy(c->step_stream);
+  delete c;
+  return PA_OK;
+}
+
+void *pa_cache_key_ptr(PagedAttnCache *c, uint32_t layer) {
+  return check_layer(c, layer) == PA_OK ? c->k[layer] : nullptr;
+}
+void *pa_cache_value_ptr(PagedAttnCache *c, uint32_t layer) {
+  return check_layer(c, layer) == PA_OK ? c->v[layer] : nullptr;
+}
+pa_status pa_cache_get_config(const PagedAttnCache *c, PagedAttnConfig *out) {
+  if (!c || !out) return fail(PA_ERR_INVALID_ARG, "null argument");
+  *out = c->cfg;
+  return PA_OK;
+}
+
+pa_status pa_cache_check_errors(PagedAttnCache *c, void *cuda_stream) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  DeviceGuard g(c->device);
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  unsigned word = 0;
+  PA_CUDA(cudaMemcpyAsync(&word, c->err_dev, sizeof(word), cudaMemcpyDeviceToHost, st));
+  PA_CUDA(cudaStreamSynchronize(st));
+  if (word == 0) return PA_OK;
+  PA_CUDA(cudaMemsetAsync(c->err_dev, 0, sizeof(word), st));
+  PA_CUDA(cudaStreamSynchronize(st));
+  if (word & pa::kErrTimeout) return fail(PA_ERR_TIMEOUT, "a bounded device-side wait ran out");
+  if (word & pa::kErrSlotRange)
+    return fail(PA_ERR_OUT_OF_RANGE, "slot_mapping entry beyond num_blocks*block_size (skipped)");
+  return fail(PA_ERR_OUT_OF_RANGE, "block id beyond num_blocks (read as block 0)");
+}
+
+pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *key,
+                               const void *value, const int64_t *slot_mapping, int64_t num_tokens,
+                               int64_t key_stride, int64_t value_stride, void *cuda_stream) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_tokens < 0) return fail(PA_ERR_INVALID_ARG, "num_tokens < 0");
+  if (num_tokens == 0) return PA_OK;
+  if (!key || !value || !slot_mapping) return fail(PA_ERR_INVALID_ARG, "null tensor pointer");
+  const int64_t row = (int64_t)c->cfg.num_kv_heads * c->cfg.head_size;
+  if (key_stride < row || value_stride < row || (key_stride & 7) || (value_stride & 7))
+    return fail(PA_ERR_INVALID_ARG, "key/value stride must be >= num_kv_heads*head_size and a multiple of 8");
+  if (!aligned16(key) || !aligned16(value))
+    return fail(PA_ERR_INVALID_ARG, "key/value must be 16-byte aligned");
+  if (num_tokens > ((int64_t)1 << 34)) return fail(PA_ERR_INVALID_ARG, "num_tokens too large");
+  DeviceGuard g(c->device);
+  PA_CUDA(pa::launch_reshape_and_cache(
+      static_cast<const __nv_bfloat16 *>(key), static_cast<const __nv_bfloat16 *>(value),
+      static_cast<__nv_bfloat16 *>(c->k[layer]), static_cast<__nv_bfloat16 *>(c->v[layer]),
+      slot_mapping, num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads,
+      c->cfg.num_blocks, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
+  return PA_OK;
+}
+
+pa_status pa_copy_blocks(PagedAttnCache *c, uint32_t layer, const int64_t *mapping,
+                         int64_t num_pairs, void *cuda_stream) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_pairs < 0) return fail(PA_ERR_INVALID_ARG, "num_pairs < 0");
+  if (num_pairs == 0) return PA_OK;
+  if (!mapping) return fail(PA_ERR_INVALID_ARG, "block_mapping is null");
+  DeviceGuard g(c->device);
+  const int64_t bpb = (int64_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2;
+  PA_CUDA(pa::launch_copy_blocks(static_cast<__nv_bfloat16 *>(c->k[layer]),
+                                 static_cast<__nv_bfloat16 *>(c->v[layer]), mapping, num_pairs, bpb,
+                                 c->cfg.num_blocks, c->err_dev,
+                                 static_cast<cudaStream_t>(cuda_stream)));
+  return PA_OK;
+}
+
+size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {
+  if (!c) return 0;
+  return pa::splitkv_workspace_bytes(c->num_sms);
+}
+
+pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                                    const int32_t *block_tables, const int32_t *context_lens,
+                                    const int32_t *cu_q_lens_host, int32_t num_seqs,
+                                    int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                    int64_t q_stride, int64_t out_stride, float scale,
+                                    float softcap, int32_t max_context_len, void *workspace,
+                                    size_t workspace_bytes, void *cuda_stream) {
+  (void)max_context_len;
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_seqs < 0) return fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
+  if (num_seqs == 0) return PA_OK;
+  if (!out || !q || !block_tables || !context_lens)
+    return fail(PA_ERR_INVALID_ARG, "null tensor pointer");
+  const int Hkv = (int)c->cfg.num_kv_heads;
+  if (num_q_heads <= 0 || num_q_heads % Hkv != 0)
+    return fail(PA_ERR_INVALID_ARG, "num_q_heads must be a positive multiple of num_kv_heads");
+  const int G = num_q_heads / Hkv;
+  if (G > pa::splitkv_max_cols() || (128 % G) != 0)
+    return fail(PA_ERR_UNSUPPORTED, "query heads per kv head must be 1, 2, 4, 8 or 16");
+  if (max_blocks_per_seq <= 0) return fail(PA_ERR_INVALID_ARG, "max_blocks_per_seq must be > 0");
+  const int64_t row = (int64_t)num_q_heads * c->cfg.head_size;
+  if (q_stride < row || out_stride < row || (q_stride & 7) || (out_stride & 7))
+    return fail(PA_ERR_INVALID_ARG, "q/out stride must be >= num_q_heads*head_size and a multiple of 8");
+  if (!aligned16(q) || !aligned16(out)) return fail(PA_ERR_INVALID_ARG, "q/out must be 16-byte aligned");
+  if (!workspace || workspace_bytes < pa_attention_workspace_bytes(c) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(PA_ERR_INVALID_ARG, "workspace missing, too small or not 256-byte aligned");
+  if (!(scale > 0.f) || !(softcap > 0.f)) return fail(PA_ERR_INVALID_ARG, "scale and softcap must be > 0");
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceGuard g(c->device);
+  pa::AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16 *>(q);
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.k_pool = static_cast<const __nv_bfloat16 *>(c->k[layer]);
+  p.v_pool = static_cast<const __nv_bfloat16 *>(c->v[layer]);
+  p.block_tables = block_tables;
+  p.context_lens = context_lens;
+  p.cu_q_lens = nullptr;
+  p.S = num_seqs;
+  p.Hq = num_q_heads;
+  p.Hkv = Hkv;
+  p.G = G;
+  p.MB = max_blocks_per_seq;
+  p.num_blocks = c->cfg.num_blocks;
+  p.q_stride = q_stride;
+  p.out_stride = out_stride;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.ws = static_cast<float *>(workspace);
+  p.err = c->err_dev;
+  p.seq_base = 0;
+
+  if (!cu_q_lens_host) {  // decode: one query per sequence
+    p.max_cols = G;
+    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
+    return PA_OK;
+  }
+
+  // Classify sequences: few columns -> split-KV kernel, many -> tile kernel.
+  const int split_cols = pa::splitkv_max_cols();
+  const int tile_q = pa::tile_queries_per_cta(G);
+  int widest_small = 0;
+  bool any_small = false;
+  std::vector<pa::TileWork> tiles;
+  for (int s = 0; s < num_seqs; s++) {
+    const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
+    if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
+    if (ql == 0) continue;
+    if (ql * G <= split_cols) {
+      any_small = true;
+      if (ql * G > widest_small) widest_small = ql * G;
+    } else {
+      // Later tiles see more keys: list them first so the long ones start early.
+      for (int qb = ((ql - 1) / tile_q) * tile_q; qb >= 0; qb -= tile_q)
+        for (int h = 0; h < Hkv; h++)
+          tiles.push_back(pa::TileWork{s, h, qb, ql - qb < tile_q ? ql - qb : tile_q});
+    }
+  }
+  const size_t cu_bytes = ((size_t)(num_seqs + 1) * 4 + 255) & ~(size_t)255;
+  const size_t need = cu_bytes + tiles.size() * sizeof(pa::TileWork);
+  st = grow(&c->meta, &c->meta_bytes, need);
+  if (st != PA_OK) return st;
+  PA_CUDA(cudaMemcpyAsync(c->meta, cu_q_lens_host, (size_t)(num_seqs + 1) * 4,
+                          cudaMemcpyHostToDevice, stream));
+  p.cu_q_lens = static_cast<const int32_t *>(c->meta);
+  if (!tiles.empty()) {
+    pa::TileWork *work_dev = reinterpret_cast<pa::TileWork *>(static_cast<char *>(c->meta) + cu_bytes);
+    PA_CUDA(cudaMemcpyAsync(work_dev, tiles.data(), tiles.size() * sizeof(pa::TileWork),
+                            cudaMemcpyHostToDevice, stream));
+    PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), stream));
+  }
+  if (any_small) {
+    // the split-KV kernel skips sequences wider than max_cols (the tile kernel has them)
+    p.max_cols = ((widest_small + 7) / 8) * 8;
+    if (p.max_cols > split_cols) p.max_cols = split_cols;
+    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
+  }
+  return PA_OK;
+}
+
+pa_status pa_paged_attention_decode(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                                    const int32_t *block_tables, const int32_t *context_lens,
+                                    int32_t num_seqs, int32_t num_q_heads,
+                                    int32_t max_blocks_per_seq, int64_t q_stride,
+                                    int64_t out_stride, float scale, float softcap,
+                                    void *workspace, size_t workspace_bytes, void *cuda_stream) {
+  return pa_paged_attention_varlen(c, layer, out, q, block_tables, context_lens, nullptr, num_seqs,
+                                   num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale,
+                                   softcap, 0, workspace, workspace_bytes, cuda_stream);
+}
+
+pa_status pa_decode_step_host(PagedAttnCache *c, uint32_t layer, void *out_host,
+                              const void *q_host, const void *k_host, const void *v_host,
+                              const int64_t *slots_host, const int32_t *tables_host,
+                              const int32_t *lens_host, int32_t num_seqs, int32_t num_q_heads,
+                              int32_t max_blocks_per_seq, float scale, float softcap) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_seqs <= 0) return num_seqs == 0 ? PA_OK : fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
+  if (!out_host || !q_host || !k_host || !v_host || !slots_host || !tables_host || !lens_host)
+    return fail(PA_ERR_INVALID_ARG, "null host pointer");
+  if (num_q_heads <= 0 || max_blocks_per_seq <= 0) return fail(PA_ERR_INVALID_ARG, "bad sizes");
+  DeviceGuard g(c->device);
+  const size_t D = c->cfg.head_size, Hkv = c->cfg.num_kv_heads, S = (size_t)num_seqs;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  const size_t q_b = S * num_q_heads * D * 2, kv_b = S * Hkv * D * 2, sl_b = S * 8,
+               tb_b = S * (size_t)max_blocks_per_seq * 4, ln_b = S * 4;
+  const size_t o_q = 0, o_k = o_q + up(q_b), o_v = o_k + up(kv_b), o_sl = o_v + up(kv_b),
+               o_tb = o_sl + up(sl_b), o_ln = o_tb + up(tb_b), o_out = o_ln + up(ln_b),
+               total = o_out + up(q_b);
+  st = grow(&c->stage, &c->stage_bytes, total);
+  if (st != PA_OK) return st;
+  st = grow(&c->ws, &c->ws_bytes, pa_attention_workspace_bytes(c));
+  if (st != PA_OK) return st;
+  char *base = static_cast<char *>(c->stage);
+  cudaStream_t s = c->step_stream;
+  PA_CUDA(cudaMemcpyAsync(base + o_q, q_host, q_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_k, k_host, kv_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_v, v_host, kv_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_sl, slots_host, sl_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_tb, tables_host, tb_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_ln, lens_host, ln_b, cudaMemcpyHostToDevice, s));
+  st = pa_reshape_and_cache(c, layer, base + o_k, base + o_v,
+                            reinterpret_cast<const int64_t *>(base + o_sl), num_seqs,
+                            (int64_t)(Hkv * D), (int64_t)(Hkv * D), s);
+  if (st != PA_OK) return st;
+  st = pa_paged_attention_decode(c, layer, base + o_out, base + o_q,
+                                 reinterpret_cast<const int32_t *>(base + o_tb),
+                                 reinterpret_cast<const int32_t *>(base + o_ln), num_seqs,
+                                 num_q_heads, max_blocks_per_seq, (int64_t)(num_q_heads * D),
+                                 (int64_t)(num_q_heads * D), scale, softcap, c->ws, c->ws_bytes, s);
+  if (st != PA_OK) return st;
+  PA_CUDA(cudaMemcpyAsync(out_host, base + o_out, q_b, cudaMemcpyDeviceToHost, s));
+  unsigned word = 0;
+  PA_CUDA(cudaMemcpyAsync(&word, c->err_dev, sizeof(word), cudaMemcpyDeviceToHost, s));
+  PA_CUDA(cudaStreamSynchronize(s));
+  if (word != 0) return pa_cache_check_errors(c, s);
+  return PA_OK;
+}
+
+/* ---- tier 1 ------------------------------------------------------------------ */
+
+mlx_array *pa_array_from_device(void *device_ptr, int32_t dtype, const int64_t *shape, size_t ndim) {
+  if (!device_ptr || !shape || ndim > 8 || dtype_size(dtype) == 0) {
+    fail(PA_ERR_INVALID_ARG, "pa_array_from_device: bad argument");
+    return nullptr;
+  }
+  mlx_array *a = new (std::nothrow) mlx_array();
+  if (!a) return nullptr;
+  a->data = device_ptr;
+  a->dtype = dtype;
+  a->device = t_device;
+  a->ndim = ndim;
+  for (size_t i = 0; i < ndim; i++) a->shape[i] = shape[i];
+  return a;
+}
+
+mlx_array *pa_array_from_host(const void *host_ptr, int32_t dtype, const int64_t *shape, size_t ndim) {
+  if (!host_ptr || !shape || ndim > 8 || dtype_size(dtype) == 0) {
+    fail(PA_ERR_INVALID_ARG, "pa_array_from_host: bad argument");
+    return nullptr;
+  }
+  size_t n = dtype_size(dtype);
+  for (size_t i = 0; i < ndim; i++) n *= (size_t)shape[i];
+  DeviceGuard g(t_device);
+  void *d = nullptr;
+  cudaError_t e = cudaMalloc(&d, n ? n : 16);
+  if (e == cudaSuccess && n) e = cudaMemcpyAsync(d, host_ptr, n, cudaMemcpyHostToDevice, t_stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(t_stream);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "pa_array_from_host");
+    if (d) cudaFree(d);
+    return nullptr;
+  }
+  mlx_array *a = pa_array_from_device(d, dtype, shape, ndim);
+  if (!a) {
+    cudaFree(d);
+    return nullptr;
+  }
+  a->owns = true;
+  return a;
+}
+
+void *pa_array_data(mlx_array *a) { return a ? a->data : nullptr; }
+size_t mlx_array_ndim(mlx_array *a) { return a ? a->ndim : 0; }
+void mlx_array_shape(mlx_array *a, int64_t *out) {
+  if (!a || !out) return;
+  for (size_t i = 0; i < a->ndim; i++) out[i] = a->shape[i];
+}
+int32_t mlx_array_dtype(mlx_array *a) { return a ? a->dtype : -1; }
+void mlx_array_delete(mlx_array *a) {
+  if (!a) return;
+  if (a->owns && a->data) {
+    DeviceGuard g(a->device);
+    cudaFree(a->data);
+  }
+  delete a;
+}
+
+PagedAttnCache *mlx_paged_attn_create_cache(const PagedAttnConfig *config) {
+  PagedAttnCache *c = nullptr;
+  if (pa_cache_create(config, t_device, &c) != PA_OK) return nullptr;
+  return c;
+}
+void mlx_paged_attn_free_cache(PagedAttnCache *cache) { pa_cache_free(cache); }
+
+static mlx_array *pool_view(PagedAttnCache *c, uint32_t layer, bool key) {
+  if (check_layer(c, layer) != PA_OK) return nullptr;
+  const PagedAttnConfig &f = c->cfg;
+  mlx_array *a = new (std::nothrow) mlx_array();
+  if (!a) return nullptr;
+  a->data = key ? c->k[layer] : c->v[layer];
+  a->dtype = (int32_t)f.dtype;
+  a->device = c->device;
+  if (key) {
+    a->ndim = 5;
+    const int64_t sh[5] = {f.num_blocks, f.num_kv_heads, f.head_size / 8, f.block_size, 8};
+    memcpy(a->shape, sh, sizeof(sh));
+  } else {
+    a->ndim = 4;
+    const int64_t sh[4] = {f.num_blocks, f.num_kv_heads, f.head_size, f.block_size};
+    memcpy(a->shape, sh, sizeof(sh));
+  }
+  return a;
+}
+mlx_array *mlx_paged_attn_get_key_cache(PagedAttnCache *c, uint32_t layer) { return pool_view(c, layer, true); }
+mlx_array *mlx_paged_attn_get_value_cache(PagedAttnCache *c, uint32_t layer) { return pool_view(c, layer, false); }
+
+void mlx_paged_attn_reshape_and_cache(PagedAttnCache *c, uint32_t layer, mlx_array *keys,
+                                      mlx_array *values, mlx_array *slot_mapping) {
+  if (!c || !keys || !values || !slot_mapping) {
+    fail(PA_ERR_INVALID_ARG, "reshape_and_cache: null argument");
+    return;
+  }
+  if (keys->ndim != 3 || values->ndim != 3 || slot_mapping->dtype != 4 || keys->dtype != 1 ||
+      values->dtype != 1 || keys->shape[1] != c->cfg.num_kv_heads ||
+      keys->shape[2] != c->cfg.head_size || slot_mapping->shape[0] != keys->shape[0]) {
+    fail(PA_ERR_INVALID_ARG, "reshape_and_cache: keys/values must be bf16 [T,Hkv,D], slots int64 [T]");
+    return;
+  }
+  const int64_t row = keys->shape[1] * keys->shape[2];
+  pa_reshape_and_cache(c, layer, keys->data, values->data,
+                       static_cast<const int64_t *>(slot_mapping->data), keys->shape[0], row, row,
+                       t_stream);
+}
+
+mlx_array *mlx_paged_attn_forward(mlx_array *q, mlx_array *kc, mlx_array *vc, mlx_array *bt,
+                                  mlx_array *cl, float scale, uint32_t block_size,
+                                  uint32_t max_context_len) {
+  if (!q || !kc || !vc || !bt || !cl) {
+    fail(PA_ERR_INVALID_ARG, "forward: null argument");
+    return nullptr;
+  }
+  if (q->ndim != 3 || kc->ndim != 5 || vc->ndim != 4 || bt->ndim != 2 || q->dtype != 1 ||
+      kc->dtype != 1 || vc->dtype != 1 || bt->dtype != 3 || cl->dtype != 3 ||
+      (int64_t)block_size != vc->shape[3] || bt->shape[0] != q->shape[0]) {
+    fail(PA_ERR_INVALID_ARG, "forward: expected bf16 q [S,Hq,D], pools, int32 tables [S,MB] and lens [S]");
+    return nullptr;
+  }
+  PagedAttnConfig cfg{(uint32_t)vc->shape[3], (uint32_t)vc->shape[0], (uint32_t)vc->shape[2],
+                      (uint32_t)vc->shape[1], 1, 1};
+  void *kp = kc->data, *vp = vc->data;
+  // A transient handle over the caller's pools: this entry takes the pools as
+  // arrays, not the cache handle (crates/mlx-sys/src/lib.rs:782-791).
+  PagedAttnCache *c = nullptr;
+  if (pa_cache_wrap(&cfg, kc->device, &kp, &vp, &c) != PA_OK) return nullptr;
+  const int64_t S = q->shape[0], Hq = q->shape[1], D = q->shape[2];
+  DeviceGuard g(c->device);
+  void *out = nullptr, *ws = nullptr;
+  const size_t ws_bytes = pa_attention_workspace_bytes(c);
+  mlx_array *res = nullptr;
+  cudaError_t e = cudaMalloc(&out, (size_t)(S * Hq * D * 2 > 0 ? S * Hq * D * 2 : 16));
+  if (e == cudaSuccess) e = cudaMalloc(&ws, ws_bytes);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "forward: allocation");
+  } else if (pa_paged_attention_varlen(c, 0, out, q->data, static_cast<const int32_t *>(bt->data),
+                                       static_cast<const int32_t *>(cl->data), nullptr, (int32_t)S,
+                                       (int32_t)Hq, (int32_t)bt->shape[1], Hq * D, Hq * D, scale,
+                                       1.0f, (int32_t)max_context_len, ws, ws_bytes,
+                                       t_stream) == PA_OK &&
+             cudaStreamSynchronize(t_stream) == cudaSuccess) {
+    const int64_t sh[3] = {S, Hq, D};
+    res = pa_array_from_device(out, 1, sh, 3);
+    if (res) {
+      res->owns = true;
+      res->device = c->device;
+      out = nullptr;
+    }
+  }
+  if (out) cudaFree(out);
+  if (ws) cudaFree(ws);
+  pa_cache_free(c);
+  return res;
+}
+
+void mlx_paged_attn_copy_blocks(PagedAttnCache *c, uint32_t layer, mlx_array *mapping) {
+  if (!c || !mapping) {
+    fail(PA_ERR_INVALID_ARG, "copy_blocks: null argument");
+    return;
+  }
+  if (mapping->dtype != 4) {
+    fail(PA_ERR_INVALID_ARG, "copy_blocks: block_mapping must be int64");
+    return;
+  }
+  // [num_pairs, 2] or flat [2*num_pairs] (crates/mlx-sys/src/mlx.cpp:4185-4192)
+  const bool is_2d = mapping->ndim == 2 && mapping->shape[1] == 2;
+  const int64_t pairs = is_2d ? mapping->shape[0] : mapping->shape[0] / 2;
+  pa_copy_blocks(c, layer, static_cast<const int64_t *>(mapping->data), pairs, t_stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,138 @@
+// KV block write (reshape_and_cache) and block copy (copy_blocks) for sm_100a.
+//
+// Semantics: crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:58-97 and
+// crates/mlx-paged-attn/metal/cache/copy_blocks.metal:6-36.  Both are pure
+// index arithmetic over 16-bit patterns, so results are bit-exact.
+#include "pa_common.cuh"
+
+namespace pa {
+
+unsigned long long g_launch_count = 0;
+
+// One CTA stages up to 16 consecutive tokens of one KV head in shared memory and
+// writes them out with the token index fastest across threads.  For a prefill
+// chunk (consecutive slots of one block) the 16-byte K pieces of neighbouring
+// tokens and the 2-byte V elements of neighbouring tokens are adjacent in the
+// pool, so a warp's stores fill whole 32-byte sectors; for decode (one token per
+// sequence) the stores are scattered, as the layout dictates.
+constexpr int kTokPerCta = 16;
+constexpr int kVPad = 2;  // bf16 elements of row padding: 65-word rows, conflict-free
+
+__global__ void __launch_bounds__(256)
+reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
+                         const __nv_bfloat16 *__restrict__ value,
+                         __nv_bfloat16 *__restrict__ k_pool, __nv_bfloat16 *__restrict__ v_pool,
+                         const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
+                         int64_t key_stride, int64_t value_stride, int Hkv, uint32_t num_blocks,
+                         unsigned *err) {
+  __shared__ uint4 k_s[kTokPerCta][kHeadSize / 8];                 // 16 x 256 B
+  __shared__ __align__(16) uint16_t v_s[kTokPerCta][kHeadSize + kVPad];
+  __shared__ int64_t slot_s[kTokPerCta];
+
+  const int h = blockIdx.y;
+  const int64_t t0 = (int64_t)blockIdx.x * kTokPerCta;
+  const int tid = threadIdx.x;
+  const int64_t n_slots = (int64_t)num_blocks * kBlockSize;
+
+  if (tid < kTokPerCta) {
+    int64_t s = -1;
+    if (t0 + tid < num_tokens) {
+      s = slot_mapping[t0 + tid];
+      if (s >= n_slots) {
+        atomicOr(err, kErrSlotRange);
+        s = -1;
+      }
+    }
+    slot_s[tid] = s;
+  }
+  // Stage: 16 tokens x 16 pieces of 16 B for K and for V; thread -> (token, piece).
+  {
+    const int tok = tid >> 4, piece = tid & 15;
+    if (t0 + tok < num_tokens) {
+      const uint4 kv = *reinterpret_cast<const uint4 *>(key + (t0 + tok) * key_stride +
+                                                        (int64_t)h * kHeadSize + piece * 8);
+      const uint4 vv = *reinterpret_cast<const uint4 *>(value + (t0 + tok) * value_stride +
+                                                        (int64_t)h * kHeadSize + piece * 8);
+      k_s[tok][piece] = kv;
+      uint32_t *vd = reinterpret_cast<uint32_t *>(&v_s[tok][piece * 8]);
+      vd[0] = vv.x; vd[1] = vv.y; vd[2] = vv.z; vd[3] = vv.w;
+    }
+  }
+  __syncthreads();
+
+  // K: piece c of token `tok` goes to chunk offset c*BS*8 + off*8 (elements).
+  {
+    const int tok = tid & 15, c = tid >> 4;
+    const int64_t slot = slot_s[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kBlockSize;
+      const int off = (int)(slot % kBlockSize);
+      __nv_bfloat16 *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunkElems + c * (kBlockSize * 8) +
+                           off * 8;
+      *reinterpret_cast<uint4 *>(dst) = k_s[tok][c];
+    }
+  }
+  // V: element d of token `tok` goes to chunk offset d*BS + off.
+  for (int e = tid; e < kTokPerCta * kHeadSize; e += 256) {
+    const int tok = e & 15, d = e >> 4;
+    const int64_t slot = slot_s[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kBlockSize;
+      const int off = (int)(slot % kBlockSize);
+      reinterpret_cast<uint16_t *>(v_pool)[(blk * Hkv + h) * (int64_t)kChunkElems +
+                                           d * kBlockSize + off] = v_s[tok][d];
+    }
+  }
+}
+
+cudaError_t launch_reshape_and_cache(const __nv_bfloat16 *key, const __nv_bfloat16 *value,
+                                     __nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+                                     const int64_t *slot_mapping, int64_t num_tokens,
+                                     int64_t key_stride, int64_t value_stride, int Hkv,
+                                     uint32_t num_blocks, unsigned *err, cudaStream_t st) {
+  if (num_tokens <= 0) return cudaSuccess;
+  const int64_t groups = (num_tokens + kTokPerCta - 1) / kTokPerCta;
+  // grid.x is 31-bit; a write of more than 2^31*16 tokens is not a real call.
+  dim3 grid((unsigned)groups, (unsigned)Hkv);
+  reshape_and_cache_kernel<<<grid, 256, 0, st>>>(key, value, k_pool, v_pool, slot_mapping,
+                                                 num_tokens, key_stride, value_stride, Hkv,
+                                                 num_blocks, err);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+// One CTA per (pair, 4 KB piece): K piece then V piece, 16 bytes per thread.
+// Pairs are independent unless a destination is also a source of a later pair;
+// the reference processes pairs in parallel as well (one threadgroup per pair).
+__global__ void __launch_bounds__(256)
+copy_blocks_kernel(__nv_bfloat16 *__restrict__ k_pool, __nv_bfloat16 *__restrict__ v_pool,
+                   const int64_t *__restrict__ mapping, int64_t bytes_per_block,
+                   uint32_t num_blocks, unsigned *err) {
+  const int64_t pair = blockIdx.x;
+  const int64_t src = mapping[2 * pair], dst = mapping[2 * pair + 1];
+  if (src < 0 || dst < 0 || src >= (int64_t)num_blocks || dst >= (int64_t)num_blocks) {
+    if (threadIdx.x == 0) atomicOr(err, kErrBlockRange);
+    return;
+  }
+  const int64_t piece = (int64_t)blockIdx.y * 4096 + threadIdx.x * 16;
+  if (piece >= bytes_per_block) return;
+  const char *ks = reinterpret_cast<const char *>(k_pool) + src * bytes_per_block + piece;
+  char *kd = reinterpret_cast<char *>(k_pool) + dst * bytes_per_block + piece;
+  const char *vs = reinterpret_cast<const char *>(v_pool) + src * bytes_per_block + piece;
+  char *vd = reinterpret_cast<char *>(v_pool) + dst * bytes_per_block + piece;
+  *reinterpret_cast<uint4 *>(kd) = *reinterpret_cast<const uint4 *>(ks);
+  *reinterpret_cast<uint4 *>(vd) = *reinterpret_cast<const uint4 *>(vs);
+}
+
+cudaError_t launch_copy_blocks(__nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+                               const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
+                               uint32_t num_blocks, unsigned *err, cudaStream_t st) {
+  if (num_pairs <= 0) return cudaSuccess;
+  dim3 grid((unsigned)num_pairs, (unsigned)((bytes_per_block + 4095) / 4096));
+  copy_blocks_kernel<<<grid, 256, 0, st>>>(k_pool, v_pool, mapping, bytes_per_block, num_blocks,
+                                           err);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+}  // namespace pa

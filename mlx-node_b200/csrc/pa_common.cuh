@@ -1,0 +1,154 @@
+// Shared device helpers and kernel-launch declarations for the sm_100a
+// paged-attention kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pa {
+
+// Fixed geometry of the tuned path: head size 128, 16-token blocks, bf16.
+// One (block, kv head) pair is a contiguous 4 KB K chunk laid out
+// [D/8][BS][8] and a contiguous 4 KB V chunk laid out [D][BS]
+// (crates/mlx-paged-attn/src/paged_kv_cache.rs:1129-1136: kv_head_stride = D*BS).
+constexpr int kHeadSize = 128;
+constexpr int kBlockSize = 16;
+constexpr int kChunkBytes = kHeadSize * kBlockSize * 2;  // 4096
+constexpr int kChunkElems = kHeadSize * kBlockSize;      // 2048
+
+// Error word bits written by kernels instead of trapping.
+constexpr unsigned kErrBlockRange = 1u;  // block-table entry >= num_blocks
+constexpr unsigned kErrSlotRange = 2u;   // slot >= num_blocks*block_size
+constexpr unsigned kErrTimeout = 4u;     // a bounded wait ran out
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier + bulk async copy (TMA, untiled) -----------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.b32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2^31 clocks (about a second), returns false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > (1ll << 31)) return false;
+  }
+  return true;
+}
+// 1-D bulk copy global -> shared of `bytes` (multiple of 16; both addresses
+// 16-byte aligned), completion counted on `bar`.  No multicast.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ---- warp-level tensor-core pieces ------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Transpose an 8x8 matrix of 16-bit elements held one 32-bit register per lane.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// Pack two floats to bf16x2 (lo in the low half), round to nearest even.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- launch parameter blocks --------------------------------------------------
+struct AttnParams {
+  const __nv_bfloat16 *q;
+  __nv_bfloat16 *out;
+  const __nv_bfloat16 *k_pool;
+  const __nv_bfloat16 *v_pool;
+  const int32_t *block_tables;  // [S, MB]
+  const int32_t *context_lens;  // [S]
+  const int32_t *cu_q_lens;     // [S+1] device copy, or null: one query per sequence
+  int S, Hq, Hkv, G, MB;
+  uint32_t num_blocks;  // pool size, for range checks
+  int64_t q_stride, out_stride;
+  float scale;    // logits multiplier
+  float softcap;  // 1.0f = off
+  float *ws;      // partial results, slot layout described in decode.cu
+  unsigned *err;  // error word
+  int seq_base;   // first sequence this launch covers
+  int max_cols;   // columns (q_len*G) a sequence may have to be taken by the split-KV kernel
+};
+
+// Host-side launchers (defined next to their kernels).
+cudaError_t launch_reshape_and_cache(const __nv_bfloat16 *key, const __nv_bfloat16 *value,
+                                     __nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+                                     const int64_t *slot_mapping, int64_t num_tokens,
+                                     int64_t key_stride, int64_t value_stride, int Hkv,
+                                     uint32_t num_blocks, unsigned *err, cudaStream_t st);
+cudaError_t launch_copy_blocks(__nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+                               const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
+                               uint32_t num_blocks, unsigned *err, cudaStream_t st);
+// Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.
+cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st);
+size_t splitkv_workspace_bytes(int num_ctas);
+int splitkv_max_cols();
+cudaError_t splitkv_configure();  // opt-in shared memory sizes, once per device
+// Tile kernel for long-query sequences; work list built by the caller.
+struct TileWork {
+  int32_t seq;       // sequence index
+  int32_t kv_head;   // kv head
+  int32_t q_begin;   // first query (within the sequence) of this tile
+  int32_t q_count;   // queries in this tile
+};
+cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
+                                  cudaStream_t st);
+cudaError_t tile_configure();
+int tile_queries_per_cta(int G);
+
+extern unsigned long long g_launch_count;  // host counter of kernel launches
+
+}  // namespace pa

@@ -1,0 +1,545 @@
+// Split-KV ("flash-decoding") paged attention for sm_100a: the memory-bound
+// kernel for decode and short multi-token (speculative-verify) sequences.
+//
+// Replaces the per-(sequence, query head, 512-token partition) kernel and its
+// reduce pass, crates/mlx-paged-attn/metal/attention/paged_attention.metal
+// :760-1147 and :1149-1260, which stream the KV blocks once per QUERY head.
+// Here one read of a (block, kv head) chunk serves every query head of the GQA
+// group and every query token of the sequence.
+//
+// Work decomposition.  A unit is one (sequence, kv head, 16-token block): a 4 KB
+// K chunk plus a 4 KB V chunk, each contiguous in the pool.  Units are numbered
+// item-major (item = sequence*Hkv + kv head, then block index) and the flat range
+// [0, W) is cut into gridDim.x equal pieces, one persistent CTA per SM each, so
+// that ragged context lengths balance to within one unit.  A CTA walks the items
+// its piece overlaps ("segments").  A segment that covers its whole item writes
+// the final bf16 rows; a segment that starts or ends inside an item writes an
+// unnormalised partial (running max, sum, accumulator) to one of the CTA's two
+// workspace slots, and a small merge kernel combines the partials of each split
+// item in a fixed order (deterministic results).
+//
+// Data movement.  Each warp owns a ring of NST stages of 8 KB.  Lane 0 issues two
+// 4 KB bulk async copies (TMA, untiled, no multicast) per unit, completion
+// counted on the stage's mbarrier; the warp consumes its own stages, so no
+// cross-warp hand-off sits on the critical path.  8 warps x NST stages x 8 KB
+// of loads are in flight per SM.  Block ids for the next 32 units of a warp are
+// looked up one batch ahead, one unit per lane, and handed to lane 0 by shuffle.
+//
+// Arithmetic.  Tensor cores through mma.sync m16n8k16 (bf16 in, fp32 out), in the
+// transposed form so that the 16 tokens of a block are the M dimension:
+//   S^T[16 tok x 8 col] = K[16 tok x 128] . Q^T[128 x 8 col]
+//   O^T[128 x 8 col]   += V^T[128 x 16 tok] . P^T[16 tok x 8 col]
+// A column is a (query token, query head of the group) pair.  The reference K
+// layout [D/8][BS][8] is exactly the 8x(16 B) core-matrix order ldmatrix wants
+// for K as the A operand, and V's [D][BS] is A-operand order for V^T, so both
+// tiles are consumed straight from the raw 4 KB chunks.  P^T is produced from the
+// S^T accumulators with one movmatrix transpose per 8x8 tile.  Online softmax in
+// fp32 with exp2; column maxima by warp shuffles.
+#include "pa_common.cuh"
+
+namespace pa {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxSeqsPerLaunch = 2048;
+constexpr int kStageBytes = 2 * kChunkBytes;
+constexpr int kMaxNT = 3;  // up to 24 columns per item
+
+template <int NT>
+struct Cfg {
+  static constexpr int kStages = NT == 1 ? 3 : 2;
+  static constexpr int kRegs = 36 * NT;  // per thread: 32NT accumulators, 2NT maxima, 2NT sums
+  static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
+  static constexpr int kMergeBytes = (kWarps / 2) * kRegs * 32 * 4;
+  static constexpr int kPreBytes = (kMaxSeqsPerLaunch + 1) * 4;
+  static constexpr int kBarBytes = kWarps * kStages * 8;
+  static constexpr int kSmemBytes = kRingBytes + kMergeBytes + kPreBytes + 12 + kBarBytes;
+};
+constexpr int kSlotFloats = 36 * kMaxNT * 32;  // one workspace slot, sized for the widest kernel
+
+__device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
+  return p.cu_q_lens ? p.cu_q_lens[seq + 1] - p.cu_q_lens[seq] : 1;
+}
+// Blocks of a sequence this kernel family handles (0 if the sequence belongs to
+// the tile kernel or has nothing to attend).
+__device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
+  const int ql = q_len_of(p, seq);
+  if (ql < 1 || ql * p.G > p.max_cols) return 0;
+  const int ctx = p.context_lens[seq];
+  return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p) {
+  using C = Cfg<NT>;
+  constexpr int NST = C::kStages;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t *ring = smem;
+  float *merge_buf = reinterpret_cast<float *>(smem + C::kRingBytes);
+  int *pre = reinterpret_cast<int *>(smem + C::kRingBytes + C::kMergeBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kRingBytes + C::kMergeBytes +
+                                                ((C::kPreBytes + 15) / 16) * 16);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index, row within it
+  const int S = p.S, Hkv = p.Hkv, G = p.G;
+
+  // ---- per-launch prefix sum of block counts --------------------------------
+  for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s);
+  if (tid == 0) pre[0] = 0;
+  if (lane == 0) {
+    for (int st = 0; st < NST; st++) mbar_init(smem_u32(&bars[warp * NST + st]), 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int running = 0;
+    for (int base = 0; base < S; base += 32) {
+      int v = (base + lane < S) ? pre[base + lane + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (base + lane < S) pre[base + lane + 1] = running + v;
+      running += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+
+  const long long W = (long long)Hkv * pre[S];
+  const long long lo = (long long)blockIdx.x * W / gridDim.x;
+  const long long hi = (long long)(blockIdx.x + 1) * W / gridDim.x;
+  const int n_local = (int)(hi - lo);
+  if (n_local <= 0) return;
+  const int n_w = n_local > warp ? (n_local - warp + kWarps - 1) / kWarps : 0;
+
+  // smallest s with Hkv*pre[s+1] > u
+  auto seq_of = [&](long long u) {
+    int a = 0, b = S - 1;
+    while (a < b) {
+      const int mid = (a + b) >> 1;
+      if ((long long)Hkv * pre[mid + 1] > u) b = mid; else a = mid + 1;
+    }
+    return a;
+  };
+  // Pool chunk index (block id * Hkv + kv head) of this warp's j-th unit.
+  auto lookup = [&](int j) -> uint32_t {
+    if (j >= n_w) return 0u;
+    const long long u = lo + warp + (long long)kWarps * j;
+    const int s = seq_of(u);
+    const int r = (int)(u - (long long)Hkv * pre[s]);
+    const int nb = pre[s + 1] - pre[s];
+    const int h = r / nb, b = r - h * nb;
+    uint32_t id = (uint32_t)p.block_tables[(long long)(p.seq_base + s) * p.MB + b];
+    if (id >= p.num_blocks) {
+      atomicOr(p.err, kErrBlockRange);
+      id = 0;
+    }
+    return id * (uint32_t)Hkv + (uint32_t)h;
+  };
+
+  const uint32_t ring_w = smem_u32(ring) + warp * NST * kStageBytes;
+  const uint32_t bar_w = smem_u32(&bars[warp * NST]);
+  uint32_t cur_ids = lookup(lane), nxt_ids = lookup(32 + lane);
+  int ji = 0;  // units issued by this warp
+  auto issue = [&]() {  // whole warp calls; lane 0 issues unit ji
+    if ((ji & 31) == 0 && ji > 0) {
+      cur_ids = nxt_ids;
+      nxt_ids = lookup(ji + 32 + lane);
+    }
+    const uint32_t chunk = __shfl_sync(0xffffffffu, cur_ids, ji & 31);
+    if (lane == 0) {
+      const int st = ji % NST;
+      const uint32_t bar = bar_w + st * 8, dst = ring_w + st * kStageBytes;
+      mbar_expect_tx(bar, kStageBytes);
+      bulk_g2s(dst, p.k_pool + (size_t)chunk * kChunkElems, kChunkBytes, bar);
+      bulk_g2s(dst + kChunkBytes, p.v_pool + (size_t)chunk * kChunkElems, kChunkBytes, bar);
+    }
+    ji++;
+  };
+  for (int j = 0; j < NST && j < n_w; j++) issue();
+
+  int jc = 0;          // units consumed by this warp
+  bool dead = false;   // a wait ran out: stop touching data, keep the barriers balanced
+  const float sc_log2 = p.scale * kLog2e;
+  const bool use_cap = p.softcap != 1.0f;
+
+  // ---- walk the segments of [lo, hi) -----------------------------------------
+  int s = seq_of(lo);
+  int nb = pre[s + 1] - pre[s];
+  int h, b0;
+  {
+    const int r = (int)(lo - (long long)Hkv * pre[s]);
+    h = r / nb;
+    b0 = r - h * nb;
+  }
+  int a = 0;  // CTA-local unit index of the segment start
+  while (a < n_local) {
+    const int seglen = min(nb - b0, n_local - a);
+    const int b1 = b0 + seglen;
+    const int seq = p.seq_base + s;
+    const int kv_len = p.context_lens[seq];
+    const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
+    const int q_len = q_len_of(p, seq);
+    const int ncols = q_len * G;
+
+    // Q^T B-fragments: column nt*8+gid, k = 16j + 2tig (+8).
+    uint32_t qf[NT][8][2];
+    int lim[NT][2];  // keys visible to columns nt*8 + 2tig + {0,1}
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int col = nt * 8 + gid;
+      if (col < ncols) {
+        const int qj = col / G, g = col - qj * G;
+        const uint32_t *qp = reinterpret_cast<const uint32_t *>(
+            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          qf[nt][j][0] = __ldg(qp + 8 * j + tig);
+          qf[nt][j][1] = __ldg(qp + 8 * j + 4 + tig);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) qf[nt][j][0] = qf[nt][j][1] = 0u;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        const int cc = nt * 8 + 2 * tig + c;
+        lim[nt][c] = cc < ncols ? kv_len - q_len + cc / G + 1 : 0;
+      }
+    }
+    const int min_lim = kv_len - q_len + 1;
+
+    float o[8][NT][4];
+    float m[NT][2], l[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      m[nt][0] = m[nt][1] = -INFINITY;
+      l[nt][0] = l[nt][1] = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[mt][nt][i] = 0.f;
+    }
+
+    for (int k = a + ((warp - a) & (kWarps - 1)); k < a + seglen; k += kWarps) {
+      const int blk = b0 + (k - a);
+      const int st = jc % NST;
+      if (!dead) {
+        const bool ok = mbar_wait_bounded(bar_w + st * 8, (jc / NST) & 1);
+        if (!__all_sync(0xffffffffu, ok)) {
+          dead = true;
+          if (lane == 0) atomicOr(p.err, kErrTimeout);
+        }
+      }
+      if (!dead) {
+        const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunkBytes;
+        float sacc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) sacc[nt][i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          uint32_t af[4];
+          ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) mma_bf16_16816(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
+        }
+        const int tok0 = blk * kBlockSize + gid, tok1 = tok0 + 8;
+        const bool need_mask = (blk + 1) * kBlockSize > min_lim;
+        float alpha[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            float x = sacc[nt][i];
+            if (use_cap) x = tanhf(x * p.scale / p.softcap) * p.softcap * kLog2e;
+            else x *= sc_log2;
+            sacc[nt][i] = x;
+          }
+          if (need_mask) {
+            if (tok0 >= lim[nt][0]) sacc[nt][0] = -INFINITY;
+            if (tok0 >= lim[nt][1]) sacc[nt][1] = -INFINITY;
+            if (tok1 >= lim[nt][0]) sacc[nt][2] = -INFINITY;
+            if (tok1 >= lim[nt][1]) sacc[nt][3] = -INFINITY;
+          }
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            float mx = fmaxf(sacc[nt][c], sacc[nt][c + 2]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[nt][c], mx);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float al = fast_exp2(m[nt][c] - m_safe);
+            const float p0 = fast_exp2(sacc[nt][c] - m_safe);
+            const float p1 = fast_exp2(sacc[nt][c + 2] - m_safe);
+            m[nt][c] = m_new;
+            l[nt][c] = l[nt][c] * al + p0 + p1;
+            sacc[nt][c] = p0;
+            sacc[nt][c + 2] = p1;
+            alpha[nt][c] = al;
+          }
+        }
+        uint32_t pb[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          pb[nt][0] = movmatrix_trans(pack_bf16(sacc[nt][0], sacc[nt][1]));
+          pb[nt][1] = movmatrix_trans(pack_bf16(sacc[nt][2], sacc[nt][3]));
+        }
+        // Tokens past the context in the last block may hold anything (NaN
+        // included) and 0*NaN is NaN: clear them in the V fragments
+        // (crates/.../paged_attention.metal:1073-1080 does the same per lane).
+        const int valid = kv_len - blk * kBlockSize;  // >= 1
+        uint32_t vmask[2] = {0xffffffffu, 0xffffffffu};
+        if (valid < kBlockSize) {
+#pragma unroll
+          for (int hh = 0; hh < 2; hh++) {
+            const int t = hh * 8 + 2 * tig;
+            vmask[hh] = (t < valid ? 0x0000ffffu : 0u) | (t + 1 < valid ? 0xffff0000u : 0u);
+          }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+          uint32_t vf[4];
+          ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
+          vf[0] &= vmask[0]; vf[1] &= vmask[0]; vf[2] &= vmask[1]; vf[3] &= vmask[1];
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
+            o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
+            mma_bf16_16816(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+          }
+        }
+      }
+      __syncwarp();
+      jc++;
+      if (ji < n_w) issue();
+    }
+
+    // ---- combine the eight warps' partials (fixed tree order) -----------------
+    for (int half = kWarps / 2; half >= 1; half >>= 1) {
+      if (warp >= half && warp < 2 * half) {
+        float *dst = merge_buf + (warp - half) * (C::kRegs * 32) + lane;
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) dst[((mt * NT + nt) * 4 + i) * 32] = o[mt][nt][i];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
+            dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
+          }
+      }
+      __syncthreads();
+      if (warp < half) {
+        const float *src = merge_buf + warp * (C::kRegs * 32) + lane;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          float wa[2], wb[2];
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            const float mb = src[(32 * NT + nt * 2 + c) * 32];
+            const float lb = src[(34 * NT + nt * 2 + c) * 32];
+            const float mm = fmaxf(m[nt][c], mb);
+            wa[c] = m[nt][c] == -INFINITY ? 0.f : fast_exp2(m[nt][c] - mm);
+            wb[c] = mb == -INFINITY ? 0.f : fast_exp2(mb - mm);
+            m[nt][c] = mm;
+            l[nt][c] = l[nt][c] * wa[c] + lb * wb[c];
+          }
+#pragma unroll
+          for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+              o[mt][nt][i] = o[mt][nt][i] * wa[i & 1] + src[((mt * NT + nt) * 4 + i) * 32] * wb[i & 1];
+        }
+      }
+      __syncthreads();
+    }
+
+    if (warp == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          float v = l[nt][c];
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          v += __shfl_xor_sync(0xffffffffu, v, 8);
+          v += __shfl_xor_sync(0xffffffffu, v, 16);
+          l[nt][c] = v;
+        }
+      const bool partial = b0 > 0 || b1 < nb;
+      if (partial) {
+        float *dst = p.ws + (size_t)(2 * blockIdx.x + (b0 > 0 ? 0 : 1)) * kSlotFloats + lane;
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) dst[((mt * NT + nt) * 4 + i) * 32] = o[mt][nt][i];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
+            dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
+          }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            const int col = nt * 8 + 2 * tig + c;
+            if (col < ncols) {
+              const int qj = col / G, g = col - qj * G;
+              const float inv = l[nt][c] > 0.f ? 1.f / l[nt][c] : 0.f;
+              __nv_bfloat16 *op = p.out + (int64_t)(q0 + qj) * p.out_stride +
+                                  (int64_t)(h * G + g) * kHeadSize;
+#pragma unroll
+              for (int mt = 0; mt < 8; mt++) {
+                op[16 * mt + gid] = __float2bfloat16_rn(o[mt][nt][c] * inv);
+                op[16 * mt + gid + 8] = __float2bfloat16_rn(o[mt][nt][c + 2] * inv);
+              }
+            }
+          }
+      }
+    }
+
+    // ---- next item ---------------------------------------------------------------
+    a += seglen;
+    b0 = 0;
+    if (++h == Hkv) {
+      h = 0;
+      do { s++; } while (s < S && pre[s + 1] == pre[s]);
+    }
+    if (s < S) nb = pre[s + 1] - pre[s];
+  }
+}
+
+// Merge of split items and zero-fill of empty ones.  grid (S, Hkv), 128 threads
+// (one per head dimension).  Recomputes the same flat partition as the main
+// kernel: CTA c owns units [c*W/N, (c+1)*W/N); the CTA holding unit u is
+// ((u+1)*N - 1) / W.
+__global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
+  __shared__ long long red[2][4];
+  const int s = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const int seq = p.seq_base + s;
+  long long before = 0, total = 0;
+  for (int i = d; i < p.S; i += 128) {
+    const int nbi = eligible_blocks(p, p.seq_base + i);
+    total += nbi;
+    if (i < s) before += nbi;
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    total += __shfl_xor_sync(0xffffffffu, total, o);
+  }
+  if ((d & 31) == 0) { red[0][d >> 5] = before; red[1][d >> 5] = total; }
+  __syncthreads();
+  before = red[0][0] + red[0][1] + red[0][2] + red[0][3];
+  total = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+
+  const int q_len = q_len_of(p, seq);
+  if (q_len < 1 || q_len * p.G > p.max_cols) return;  // not ours
+  const int ncols = q_len * p.G;
+  const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
+  const int nb = eligible_blocks(p, seq);
+  if (nb == 0) {  // empty context: zero rows (crates/mlx-sys/src/mlx.cpp:4084-4088)
+    for (int col = 0; col < ncols; col++) {
+      const int qj = col / p.G, g = col - qj * p.G;
+      p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
+          __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const long long W = (long long)p.Hkv * total;
+  const long long U0 = (long long)p.Hkv * before + (long long)h * nb, U1 = U0 + nb;
+  const int c_first = (int)(((U0 + 1) * num_ctas - 1) / W);
+  const int c_last = (int)((U1 * num_ctas - 1) / W);
+  if (c_first == c_last) return;  // written by the main kernel
+
+  const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
+  for (int col = 0; col < ncols; col++) {
+    const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
+    const int lane = gid * 4 + tig;
+    const int o_idx = (((mt * NT + nt) * 4 + upper * 2 + par) * 32) + lane;
+    const int m_idx = (32 * NT + nt * 2 + par) * 32 + lane;
+    const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
+    float mm = -INFINITY;
+    for (int c = c_first; c <= c_last; c++) {
+      const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
+      mm = fmaxf(mm, slot[m_idx]);
+    }
+    float acc = 0.f, lsum = 0.f;
+    for (int c = c_first; c <= c_last; c++) {
+      const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
+      const float mj = slot[m_idx];
+      const float w = mj == -INFINITY ? 0.f : exp2f(mj - mm);
+      acc += slot[o_idx] * w;
+      lsum += slot[l_idx] * w;
+    }
+    const int qj = col / p.G, g = col - qj * p.G;
+    p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
+        __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+  }
+}
+
+template <int NT>
+cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
+  splitkv_kernel<NT><<<num_ctas, kThreads, Cfg<NT>::kSmemBytes, st>>>(p);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int splitkv_max_cols() { return 8 * kMaxNT; }
+
+size_t splitkv_workspace_bytes(int num_ctas) {
+  return (size_t)num_ctas * 2 * kSlotFloats * sizeof(float);
+}
+
+cudaError_t splitkv_configure() {
+  cudaError_t e;
+  e = cudaFuncSetAttribute(splitkv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg<1>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(splitkv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg<2>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(splitkv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg<3>::kSmemBytes);
+}
+
+cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_ctas, cudaStream_t st) {
+  // Width of the kernel: enough 8-column tiles for the widest item it may meet.
+  const int nt = (p_in.max_cols + 7) / 8;
+  for (int base = 0; base < p_in.S; base += kMaxSeqsPerLaunch) {
+    AttnParams p = p_in;
+    p.seq_base = p_in.seq_base + base;
+    p.S = min(kMaxSeqsPerLaunch, p_in.S - base);
+    cudaError_t e;
+    if (nt <= 1) e = launch_nt<1>(p, num_ctas, st);
+    else if (nt == 2) e = launch_nt<2>(p, num_ctas, st);
+    else e = launch_nt<3>(p, num_ctas, st);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)p.S, (unsigned)p.Hkv);
+    splitkv_merge_kernel<<<grid, 128, 0, st>>>(p, num_ctas, nt <= 1 ? 1 : (nt == 2 ? 2 : 3));
+    __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace pa

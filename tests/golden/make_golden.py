@@ -1,0 +1,74 @@
+"""Regenerates tests/golden/*.npz.
+
+The reference keeps no golden vector for the numerical result of its kernels,
+so these fixtures pin the C oracle against an independent implementation
+instead: expected outputs come from tests/numpy_reference.py (float64 numpy
+following the reference's gather/transposes), inputs from the seeded case
+builder.  Stored: the case parameters, a checksum of the inputs, the expected
+pool bits after the write (as a checksum plus a sampled slice) and the expected
+attention output in float32.
+
+Run from the repository root:  python tests/golden/make_golden.py
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+import numpy_reference  # noqa: E402
+from pa_testlib import Case  # noqa: E402
+
+CASES = {
+    # name: (kv_lens, q_lens, Hq, Hkv, NB, seed)
+    "decode_g2": ([1, 15, 16, 17, 100, 33], [1, 1, 1, 1, 1, 1], 4, 2, 32, 11),
+    "decode_g4": ([257, 64, 5, 300], [1, 1, 1, 1], 8, 2, 64, 12),
+    "decode_g8": ([40, 129], [1, 1], 8, 1, 16, 13),
+    "verify_g4": ([37, 70, 21], [5, 5, 1], 8, 2, 16, 14),
+    "prefill_g4": ([96, 50], [64, 50], 4, 1, 16, 15),
+}
+
+
+def digest(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def build(name):
+    kv, ql, Hq, Hkv, NB, seed = CASES[name]
+    return Case(kv, ql, Hq, Hkv, NB, seed=seed)
+
+
+def main():
+    for name in CASES:
+        case = build(name)
+        k_pool, v_pool = case.pools_after_write()
+        # pool after the write, by fancy indexing (no shared index arithmetic)
+        k_exp = case.k_pool.copy()
+        v_exp = case.v_pool.copy()
+        blk, off = case.slots_all // 16, case.slots_all % 16
+        k_exp[blk, :, :, off, :] = case.k_all.reshape(-1, case.Hkv, 16, 8)
+        v_exp[blk, :, :, off] = case.v_all
+        assert (k_exp == k_pool).all() and (v_exp == v_pool).all(), name
+        out = numpy_reference.paged_attention(case.q, k_exp, v_exp, case.block_tables,
+                                              case.kv_lens, case.cu_q, Hq=case.Hq, Hkv=case.Hkv,
+                                              scale=case.scale).astype(np.float32)
+        out_cap = numpy_reference.paged_attention(case.q, k_exp, v_exp, case.block_tables,
+                                                  case.kv_lens, case.cu_q, Hq=case.Hq,
+                                                  Hkv=case.Hkv, scale=case.scale,
+                                                  softcap=30.0).astype(np.float32)
+        np.savez_compressed(
+            os.path.join(HERE, name + ".npz"),
+            inputs_sha256=digest(case.q, case.k_all, case.v_all, case.block_tables),
+            pools_sha256=digest(k_exp, v_exp), k_pool_block0=k_exp[case.block_tables[0, 0]],
+            v_pool_block0=v_exp[case.block_tables[0, 0]], out=out, out_softcap30=out_cap)
+        print(name, out.shape)
+
+
+if __name__ == "__main__":
+    main()

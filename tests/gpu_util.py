@@ -1,0 +1,67 @@
+"""Device-side helpers for the GPU tests: numpy bf16 bit patterns <-> torch
+tensors, and a runner that pushes a Case through the C ABI."""
+import numpy as np
+import torch
+
+import paged_attn_b200 as pa
+from pa_testlib import BS, CANARY, D, X, bf16_to_f32
+
+
+def to_dev(bits: np.ndarray) -> torch.Tensor:
+    """uint16 bf16 bit patterns -> bf16 tensor on the device."""
+    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+class _Raw:
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<i2",
+                                         "data": (int(ptr), False), "version": 2}
+
+
+def device_view(ptr: int, shape) -> torch.Tensor:
+    """bf16 tensor over device memory the library owns (no copy)."""
+    return torch.as_tensor(_Raw(ptr, shape), device="cuda").view(torch.bfloat16)
+
+
+class DeviceCase:
+    """Uploads a Case and owns the pool tensors the cache handle wraps."""
+
+    def __init__(self, case, k_pool=None, v_pool=None):
+        self.case = case
+        self.k_pool = to_dev(case.k_pool if k_pool is None else k_pool)
+        self.v_pool = to_dev(case.v_pool if v_pool is None else v_pool)
+        self.cache = pa.PagedCache(BS, case.NB, D, case.Hkv, key_pools=[self.k_pool],
+                                   value_pools=[self.v_pool])
+        self.q = to_dev(case.q)
+        self.k_new = to_dev(case.k_new)
+        self.v_new = to_dev(case.v_new)
+        self.slots = torch.from_numpy(case.slot_mapping).cuda()
+        self.tables = torch.from_numpy(case.block_tables).cuda()
+        self.lens = torch.from_numpy(case.kv_lens).cuda()
+        self.ws_bytes = self.cache.workspace_bytes()
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device="cuda")
+        # fill the scratch with NaN patterns so stale partials cannot pass for results
+        self.ws.view(torch.int16).fill_(0x7FFF)
+
+    def write(self):
+        c = self.case
+        self.cache.reshape_and_cache(self.k_new, self.v_new, self.slots, len(c.slot_mapping),
+                                     c.Hkv * D, c.Hkv * D)
+
+    def attend(self, varlen=True, softcap=1.0):
+        c = self.case
+        out = torch.full((max(c.total_q, 1), c.Hq, D), float("nan"), dtype=torch.bfloat16,
+                         device="cuda")
+        if varlen:
+            self.cache.varlen(out, self.q, self.tables, self.lens, c.cu_q, c.S, c.Hq, c.MB,
+                              c.scale, self.ws, self.ws_bytes, softcap=softcap)
+        else:
+            self.cache.decode(out, self.q, self.tables, self.lens, c.S, c.Hq, c.MB, c.scale,
+                              self.ws, self.ws_bytes, softcap=softcap)
+        torch.cuda.synchronize()
+        self.cache.check_errors()
+        return bf16_to_f32(to_bits(out))[:c.total_q]

@@ -1,0 +1,48 @@
+"""An independent float64 numpy statement of paged attention, used to pin the C
+oracle.  It follows the reference's software path step for step
+(crates/mlx-sys/src/mlx.cpp:4080-4156): take the sequence's blocks, transpose
+{1,0,2,3,4} then {0,1,3,2,4} (K) / {1,0,2,3} then {0,1,3,2} (V), reshape to
+[Hkv, nb*BS, D], slice to the context, map query head -> kv head by integer
+division, scores*scale, softmax, @V.  Multi-token sequences add the causal limit
+kv_len - q_len + j + 1.  It shares no index arithmetic with oracle/paged_oracle.c."""
+import numpy as np
+
+from pa_testlib import BS, D, X, bf16_to_f32
+
+
+def gather_sequence(k_pool, v_pool, table_row, kv_len):
+    nb = (kv_len + BS - 1) // BS
+    blocks = table_row[:nb]
+    k = k_pool[blocks]                                  # [nb, Hkv, D/X, BS, X]
+    k = k.transpose(1, 0, 2, 3, 4).transpose(0, 1, 3, 2, 4)  # [Hkv, nb, BS, D/X, X]
+    k = k.reshape(k.shape[0], nb * BS, D)[:, :kv_len]
+    v = v_pool[blocks]                                  # [nb, Hkv, D, BS]
+    v = v.transpose(1, 0, 2, 3).transpose(0, 1, 3, 2)   # [Hkv, nb, BS, D]
+    v = v.reshape(v.shape[0], nb * BS, D)[:, :kv_len]
+    return bf16_to_f32(np.ascontiguousarray(k)).astype(np.float64), \
+        bf16_to_f32(np.ascontiguousarray(v)).astype(np.float64)
+
+
+def paged_attention(q_bits, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv, scale,
+                    softcap=1.0):
+    q = bf16_to_f32(q_bits).astype(np.float64)
+    out = np.zeros(q.shape, dtype=np.float64)
+    G = Hq // Hkv
+    for s in range(len(kv_lens)):
+        kv_len = int(kv_lens[s])
+        q0, q1 = int(cu_q[s]), int(cu_q[s + 1])
+        if kv_len == 0 or q1 == q0:
+            continue
+        k, v = gather_sequence(k_pool, v_pool, block_tables[s], kv_len)
+        for j in range(q1 - q0):
+            n = kv_len - (q1 - q0) + j + 1
+            if n <= 0:
+                continue
+            for hq in range(Hq):
+                h = hq // G
+                logits = (k[h, :n] @ q[q0 + j, hq]) * scale
+                if softcap != 1.0:
+                    logits = np.tanh(logits / softcap) * softcap
+                w = np.exp(logits - logits.max())
+                out[q0 + j, hq] = (w / w.sum()) @ v[h, :n]
+    return out

@@ -1,0 +1,225 @@
+"""Shared test infrastructure: the oracle binding, seeded case builders and the
+parity rule.  Only tests, the smoke check and the benchmark's CPU-baseline leg
+import this module."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_DIR = os.path.join(ROOT, "mlx-node_b200")
+if PKG_DIR not in sys.path:
+    sys.path.insert(0, PKG_DIR)
+
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_LIB = os.path.join(ORACLE_DIR, "liboracle.so")
+
+D = 128
+BS = 16
+X = 8
+CANARY = 0x7FFF  # bf16 NaN pattern in never-written pool slots
+
+_oracle = None
+
+
+def oracle() -> C.CDLL:
+    global _oracle
+    if _oracle is not None:
+        return _oracle
+    if not os.path.exists(ORACLE_LIB):
+        subprocess.run(["make", "-C", ORACLE_DIR], check=True, capture_output=True)
+    lib = C.CDLL(ORACLE_LIB)
+    vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+    lib.oracle_num_threads.restype = i32
+    lib.oracle_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32]
+    lib.oracle_reshape_and_cache.restype = None
+    lib.oracle_copy_blocks.argtypes = [vp, vp, vp, i64, i64]
+    lib.oracle_copy_blocks.restype = None
+    lib.oracle_paged_attention_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                                  i32, i32, i64, f32, f32]
+    lib.oracle_paged_attention_varlen.restype = None
+    lib.oracle_paged_attention_rows.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32,
+                                                i32, i32, i64, f32, f32]
+    lib.oracle_paged_attention_rows.restype = None
+    lib.oracle_dense_causal.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32]
+    lib.oracle_dense_causal.restype = None
+    lib.baseline_mlx_paged_forward.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                                               i32, f32]
+    lib.baseline_mlx_paged_forward.restype = i32
+    lib.oracle_fill_normal_bf16.argtypes = [vp, i64, C.c_uint64, C.c_uint64, i64]
+    lib.oracle_fill_normal_bf16.restype = None
+    lib.oracle_f32_to_bf16.argtypes = [vp, vp, i64]
+    lib.oracle_f32_to_bf16.restype = None
+    lib.oracle_bf16_to_f32.argtypes = [vp, vp, i64]
+    lib.oracle_bf16_to_f32.restype = None
+    _oracle = lib
+    return lib
+
+
+def p(a: np.ndarray) -> int:
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+# ---- bf16 <-> numpy ----------------------------------------------------------------
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round to nearest even, NaN -> 0x7FC0 (crates/mlx-paged-attn/metal/utils.metal:14-27)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u.astype(np.uint64) + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r[nan] = 0x7FC0
+    return r
+
+
+def normal_bf16(shape, seed: int, stream: int) -> np.ndarray:
+    """Seeded N(0,1) bf16 bit patterns from the oracle's counter-based generator."""
+    out = np.empty(shape, dtype=np.uint16)
+    oracle().oracle_fill_normal_bf16(p(out), out.size, seed, stream, 0)
+    return out
+
+
+# ---- case construction ---------------------------------------------------------------
+class Case:
+    """One seeded workload: pool pre-filled with every sequence's prefix, the
+    step's new tokens and queries held apart for the code under test."""
+
+    def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True):
+        self.S = len(kv_lens)
+        self.Hq, self.Hkv, self.NB = Hq, Hkv, NB
+        self.G = Hq // Hkv
+        self.kv_lens = np.asarray(kv_lens, dtype=np.int32)
+        self.q_lens = np.asarray(q_lens, dtype=np.int32)
+        assert (self.q_lens <= self.kv_lens).all()
+        self.cu_q = np.zeros(self.S + 1, dtype=np.int32)
+        self.cu_q[1:] = np.cumsum(self.q_lens)
+        self.total_q = int(self.cu_q[-1])
+        nblk = (self.kv_lens + BS - 1) // BS
+        assert int(nblk.sum()) <= NB, "pool too small"
+        rng = np.random.Generator(np.random.PCG64(seed))
+        perm = rng.permutation(NB).astype(np.int32)
+        self.MB = max(int(nblk.max()) if self.S else 1, 1) + mb_extra
+        self.block_tables = np.zeros((self.S, self.MB), dtype=np.int32)  # zero padded
+        pos = 0
+        for s in range(self.S):
+            self.block_tables[s, :nblk[s]] = perm[pos:pos + nblk[s]]
+            pos += nblk[s]
+        self.scale = 1.0 / math.sqrt(D)
+        # tensors
+        self.q = normal_bf16((self.total_q, Hq, D), seed, 1)
+        tot_kv = int(self.kv_lens.sum())
+        self.cu_kv = np.zeros(self.S + 1, dtype=np.int32)
+        self.cu_kv[1:] = np.cumsum(self.kv_lens)
+        self.k_all = normal_bf16((tot_kv, Hkv, D), seed, 2)  # every token of every sequence
+        self.v_all = normal_bf16((tot_kv, Hkv, D), seed, 3)
+        slots_all = np.empty(tot_kv, dtype=np.int64)
+        is_new = np.zeros(tot_kv, dtype=bool)
+        for s in range(self.S):
+            t = np.arange(self.kv_lens[s])
+            slots_all[self.cu_kv[s]:self.cu_kv[s + 1]] = (
+                self.block_tables[s, t // BS].astype(np.int64) * BS + t % BS)
+            is_new[self.cu_kv[s + 1] - self.q_lens[s]:self.cu_kv[s + 1]] = True
+        self.slots_all = slots_all
+        self.k_new = np.ascontiguousarray(self.k_all[is_new])
+        self.v_new = np.ascontiguousarray(self.v_all[is_new])
+        self.slot_mapping = np.ascontiguousarray(slots_all[is_new])
+        self.k_pool = np.full((NB, Hkv, D // X, BS, X), CANARY, dtype=np.uint16)
+        self.v_pool = np.full((NB, Hkv, D, BS), CANARY, dtype=np.uint16)
+        if prefill:
+            old = ~is_new
+            write_oracle(self.k_pool, self.v_pool, np.ascontiguousarray(self.k_all[old]),
+                         np.ascontiguousarray(self.v_all[old]),
+                         np.ascontiguousarray(slots_all[old]), Hkv)
+
+    def pools_after_write(self):
+        k, v = self.k_pool.copy(), self.v_pool.copy()
+        write_oracle(k, v, self.k_new, self.v_new, self.slot_mapping, self.Hkv)
+        return k, v
+
+
+def write_oracle(k_pool, v_pool, key, value, slots, Hkv, key_stride=None, value_stride=None):
+    n = len(slots)
+    if n == 0:
+        return
+    oracle().oracle_reshape_and_cache(p(key), p(value), p(k_pool), p(v_pool), p(slots), n,
+                                      key_stride or Hkv * D, value_stride or Hkv * D, Hkv, D, BS, X)
+
+
+def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np.ndarray:
+    out = np.zeros((case.total_q, case.Hq, D), dtype=np.float32)
+    cu = p(case.cu_q) if varlen else None
+    oracle().oracle_paged_attention_varlen(p(out), p(case.q), p(k_pool), p(v_pool),
+                                           p(case.block_tables), p(case.kv_lens), cu, case.S,
+                                           case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
+                                           case.scale, softcap)
+    return out
+
+
+def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv, MB, scale,
+                          softcap=1.0) -> np.ndarray:
+    rows = np.ascontiguousarray(rows, dtype=np.int32).reshape(-1, 3)
+    out = np.zeros((len(rows), D), dtype=np.float32)
+    oracle().oracle_paged_attention_rows(p(out), p(rows), len(rows), p(q), p(k_pool), p(v_pool),
+                                         p(block_tables), p(kv_lens),
+                                         p(cu_q) if cu_q is not None else None, Hq, Hkv, D, BS, MB,
+                                         Hq * D, scale, softcap)
+    return out
+
+
+# ---- parity rule ------------------------------------------------------------------------
+ATOL = 2e-2   # max-abs bound stated for the path
+RTOL = 1e-2   # max-rel bound, applied with an RMS floor so near-zero elements do not dominate
+
+
+def check_attention(got_f32: np.ndarray, ref_f32: np.ndarray, what: str = "") -> dict:
+    """bf16 output with fp32 accumulation vs the fp64-accumulated oracle:
+    (i) max|a-b| <= 2e-2; (ii) |a-b| <= 1e-2*|ref| + 1e-2*rms(ref) element-wise."""
+    got = got_f32.astype(np.float64).reshape(-1)
+    ref = ref_f32.astype(np.float64).reshape(-1)
+    assert got.shape == ref.shape
+    assert np.isfinite(got).all(), f"{what}: non-finite values in the output"
+    diff = np.abs(got - ref)
+    rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
+    bound = RTOL * np.abs(ref) + RTOL * rms
+    worst = int(np.argmax(diff - bound)) if ref.size else 0
+    stats = {"max_abs": float(diff.max()) if ref.size else 0.0, "rms_ref": rms,
+             "max_over_bound": float((diff / np.maximum(bound, 1e-30)).max()) if ref.size else 0.0,
+             "worst_index": worst}
+    assert stats["max_abs"] <= ATOL, f"{what}: max abs error {stats['max_abs']:.3e} > {ATOL}"
+    assert (diff <= bound).all(), (
+        f"{what}: element {worst}: got {got[worst]:.6f} ref {ref[worst]:.6f} "
+        f"|diff| {diff[worst]:.3e} > bound {bound[worst]:.3e} (rms {rms:.3e})")
+    return stats
+
+
+# ---- the five benchmark configurations (lengths only; seeded) ---------------------------
+def config_lengths(name: str, seed: int = 0):
+    """(kv_lens, q_lens, Hq, Hkv, NB) of the named configuration.  kv_lens count the
+    tokens written this step."""
+    rng = np.random.Generator(np.random.PCG64(seed + 1000))
+    if name == "c1":   # Qwen3-0.6B-shaped decode
+        return rng.integers(512, 2049, 8), np.ones(8, int), 16, 8, 1024
+    if name == "c2":   # Qwen3-8B-shaped decode
+        return rng.integers(1024, 8193, 64), np.ones(64, int), 32, 8, 40000
+    if name == "c3":   # Qwen3-32B-shaped decode, lognormal lengths (median 4096, sigma 1)
+        z = rng.standard_normal(128)
+        kv = np.clip(np.rint(np.exp(math.log(4096.0) + z)), 256, 32768).astype(int)
+        return kv, np.ones(128, int), 64, 8, 65536
+    if name == "c4":   # chunked prefill: 8192 cached + 2048 new, causal
+        return np.full(8, 8192 + 2048), np.full(8, 2048), 32, 8, 8192
+    if name == "c5":   # mixed batch: 48 decode + 8 verify (5 queries) + 2 prefill chunks
+        dec = rng.integers(1024, 16385, 48)
+        ver = rng.integers(2048, 8193, 8) + 5
+        pre = np.full(2, 4096 + 1024)
+        kv = np.concatenate([dec, ver, pre])
+        ql = np.concatenate([np.ones(48, int), np.full(8, 5), np.full(2, 1024)])
+        return kv, ql, 32, 8, 60000
+    raise KeyError(name)

@@ -1,0 +1,85 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the
+header declares, and rejects bad arguments before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import paged_attn_b200 as pa
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "paged_attn_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b((?:pa|mlx)_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_and_binding_list_the_same_symbols():
+    assert declared_functions() == sorted(pa.EXPORTED_SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = pa.load_library()
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} missing from {pa.LIB_PATH}"
+
+
+def test_no_torch_or_oracle_in_the_library():
+    # The shipped library must not depend on the oracle or on a tensor library.
+    import subprocess
+    out = subprocess.run(["ldd", pa.LIB_PATH], capture_output=True, text=True).stdout
+    assert "liboracle" not in out and "torch" not in out and "c10" not in out
+
+
+def test_version_and_error_string():
+    lib = pa.load_library()
+    assert lib.pa_version() >= 100
+    assert isinstance(pa.last_error(), str)
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("block_size", 64, 1),      # crates/mlx-paged-attn/src/config.rs:144-160: block 64 rejected
+    ("head_size", 100, 1),      # head 100 rejected
+    ("num_blocks", 0, 1),
+    ("dtype", 7, 1),
+    ("dtype", 0, 2),            # f16 accepted by the reference, not built here
+    ("block_size", 32, 2),      # valid in the reference, not built here
+    ("head_size", 64, 2),
+])
+def test_config_validation_needs_no_device(field, value, status):
+    lib = pa.load_library()
+    cfg = pa.PagedAttnConfig(16, 8, 128, 2, 1, 1)
+    setattr(cfg, field, value)
+    handle = C.c_void_p()
+    assert lib.pa_cache_create(C.byref(cfg), 0, C.byref(handle)) == status
+    assert not handle.value
+    assert pa.last_error()
+    assert lib.mlx_paged_attn_create_cache(C.byref(cfg)) is None
+
+
+def test_null_arguments_are_rejected():
+    lib = pa.load_library()
+    assert lib.pa_cache_create(None, 0, C.byref(C.c_void_p())) == 1
+    assert lib.pa_reshape_and_cache(None, 0, None, None, None, 1, 1, 1, None) == 1
+    assert lib.pa_paged_attention_decode(None, 0, None, None, None, None, 1, 1, 1, 1, 1, 1.0, 1.0,
+                                         None, 0, None) == 1
+    assert lib.pa_copy_blocks(None, 0, None, 1, None) == 1
+    assert lib.pa_cache_free(None) == 0
+    assert lib.pa_attention_workspace_bytes(None) == 0
+    assert lib.mlx_paged_attn_forward(None, None, None, None, None, 1.0, 16, 0) is None
+    lib.mlx_paged_attn_reshape_and_cache(None, 0, None, None, None)   # silent no-op
+    lib.mlx_paged_attn_copy_blocks(None, 0, None)
+    lib.mlx_array_delete(None)
+
+
+def test_compute_fails_loudly_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    with pytest.raises(pa.PagedAttnError):
+        pa.PagedCache(16, 8, 128, 2)
