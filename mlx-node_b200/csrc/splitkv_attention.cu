@@ -468,6 +468,10 @@ __global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, 
   const int c_last = (int)((U1 * num_ctas - 1) / W);
   if (c_first == c_last) return;  // written by the main kernel
 
+  // With fewer units than CTAs some CTAs between c_first and c_last own nothing.
+  auto cta_empty = [&](int c) {
+    return (long long)(c + 1) * W / num_ctas <= (long long)c * W / num_ctas;
+  };
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
   for (int col = 0; col < ncols; col++) {
     const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
@@ -477,11 +481,13 @@ __global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, 
     const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
     float mm = -INFINITY;
     for (int c = c_first; c <= c_last; c++) {
+      if (cta_empty(c)) continue;
       const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
       mm = fmaxf(mm, slot[m_idx]);
     }
     float acc = 0.f, lsum = 0.f;
     for (int c = c_first; c <= c_last; c++) {
+      if (cta_empty(c)) continue;
       const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
       const float mj = slot[m_idx];
       const float w = mj == -INFINITY ? 0.f : exp2f(mj - mm);

@@ -176,27 +176,35 @@ def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, 
 
 # ---- parity rule ------------------------------------------------------------------------
 ATOL = 2e-2   # max-abs bound stated for the path
-RTOL = 1e-2   # max-rel bound, applied with an RMS floor so near-zero elements do not dominate
+RTOL = 1e-2   # max-rel bound, applied with a per-row RMS floor
 
 
 def check_attention(got_f32: np.ndarray, ref_f32: np.ndarray, what: str = "") -> dict:
     """bf16 output with fp32 accumulation vs the fp64-accumulated oracle:
-    (i) max|a-b| <= 2e-2; (ii) |a-b| <= 1e-2*|ref| + 1e-2*rms(ref) element-wise."""
-    got = got_f32.astype(np.float64).reshape(-1)
-    ref = ref_f32.astype(np.float64).reshape(-1)
+    (i) max|a-b| <= 2e-2;
+    (ii) |a-b| <= 1e-2*|ref| + 1e-2*rms(row) element-wise, where a row is the D
+    outputs of one (query, head).  The floor is per row because a batch mixes
+    short contexts (outputs ~0.3) with long ones (outputs ~0.01): a global floor
+    would be loose for the long rows and meaningless for the short ones, and a
+    pure relative test would be dominated by elements that happen to be near 0."""
+    got = got_f32.astype(np.float64).reshape(-1, D)
+    ref = ref_f32.astype(np.float64).reshape(-1, D)
     assert got.shape == ref.shape
     assert np.isfinite(got).all(), f"{what}: non-finite values in the output"
+    if ref.size == 0:
+        return {"max_abs": 0.0, "max_over_bound": 0.0, "rms_ref": 0.0}
     diff = np.abs(got - ref)
-    rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
+    rms = np.sqrt(np.mean(ref * ref, axis=1, keepdims=True))
     bound = RTOL * np.abs(ref) + RTOL * rms
-    worst = int(np.argmax(diff - bound)) if ref.size else 0
-    stats = {"max_abs": float(diff.max()) if ref.size else 0.0, "rms_ref": rms,
-             "max_over_bound": float((diff / np.maximum(bound, 1e-30)).max()) if ref.size else 0.0,
-             "worst_index": worst}
+    ratio = diff / np.maximum(bound, 1e-30)
+    ratio[(diff == 0)] = 0.0
+    worst = np.unravel_index(int(np.argmax(ratio)), ratio.shape)
+    stats = {"max_abs": float(diff.max()), "rms_ref": float(np.sqrt(np.mean(ref * ref))),
+             "max_over_bound": float(ratio.max()), "worst_row": int(worst[0])}
     assert stats["max_abs"] <= ATOL, f"{what}: max abs error {stats['max_abs']:.3e} > {ATOL}"
-    assert (diff <= bound).all(), (
-        f"{what}: element {worst}: got {got[worst]:.6f} ref {ref[worst]:.6f} "
-        f"|diff| {diff[worst]:.3e} > bound {bound[worst]:.3e} (rms {rms:.3e})")
+    assert stats["max_over_bound"] <= 1.0, (
+        f"{what}: row {worst[0]} dim {worst[1]}: got {got[worst]:.6f} ref {ref[worst]:.6f} "
+        f"|diff| {diff[worst]:.3e} > bound {bound[worst]:.3e} (row rms {rms[worst[0], 0]:.3e})")
     return stats
 
 
