@@ -190,6 +190,36 @@ pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
                                     float softcap, void *workspace,
                                     size_t workspace_bytes, void *cuda_stream);
 
+/* Decode attention for callers that cannot allocate device memory.
+ * No counterpart in the reference.  Some hosts of this library are handed
+ * their buffers by someone else and have no way to ask for more: a plugin
+ * running inside another runtime's memory pool, a caller whose allocator is
+ * locked down once serving has started, code that runs where a cudaMalloc
+ * would stall every stream of the process.  For them this entry computes
+ * exactly what pa_paged_attention_decode computes, but keeps the split-KV
+ * partial results in an array that is part of the library image instead of a
+ * caller workspace; it calls no allocator, the CUDA one or any other.
+ *   Limit: the array holds partials for 160 CTAs (one per SM), 4.2 MiB.  It is
+ * resident on every GPU this process uses the library on, from load to exit,
+ * whether or not this entry is ever called.  On a GPU with more than 160 SMs
+ * the call is refused with PA_ERR_UNSUPPORTED and a message saying so.
+ *   The first call on each device looks up the array's device address (one
+ * runtime query, remembered afterwards); make that first call outside any
+ * stream capture.
+ *   All calls on a device share the one array.  Nothing in it has to start at
+ * zero - every slot is written before it is read within a call - but two calls
+ * whose kernels overlap on the GPU (different streams, no ordering between
+ * them) would overwrite each other's partials: keep calls to this entry
+ * ordered on a device.  Arguments are those of pa_paged_attention_decode minus
+ * the workspace.                                                              */
+pa_status pa_paged_attention_decode_static(PagedAttnCache *cache, uint32_t layer_idx,
+                                           void *out, const void *q,
+                                           const int32_t *block_tables,
+                                           const int32_t *context_lens, int32_t num_seqs,
+                                           int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                           int64_t q_stride, int64_t out_stride, float scale,
+                                           float softcap, void *cuda_stream);
+
 /* Variable-length paged attention: decode, speculative-verify and
  * chunked-prefill sequences mixed in one call.  The reference has no such
  * entry (its scheduler says so, crates/mlx-paged-attn/src/scheduler.rs:237-242);

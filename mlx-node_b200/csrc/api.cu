@@ -436,6 +436,29 @@ pa_status pa_paged_attention_decode(PagedAttnCache *c, uint32_t layer, void *out
                                    softcap, 0, workspace, workspace_bytes, cuda_stream);
 }
 
+pa_status pa_paged_attention_decode_static(PagedAttnCache *c, uint32_t layer, void *out,
+                                           const void *q, const int32_t *block_tables,
+                                           const int32_t *context_lens, int32_t num_seqs,
+                                           int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                           int64_t q_stride, int64_t out_stride, float scale,
+                                           float softcap, void *cuda_stream) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (c->num_sms > pa::splitkv_static_max_ctas())
+    return fail(PA_ERR_UNSUPPORTED,
+                "this GPU has " + std::to_string(c->num_sms) + " SMs; the library-resident scratch "
+                "holds partial results for at most " + std::to_string(pa::splitkv_static_max_ctas()) +
+                " CTAs - use pa_paged_attention_decode with a caller workspace");
+  DeviceGuard g(c->device);
+  if (!g.ok) return fail(PA_ERR_CUDA, "cannot select device");
+  float *scratch = nullptr;
+  PA_CUDA(pa::splitkv_static_scratch(c->device, &scratch));
+  return pa_paged_attention_decode(c, layer, out, q, block_tables, context_lens, num_seqs,
+                                   num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale,
+                                   softcap, scratch, pa::splitkv_workspace_bytes(c->num_sms),
+                                   cuda_stream);
+}
+
 pa_status pa_decode_step_host(PagedAttnCache *c, uint32_t layer, void *out_host,
                               const void *q_host, const void *k_host, const void *v_host,
                               const int64_t *slots_host, const int32_t *tables_host,

@@ -137,6 +137,9 @@ cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStre
 size_t splitkv_workspace_bytes(int num_ctas);
 int splitkv_max_cols();
 cudaError_t splitkv_configure();  // opt-in shared memory sizes, once per device
+// Library-resident scratch for callers that cannot allocate (see splitkv_attention.cu).
+int splitkv_static_max_ctas();
+cudaError_t splitkv_static_scratch(int device, float **out);
 // Tile kernel for long-query sequences; work list built by the caller.
 struct TileWork {
   int32_t seq;       // sequence index

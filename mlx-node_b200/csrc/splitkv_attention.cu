@@ -35,6 +35,8 @@
 // tiles are consumed straight from the raw 4 KB chunks.  P^T is produced from the
 // S^T accumulators with one movmatrix transpose per 8x8 tile.  Online softmax in
 // fp32 with exp2; column maxima by warp shuffles.
+#include <mutex>
+
 #include "pa_common.cuh"
 
 namespace pa {
@@ -508,6 +510,33 @@ cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
 }
 
 }  // namespace
+
+// ---- scratch that needs no allocation ----------------------------------------
+// Partial-result slots for up to kStaticMaxCtas CTAs, resident in every process
+// that loads the library on every GPU it touches (4.2 MiB each) until exit.
+constexpr int kStaticMaxCtas = 160;
+static __device__ __align__(256) float g_static_scratch[(size_t)kStaticMaxCtas * 2 * kSlotFloats];
+
+int splitkv_static_max_ctas() { return kStaticMaxCtas; }
+
+// Device address of the static scratch on `device`, which must be the current
+// device.  In host code the array's name is only a handle, so the address is asked
+// of the runtime once per device and remembered.
+cudaError_t splitkv_static_scratch(int device, float **out) {
+  constexpr int kMaxDevices = 64;
+  static float *ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[device]) {
+    float *ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
+    if (e != cudaSuccess) return e;
+    ptrs[device] = ptr;
+  }
+  *out = ptrs[device];
+  return cudaSuccess;
+}
 
 int splitkv_max_cols() { return 8 * kMaxNT; }
 

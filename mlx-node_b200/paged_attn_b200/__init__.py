@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "pa_cache_create", "pa_cache_wrap", "pa_cache_free", "pa_cache_key_ptr", "pa_cache_value_ptr",
     "pa_cache_get_config", "pa_cache_check_errors", "pa_reshape_and_cache", "pa_copy_blocks",
     "pa_attention_workspace_bytes", "pa_paged_attention_decode", "pa_paged_attention_varlen",
+    "pa_paged_attention_decode_static",
     "pa_decode_step_host", "pa_kernel_launch_count",
 ]
 
@@ -83,6 +84,8 @@ def load_library() -> C.CDLL:
     lib.pa_attention_workspace_bytes.restype = sz
     lib.pa_paged_attention_decode.argtypes = [vp, u32, vp, vp, vp, vp, i32, i32, i32, i64, i64,
                                               f32, f32, vp, sz, vp]
+    lib.pa_paged_attention_decode_static.argtypes = [vp, u32, vp, vp, vp, vp, i32, i32, i32, i64,
+                                                     i64, f32, f32, vp]
     lib.pa_paged_attention_varlen.argtypes = [vp, u32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
                                               f32, f32, i32, vp, sz, vp]
     lib.pa_decode_step_host.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32]
@@ -207,6 +210,17 @@ class PagedCache:
             self.handle, layer, _ptr(out), _ptr(q), _ptr(block_tables), _ptr(context_lens),
             num_seqs, num_q_heads, max_blocks_per_seq, q_stride or row, out_stride or row, scale,
             softcap, _ptr(workspace), workspace_bytes, stream))
+
+    def decode_static(self, out, q, block_tables, context_lens, num_seqs: int, num_q_heads: int,
+                      max_blocks_per_seq: int, scale: float, softcap: float = 1.0,
+                      q_stride: int | None = None, out_stride: int | None = None, layer: int = 0,
+                      stream: int = 0) -> None:
+        """Decode attention with the library-resident scratch (no workspace, no allocation)."""
+        row = num_q_heads * self.cfg.head_size
+        _check(self.lib.pa_paged_attention_decode_static(
+            self.handle, layer, _ptr(out), _ptr(q), _ptr(block_tables), _ptr(context_lens),
+            num_seqs, num_q_heads, max_blocks_per_seq, q_stride or row, out_stride or row, scale,
+            softcap, stream))
 
     def varlen(self, out, q, block_tables, context_lens, cu_q_lens_host, num_seqs: int,
                num_q_heads: int, max_blocks_per_seq: int, scale: float, workspace,
