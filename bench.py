@@ -207,6 +207,9 @@ def main() -> None:
     ap.add_argument("--gather", action="store_true",
                     help="all-gather the head outputs over NCCL inside the step (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--seqs", type=int, default=0, help="use only the first N sequences (small captures)")
+    ap.add_argument("--pool-blocks", type=int, default=0, help="override the pool size in blocks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -228,7 +231,11 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     kv, ql, Hq, Hkv, NB = workload_lengths(args.workload, world)
-    assert Hkv % world == 0
+    if args.seqs:
+        kv, ql = kv[:args.seqs], ql[:args.seqs]
+    if args.pool_blocks:
+        NB = args.pool_blocks
+    assert Hkv % world == 0 and int(((kv + BS - 1) // BS).sum()) <= NB
     hkv_l, hq_l = Hkv // world, Hq // world
     S, total_q = len(kv), int(np.sum(ql))
     nblk = (kv + BS - 1) // BS
@@ -337,7 +344,7 @@ def main() -> None:
 
     # end to end through the host-buffer entry: H2D of the step's inputs + kernels + D2H
     e2e = None
-    if decode_only:
+    if decode_only and not args.no_e2e:
         pin = lambda t: t.cpu().pin_memory()
         q_h, k_h, v_h, out_h = pin(q), pin(k_new), pin(v_new), torch.empty_like(q, device="cpu").pin_memory()
         slots_h, tables_p, lens_h = pin(slots), pin(tables), pin(lens)
