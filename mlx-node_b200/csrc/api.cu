@@ -397,9 +397,10 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       any_small = true;
       if (ql * G > widest_small) widest_small = ql * G;
     } else {
-      // Later tiles see more keys: list them first so the long ones start early.
-      for (int qb = ((ql - 1) / tile_q) * tile_q; qb >= 0; qb -= tile_q)
-        for (int h = 0; h < Hkv; h++)
+      // Tiles of one (sequence, kv head) are neighbours in launch order so that they
+      // share the head's KV blocks in L2; later tiles see more keys and go first.
+      for (int h = 0; h < Hkv; h++)
+        for (int qb = ((ql - 1) / tile_q) * tile_q; qb >= 0; qb -= tile_q)
           tiles.push_back(pa::TileWork{s, h, qb, ql - qb < tile_q ? ql - qb : tile_q});
     }
   }

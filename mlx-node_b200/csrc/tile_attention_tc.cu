@@ -1,0 +1,510 @@
+// Tile kernel for long-query sequences (chunked prefill) over the paged cache:
+// tcgen05 tensor cores with TMEM accumulators, sm_100a.
+//
+// The reference has no paged prefill kernel: its prefill is dense causal
+// attention followed by a scatter into the pool
+// (crates/mlx-core/src/transformer/block.rs:279-317).  This kernel attends
+// directly over the pool: query j of a sequence sees keys [0, kv_len-q_len+j].
+//
+// One CTA = 256 rows of one (sequence, kv head): a row is a (query token, query
+// head of the GQA group) pair, token-major, i.e. two 128-row Q tiles that share
+// every KV tile.  KV tiles are 128 tokens (8 blocks).
+//
+// Roles (13 warps):
+//   warps 0-3   softmax of Q tile 0 (thread = row = TMEM lane)
+//   warps 4-7   softmax of Q tile 1
+//   warps 8-11  producers: gather the 4 KB K and V chunks of the tile's blocks
+//               through the block table with 16-byte cp.async, writing them
+//               straight into the 128-byte-swizzled K-major operand layout
+//               the tensor core reads (K chunk [d/8][tok][8] -> rows = tokens;
+//               V chunk [d][tok] -> rows = d, 64 tokens per 128-byte row)
+//   warp 12     allocates TMEM; one lane issues every tcgen05.mma
+//
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16) is
+// written over the first 64 columns of its S and fed back as the A operand of
+// the P.V product, so P never touches shared memory.
+//   S_i = Q_i . K^T        A = Q_i (smem), B = K tile (smem), 8 x (M128 N128 K16)
+//   O_i += P_i . V         A = P_i (TMEM), B = V tile (smem), 8 x (M128 N128 K16)
+// Issue order S0 S1 | PV0 S0' PV1 S1' | ... so that the softmax of one Q tile
+// overlaps the tensor work of the other.  Online softmax keeps a stale row
+// maximum and rescales O only when the maximum grows by more than 2^8.
+//
+// Every wait is bounded; on expiry the CTA raises the error word, every role
+// leaves its loop, in-flight copies are drained and TMEM is freed.
+#include "pa_common.cuh"
+
+namespace pa {
+
+namespace {
+
+constexpr int kQRows = 128;            // rows per Q tile
+constexpr int kTileTok = 128;          // tokens per KV tile
+constexpr int kSlab = 128 * 128;       // one operand slab: 128 rows x 128 B
+constexpr int kQBytes = 4 * kSlab;     // 2 Q tiles x 2 slabs
+constexpr int kStage = 2 * kSlab;      // one K or V tile
+constexpr int kTblCap = 2048;          // block ids staged per CTA (32768 tokens)
+constexpr int kNumBars = 16;
+constexpr int kSmemTc = 1024 + kQBytes + 4 * kStage + kTblCap * 4 + kNumBars * 8 + 16;
+constexpr int kTcThreads = 13 * 32;
+
+// barrier slots
+enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9,
+       B_PREADY = 11, B_PVDONE = 13 };
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
+      "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B
+// apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// Byte offset of 16-byte unit `u` (0..7) of row `r` inside a 128-row slab.
+__device__ __forceinline__ uint32_t sw128_off(int r, int u) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((u ^ (r & 7)) << 4));
+}
+
+// Wait that gives up when the budget runs out or another role has raised the flag.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > (1ll << 31)) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_s = base, k_s = base + kQBytes, v_s = k_s + 2 * kStage;
+  int *tbl = reinterpret_cast<int *>(gen + kQBytes + 4 * kStage);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(gen + kQBytes + 4 * kStage + kTblCap * 4);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + kNumBars);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const TileWork w = work[blockIdx.x];
+  const int seq = w.seq, h = w.kv_head, G = p.G;
+  const int kv_len = p.context_lens[seq];
+  const int q0 = p.cu_q_lens[seq];
+  const int q_len = p.cu_q_lens[seq + 1] - q0;
+  const int kv_hi = max(0, min(kv_len, kv_len - q_len + w.q_begin + w.q_count));
+  const int n_tiles = (kv_hi + kTileTok - 1) / kTileTok;
+  const int nblk = (kv_hi + kBlockSize - 1) / kBlockSize;
+  const int32_t *table = p.block_tables + (int64_t)seq * p.MB;
+
+  // ---- set-up ---------------------------------------------------------------------
+  for (int i = tid; i < nblk && i < kTblCap; i += kTcThreads) {
+    uint32_t id = (uint32_t)table[i];
+    if (id >= p.num_blocks) {
+      atomicOr(p.err, kErrBlockRange);
+      id = 0;
+    }
+    tbl[i] = (int)id;
+  }
+  if (tid == 0) {
+    mbar_init(bar(B_QFULL), 128);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar(B_KFULL + s), 128);
+      mbar_init(bar(B_VFULL + s), 128);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+      mbar_init(bar(B_SFULL + s), 1);
+      mbar_init(bar(B_PREADY + s), 128);
+      mbar_init(bar(B_PVDONE + s), 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 12) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
+        smem_u32(tmem_holder)));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_holder;
+  bool failed = false;
+
+  if (n_tiles > 0) {
+    if (warp >= 8 && warp < 12) {
+      // =========================== producers ========================================
+      const int pt = tid - 256;  // 0..127
+      const int pw = warp - 8;
+      auto block_id = [&](int b) -> uint32_t {
+        if (b < kTblCap) return (uint32_t)tbl[b];
+        uint32_t id = (uint32_t)table[b];
+        if (id >= p.num_blocks) {
+          atomicOr(p.err, kErrBlockRange);
+          id = 0;
+        }
+        return id;
+      };
+      // Q: 2 tiles x 128 rows x 16 pieces of 16 B
+      for (int it = 0; it < 32; it++) {
+        const int e = it * 128 + pt;
+        const int row = e >> 4, c = e & 15;  // row 0..255
+        const int tile = row >> 7, r = row & 127;
+        const int qi = row / G, g = row - qi * G;
+        const bool have = qi < w.q_count;
+        const __nv_bfloat16 *src =
+            have ? p.q + (int64_t)(q0 + w.q_begin + qi) * p.q_stride + (int64_t)(h * G + g) * kHeadSize + c * 8
+                 : p.q;
+        cp_async16(q_s + (tile * 2 + (c >> 3)) * kSlab + sw128_off(r, c & 7), src, have ? 16u : 0u);
+      }
+      cp_async_commit();
+      // half-tiles: even = K(j), odd = V(j)
+      auto issue_half = [&](int hf) {
+        const int j = hf >> 1;
+        const bool is_v = hf & 1;
+        const uint32_t stage = (is_v ? v_s : k_s) + (j & 1) * kStage;
+        for (int bb = 0; bb < 2; bb++) {
+          const int b = pw * 2 + bb;           // block within the tile
+          const int gb = j * 8 + b;            // block within the sequence
+          const bool have = gb < nblk;
+          const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
+          const __nv_bfloat16 *src = (is_v ? p.v_pool : p.k_pool) + chunk * kChunkElems;
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const int e = it * 32 + lane;  // 16-byte piece of the 4 KB chunk, in memory order
+            if (!is_v) {
+              const int c = e >> 4, t = e & 15;  // K chunk [c][t][8]
+              cp_async16(stage + (c >> 3) * kSlab + sw128_off(b * 16 + t, c & 7), src + e * 8,
+                         have ? 16u : 0u);
+            } else {
+              const int d = e >> 1, hh = e & 1;  // V chunk [d][16 tok]
+              cp_async16(stage + (b >> 2) * kSlab + sw128_off(d, 2 * (b & 3) + hh), src + e * 8,
+                         have ? 16u : 0u);
+            }
+          }
+        }
+        cp_async_commit();
+      };
+      // Tokens past the context inside the last block may hold anything; P is 0 there
+      // but 0*NaN is NaN, so clear those V columns once the copy has landed.
+      auto scrub_v_tail = [&](int j) {
+        const int last_gb = (kv_len - 1) >> 4;
+        const int valid = kv_len - last_gb * kBlockSize;
+        if (valid >= kBlockSize || (last_gb >> 3) != j) return;
+        const int b = last_gb & 7;
+        if ((b >> 1) != pw) return;
+        const uint32_t off_base = (uint32_t)((j & 1) * kStage + (b >> 2) * kSlab);
+        uint8_t *vgen = gen + kQBytes + 2 * kStage + off_base;
+        for (int d = lane; d < 128; d += 32)
+          for (int t = valid; t < kBlockSize; t++) {
+            const int u = 2 * (b & 3) + (t >> 3);
+            *reinterpret_cast<uint16_t *>(vgen + sw128_off(d, u) + (t & 7) * 2) = 0;
+          }
+      };
+      auto land = [&](int hf) {  // copies of half-tile hf (and Q before the first) are complete
+        __syncwarp();  // every lane's pieces of the warp's two blocks have landed
+        if (hf & 1) scrub_v_tail(hf >> 1);
+        fence_proxy_async();
+        if (hf == 0) mbar_arrive(bar(B_QFULL));
+        mbar_arrive(bar(((hf & 1) ? B_VFULL : B_KFULL) + ((hf >> 1) & 1)));
+      };
+      const int n_half = 2 * n_tiles;
+      for (int hf = 0; hf < n_half && !failed; hf++) {
+        const int j = hf >> 1;
+        if (j >= 2) {
+          const uint32_t eb = bar(((hf & 1) ? B_VEMPTY : B_KEMPTY) + (j & 1));
+          if (!wait_bar(eb, ((j >> 1) - 1) & 1, abort_flag)) {
+            failed = true;
+            break;
+          }
+        }
+        issue_half(hf);
+        if (hf > 0) {
+          cp_async_wait<1>();
+          land(hf - 1);
+        }
+      }
+      cp_async_wait<0>();
+      if (!failed) land(n_half - 1);
+    } else if (warp == 12) {
+      // =========================== MMA issuer ========================================
+      if (lane == 0) {
+        auto issue_s = [&](int i, int j) {
+          const uint32_t kst = k_s + (j & 1) * kStage;
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const uint32_t koff = (kk >> 2) * kSlab + (kk & 3) * 32;
+            umma_ss(tmem + i * 128, sw128_desc(q_s + i * 2 * kSlab + koff), sw128_desc(kst + koff),
+                    kIdesc, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(B_SFULL + i));
+        };
+        auto issue_pv = [&](int i, int j) {
+          const uint32_t vst = v_s + (j & 1) * kStage;
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const uint32_t koff = (kk >> 2) * kSlab + (kk & 3) * 32;
+            umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, sw128_desc(vst + koff), kIdesc,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(B_PVDONE + i));
+        };
+        do {
+          if (!wait_bar(bar(B_QFULL), 0, abort_flag)) { failed = true; break; }
+          if (!wait_bar(bar(B_KFULL + 0), 0, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          issue_s(0, 0);
+          issue_s(1, 0);
+          tc_commit(bar(B_KEMPTY + 0));
+          for (int j = 0; j < n_tiles && !failed; j++) {
+            if (!wait_bar(bar(B_VFULL + (j & 1)), (j >> 1) & 1, abort_flag)) { failed = true; break; }
+            const bool more = j + 1 < n_tiles;
+            if (more && !wait_bar(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) {
+              failed = true;
+              break;
+            }
+            for (int i = 0; i < 2; i++) {
+              if (!wait_bar(bar(B_PREADY + i), j & 1, abort_flag)) { failed = true; break; }
+              tc_fence_after();
+              issue_pv(i, j);
+              if (i == 1) tc_commit(bar(B_VEMPTY + (j & 1)));
+              if (more) issue_s(i, j + 1);
+            }
+            if (more && !failed) tc_commit(bar(B_KEMPTY + ((j + 1) & 1)));
+          }
+        } while (false);
+      }
+    } else {
+      // =========================== softmax + epilogue ================================
+      const int i = warp >> 2;                     // Q tile
+      const int row = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
+      const int grow = i * 128 + row;              // row within the CTA
+      const int qi = grow / G, g = grow - qi * G;
+      const bool have = qi < w.q_count;
+      const int lim = have ? max(kv_len - q_len + w.q_begin + qi + 1, 0) : 0;
+      int warp_min_lim = lim;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1)
+        warp_min_lim = min(warp_min_lim, __shfl_xor_sync(0xffffffffu, warp_min_lim, o));
+      const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+      const uint32_t s_t = tmem + lane_base + i * 128;
+      const uint32_t o_t = tmem + lane_base + 256 + i * 128;
+      const float c = p.scale * kLog2e;
+      const bool use_cap = p.softcap != 1.0f;
+      float m_used = -INFINITY, l = 0.f;
+
+      for (int j = 0; j < n_tiles && !failed; j++) {
+        if (!wait_bar(bar(B_SFULL + i), j & 1, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const bool need_mask = (j + 1) * kTileTok > warp_min_lim;
+        const int tok0 = j * kTileTok;
+        uint32_t r[32];
+        // pass 1: row maximum of the raw logits
+        float mx = -INFINITY;
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+          tmem_ld32(s_t + ch * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e++) {
+            float x = __uint_as_float(r[e]);
+            if (use_cap) x = tanhf(x * p.scale / p.softcap) * p.softcap / p.scale;
+            if (need_mask && tok0 + ch * 32 + e >= lim) x = -INFINITY;
+            mx = fmaxf(mx, x);
+          }
+        }
+        // stale-maximum rule: move the reference only when it would grow by > 2^8
+        float factor = 1.f;
+        if (mx > m_used && (mx - m_used) * c > 8.f) {
+          factor = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * c);
+          m_used = mx;
+        }
+        if (__any_sync(0xffffffffu, factor != 1.f) && j > 0) {
+          // O_i of the previous tile is complete: its P.V was issued before this S
+          if (!wait_bar(bar(B_PVDONE + i), (j - 1) & 1, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int ch = 0; ch < 4; ch++) {
+            tmem_ld32(o_t + ch * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+            tmem_st32(o_t + ch * 32, r);
+          }
+          tmem_wait_st();
+        }
+        l *= factor;
+        const float mc = m_used == -INFINITY ? 0.f : m_used * c;
+        // pass 2: probabilities, row sum, bf16 P over the first 64 columns of S
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+          tmem_ld32(s_t + ch * 32, r);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float x0 = __uint_as_float(r[e]), x1 = __uint_as_float(r[e + 1]);
+            if (use_cap) {
+              x0 = tanhf(x0 * p.scale / p.softcap) * p.softcap / p.scale;
+              x1 = tanhf(x1 * p.scale / p.softcap) * p.softcap / p.scale;
+            }
+            float p0 = fast_exp2(fmaf(x0, c, -mc)), p1 = fast_exp2(fmaf(x1, c, -mc));
+            if (need_mask) {
+              if (tok0 + ch * 32 + e >= lim) p0 = 0.f;
+              if (tok0 + ch * 32 + e + 1 >= lim) p1 = 0.f;
+            }
+            l += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+          tmem_st16(s_t + ch * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PREADY + i));
+      }
+      // epilogue: O / l -> bf16 rows
+      if (!failed && wait_bar(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag)) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16 *orow = have ? p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
+                                         (int64_t)(h * G + g) * kHeadSize
+                                   : nullptr;
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+          uint32_t r[32];
+          tmem_ld32(o_t + ch * 32, r);
+          tmem_wait_ld();
+          if (have) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+              *reinterpret_cast<uint4 *>(orow + ch * 32 + e) = v;
+            }
+          }
+        }
+      } else {
+        failed = true;
+      }
+    }
+  } else if (warp < 8) {
+    // nothing to attend: zero rows
+    const int grow = (warp >> 2) * 128 + (warp & 3) * 32 + lane;
+    const int qi = grow / G, g = grow - qi * G;
+    if (qi < w.q_count) {
+      uint4 *orow = reinterpret_cast<uint4 *>(p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
+                                              (int64_t)(h * G + g) * kHeadSize);
+      for (int e = 0; e < 16; e++) orow[e] = make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  if (failed) atomicOr(p.err, kErrTimeout);
+  // ---- teardown -------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem));
+  }
+}
+
+}  // namespace
+
+int tile_queries_per_cta(int G) { return 2 * kQRows / G; }
+
+cudaError_t tile_configure() {
+  return cudaFuncSetAttribute(tile_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kSmemTc);
+}
+
+cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
+                                  cudaStream_t st) {
+  if (num_work <= 0) return cudaSuccess;
+  tile_attention_tc_kernel<<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+}  // namespace pa
