@@ -140,7 +140,7 @@ def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     from pa_testlib import Case, oracle, p, write_oracle
-    kv, ql, Hq, Hkv, _ = workload_lengths(args.workload, 1)
+    kv, ql, Hq, Hkv, _ = workload_lengths(args.workload, max(world, 1))
     if args.workload in ("c4", "c5"):
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference has no paged multi-token attention "
@@ -148,6 +148,7 @@ def run_reference(args, rank: int, world: int) -> None:
                           "have a CPU path"}))
         return
     lib = oracle()
+    lib.oracle_set_num_threads(len(os.sched_getaffinity(0)))
     cores = int(lib.oracle_num_threads())
     n_s = min(len(kv), max(cores, 8))
     kv_s, ql_s = kv[:n_s], ql[:n_s]
@@ -178,7 +179,7 @@ def run_reference(args, rank: int, world: int) -> None:
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.workload, 1, kv, ql, Hq, Hkv),
+        "config": workload_config(args.workload, max(world, 1), kv, ql, Hq, Hkv),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
@@ -235,8 +236,11 @@ def main() -> None:
         kv, ql = kv[:args.seqs], ql[:args.seqs]
     if args.pool_blocks:
         NB = args.pool_blocks
-    assert Hkv % world == 0 and int(((kv + BS - 1) // BS).sum()) <= NB
-    hkv_l, hq_l = Hkv // world, Hq // world
+    assert int(((kv + BS - 1) // BS).sum()) <= NB
+    from paged_attn_b200 import sharding
+    ka, kb = sharding.kv_head_range(rank, world, Hkv)
+    qa, qb = sharding.q_head_range(rank, world, Hq, Hkv)
+    hkv_l, hq_l = kb - ka, qb - qa
     S, total_q = len(kv), int(np.sum(ql))
     nblk = (kv + BS - 1) // BS
     MB = int(nblk.max())
@@ -289,8 +293,7 @@ def main() -> None:
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     scale = 1.0 / math.sqrt(D)
     decode_only = bool((ql == 1).all())
-    gathered = torch.empty(world, total_q, hq_l, D, dtype=torch.bfloat16, device=dev) \
-        if (args.gather and world > 1) else None
+    do_gather = args.gather and world > 1
     stream = torch.cuda.current_stream().cuda_stream
 
     def step():
@@ -300,8 +303,8 @@ def main() -> None:
         else:
             cache.varlen(out, q, tables, lens, cu_q, S, hq_l, MB, scale, ws, ws_bytes,
                          max_context_len=int(kv.max()), stream=stream)
-        if gathered is not None:
-            dist.all_gather_into_tensor(gathered, out)
+        if do_gather:
+            sharding.gather_heads(out, world)
 
     def barrier():
         if dist is not None:
@@ -404,7 +407,7 @@ def main() -> None:
             "step_bytes": kv_bytes + write_bytes(ql, hkv_l),
             "step_gbs": (kv_bytes + write_bytes(ql, hkv_l)) / (ms_per_step * 1e-3) / 1e9,
         }
-        if gathered is not None:
+        if do_gather:
             line["config"]["gather"] = "NCCL all_gather of head outputs inside the step"
         print(json.dumps(line))
     if dist is not None:
@@ -419,6 +422,7 @@ def cpu_baseline_and_spot_check(kv, ql, Hq, Hkv, tables_h, k_pool, v_pool, q, ou
     from pa_testlib import attention_oracle_rows, bf16_to_f32, check_attention, oracle, p
     from gpu_util import to_bits
     lib = oracle()
+    lib.oracle_set_num_threads(len(os.sched_getaffinity(0)))
     cores = int(lib.oracle_num_threads())
     n_s = min(len(kv), max(cores, 8))
     nblk = (kv[:n_s] + BS - 1) // BS

@@ -61,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   return true;
 }
 // 1-D bulk copy global -> shared of `bytes` (multiple of 16; both addresses
-// 16-byte aligned), completion counted on `bar`.  No multicast.
+// 16-byte aligned), completion counted on `bar`.  Delivered to this CTA only.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
                                          uint32_t bar) {
   asm volatile(

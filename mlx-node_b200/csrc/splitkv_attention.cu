@@ -19,7 +19,7 @@
 // item in a fixed order (deterministic results).
 //
 // Data movement.  Each warp owns a ring of NST stages of 8 KB.  Lane 0 issues two
-// 4 KB bulk async copies (TMA, untiled, no multicast) per unit, completion
+// 4 KB bulk async copies (TMA, untiled, this CTA only) per unit, completion
 // counted on the stage's mbarrier; the warp consumes its own stages, so no
 // cross-warp hand-off sits on the critical path.  8 warps x NST stages x 8 KB
 // of loads are in flight per SM.  Block ids for the next 32 units of a warp are

@@ -51,6 +51,16 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline asks for
+ * the host's cores explicitly. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void oracle_f32_to_bf16(const float *src, uint16_t *dst, int64_t n) {
   for (int64_t i = 0; i < n; i++) dst[i] = f32_to_bf16(src[i]);
 }

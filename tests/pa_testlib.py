@@ -36,6 +36,8 @@ def oracle() -> C.CDLL:
     lib = C.CDLL(ORACLE_LIB)
     vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
     lib.oracle_num_threads.restype = i32
+    lib.oracle_set_num_threads.argtypes = [i32]
+    lib.oracle_set_num_threads.restype = None
     lib.oracle_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32]
     lib.oracle_reshape_and_cache.restype = None
     lib.oracle_copy_blocks.argtypes = [vp, vp, vp, i64, i64]
