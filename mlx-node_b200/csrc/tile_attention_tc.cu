@@ -10,15 +10,18 @@
 // head of the GQA group) pair, token-major, i.e. two 128-row Q tiles that share
 // every KV tile.  KV tiles are 128 tokens (8 blocks).
 //
-// Roles (13 warps):
+// Roles (16 warps, four warpgroups):
 //   warps 0-3   softmax of Q tile 0 (thread = row = TMEM lane)
 //   warps 4-7   softmax of Q tile 1
 //   warps 8-11  producers: gather the 4 KB K and V chunks of the tile's blocks
-//               through the block table with 16-byte cp.async, writing them
-//               straight into the 128-byte-swizzled K-major operand layout
-//               the tensor core reads (K chunk [d/8][tok][8] -> rows = tokens;
-//               V chunk [d][tok] -> rows = d, 64 tokens per 128-byte row)
-//   warp 12     allocates TMEM; one lane issues every tcgen05.mma
+//               through the block table with 16-byte cp.async.  The pool layouts
+//               are already tensor-core operand layouts up to a block interleave:
+//               K chunk [d/8][tok][8] is the un-swizzled K-major core-matrix order
+//               (256-byte runs placed as [d/8][block][tok][8]); V chunk [d][tok] is
+//               the 32-byte-swizzle K-major order (halves of rows 4..7 swapped).
+//               Runs stay contiguous on both sides of the copy.
+//   warp 12     allocates TMEM; one lane issues every tcgen05.mma (warps 13-15 only
+//               complete the fourth warpgroup)
 //
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16) is
 // written over the first 64 columns of its S and fed back as the A operand of
@@ -45,7 +48,8 @@ constexpr int kStage = 2 * kSlab;      // one K or V tile
 constexpr int kTblCap = 2048;          // block ids staged per CTA (32768 tokens)
 constexpr int kNumBars = 16;
 constexpr int kSmemTc = 1024 + kQBytes + 4 * kStage + kTblCap * 4 + kNumBars * 8 + 16;
-constexpr int kTcThreads = 13 * 32;
+constexpr int kTcThreads = 16 * 32;  // four warpgroups
+constexpr int kRegsSoftmax = 200, kRegsOther = 56;
 
 // barrier slots
 enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9,
@@ -62,6 +66,14 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// True in exactly one lane of the (fully active) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.b32 %0, 1, 0, P;\n}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -119,6 +131,37 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Wait for outstanding TMEM loads; the registers are named as in/out operands so that
+// no use of them can be scheduled above the wait.
+__device__ __forceinline__ void tmem_wait_ld16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld32(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                 "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -128,6 +171,18 @@ __device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
          (2ull << 61);
 }
+// K tile, K-major without swizzle: core matrix = 8 tokens x 16 B contiguous (the pool's
+// own [d/8][tok][8] order); 8-token groups 128 B apart (stride byte offset), the two
+// 8-element d-chunks of one K=16 step 2048 B apart (leading byte offset).
+__device__ __forceinline__ uint64_t k_tile_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (128ull << 16) | (8ull << 32) | (1ull << 46);
+}
+// One V block, K-major with 32-byte swizzle: rows = d, 32 B = the block's 16 tokens;
+// 8-row groups 256 B apart.  Layout type 6.
+__device__ __forceinline__ uint64_t v_block_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (16ull << 32) | (1ull << 46) |
+         (6ull << 61);
+}
 // Instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -135,6 +190,16 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) <<
 __device__ __forceinline__ uint32_t sw128_off(int r, int u) {
   return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((u ^ (r & 7)) << 4));
 }
+
+#ifdef PA_TILE_TIMING
+// Debug builds only: cycles each role spends waiting, summed over CTAs.
+__device__ unsigned long long g_tile_timing[16];
+#define PA_T0() const long long t_dbg0 = clock64()
+#define PA_T1(slot) atomicAdd(&g_tile_timing[slot], (unsigned long long)(clock64() - t_dbg0))
+#else
+#define PA_T0()
+#define PA_T1(slot)
+#endif
 
 // Wait that gives up when the budget runs out or another role has raised the flag.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -153,6 +218,68 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return true;
 }
 
+// One pass over a row's 128 logits of the current KV tile (thread = row): probabilities
+// against the reference maximum (mc = m_used*c) packed to bf16 pairs in pk, the raw row
+// maximum and the row sum.  The whole row is fetched from TMEM with four loads in flight
+// at once (one latency instead of several), which is why the softmax warps raise their
+// register budget.  MASK and CAP are compile-time so the common loop is five
+// instructions per element with no branches.
+template <bool CAP, bool MASK>
+__device__ __forceinline__ void row_pass(uint32_t s_t, float c, float mc, int lim, int tok0,
+                                         float cap_in, float cap_out, uint32_t (&pk)[64],
+                                         float &mx_out, float &sum_out) {
+  float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  float sma[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t s0[32], s1[32], s2[32], s3[32];
+  tmem_ld32(s_t, s0);
+  tmem_ld32(s_t + 32, s1);
+  tmem_ld32(s_t + 64, s2);
+  tmem_ld32(s_t + 96, s3);
+  auto process32 = [&](const uint32_t (&r)[32], int col0, uint32_t *dst) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float x0 = __uint_as_float(r[e]), x1 = __uint_as_float(r[e + 1]);
+      if (CAP) {
+        x0 = tanhf(x0 * cap_in) * cap_out;
+        x1 = tanhf(x1 * cap_in) * cap_out;
+      }
+      if (MASK) {
+        if (tok0 + col0 + e >= lim) x0 = -INFINITY;
+        if (tok0 + col0 + e + 1 >= lim) x1 = -INFINITY;
+      }
+      mxa[(e >> 1) & 3] = fmaxf(mxa[(e >> 1) & 3], fmaxf(x0, x1));
+      const float p0 = fast_exp2(fmaf(x0, c, -mc)), p1 = fast_exp2(fmaf(x1, c, -mc));
+      sma[(e >> 1) & 3] += p0 + p1;
+      dst[e >> 1] = pack_bf16(p0, p1);
+    }
+  };
+  tmem_wait_ld32(s0);  // waits for all four loads
+  process32(s0, 0, &pk[0]);
+  tmem_wait_ld32(s1);  // already complete: ties s1 to the wait
+  process32(s1, 32, &pk[16]);
+  tmem_wait_ld32(s2);
+  process32(s2, 64, &pk[32]);
+  tmem_wait_ld32(s3);
+  process32(s3, 96, &pk[48]);
+  mx_out = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+  sum_out = (sma[0] + sma[1]) + (sma[2] + sma[3]);
+}
+
+// Debug builds add the cycles spent in the wait to a per-site counter.
+__device__ __forceinline__ bool wait_bar_at(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                            int site) {
+#ifdef PA_TILE_TIMING
+  const long long t0 = clock64();
+  const bool ok = wait_bar(bar, parity, abort_flag);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&g_tile_timing[site], (unsigned long long)(clock64() - t0));
+  return ok;
+#else
+  (void)site;
+  return wait_bar(bar, parity, abort_flag);
+#endif
+}
+
+template <bool CAP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) {
   extern __shared__ uint8_t smem_raw[];
@@ -166,6 +293,9 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
   auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef PA_TILE_TIMING
+  const long long t_cta0 = clock64();
+#endif
   const TileWork w = work[blockIdx.x];
   const int seq = w.seq, h = w.kv_head, G = p.G;
   const int kv_len = p.context_lens[seq];
@@ -212,6 +342,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
 
   if (n_tiles > 0) {
     if (warp >= 8 && warp < 12) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
       // =========================== producers ========================================
       const int pt = tid - 256;  // 0..127
       const int pw = warp - 8;
@@ -252,12 +383,14 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
           for (int it = 0; it < 8; it++) {
             const int e = it * 32 + lane;  // 16-byte piece of the 4 KB chunk, in memory order
             if (!is_v) {
-              const int c = e >> 4, t = e & 15;  // K chunk [c][t][8]
-              cp_async16(stage + (c >> 3) * kSlab + sw128_off(b * 16 + t, c & 7), src + e * 8,
-                         have ? 16u : 0u);
+              // K chunk [c][t][8] -> [c][block][t][8]: 256-byte runs stay contiguous
+              const int c = e >> 4, t = e & 15;
+              cp_async16(stage + c * 2048 + b * 256 + t * 16, src + e * 8, have ? 16u : 0u);
             } else {
-              const int d = e >> 1, hh = e & 1;  // V chunk [d][16 tok]
-              cp_async16(stage + (b >> 2) * kSlab + sw128_off(d, 2 * (b & 3) + hh), src + e * 8,
+              // V chunk [d][16 tok] stays in place; the 32-byte swizzle swaps the two
+              // 16-byte halves of rows 4..7 of every 8-row group
+              const int d = e >> 1, hh = e & 1;
+              cp_async16(stage + b * 4096 + d * 32 + ((hh ^ ((d >> 2) & 1)) << 4), src + e * 8,
                          have ? 16u : 0u);
             }
           }
@@ -272,13 +405,11 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         if (valid >= kBlockSize || (last_gb >> 3) != j) return;
         const int b = last_gb & 7;
         if ((b >> 1) != pw) return;
-        const uint32_t off_base = (uint32_t)((j & 1) * kStage + (b >> 2) * kSlab);
-        uint8_t *vgen = gen + kQBytes + 2 * kStage + off_base;
+        uint8_t *vgen = gen + kQBytes + 2 * kStage + (j & 1) * kStage + b * 4096;
         for (int d = lane; d < 128; d += 32)
-          for (int t = valid; t < kBlockSize; t++) {
-            const int u = 2 * (b & 3) + (t >> 3);
-            *reinterpret_cast<uint16_t *>(vgen + sw128_off(d, u) + (t & 7) * 2) = 0;
-          }
+          for (int t = valid; t < kBlockSize; t++)
+            *reinterpret_cast<uint16_t *>(vgen + d * 32 + ((((t >> 3) ^ (d >> 2)) & 1) << 4) +
+                                          (t & 7) * 2) = 0;
       };
       auto land = [&](int hf) {  // copies of half-tile hf (and Q before the first) are complete
         __syncwarp();  // every lane's pieces of the warp's two blocks have landed
@@ -292,69 +423,78 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         const int j = hf >> 1;
         if (j >= 2) {
           const uint32_t eb = bar(((hf & 1) ? B_VEMPTY : B_KEMPTY) + (j & 1));
-          if (!wait_bar(eb, ((j >> 1) - 1) & 1, abort_flag)) {
+          if (!wait_bar_at(eb, ((j >> 1) - 1) & 1, abort_flag, 0)) {
             failed = true;
             break;
           }
         }
         issue_half(hf);
         if (hf > 0) {
+          PA_T0();
           cp_async_wait<1>();
+          if (lane == 0) PA_T1(10);
           land(hf - 1);
         }
       }
       cp_async_wait<0>();
       if (!failed) land(n_half - 1);
-    } else if (warp == 12) {
+    } else if (warp >= 12) {
       // =========================== MMA issuer ========================================
-      if (lane == 0) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+      // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
+      // (uniform registers feed tcgen05.mma directly); one elected lane issues.
+      if (warp == 12) {
+        const bool leader = elect_one();
         auto issue_s = [&](int i, int j) {
           const uint32_t kst = k_s + (j & 1) * kStage;
 #pragma unroll
           for (int kk = 0; kk < 8; kk++) {
             const uint32_t koff = (kk >> 2) * kSlab + (kk & 3) * 32;
-            umma_ss(tmem + i * 128, sw128_desc(q_s + i * 2 * kSlab + koff), sw128_desc(kst + koff),
-                    kIdesc, kk > 0 ? 1u : 0u);
+            if (leader)
+              umma_ss(tmem + i * 128, sw128_desc(q_s + i * 2 * kSlab + koff),
+                      k_tile_desc(kst + kk * 4096), kIdesc, kk > 0 ? 1u : 0u);
           }
-          tc_commit(bar(B_SFULL + i));
+          if (leader) tc_commit(bar(B_SFULL + i));
         };
         auto issue_pv = [&](int i, int j) {
           const uint32_t vst = v_s + (j & 1) * kStage;
 #pragma unroll
           for (int kk = 0; kk < 8; kk++) {
-            const uint32_t koff = (kk >> 2) * kSlab + (kk & 3) * 32;
-            umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, sw128_desc(vst + koff), kIdesc,
-                    (j > 0 || kk > 0) ? 1u : 0u);
+            if (leader)
+              umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, v_block_desc(vst + kk * 4096),
+                      kIdesc, (j > 0 || kk > 0) ? 1u : 0u);
           }
-          tc_commit(bar(B_PVDONE + i));
+          if (leader) tc_commit(bar(B_PVDONE + i));
         };
         do {
-          if (!wait_bar(bar(B_QFULL), 0, abort_flag)) { failed = true; break; }
-          if (!wait_bar(bar(B_KFULL + 0), 0, abort_flag)) { failed = true; break; }
+          if (!wait_bar_at(bar(B_QFULL), 0, abort_flag, 1)) { failed = true; break; }
+          if (!wait_bar_at(bar(B_KFULL + 0), 0, abort_flag, 1)) { failed = true; break; }
           tc_fence_after();
           issue_s(0, 0);
           issue_s(1, 0);
-          tc_commit(bar(B_KEMPTY + 0));
+          if (leader) tc_commit(bar(B_KEMPTY + 0));
           for (int j = 0; j < n_tiles && !failed; j++) {
-            if (!wait_bar(bar(B_VFULL + (j & 1)), (j >> 1) & 1, abort_flag)) { failed = true; break; }
+            if (!wait_bar_at(bar(B_VFULL + (j & 1)), (j >> 1) & 1, abort_flag, 2)) { failed = true; break; }
             const bool more = j + 1 < n_tiles;
-            if (more && !wait_bar(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) {
+            if (more && !wait_bar_at(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag, 3)) {
               failed = true;
               break;
             }
             for (int i = 0; i < 2; i++) {
-              if (!wait_bar(bar(B_PREADY + i), j & 1, abort_flag)) { failed = true; break; }
+              if (!wait_bar_at(bar(B_PREADY + i), j & 1, abort_flag, 4 + i)) { failed = true; break; }
               tc_fence_after();
               issue_pv(i, j);
-              if (i == 1) tc_commit(bar(B_VEMPTY + (j & 1)));
+              if (i == 1 && leader) tc_commit(bar(B_VEMPTY + (j & 1)));
               if (more) issue_s(i, j + 1);
             }
-            if (more && !failed) tc_commit(bar(B_KEMPTY + ((j + 1) & 1)));
+            if (more && !failed && leader) tc_commit(bar(B_KEMPTY + ((j + 1) & 1)));
+            __syncwarp();
           }
         } while (false);
       }
     } else {
       // =========================== softmax + epilogue ================================
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
       const int i = warp >> 2;                     // Q tile
       const int row = (warp & 3) * 32 + lane;      // row within the tile = TMEM lane
       const int grow = i * 128 + row;              // row within the CTA
@@ -369,80 +509,66 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
       const uint32_t s_t = tmem + lane_base + i * 128;
       const uint32_t o_t = tmem + lane_base + 256 + i * 128;
       const float c = p.scale * kLog2e;
-      const bool use_cap = p.softcap != 1.0f;
+      // soft-capping: x -> tanh(x*scale/cap)*cap/scale, so that x*c is the capped logit
+      const float cap_in = p.scale / p.softcap, cap_out = p.softcap / p.scale;
       float m_used = -INFINITY, l = 0.f;
+      auto pass = [&](bool need_mask, int tok0, uint32_t (&pk)[64], float &mx, float &sum) {
+        const float mc = m_used == -INFINITY ? 0.f : m_used * c;
+        if (need_mask) row_pass<CAP, true>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
+        else row_pass<CAP, false>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
+      };
 
       for (int j = 0; j < n_tiles && !failed; j++) {
-        if (!wait_bar(bar(B_SFULL + i), j & 1, abort_flag)) { failed = true; break; }
+        if (!wait_bar_at(bar(B_SFULL + i), j & 1, abort_flag, 6 + i)) { failed = true; break; }
         tc_fence_after();
         const bool need_mask = (j + 1) * kTileTok > warp_min_lim;
         const int tok0 = j * kTileTok;
-        uint32_t r[32];
-        // pass 1: row maximum of the raw logits
-        float mx = -INFINITY;
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-          tmem_ld32(s_t + ch * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; e++) {
-            float x = __uint_as_float(r[e]);
-            if (use_cap) x = tanhf(x * p.scale / p.softcap) * p.softcap / p.scale;
-            if (need_mask && tok0 + ch * 32 + e >= lim) x = -INFINITY;
-            mx = fmaxf(mx, x);
-          }
-        }
+        uint32_t pk[64];
+        float mx, sum;
+        // Optimistic pass against the maximum carried from earlier tiles (for the first
+        // tile: against 0, result discarded unless the logits happen to be small).
+        pass(need_mask, tok0, pk, mx, sum);
         // stale-maximum rule: move the reference only when it would grow by > 2^8
-        float factor = 1.f;
-        if (mx > m_used && (mx - m_used) * c > 8.f) {
-          factor = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * c);
-          m_used = mx;
-        }
-        if (__any_sync(0xffffffffu, factor != 1.f) && j > 0) {
-          // O_i of the previous tile is complete: its P.V was issued before this S
-          if (!wait_bar(bar(B_PVDONE + i), (j - 1) & 1, abort_flag)) { failed = true; break; }
-          tc_fence_after();
-#pragma unroll
-          for (int ch = 0; ch < 4; ch++) {
-            tmem_ld32(o_t + ch * 32, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-            tmem_st32(o_t + ch * 32, r);
+        const bool grew = mx > m_used && !((mx - m_used) * c <= 8.f);
+        if (__any_sync(0xffffffffu, grew)) {
+          float factor = 1.f;
+          if (grew) {
+            factor = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * c);
+            m_used = mx;
           }
-          tmem_wait_st();
+          if (j > 0) {
+            // O_i of the previous tile is complete: its P.V was issued before this S
+            if (!wait_bar_at(bar(B_PVDONE + i), (j - 1) & 1, abort_flag, 8)) { failed = true; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+              uint32_t r[32];
+              tmem_ld32(o_t + ch * 32, r);
+              tmem_wait_ld32(r);
+#pragma unroll
+              for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+              tmem_st32(o_t + ch * 32, r);
+            }
+            tmem_wait_st();
+          }
+          l *= factor;
+          pass(need_mask, tok0, pk, mx, sum);
         }
-        l *= factor;
-        const float mc = m_used == -INFINITY ? 0.f : m_used * c;
-        // pass 2: probabilities, row sum, bf16 P over the first 64 columns of S
+        l += sum;
+        // bf16 P over the first 64 columns of S (every logit of the row has been read)
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) {
-          tmem_ld32(s_t + ch * 32, r);
-          tmem_wait_ld();
-          uint32_t pk[16];
+          uint32_t t16[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float x0 = __uint_as_float(r[e]), x1 = __uint_as_float(r[e + 1]);
-            if (use_cap) {
-              x0 = tanhf(x0 * p.scale / p.softcap) * p.softcap / p.scale;
-              x1 = tanhf(x1 * p.scale / p.softcap) * p.softcap / p.scale;
-            }
-            float p0 = fast_exp2(fmaf(x0, c, -mc)), p1 = fast_exp2(fmaf(x1, c, -mc));
-            if (need_mask) {
-              if (tok0 + ch * 32 + e >= lim) p0 = 0.f;
-              if (tok0 + ch * 32 + e + 1 >= lim) p1 = 0.f;
-            }
-            l += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-          tmem_st16(s_t + ch * 16, pk);
+          for (int e = 0; e < 16; e++) t16[e] = pk[ch * 16 + e];
+          tmem_st16(s_t + ch * 16, t16);
         }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + i));
       }
       // epilogue: O / l -> bf16 rows
-      if (!failed && wait_bar(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag)) {
+      if (!failed && wait_bar_at(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag, 9)) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16 *orow = have ? p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
@@ -452,7 +578,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         for (int ch = 0; ch < 4; ch++) {
           uint32_t r[32];
           tmem_ld32(o_t + ch * 32, r);
-          tmem_wait_ld();
+          tmem_wait_ld32(r);
           if (have) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
@@ -481,6 +607,10 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
   }
 
   if (failed) atomicOr(p.err, kErrTimeout);
+#ifdef PA_TILE_TIMING
+  if (tid == 0) atomicAdd(&g_tile_timing[11], (unsigned long long)(clock64() - t_cta0));
+  if (tid == 0) atomicAdd(&g_tile_timing[12], (unsigned long long)n_tiles);
+#endif
   // ---- teardown -------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -492,17 +622,32 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
 
 }  // namespace
 
+#ifdef PA_TILE_TIMING
+extern "C" int pa_debug_tile_timing(unsigned long long *out16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out16, g_tile_timing, sizeof(unsigned long long) * 16);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[16] = {0};
+    e = cudaMemcpyToSymbol(g_tile_timing, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
+
 int tile_queries_per_cta(int G) { return 2 * kQRows / G; }
 
 cudaError_t tile_configure() {
-  return cudaFuncSetAttribute(tile_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              kSmemTc);
+  cudaError_t e = cudaFuncSetAttribute(tile_attention_tc_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(tile_attention_tc_kernel<true>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
 }
 
 cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
                                   cudaStream_t st) {
   if (num_work <= 0) return cudaSuccess;
-  tile_attention_tc_kernel<<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  if (p.softcap != 1.0f) tile_attention_tc_kernel<true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  else tile_attention_tc_kernel<false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }
