@@ -49,6 +49,11 @@ struct DeviceGuard {
 
 }  // namespace
 
+namespace pa {
+// shared with the host-logic ABI (host_api.cpp): same per-thread error string
+int32_t set_error(int32_t code, const std::string &msg) { return fail(code, msg); }
+}  // namespace pa
+
 struct PagedAttnCache {
   PagedAttnConfig cfg{};
   int device = 0;

@@ -1,0 +1,706 @@
+// Implementation of the host-side pool management (see host_logic.hpp).
+#include "host_logic.hpp"
+
+#include <algorithm>
+
+namespace pa_host {
+
+// ---- BlockAllocator (crates/mlx-paged-attn/src/block_allocator.rs:62-236) ----------
+BlockAllocator::BlockAllocator(uint32_t num_blocks, uint32_t block_size)
+    : num_blocks_(num_blocks), block_size_(block_size) {
+  for (uint32_t i = 0; i < num_blocks; i++) free_.push_back(i);
+  allocated_.reserve(num_blocks);
+}
+
+BlockRef BlockAllocator::allocate() {
+  if (free_.empty()) return nullptr;
+  const uint32_t id = free_.front();
+  free_.pop_front();
+  auto b = std::make_shared<PhysicalBlock>(id);
+  allocated_[id] = b;
+  return b;
+}
+
+void BlockAllocator::free(const BlockRef &block) {
+  const uint32_t id = block->block_id;
+  if (!block->decref()) return;
+  allocated_.erase(id);
+  auto it = block_hashes_.find(id);
+  if (it != block_hashes_.end()) {
+    const uint64_t hash = it->second;
+    block_hashes_.erase(it);
+    prefix_cache_.erase(hash);
+    lru_.erase(std::remove(lru_.begin(), lru_.end(), hash), lru_.end());
+  }
+  free_.push_back(id);
+}
+
+BlockRef BlockAllocator::copy_on_write(const BlockRef &block) {
+  if (!block->is_shared()) return nullptr;
+  BlockRef fresh = allocate();
+  if (!fresh) return nullptr;
+  block->decref();
+  return fresh;
+}
+
+void BlockAllocator::register_prefix(const BlockRef &block, uint64_t hash) {
+  if (max_prefix_cache_entries == 0) return;
+  while (prefix_cache_.size() >= max_prefix_cache_entries) {
+    if (lru_.empty()) break;  // desynchronised: do not spin
+    const uint64_t old = lru_.front();
+    lru_.pop_front();
+    auto it = prefix_cache_.find(old);
+    if (it != prefix_cache_.end()) {
+      block_hashes_.erase(it->second->block_id);
+      prefix_cache_.erase(it);
+    }
+  }
+  lru_.erase(std::remove(lru_.begin(), lru_.end(), hash), lru_.end());
+  lru_.push_back(hash);
+  block_hashes_[block->block_id] = hash;
+  prefix_cache_[hash] = block;
+}
+
+BlockRef BlockAllocator::lookup_prefix(uint64_t hash) {
+  auto it = prefix_cache_.find(hash);
+  if (it == prefix_cache_.end()) return nullptr;
+  lru_.erase(std::remove(lru_.begin(), lru_.end(), hash), lru_.end());
+  lru_.push_back(hash);
+  it->second->incref();
+  return it->second;
+}
+
+namespace {
+inline uint64_t rotl(uint64_t x, int b) { return (x << b) | (x >> (64 - b)); }
+struct Sip13 {
+  uint64_t v0 = 0x736f6d6570736575ull, v1 = 0x646f72616e646f6dull, v2 = 0x6c7967656e657261ull,
+           v3 = 0x7465646279746573ull;  // zero key
+  uint64_t tail = 0;
+  int ntail = 0;
+  uint64_t length = 0;
+  void round() {
+    v0 += v1; v1 = rotl(v1, 13); v1 ^= v0; v0 = rotl(v0, 32);
+    v2 += v3; v3 = rotl(v3, 16); v3 ^= v2;
+    v0 += v3; v3 = rotl(v3, 21); v3 ^= v0;
+    v2 += v1; v1 = rotl(v1, 17); v1 ^= v2; v2 = rotl(v2, 32);
+  }
+  void write(const uint8_t *p, size_t n) {
+    length += n;
+    for (size_t i = 0; i < n; i++) {
+      tail |= (uint64_t)p[i] << (8 * ntail);
+      if (++ntail == 8) {
+        v3 ^= tail; round(); v0 ^= tail;
+        tail = 0; ntail = 0;
+      }
+    }
+  }
+  uint64_t finish() {
+    const uint64_t b = (length << 56) | tail;
+    v3 ^= b; round(); v0 ^= b;
+    v2 ^= 0xff;
+    round(); round(); round();
+    return v0 ^ v1 ^ v2 ^ v3;
+  }
+};
+}  // namespace
+
+uint64_t hash_tokens(const uint32_t *tokens, size_t n, uint64_t parent_hash) {
+  Sip13 h;
+  uint8_t buf[8];
+  for (int i = 0; i < 8; i++) buf[i] = (uint8_t)(parent_hash >> (8 * i));
+  h.write(buf, 8);
+  for (size_t t = 0; t < n; t++) {
+    for (int i = 0; i < 4; i++) buf[i] = (uint8_t)(tokens[t] >> (8 * i));
+    h.write(buf, 4);
+  }
+  return h.finish();
+}
+
+// ---- block tables (crates/mlx-paged-attn/src/block_table.rs) -----------------------------
+bool SequenceBlockTable::replace_block(size_t i, BlockRef b) {
+  if (i >= blocks_.size()) return false;
+  blocks_[i] = std::move(b);
+  return true;
+}
+bool SequenceBlockTable::is_last_block_full() const {
+  return num_tokens_ % block_size_ == 0 && num_tokens_ > 0;
+}
+uint32_t SequenceBlockTable::free_slots_in_last_block() const {
+  if (blocks_.empty()) return 0;
+  const uint32_t in_last = num_tokens_ % block_size_;
+  if (in_last == 0 && num_tokens_ > 0) return 0;
+  return block_size_ - in_last;
+}
+uint32_t SequenceBlockTable::blocks_needed(uint32_t new_tokens) const {
+  const uint32_t free_slots = free_slots_in_last_block();
+  if (new_tokens <= free_slots) return 0;
+  return (new_tokens - free_slots + block_size_ - 1) / block_size_;
+}
+std::pair<uint32_t, uint32_t> SequenceBlockTable::slot_index(uint32_t token_pos) const {
+  return {token_pos / block_size_, token_pos % block_size_};
+}
+bool SequenceBlockTable::absolute_slot_index(uint32_t token_pos, int64_t *slot) const {
+  const auto [blk, off] = slot_index(token_pos);
+  if (blk >= blocks_.size()) return false;
+  *slot = (int64_t)blocks_[blk]->block_id * (int64_t)block_size_ + (int64_t)off;
+  return true;
+}
+
+uint32_t BlockTable::add_sequence() {
+  const uint32_t id = next_seq_id_++;
+  idx_[id] = tables_.size();
+  tables_.emplace_back(id, block_size_);
+  return id;
+}
+bool BlockTable::remove_sequence(uint32_t seq_id, SequenceBlockTable *out) {
+  auto it = idx_.find(seq_id);
+  if (it == idx_.end()) return false;
+  const size_t i = it->second;
+  idx_.erase(it);
+  if (out) *out = tables_[i];
+  if (i + 1 != tables_.size()) {
+    tables_[i] = std::move(tables_.back());
+    idx_[tables_[i].seq_id] = i;
+  }
+  tables_.pop_back();
+  return true;
+}
+SequenceBlockTable *BlockTable::get(uint32_t seq_id) {
+  auto it = idx_.find(seq_id);
+  return it == idx_.end() ? nullptr : &tables_[it->second];
+}
+const SequenceBlockTable *BlockTable::get(uint32_t seq_id) const {
+  auto it = idx_.find(seq_id);
+  return it == idx_.end() ? nullptr : &tables_[it->second];
+}
+std::vector<uint32_t> BlockTable::seq_ids() const {
+  std::vector<uint32_t> r;
+  for (const auto &t : tables_) r.push_back(t.seq_id);
+  return r;
+}
+std::vector<uint32_t> BlockTable::build_block_tables_array(size_t mb) const {
+  std::vector<uint32_t> r(tables_.size() * mb, 0u);
+  for (size_t s = 0; s < tables_.size(); s++) {
+    const auto &blocks = tables_[s].blocks();
+    for (size_t b = 0; b < blocks.size() && b < mb; b++) r[s * mb + b] = blocks[b]->block_id;
+  }
+  return r;
+}
+std::vector<uint32_t> BlockTable::build_context_lens_array() const {
+  std::vector<uint32_t> r;
+  for (const auto &t : tables_) r.push_back(t.num_tokens());
+  return r;
+}
+
+// ---- config (crates/mlx-paged-attn/src/config.rs:36-123) ------------------------------------
+std::string PagedAttentionConfig::validate() const {
+  if (block_size != 8 && block_size != 16 && block_size != 32)
+    return "Invalid block_size: " + std::to_string(block_size) + ". Must be 8, 16, or 32.";
+  static const uint32_t heads[] = {32, 64, 80, 96, 112, 120, 128, 192, 256};
+  bool ok = false;
+  for (uint32_t h : heads) ok |= h == head_size;
+  if (!ok)
+    return "Invalid head_size: " + std::to_string(head_size) +
+           ". Must be one of [32, 64, 80, 96, 112, 120, 128, 192, 256].";
+  if (gpu_memory_mb < 256)
+    return "gpu_memory_mb too small: " + std::to_string(gpu_memory_mb) + ". Minimum is 256 MB.";
+  if (num_layers == 0) return "num_layers must be > 0";
+  if (num_kv_heads == 0) return "num_kv_heads must be > 0";
+  if (use_fp8_cache && block_size == 8)
+    return "FP8 cache requires block_size 16 or 32 for optimal alignment.";
+  return "";
+}
+uint32_t PagedAttentionConfig::calculate_num_blocks() const {
+  const uint64_t elem = use_fp8_cache ? 1 : 2;
+  const uint64_t per_block = 2ull * num_kv_heads * head_size * block_size * elem * num_layers;
+  return (uint32_t)((uint64_t)gpu_memory_mb * 1024 * 1024 / per_block);
+}
+
+// ---- token tracker (crates/mlx-paged-attn/src/token_tracker.rs) -----------------------------
+uint64_t compute_token_hash(const uint32_t *tokens, size_t n) {
+  uint64_t state = 0xcbf29ce484222325ull;
+  for (size_t t = 0; t < n; t++)
+    for (int i = 0; i < 4; i++) {
+      state ^= (uint8_t)(tokens[t] >> (8 * i));
+      state *= 0x100000001b3ull;
+    }
+  return state;
+}
+
+uint64_t TokenTracker::track_tokens(uint32_t block_id, const uint32_t *tokens, size_t n,
+                                    uint32_t start_offset) {
+  if (!enabled_) return 0;
+  bool had_old = false;
+  uint64_t old_hash = 0;
+  auto it = block_tokens_.find(block_id);
+  if (it != block_tokens_.end() && !it->second.empty()) {
+    had_old = true;
+    old_hash = compute_token_hash(it->second.data(), it->second.size());
+  }
+  auto &vec = block_tokens_[block_id];
+  if (vec.size() < start_offset) vec.resize(start_offset, 0);
+  for (size_t i = 0; i < n; i++) {
+    const size_t pos = start_offset + i;
+    if (pos < vec.size()) vec[pos] = tokens[i];
+    else vec.push_back(tokens[i]);
+  }
+  const uint64_t hash = compute_token_hash(vec.data(), vec.size());
+  const uint32_t count = (uint32_t)vec.size();
+  if (had_old && old_hash != hash) {
+    auto pi = prefix_index_.find(old_hash);
+    if (pi != prefix_index_.end() && pi->second.first == block_id) prefix_index_.erase(pi);
+  }
+  prefix_index_[hash] = {block_id, count};
+  return hash;
+}
+
+const std::vector<uint32_t> &TokenTracker::get_block_tokens(uint32_t block_id) const {
+  static const std::vector<uint32_t> empty;
+  auto it = block_tokens_.find(block_id);
+  return it == block_tokens_.end() ? empty : it->second;
+}
+
+void TokenTracker::remove_block(uint32_t block_id) {
+  if (!enabled_) return;
+  auto it = block_tokens_.find(block_id);
+  if (it != block_tokens_.end()) {
+    const uint64_t hash = compute_token_hash(it->second.data(), it->second.size());
+    auto pi = prefix_index_.find(hash);
+    if (pi != prefix_index_.end() && pi->second.first == block_id) prefix_index_.erase(pi);
+    block_tokens_.erase(it);
+  }
+}
+
+void TokenTracker::copy_block(uint32_t src, uint32_t dst) {
+  if (!enabled_) return;
+  auto si = block_tokens_.find(src);
+  if (si == block_tokens_.end()) return;  // destination untouched
+  std::vector<uint32_t> tokens = si->second;
+  auto di = block_tokens_.find(dst);
+  if (di != block_tokens_.end() && !di->second.empty()) {
+    const uint64_t old = compute_token_hash(di->second.data(), di->second.size());
+    auto pi = prefix_index_.find(old);
+    if (pi != prefix_index_.end() && pi->second.first == dst) prefix_index_.erase(pi);
+  }
+  const uint64_t hash = compute_token_hash(tokens.data(), tokens.size());
+  const uint32_t count = (uint32_t)tokens.size();
+  block_tokens_[dst] = std::move(tokens);
+  prefix_index_[hash] = {dst, count};
+}
+
+std::vector<std::pair<uint32_t, uint32_t>> TokenTracker::find_prefix_matches(const uint32_t *tokens,
+                                                                             size_t n) const {
+  std::vector<std::pair<uint32_t, uint32_t>> matches;
+  if (!enabled_ || n == 0) return matches;
+  const size_t full = n / block_size_;
+  for (size_t b = 0; b <= full; b++) {
+    const size_t start = b * block_size_;
+    if (start >= n) break;
+    const size_t end = std::min(start + block_size_, n);
+    const uint64_t hash = compute_token_hash(tokens + start, end - start);
+    auto pi = prefix_index_.find(hash);
+    if (pi == prefix_index_.end()) continue;
+    auto bt = block_tokens_.find(pi->second.first);
+    if (bt != block_tokens_.end() && bt->second.size() >= end - start &&
+        std::equal(tokens + start, tokens + end, bt->second.begin()))
+      matches.push_back(pi->second);
+  }
+  return matches;
+}
+
+std::pair<std::vector<uint32_t>, uint32_t> TokenTracker::find_longest_prefix(const uint32_t *tokens,
+                                                                             size_t n) const {
+  std::vector<uint32_t> blocks;
+  uint32_t total = 0;
+  if (!enabled_ || n == 0) return {blocks, 0};
+  size_t pos = 0;
+  while (pos < n) {
+    const size_t len = std::min<size_t>(block_size_, n - pos);
+    const uint64_t hash = compute_token_hash(tokens + pos, len);
+    auto pi = prefix_index_.find(hash);
+    if (pi == prefix_index_.end()) break;
+    auto bt = block_tokens_.find(pi->second.first);
+    if (bt == block_tokens_.end() || bt->second.size() < len ||
+        !std::equal(tokens + pos, tokens + pos + len, bt->second.begin()))
+      break;
+    blocks.push_back(pi->second.first);
+    total += pi->second.second;
+    pos += pi->second.second;
+  }
+  return {blocks, total};
+}
+
+TokenTrackerStats TokenTracker::stats() const {
+  size_t total = 0;
+  for (const auto &kv : block_tokens_) total += kv.second.size();
+  const uint32_t nb = (uint32_t)block_tokens_.size();
+  return {nb, (uint32_t)total, nb ? (float)total / (float)nb : 0.f, (uint32_t)prefix_index_.size()};
+}
+void TokenTracker::clear() {
+  block_tokens_.clear();
+  prefix_index_.clear();
+}
+size_t TokenTracker::memory_usage() const {
+  size_t bytes = 0;
+  for (const auto &kv : block_tokens_) bytes += kv.second.capacity() * sizeof(uint32_t);
+  return bytes + prefix_index_.bucket_count() * (sizeof(uint64_t) + 2 * sizeof(uint32_t));
+}
+
+// ---- PagedKVCache host methods (crates/mlx-paged-attn/src/paged_kv_cache.rs) ----------------
+std::unique_ptr<PagedKVCache> PagedKVCache::create(const PagedAttentionConfig &cfg, std::string *error) {
+  const std::string msg = cfg.validate();
+  if (!msg.empty()) {
+    if (error) *error = msg;
+    return nullptr;
+  }
+  return std::unique_ptr<PagedKVCache>(new PagedKVCache(cfg, cfg.calculate_num_blocks()));
+}
+
+bool PagedKVCache::add_sequence(uint32_t prompt_len, uint32_t *seq_id, std::string *error) {
+  const uint32_t need = (prompt_len + cfg_.block_size - 1) / cfg_.block_size;
+  if (!alloc_.can_allocate(need)) {
+    *error = "Not enough memory to allocate " + std::to_string(need) + " blocks for " +
+             std::to_string(prompt_len) + " tokens";
+    return false;
+  }
+  const uint32_t id = table_.add_sequence();
+  SequenceBlockTable *t = table_.get(id);
+  for (uint32_t i = 0; i < need; i++) t->add_block(alloc_.allocate());
+  t->set_num_tokens(prompt_len);
+  *seq_id = id;
+  return true;
+}
+
+bool PagedKVCache::remove_sequence(uint32_t seq_id, std::string *error) {
+  SequenceBlockTable t(0, cfg_.block_size);
+  if (!table_.remove_sequence(seq_id, &t)) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  for (const auto &b : t.blocks()) {
+    if (b->ref_count == 1) tracker_.remove_block(b->block_id);  // last user: drop its tokens
+    alloc_.free(b);
+  }
+  return true;
+}
+
+bool PagedKVCache::extend_sequence(uint32_t seq_id, uint32_t n, std::string *error) {
+  SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  const uint32_t need = t->blocks_needed(n);
+  for (uint32_t i = 0; i < need; i++) {
+    BlockRef b = alloc_.allocate();
+    if (!b) {
+      *error = "Block allocation failed";
+      return false;
+    }
+    t->add_block(b);
+  }
+  t->set_num_tokens(t->num_tokens() + n);
+  return true;
+}
+
+bool PagedKVCache::fork_sequence(uint32_t parent, uint32_t *child, std::string *error) {
+  const SequenceBlockTable *p = table_.get(parent);
+  if (!p) {
+    *error = "Parent sequence " + std::to_string(parent) + " not found";
+    return false;
+  }
+  const std::vector<BlockRef> blocks = p->blocks();
+  const uint32_t tokens = p->num_tokens();
+  const uint32_t id = table_.add_sequence();
+  SequenceBlockTable *c = table_.get(id);
+  for (const auto &b : blocks) {
+    b->incref();
+    c->add_block(b);
+  }
+  c->set_num_tokens(tokens);
+  *child = id;
+  return true;
+}
+
+bool PagedKVCache::handle_cow(uint32_t seq_id, size_t block_idx, bool *copied, uint32_t *src, uint32_t *dst,
+                              std::string *error) {
+  SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  if (block_idx >= t->blocks().size()) {
+    *error = "Block index " + std::to_string(block_idx) + " out of range";
+    return false;
+  }
+  const BlockRef block = t->blocks()[block_idx];
+  *copied = false;
+  if (!block->is_shared()) return true;
+  BlockRef fresh = alloc_.copy_on_write(block);
+  if (!fresh) {
+    *error = "Failed to allocate block for copy-on-write";
+    return false;
+  }
+  *src = block->block_id;
+  *dst = fresh->block_id;
+  *copied = true;
+  t->replace_block(block_idx, fresh);
+  return true;
+}
+
+bool PagedKVCache::build_block_tables_batch(const uint32_t *seq_ids, size_t n,
+                                            std::vector<std::vector<uint32_t>> *out, std::string *error) const {
+  out->clear();
+  for (size_t i = 0; i < n; i++) {
+    const SequenceBlockTable *t = table_.get(seq_ids[i]);
+    if (!t) {
+      *error = "Sequence " + std::to_string(seq_ids[i]) + " not found";
+      return false;
+    }
+    std::vector<uint32_t> ids;
+    for (const auto &b : t->blocks()) ids.push_back(b->block_id);
+    out->push_back(std::move(ids));
+  }
+  return true;
+}
+
+bool PagedKVCache::get_slot_mapping(uint32_t seq_id, uint32_t start, uint32_t n, std::vector<int64_t> *out,
+                                    std::string *error) const {
+  const SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  for (uint32_t i = 0; i < n; i++) {
+    int64_t slot;
+    if (!t->absolute_slot_index(start + i, &slot)) {
+      *error = "Token position " + std::to_string(start + i) + " out of range for sequence " +
+               std::to_string(seq_id);
+      return false;
+    }
+    out->push_back(slot);
+  }
+  return true;
+}
+
+bool PagedKVCache::get_slot_mapping_batch(const uint32_t *seq_ids, const uint32_t *context_lens,
+                                          const uint8_t *is_prefill, const uint32_t *input_lens, size_t n,
+                                          std::vector<int64_t> *out, std::string *error) const {
+  for (size_t i = 0; i < n; i++) {
+    if (is_prefill && is_prefill[i]) {
+      if (!get_slot_mapping(seq_ids[i], 0, input_lens ? input_lens[i] : 1, out, error)) return false;
+    } else {
+      // decode: the token being processed sits at position context_len - 1
+      const uint32_t ctx = context_lens ? context_lens[i] : 0;
+      if (ctx == 0) {
+        *error = "Decode sequence " + std::to_string(seq_ids[i]) +
+                 " has context_len=0. This indicates prefill was not completed. "
+                 "Prefill must run before decode.";
+        return false;
+      }
+      if (!get_slot_mapping(seq_ids[i], ctx - 1, 1, out, error)) return false;
+    }
+  }
+  return true;
+}
+
+bool PagedKVCache::build_input_metadata(const uint32_t *seq_ids, const uint32_t *input_lens,
+                                        const uint8_t *is_prefill, size_t n, InputMetadata *out,
+                                        std::string *error) const {
+  InputMetadata m;
+  std::vector<uint32_t> ctx(n);
+  for (size_t i = 0; i < n; i++) {
+    const SequenceBlockTable *t = table_.get(seq_ids[i]);
+    ctx[i] = t ? t->num_tokens() : 0;
+    m.context_lens.push_back((int32_t)ctx[i]);
+    m.max_context_len = std::max(m.max_context_len, ctx[i]);
+  }
+  if (!get_slot_mapping_batch(seq_ids, ctx.data(), is_prefill, input_lens, n, &m.slot_mappings, error))
+    return false;
+  std::vector<std::vector<uint32_t>> tables;
+  if (!build_block_tables_batch(seq_ids, n, &tables, error)) return false;
+  const size_t mb = max_blocks_per_seq();
+  for (const auto &t : tables) {
+    if (t.size() > mb) {
+      *error = "sequence holds more blocks than max_seq_len allows";
+      return false;
+    }
+    for (uint32_t id : t) m.block_tables.push_back((int32_t)id);
+    m.block_tables.insert(m.block_tables.end(), mb - t.size(), 0);
+  }
+  m.is_prefill = true;
+  for (size_t i = 0; i < n; i++) m.is_prefill = m.is_prefill && is_prefill && is_prefill[i];
+  m.num_seqs = (uint32_t)n;
+  m.max_blocks_per_seq = (uint32_t)mb;
+  *out = std::move(m);
+  return true;
+}
+
+MemoryStats PagedKVCache::get_memory_stats() const {
+  const uint64_t per_block = 2ull * cfg_.num_kv_heads * cfg_.head_size * cfg_.block_size * cfg_.num_layers *
+                             (cfg_.use_fp8_cache ? 1 : 2);
+  const uint32_t total = alloc_.total_blocks(), used = alloc_.num_allocated_blocks();
+  return {total,
+          alloc_.num_free_blocks(),
+          used,
+          (uint32_t)((uint64_t)total * per_block / 1024 / 1024),
+          (uint32_t)((uint64_t)used * per_block / 1024 / 1024),
+          total ? (double)used / (double)total * 100.0 : 0.0};
+}
+
+bool PagedKVCache::track_sequence_tokens(uint32_t seq_id, const uint32_t *tokens, size_t n, uint32_t start_pos,
+                                         std::string *error) {
+  const SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  for (size_t i = 0; i < n; i++) {
+    const uint32_t pos = start_pos + (uint32_t)i;
+    const size_t blk = pos / cfg_.block_size;
+    if (blk < t->blocks().size())
+      tracker_.track_tokens(t->blocks()[blk]->block_id, &tokens[i], 1, pos % cfg_.block_size);
+  }
+  return true;
+}
+
+bool PagedKVCache::get_sequence_tokens(uint32_t seq_id, std::vector<uint32_t> *out, std::string *error) const {
+  const SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  out->clear();
+  for (const auto &b : t->blocks()) {
+    const auto &v = tracker_.get_block_tokens(b->block_id);
+    out->insert(out->end(), v.begin(), v.end());
+  }
+  if (out->size() > t->num_tokens()) out->resize(t->num_tokens());
+  return true;
+}
+
+// ---- scheduler (crates/mlx-paged-attn/src/scheduler.rs:143-466) -----------------------------
+void ContinuousBatchingScheduler::add_request(PendingRequest r) {
+  auto pos = waiting_.begin();
+  while (pos != waiting_.end() && pos->priority >= r.priority) ++pos;
+  waiting_.insert(pos, std::move(r));
+}
+
+bool ContinuousBatchingScheduler::schedule_step(PagedKVCache &cache, ScheduledBatch *out) {
+  if (running_.empty() && waiting_.empty()) return false;
+  ScheduledBatch b;
+  size_t total = 0;
+  auto add_decodes = [&](bool skip_present) {
+    for (const auto &kv : running_) {
+      if (b.seq_ids.size() >= cfg_.max_batch_size) break;
+      const ActiveSequence &s = kv.second;
+      if (s.is_prefill || total >= cfg_.max_tokens_per_step) continue;
+      if (skip_present && std::find(b.seq_ids.begin(), b.seq_ids.end(), kv.first) != b.seq_ids.end()) continue;
+      b.seq_ids.push_back(kv.first);
+      b.request_ids.push_back(s.request_id);
+      b.input_tokens.push_back({s.generated_tokens.empty() ? 0u : s.generated_tokens.back()});
+      b.is_prefill.push_back(0);
+      b.context_lens.push_back(s.position);
+      total += 1;
+      b.num_decode++;
+    }
+  };
+  if (cfg_.prioritize_decode) add_decodes(false);
+  // admit waiting requests: prefill = the whole prompt in one step
+  while (b.seq_ids.size() < cfg_.max_batch_size && b.num_prefill < cfg_.max_prefill_per_step &&
+         !waiting_.empty()) {
+    const PendingRequest &front = waiting_.front();
+    const uint32_t prompt_len = (uint32_t)front.prompt_tokens.size();
+    const uint32_t need = (prompt_len + block_size_ - 1) / block_size_;
+    if (total + prompt_len > cfg_.max_tokens_per_step) break;
+    if (!cache.can_allocate(need)) break;  // back-pressure: leave it queued
+    PendingRequest req = std::move(waiting_.front());
+    waiting_.pop_front();
+    uint32_t seq_id;
+    std::string err;
+    if (!cache.add_sequence(prompt_len, &seq_id, &err)) {
+      waiting_.push_front(std::move(req));
+      break;
+    }
+    running_[seq_id] = ActiveSequence{seq_id, req.request_id, {}, req.max_new_tokens, prompt_len, true, prompt_len};
+    b.seq_ids.push_back(seq_id);
+    b.request_ids.push_back(req.request_id);
+    b.input_tokens.push_back(std::move(req.prompt_tokens));
+    b.is_prefill.push_back(1);
+    b.context_lens.push_back(prompt_len);
+    total += prompt_len;
+    b.num_prefill++;
+  }
+  if (!cfg_.prioritize_decode) add_decodes(true);
+  if (b.seq_ids.empty()) return false;
+  b.total_tokens = (uint32_t)total;
+  *out = std::move(b);
+  return true;
+}
+
+bool ContinuousBatchingScheduler::process_outputs(const std::vector<TokenOutput> &outputs, PagedKVCache &cache,
+                                                  std::string *error) {
+  for (const TokenOutput &o : outputs) {
+    auto it = running_.find(o.seq_id);
+    if (it == running_.end()) continue;
+    ActiveSequence &s = it->second;
+    s.is_prefill = false;
+    s.generated_tokens.push_back(o.token);
+    s.position += 1;
+    if (!cache.extend_sequence(o.seq_id, 1, error)) return false;
+    const bool eos = o.is_eos || o.token == cfg_.eos_token_id;
+    if (eos || s.generated_tokens.size() >= s.max_new_tokens) {
+      const uint32_t gen = (uint32_t)s.generated_tokens.size();
+      completed_.push_back(
+          CompletedSequence{s.request_id, std::move(s.generated_tokens), eos ? "stop" : "length", s.prompt_len + gen});
+      running_.erase(it);
+      if (!cache.remove_sequence(o.seq_id, error)) return false;
+    }
+  }
+  return true;
+}
+
+std::vector<CompletedSequence> ContinuousBatchingScheduler::get_completed() {
+  std::vector<CompletedSequence> r;
+  r.swap(completed_);
+  return r;
+}
+
+bool ContinuousBatchingScheduler::abort_request(const std::string &request_id, PagedKVCache &cache, bool *found,
+                                                std::string *error) {
+  *found = false;
+  for (auto it = waiting_.begin(); it != waiting_.end(); ++it)
+    if (it->request_id == request_id) {
+      waiting_.erase(it);
+      *found = true;
+      return true;
+    }
+  for (auto it = running_.begin(); it != running_.end(); ++it)
+    if (it->second.request_id == request_id) {
+      const uint32_t seq_id = it->first;
+      running_.erase(it);
+      *found = true;
+      return cache.remove_sequence(seq_id, error);
+    }
+  return true;
+}
+
+SchedulerStats ContinuousBatchingScheduler::get_stats() const {
+  uint32_t tokens = 0, prefill = 0;
+  for (const auto &kv : running_) {
+    tokens += kv.second.position;
+    prefill += kv.second.is_prefill ? 1 : 0;
+  }
+  return {(uint32_t)waiting_.size(), (uint32_t)running_.size(), (uint32_t)completed_.size(), prefill,
+          (uint32_t)running_.size() - prefill, tokens};
+}
+
+const ActiveSequence *ContinuousBatchingScheduler::running(uint32_t seq_id) const {
+  auto it = running_.find(seq_id);
+  return it == running_.end() ? nullptr : &it->second;
+}
+
+// ---- kv_scale.rs:165-174 -------------------------------------------------------------------------
+float kv_compute_scale(float max_abs) { return max_abs < 1e-12f ? 1.0f : 448.0f / max_abs; }
+
+}  // namespace pa_host

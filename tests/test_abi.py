@@ -9,18 +9,21 @@ import pytest
 import paged_attn_b200 as pa
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADER = os.path.join(ROOT, "include", "paged_attn_b200.h")
+HEADERS = [os.path.join(ROOT, "include", n) for n in ("paged_attn_b200.h", "paged_attn_b200_host.h")]
 
 
 def declared_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"\b((?:pa|mlx)_[a-z0-9_]+)\s*\(", text)
+    names = []
+    for header in HEADERS:
+        text = open(header).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names += re.findall(r"\b((?:pa|mlx)_[a-z0-9_]+)\s*\(", text)
     return sorted(set(names))
 
 
 def test_header_and_binding_list_the_same_symbols():
-    assert declared_functions() == sorted(pa.EXPORTED_SYMBOLS)
+    from paged_attn_b200 import host
+    assert declared_functions() == sorted(pa.EXPORTED_SYMBOLS + host.HOST_SYMBOLS)
 
 
 def test_library_exports_every_declared_symbol():
