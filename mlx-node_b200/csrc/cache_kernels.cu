@@ -29,6 +29,9 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
   __shared__ __align__(16) uint16_t v_s[kTokPerCta][kHeadSize + kVPad];
   __shared__ int64_t slot_s[kTokPerCta];
 
+  // the attention kernel that follows may set up (it reads no pool data before its
+  // own griddepcontrol.wait)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int h = blockIdx.y;
   const int64_t t0 = (int64_t)blockIdx.x * kTokPerCta;
   const int tid = threadIdx.x;

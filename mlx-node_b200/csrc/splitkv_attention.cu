@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
   const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index, row within it
   const int S = p.S, Hkv = p.Hkv, G = p.G;
 
+  // The merge kernel may be scheduled now; it waits for this grid to finish.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- per-launch prefix sum of block counts --------------------------------
   for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s);
   if (tid == 0) pre[0] = 0;
@@ -144,6 +146,10 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
     return id * (uint32_t)Hkv + (uint32_t)h;
   };
 
+  // This grid may have started while the KV write before it was still running: the
+  // pool (and the workspace and output rows a previous call may still be reading or
+  // writing) must not be touched before the predecessor has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t ring_w = smem_u32(ring) + warp * NST * kStageBytes;
   const uint32_t bar_w = smem_u32(&bars[warp * NST]);
   uint32_t cur_ids = lookup(lane), nxt_ids = lookup(32 + lane);
@@ -427,16 +433,24 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
   }
 }
 
-// Merge of split items and zero-fill of empty ones.  grid (S, Hkv), 128 threads
-// (one per head dimension).  Recomputes the same flat partition as the main
-// kernel: CTA c owns units [c*W/N, (c+1)*W/N); the CTA holding unit u is
-// ((u+1)*N - 1) / W.
-__global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
-  __shared__ long long red[2][4];
+// Merge of split items and zero-fill of empty ones.  grid (S, Hkv), block (128, 4):
+// x = head dimension, y = column (query token x head of the group), so every load of a
+// thread is independent of its other loads.  Recomputes the same flat partition as the
+// main kernel: CTA c owns units [c*W/N, (c+1)*W/N); the CTA holding unit u is
+// ((u+1)*N - 1) / W.  Launched as a programmatic dependent of the main kernel: the part
+// above griddepcontrol.wait only reads the call's inputs.
+constexpr int kMergeCols = 4;
+__global__ void __launch_bounds__(128 * kMergeCols)
+splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
+  __shared__ long long red[2][4 * kMergeCols];
+  // a following attention call may set up while this grid runs (it waits before it
+  // touches the workspace or the output)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int s = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const int tid = threadIdx.y * 128 + d, nthreads = 128 * kMergeCols;
   const int seq = p.seq_base + s;
   long long before = 0, total = 0;
-  for (int i = d; i < p.S; i += 128) {
+  for (int i = tid; i < p.S; i += nthreads) {
     const int nbi = eligible_blocks(p, p.seq_base + i);
     total += nbi;
     if (i < s) before += nbi;
@@ -446,28 +460,32 @@ __global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, 
     before += __shfl_xor_sync(0xffffffffu, before, o);
     total += __shfl_xor_sync(0xffffffffu, total, o);
   }
-  if ((d & 31) == 0) { red[0][d >> 5] = before; red[1][d >> 5] = total; }
+  if ((tid & 31) == 0) { red[0][tid >> 5] = before; red[1][tid >> 5] = total; }
   __syncthreads();
-  before = red[0][0] + red[0][1] + red[0][2] + red[0][3];
-  total = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+  before = 0; total = 0;
+#pragma unroll
+  for (int i = 0; i < 4 * kMergeCols; i++) { before += red[0][i]; total += red[1][i]; }
 
   const int q_len = q_len_of(p, seq);
-  if (q_len < 1 || q_len * p.G > p.max_cols) return;  // not ours
+  const bool ours = q_len >= 1 && q_len * p.G <= p.max_cols;
   const int ncols = q_len * p.G;
   const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
-  const int nb = eligible_blocks(p, seq);
+  const int nb = ours ? eligible_blocks(p, seq) : 0;
+  const long long W = (long long)p.Hkv * total;
+  const long long U0 = (long long)p.Hkv * before + (long long)h * nb, U1 = U0 + nb;
+  const int c_first = nb ? (int)(((U0 + 1) * num_ctas - 1) / W) : 0;
+  const int c_last = nb ? (int)((U1 * num_ctas - 1) / W) : 0;
+  // everything below depends on what the main kernel wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!ours) return;
   if (nb == 0) {  // empty context: zero rows (crates/mlx-sys/src/mlx.cpp:4084-4088)
-    for (int col = 0; col < ncols; col++) {
+    for (int col = threadIdx.y; col < ncols; col += kMergeCols) {
       const int qj = col / p.G, g = col - qj * p.G;
       p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
           __float2bfloat16_rn(0.f);
     }
     return;
   }
-  const long long W = (long long)p.Hkv * total;
-  const long long U0 = (long long)p.Hkv * before + (long long)h * nb, U1 = U0 + nb;
-  const int c_first = (int)(((U0 + 1) * num_ctas - 1) / W);
-  const int c_last = (int)((U1 * num_ctas - 1) / W);
   if (c_first == c_last) return;  // written by the main kernel
 
   // With fewer units than CTAs some CTAs between c_first and c_last own nothing.
@@ -475,26 +493,36 @@ __global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, 
     return (long long)(c + 1) * W / num_ctas <= (long long)c * W / num_ctas;
   };
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
-  for (int col = 0; col < ncols; col++) {
+  for (int col = threadIdx.y; col < ncols; col += kMergeCols) {
     const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
     const int lane = gid * 4 + tig;
     const int o_idx = (((mt * NT + nt) * 4 + upper * 2 + par) * 32) + lane;
     const int m_idx = (32 * NT + nt * 2 + par) * 32 + lane;
     const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
-    float mm = -INFINITY;
-    for (int c = c_first; c <= c_last; c++) {
-      if (cta_empty(c)) continue;
-      const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
-      mm = fmaxf(mm, slot[m_idx]);
-    }
-    float acc = 0.f, lsum = 0.f;
-    for (int c = c_first; c <= c_last; c++) {
-      if (cta_empty(c)) continue;
-      const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
-      const float mj = slot[m_idx];
-      const float w = mj == -INFINITY ? 0.f : exp2f(mj - mm);
-      acc += slot[o_idx] * w;
-      lsum += slot[l_idx] * w;
+    // partials in CTA order, four at a time so that their loads overlap
+    float mm = -INFINITY, acc = 0.f, lsum = 0.f;
+    for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+      float mj[4], oj[4], lj[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int c = c0 + k;
+        const bool use = c <= c_last && !cta_empty(c);
+        const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
+        mj[k] = use ? slot[m_idx] : -INFINITY;
+        oj[k] = use ? slot[o_idx] : 0.f;
+        lj[k] = use ? slot[l_idx] : 0.f;
+      }
+      const float m_new = fmaxf(fmaxf(fmaxf(mj[0], mj[1]), fmaxf(mj[2], mj[3])), mm);
+      const float keep = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
+      acc *= keep;
+      lsum *= keep;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const float w = mj[k] == -INFINITY ? 0.f : exp2f(mj[k] - m_new);
+        acc += oj[k] * w;
+        lsum += lj[k] * w;
+      }
+      mm = m_new;
     }
     const int qj = col / p.G, g = col - qj * p.G;
     p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
@@ -502,11 +530,30 @@ __global__ void __launch_bounds__(128) splitkv_merge_kernel(const AttnParams p, 
   }
 }
 
+// Launch with programmatic stream serialisation: the grid may start while its
+// predecessor in the stream drains; it orders itself with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int NT>
 cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
-  splitkv_kernel<NT><<<num_ctas, kThreads, Cfg<NT>::kSmemBytes, st>>>(p);
+  const cudaError_t e = launch_dependent(splitkv_kernel<NT>, dim3(num_ctas), dim3(kThreads),
+                                         Cfg<NT>::kSmemBytes, st, p);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace
@@ -568,10 +615,9 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_ctas, cudaS
     else if (nt == 2) e = launch_nt<2>(p, num_ctas, st);
     else e = launch_nt<3>(p, num_ctas, st);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)p.S, (unsigned)p.Hkv);
-    splitkv_merge_kernel<<<grid, 128, 0, st>>>(p, num_ctas, nt <= 1 ? 1 : (nt == 2 ? 2 : 3));
+    e = launch_dependent(splitkv_merge_kernel, dim3((unsigned)p.S, (unsigned)p.Hkv),
+                         dim3(128, kMergeCols), 0, st, p, num_ctas, nt <= 1 ? 1 : (nt == 2 ? 2 : 3));
     __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
-    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
