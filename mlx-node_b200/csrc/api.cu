@@ -383,24 +383,26 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.seq_base = 0;
 
   if (!cu_q_lens_host) {  // decode: one query per sequence
+    p.min_cols = 1;
     p.max_cols = G;
     PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
     return PA_OK;
   }
 
-  // Classify sequences: few columns -> split-KV kernel, many -> tile kernel.
+  // Classify sequences by their number of columns (queries x heads of a group):
+  // up to 24 columns -> split-KV kernel, one launch per 8-column width class so that
+  // plain decode sequences run in the narrow, deepest-pipelined variant even when the
+  // batch also holds multi-token (verify) sequences; more -> tile kernel.
   const int split_cols = pa::splitkv_max_cols();
   const int tile_q = pa::tile_queries_per_cta(G);
-  int widest_small = 0;
-  bool any_small = false;
+  bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
   for (int s = 0; s < num_seqs; s++) {
     const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
     if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
     if (ql == 0) continue;
     if (ql * G <= split_cols) {
-      any_small = true;
-      if (ql * G > widest_small) widest_small = ql * G;
+      have_class[(ql * G - 1) / 8] = true;
     } else {
       // Tiles of one (sequence, kv head) are neighbours in launch order so that they
       // share the head's KV blocks in L2; later tiles see more keys and go first.
@@ -422,10 +424,10 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
                             cudaMemcpyHostToDevice, stream));
     PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), stream));
   }
-  if (any_small) {
-    // the split-KV kernel skips sequences wider than max_cols (the tile kernel has them)
-    p.max_cols = ((widest_small + 7) / 8) * 8;
-    if (p.max_cols > split_cols) p.max_cols = split_cols;
+  for (int k = 0; k < 3; k++) {
+    if (!have_class[k]) continue;
+    p.min_cols = 8 * k + 1;
+    p.max_cols = 8 * k + 8;
     PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
   }
   return PA_OK;

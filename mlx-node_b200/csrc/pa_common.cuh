@@ -120,7 +120,8 @@ struct AttnParams {
   float *ws;      // partial results, slot layout described in decode.cu
   unsigned *err;  // error word
   int seq_base;   // first sequence this launch covers
-  int max_cols;   // columns (q_len*G) a sequence may have to be taken by the split-KV kernel
+  int min_cols;   // a sequence is taken by the split-KV launch iff min_cols <= q_len*G <= max_cols
+  int max_cols;
 };
 
 // Host-side launchers (defined next to their kernels).

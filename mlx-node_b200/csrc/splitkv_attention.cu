@@ -68,7 +68,7 @@ __device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
 // the tile kernel or has nothing to attend).
 __device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
   const int ql = q_len_of(p, seq);
-  if (ql < 1 || ql * p.G > p.max_cols) return 0;
+  if (ql < 1 || ql * p.G > p.max_cols || ql * p.G < p.min_cols) return 0;
   const int ctx = p.context_lens[seq];
   return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
 }
@@ -467,7 +467,7 @@ splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
   for (int i = 0; i < 4 * kMergeCols; i++) { before += red[0][i]; total += red[1][i]; }
 
   const int q_len = q_len_of(p, seq);
-  const bool ours = q_len >= 1 && q_len * p.G <= p.max_cols;
+  const bool ours = q_len >= 1 && q_len * p.G <= p.max_cols && q_len * p.G >= p.min_cols;
   const int ncols = q_len * p.G;
   const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
   const int nb = ours ? eligible_blocks(p, seq) : 0;
