@@ -15,7 +15,9 @@
  * from every call.  It is what a CUDA port of the crate's `metal` module
  * (crates/mlx-paged-attn/src/metal/mod.rs:29-44) binds.
  *
- * All tensors are bf16 (dtype code 1) on the tuned path.  Pool layout is the
+ * Tensors are f16 (dtype code 0, the reference's default) or bf16 (code 1); q,
+ * k, v and out of a call have the cache's dtype.  f32 (code 2) is not built.
+ * Pool layout is the
  * reference's (crates/mlx-paged-attn/src/cache_engine.rs:58-106):
  *   key   [num_blocks, num_kv_heads, head_size/8, block_size, 8]
  *   value [num_blocks, num_kv_heads, head_size, block_size]
@@ -41,7 +43,7 @@ typedef int32_t pa_status;
 enum {
   PA_OK = 0,
   PA_ERR_INVALID_ARG = 1,  /* null pointer, bad size/stride/alignment          */
-  PA_ERR_UNSUPPORTED = 2,  /* dtype / head size / block size not built         */
+  PA_ERR_UNSUPPORTED = 2,  /* f32 / head size / block size not built           */
   PA_ERR_OOM = 3,          /* device allocation failed                         */
   PA_ERR_OUT_OF_RANGE = 4, /* a block id or slot outside the pool was seen     */
   PA_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out               */
@@ -83,7 +85,7 @@ void mlx_paged_attn_free_cache(PagedAttnCache *cache);
 mlx_array *mlx_paged_attn_get_key_cache(PagedAttnCache *cache, uint32_t layer_idx);
 mlx_array *mlx_paged_attn_get_value_cache(PagedAttnCache *cache, uint32_t layer_idx);
 /* crates/mlx-sys/src/lib.rs:760-766, mlx.cpp:3900-4012.
- * keys/values [num_tokens, num_kv_heads, head_size] bf16, slot_mapping
+ * keys/values [num_tokens, num_kv_heads, head_size] in the cache dtype, slot_mapping
  * [num_tokens] int64 (a negative slot is skipped).  Silent no-op on null or
  * bad layer, like the reference; the reason is left in the error string.      */
 void mlx_paged_attn_reshape_and_cache(PagedAttnCache *cache, uint32_t layer_idx,
@@ -146,7 +148,7 @@ pa_status pa_cache_check_errors(PagedAttnCache *cache, void *cuda_stream);
 /* KV block write.  dispatch_reshape_and_cache_raw
  * (crates/mlx-paged-attn/src/metal/reshape_and_cache.rs:177-270) over the
  * kernel crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:33-98.
- * key/value: bf16 [num_tokens, num_kv_heads, head_size] with row strides
+ * key/value: [num_tokens, num_kv_heads, head_size] in the cache dtype, row strides
  * key_stride/value_stride in elements; slot_mapping: int64 [num_tokens] on
  * the device, slot < 0 skipped, slot >= num_blocks*block_size skipped and
  * reported through pa_cache_check_errors.                                     */
@@ -174,7 +176,7 @@ size_t pa_attention_workspace_bytes(const PagedAttnCache *cache);
  * paged_attention.rs:954-991; kernels crates/mlx-paged-attn/metal/attention/
  * paged_attention.metal:760-1260) and mlx_paged_attn_forward
  * (crates/mlx-sys/src/mlx.cpp:4041-4162).
- *   out, q        bf16 [num_seqs, num_q_heads, head_size]; row strides
+ *   out, q        [num_seqs, num_q_heads, head_size] in the cache dtype; row strides
  *                 q_stride / out_stride in elements
  *   block_tables  int32 [num_seqs, max_blocks_per_seq], device
  *   context_lens  int32 [num_seqs], device; counts the token written this step
@@ -228,7 +230,7 @@ pa_status pa_paged_attention_decode_static(PagedAttnCache *cache, uint32_t layer
  * sequence s has context_lens[s] tokens in the pool after this step's write
  * and q_len_s = cu_q_lens[s+1]-cu_q_lens[s] >= 0 queries that occupy the last
  * q_len_s positions; query j attends keys [0, context_lens[s]-q_len_s+j].
- *   out, q        bf16 [total_q, num_q_heads, head_size], packed by sequence
+ *   out, q        [total_q, num_q_heads, head_size] in the cache dtype, packed by sequence
  *   cu_q_lens     int32 [num_seqs+1] in HOST memory (the scheduler has it);
  *                 the library uploads what its kernels need
  *   max_context_len  upper bound of context_lens (0 = unknown)                */

@@ -105,7 +105,7 @@ pa_status validate_config(const PagedAttnConfig *c) {
   if (c->num_blocks == 0 || c->num_kv_heads == 0 || c->num_layers == 0)
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
-  if (c->dtype != 1) return fail(PA_ERR_UNSUPPORTED, "only dtype 1 (bf16) is built");
+  if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
   if (c->head_size != pa::kHeadSize || c->block_size != pa::kBlockSize)
     return fail(PA_ERR_UNSUPPORTED, "only head_size 128 with block_size 16 is built");
   return PA_OK;
@@ -300,8 +300,8 @@ pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *ke
   if (num_tokens > ((int64_t)1 << 34)) return fail(PA_ERR_INVALID_ARG, "num_tokens too large");
   DeviceGuard g(c->device);
   PA_CUDA(pa::launch_reshape_and_cache(
-      static_cast<const __nv_bfloat16 *>(key), static_cast<const __nv_bfloat16 *>(value),
-      static_cast<__nv_bfloat16 *>(c->k[layer]), static_cast<__nv_bfloat16 *>(c->v[layer]),
+      static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
+      static_cast<pa::elem16 *>(c->k[layer]), static_cast<pa::elem16 *>(c->v[layer]),
       slot_mapping, num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads,
       c->cfg.num_blocks, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
   return PA_OK;
@@ -316,8 +316,8 @@ pa_status pa_copy_blocks(PagedAttnCache *c, uint32_t layer, const int64_t *mappi
   if (!mapping) return fail(PA_ERR_INVALID_ARG, "block_mapping is null");
   DeviceGuard g(c->device);
   const int64_t bpb = (int64_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2;
-  PA_CUDA(pa::launch_copy_blocks(static_cast<__nv_bfloat16 *>(c->k[layer]),
-                                 static_cast<__nv_bfloat16 *>(c->v[layer]), mapping, num_pairs, bpb,
+  PA_CUDA(pa::launch_copy_blocks(static_cast<pa::elem16 *>(c->k[layer]),
+                                 static_cast<pa::elem16 *>(c->v[layer]), mapping, num_pairs, bpb,
                                  c->cfg.num_blocks, c->err_dev,
                                  static_cast<cudaStream_t>(cuda_stream)));
   return PA_OK;
@@ -361,10 +361,10 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   DeviceGuard g(c->device);
   pa::AttnParams p{};
-  p.q = static_cast<const __nv_bfloat16 *>(q);
-  p.out = static_cast<__nv_bfloat16 *>(out);
-  p.k_pool = static_cast<const __nv_bfloat16 *>(c->k[layer]);
-  p.v_pool = static_cast<const __nv_bfloat16 *>(c->v[layer]);
+  p.q = static_cast<const pa::elem16 *>(q);
+  p.out = static_cast<pa::elem16 *>(out);
+  p.k_pool = static_cast<const pa::elem16 *>(c->k[layer]);
+  p.v_pool = static_cast<const pa::elem16 *>(c->v[layer]);
   p.block_tables = block_tables;
   p.context_lens = context_lens;
   p.cu_q_lens = nullptr;
@@ -381,6 +381,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.ws = static_cast<float *>(workspace);
   p.err = c->err_dev;
   p.seq_base = 0;
+  p.is_f16 = c->cfg.dtype == 0 ? 1 : 0;
 
   if (!cu_q_lens_host) {  // decode: one query per sequence
     p.min_cols = 1;
@@ -610,10 +611,11 @@ void mlx_paged_attn_reshape_and_cache(PagedAttnCache *c, uint32_t layer, mlx_arr
     fail(PA_ERR_INVALID_ARG, "reshape_and_cache: null argument");
     return;
   }
-  if (keys->ndim != 3 || values->ndim != 3 || slot_mapping->dtype != 4 || keys->dtype != 1 ||
-      values->dtype != 1 || keys->shape[1] != c->cfg.num_kv_heads ||
+  if (keys->ndim != 3 || values->ndim != 3 || slot_mapping->dtype != 4 ||
+      keys->dtype != (int32_t)c->cfg.dtype || values->dtype != (int32_t)c->cfg.dtype ||
+      keys->shape[1] != c->cfg.num_kv_heads ||
       keys->shape[2] != c->cfg.head_size || slot_mapping->shape[0] != keys->shape[0]) {
-    fail(PA_ERR_INVALID_ARG, "reshape_and_cache: keys/values must be bf16 [T,Hkv,D], slots int64 [T]");
+    fail(PA_ERR_INVALID_ARG, "reshape_and_cache: keys/values must be [T,Hkv,D] in the cache dtype, slots int64 [T]");
     return;
   }
   const int64_t row = keys->shape[1] * keys->shape[2];
@@ -629,14 +631,14 @@ mlx_array *mlx_paged_attn_forward(mlx_array *q, mlx_array *kc, mlx_array *vc, ml
     fail(PA_ERR_INVALID_ARG, "forward: null argument");
     return nullptr;
   }
-  if (q->ndim != 3 || kc->ndim != 5 || vc->ndim != 4 || bt->ndim != 2 || q->dtype != 1 ||
-      kc->dtype != 1 || vc->dtype != 1 || bt->dtype != 3 || cl->dtype != 3 ||
+  if (q->ndim != 3 || kc->ndim != 5 || vc->ndim != 4 || bt->ndim != 2 || q->dtype > 1 ||
+      kc->dtype != q->dtype || vc->dtype != q->dtype || bt->dtype != 3 || cl->dtype != 3 ||
       (int64_t)block_size != vc->shape[3] || bt->shape[0] != q->shape[0]) {
-    fail(PA_ERR_INVALID_ARG, "forward: expected bf16 q [S,Hq,D], pools, int32 tables [S,MB] and lens [S]");
+    fail(PA_ERR_INVALID_ARG, "forward: expected f16/bf16 q [S,Hq,D], pools of the same dtype, int32 tables [S,MB] and lens [S]");
     return nullptr;
   }
   PagedAttnConfig cfg{(uint32_t)vc->shape[3], (uint32_t)vc->shape[0], (uint32_t)vc->shape[2],
-                      (uint32_t)vc->shape[1], 1, 1};
+                      (uint32_t)vc->shape[1], 1, (uint32_t)q->dtype};
   void *kp = kc->data, *vp = vc->data;
   // A transient handle over the caller's pools: this entry takes the pools as
   // arrays, not the cache handle (crates/mlx-sys/src/lib.rs:782-791).
@@ -658,7 +660,7 @@ mlx_array *mlx_paged_attn_forward(mlx_array *q, mlx_array *kc, mlx_array *vc, ml
                                        t_stream) == PA_OK &&
              cudaStreamSynchronize(t_stream) == cudaSuccess) {
     const int64_t sh[3] = {S, Hq, D};
-    res = pa_array_from_device(out, 1, sh, 3);
+    res = pa_array_from_device(out, q->dtype, sh, 3);
     if (res) {
       res->owns = true;
       res->device = c->device;

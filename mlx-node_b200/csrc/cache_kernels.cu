@@ -19,9 +19,9 @@ constexpr int kTokPerCta = 16;
 constexpr int kVPad = 2;  // bf16 elements of row padding: 65-word rows, conflict-free
 
 __global__ void __launch_bounds__(256)
-reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
-                         const __nv_bfloat16 *__restrict__ value,
-                         __nv_bfloat16 *__restrict__ k_pool, __nv_bfloat16 *__restrict__ v_pool,
+reshape_and_cache_kernel(const elem16 *__restrict__ key,
+                         const elem16 *__restrict__ value,
+                         elem16 *__restrict__ k_pool, elem16 *__restrict__ v_pool,
                          const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
                          int64_t key_stride, int64_t value_stride, int Hkv, uint32_t num_blocks,
                          unsigned *err) {
@@ -70,7 +70,7 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
     if (slot >= 0) {
       const int64_t blk = slot / kBlockSize;
       const int off = (int)(slot % kBlockSize);
-      __nv_bfloat16 *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunkElems + c * (kBlockSize * 8) +
+      elem16 *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunkElems + c * (kBlockSize * 8) +
                            off * 8;
       *reinterpret_cast<uint4 *>(dst) = k_s[tok][c];
     }
@@ -88,8 +88,8 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
   }
 }
 
-cudaError_t launch_reshape_and_cache(const __nv_bfloat16 *key, const __nv_bfloat16 *value,
-                                     __nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
+                                     elem16 *k_pool, elem16 *v_pool,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
                                      uint32_t num_blocks, unsigned *err, cudaStream_t st) {
@@ -108,7 +108,7 @@ cudaError_t launch_reshape_and_cache(const __nv_bfloat16 *key, const __nv_bfloat
 // Pairs are independent unless a destination is also a source of a later pair;
 // the reference processes pairs in parallel as well (one threadgroup per pair).
 __global__ void __launch_bounds__(256)
-copy_blocks_kernel(__nv_bfloat16 *__restrict__ k_pool, __nv_bfloat16 *__restrict__ v_pool,
+copy_blocks_kernel(elem16 *__restrict__ k_pool, elem16 *__restrict__ v_pool,
                    const int64_t *__restrict__ mapping, int64_t bytes_per_block,
                    uint32_t num_blocks, unsigned *err) {
   const int64_t pair = blockIdx.x;
@@ -127,7 +127,7 @@ copy_blocks_kernel(__nv_bfloat16 *__restrict__ k_pool, __nv_bfloat16 *__restrict
   *reinterpret_cast<uint4 *>(vd) = *reinterpret_cast<const uint4 *>(vs);
 }
 
-cudaError_t launch_copy_blocks(__nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
                                const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
                                uint32_t num_blocks, unsigned *err, cudaStream_t st) {
   if (num_pairs <= 0) return cudaSuccess;

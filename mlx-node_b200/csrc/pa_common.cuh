@@ -1,13 +1,16 @@
 // Shared device helpers and kernel-launch declarations for the sm_100a
 // paged-attention kernels.
 #pragma once
-#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace pa {
 
-// Fixed geometry of the tuned path: head size 128, 16-token blocks, bf16.
+// One 16-bit element: a bf16 or an f16 bit pattern (cache dtype 1 or 0).  The copies
+// never interpret it; the attention kernels are compiled for both formats.
+using elem16 = uint16_t;
+
+// Fixed geometry of the tuned path: head size 128, 16-token blocks, 16-bit elements.
 // One (block, kv head) pair is a contiguous 4 KB K chunk laid out
 // [D/8][BS][8] and a contiguous 4 KB V chunk laid out [D][BS]
 // (crates/mlx-paged-attn/src/paged_kv_cache.rs:1129-1136: kv_head_stride = D*BS).
@@ -76,14 +79,22 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
-// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
-                                               uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-      "{%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D(16x8,f32) += A(16x16,row) * B(16x8,col), operands bf16 or f16
+template <bool F16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  if (F16)
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // Transpose an 8x8 matrix of 16-bit elements held one 32-bit register per lane.
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -91,11 +102,20 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-// Pack two floats to bf16x2 (lo in the low half), round to nearest even.
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+// Pack two floats to a 16-bit pair (lo in the low half), round to nearest even.
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+template <bool F16>
+__device__ __forceinline__ elem16 to_elem(float x) {
+  return (elem16)(pack2<F16>(x, 0.f) & 0xffffu);
+}
+__device__ __forceinline__ elem16 to_elem_rt(float x, bool f16) {
+  return f16 ? to_elem<true>(x) : to_elem<false>(x);
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -105,14 +125,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // ---- launch parameter blocks --------------------------------------------------
 struct AttnParams {
-  const __nv_bfloat16 *q;
-  __nv_bfloat16 *out;
-  const __nv_bfloat16 *k_pool;
-  const __nv_bfloat16 *v_pool;
+  const elem16 *q;
+  elem16 *out;
+  const elem16 *k_pool;
+  const elem16 *v_pool;
   const int32_t *block_tables;  // [S, MB]
   const int32_t *context_lens;  // [S]
   const int32_t *cu_q_lens;     // [S+1] device copy, or null: one query per sequence
   int S, Hq, Hkv, G, MB;
+  int is_f16;  // element format: 1 = f16, 0 = bf16
   uint32_t num_blocks;  // pool size, for range checks
   int64_t q_stride, out_stride;
   float scale;    // logits multiplier
@@ -125,12 +146,12 @@ struct AttnParams {
 };
 
 // Host-side launchers (defined next to their kernels).
-cudaError_t launch_reshape_and_cache(const __nv_bfloat16 *key, const __nv_bfloat16 *value,
-                                     __nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
+                                     elem16 *k_pool, elem16 *v_pool,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
                                      uint32_t num_blocks, unsigned *err, cudaStream_t st);
-cudaError_t launch_copy_blocks(__nv_bfloat16 *k_pool, __nv_bfloat16 *v_pool,
+cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
                                const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
                                uint32_t num_blocks, unsigned *err, cudaStream_t st);
 // Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.

@@ -73,7 +73,7 @@ __device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
   return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
 }
 
-template <int NT>
+template <int NT, bool F16>
 __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p) {
   using C = Cfg<NT>;
   constexpr int NST = C::kStages;
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
           uint32_t af[4];
           ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++) mma_bf16_16816(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
+          for (int nt = 0; nt < NT; nt++) mma_16816<F16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
         }
         const int tok0 = blk * kBlockSize + gid, tok1 = tok0 + 8;
         const bool need_mask = (blk + 1) * kBlockSize > min_lim;
@@ -297,8 +297,8 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         uint32_t pb[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-          pb[nt][0] = movmatrix_trans(pack_bf16(sacc[nt][0], sacc[nt][1]));
-          pb[nt][1] = movmatrix_trans(pack_bf16(sacc[nt][2], sacc[nt][3]));
+          pb[nt][0] = movmatrix_trans(pack2<F16>(sacc[nt][0], sacc[nt][1]));
+          pb[nt][1] = movmatrix_trans(pack2<F16>(sacc[nt][2], sacc[nt][3]));
         }
         // Tokens past the context in the last block may hold anything (NaN
         // included) and 0*NaN is NaN: clear them in the V fragments
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
           for (int nt = 0; nt < NT; nt++) {
             o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
             o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
-            mma_bf16_16816(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+            mma_16816<F16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
           }
         }
       }
@@ -410,12 +410,12 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
             if (col < ncols) {
               const int qj = col / G, g = col - qj * G;
               const float inv = l[nt][c] > 0.f ? 1.f / l[nt][c] : 0.f;
-              __nv_bfloat16 *op = p.out + (int64_t)(q0 + qj) * p.out_stride +
+              elem16 *op = p.out + (int64_t)(q0 + qj) * p.out_stride +
                                   (int64_t)(h * G + g) * kHeadSize;
 #pragma unroll
               for (int mt = 0; mt < 8; mt++) {
-                op[16 * mt + gid] = __float2bfloat16_rn(o[mt][nt][c] * inv);
-                op[16 * mt + gid + 8] = __float2bfloat16_rn(o[mt][nt][c + 2] * inv);
+                op[16 * mt + gid] = to_elem<F16>(o[mt][nt][c] * inv);
+                op[16 * mt + gid + 8] = to_elem<F16>(o[mt][nt][c + 2] * inv);
               }
             }
           }
@@ -482,7 +482,7 @@ splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
     for (int col = threadIdx.y; col < ncols; col += kMergeCols) {
       const int qj = col / p.G, g = col - qj * p.G;
       p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
-          __float2bfloat16_rn(0.f);
+          (elem16)0;
     }
     return;
   }
@@ -526,7 +526,7 @@ splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
     }
     const int qj = col / p.G, g = col - qj * p.G;
     p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
-        __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        to_elem_rt(lsum > 0.f ? acc / lsum : 0.f, p.is_f16 != 0);
   }
 }
 
@@ -550,8 +550,11 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 template <int NT>
 cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
-  const cudaError_t e = launch_dependent(splitkv_kernel<NT>, dim3(num_ctas), dim3(kThreads),
-                                         Cfg<NT>::kSmemBytes, st, p);
+  const cudaError_t e =
+      p.is_f16 ? launch_dependent(splitkv_kernel<NT, true>, dim3(num_ctas), dim3(kThreads),
+                                  Cfg<NT>::kSmemBytes, st, p)
+               : launch_dependent(splitkv_kernel<NT, false>, dim3(num_ctas), dim3(kThreads),
+                                  Cfg<NT>::kSmemBytes, st, p);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return e;
 }
@@ -591,16 +594,20 @@ size_t splitkv_workspace_bytes(int num_ctas) {
   return (size_t)num_ctas * 2 * kSlotFloats * sizeof(float);
 }
 
+template <int NT>
+static cudaError_t configure_nt() {
+  cudaError_t e = cudaFuncSetAttribute(splitkv_kernel<NT, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(splitkv_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg<NT>::kSmemBytes);
+}
+
 cudaError_t splitkv_configure() {
-  cudaError_t e;
-  e = cudaFuncSetAttribute(splitkv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           Cfg<1>::kSmemBytes);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(splitkv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           Cfg<2>::kSmemBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(splitkv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Cfg<3>::kSmemBytes);
+  cudaError_t e = configure_nt<1>();
+  if (e == cudaSuccess) e = configure_nt<2>();
+  if (e == cudaSuccess) e = configure_nt<3>();
+  return e;
 }
 
 cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_ctas, cudaStream_t st) {

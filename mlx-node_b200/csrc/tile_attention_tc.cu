@@ -183,8 +183,10 @@ __device__ __forceinline__ uint64_t v_block_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (16ull << 32) | (1ull << 46) |
          (6ull << 61);
 }
-// Instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: D fp32, A/B bf16 (format 1) or f16 (format 0), both K-major,
+// N = 128, M = 128.
+constexpr uint32_t kIdescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescF16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
 // Byte offset of 16-byte unit `u` (0..7) of row `r` inside a 128-row slab.
 __device__ __forceinline__ uint32_t sw128_off(int r, int u) {
@@ -224,7 +226,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 // at once (one latency instead of several), which is why the softmax warps raise their
 // register budget.  MASK and CAP are compile-time so the common loop is five
 // instructions per element with no branches.
-template <bool CAP, bool MASK>
+template <bool CAP, bool MASK, bool F16>
 __device__ __forceinline__ void row_pass(uint32_t s_t, float c, float mc, int lim, int tok0,
                                          float cap_in, float cap_out, uint32_t (&pk)[64],
                                          float &mx_out, float &sum_out) {
@@ -250,7 +252,7 @@ __device__ __forceinline__ void row_pass(uint32_t s_t, float c, float mc, int li
       mxa[(e >> 1) & 3] = fmaxf(mxa[(e >> 1) & 3], fmaxf(x0, x1));
       const float p0 = fast_exp2(fmaf(x0, c, -mc)), p1 = fast_exp2(fmaf(x1, c, -mc));
       sma[(e >> 1) & 3] += p0 + p1;
-      dst[e >> 1] = pack_bf16(p0, p1);
+      dst[e >> 1] = pack2<F16>(p0, p1);
     }
   };
   tmem_wait_ld32(s0);  // waits for all four loads
@@ -279,7 +281,7 @@ __device__ __forceinline__ bool wait_bar_at(uint32_t bar, uint32_t parity, volat
 #endif
 }
 
-template <bool CAP>
+template <bool CAP, bool F16>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) {
   extern __shared__ uint8_t smem_raw[];
@@ -362,7 +364,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         const int tile = row >> 7, r = row & 127;
         const int qi = row / G, g = row - qi * G;
         const bool have = qi < w.q_count;
-        const __nv_bfloat16 *src =
+        const elem16 *src =
             have ? p.q + (int64_t)(q0 + w.q_begin + qi) * p.q_stride + (int64_t)(h * G + g) * kHeadSize + c * 8
                  : p.q;
         cp_async16(q_s + (tile * 2 + (c >> 3)) * kSlab + sw128_off(r, c & 7), src, have ? 16u : 0u);
@@ -378,7 +380,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
           const int gb = j * 8 + b;            // block within the sequence
           const bool have = gb < nblk;
           const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
-          const __nv_bfloat16 *src = (is_v ? p.v_pool : p.k_pool) + chunk * kChunkElems;
+          const elem16 *src = (is_v ? p.v_pool : p.k_pool) + chunk * kChunkElems;
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const int e = it * 32 + lane;  // 16-byte piece of the 4 KB chunk, in memory order
@@ -444,6 +446,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
       // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
       // (uniform registers feed tcgen05.mma directly); one elected lane issues.
       if (warp == 12) {
+        constexpr uint32_t kIdesc = F16 ? kIdescF16 : kIdescBf16;
         const bool leader = elect_one();
         auto issue_s = [&](int i, int j) {
           const uint32_t kst = k_s + (j & 1) * kStage;
@@ -514,8 +517,8 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
       float m_used = -INFINITY, l = 0.f;
       auto pass = [&](bool need_mask, int tok0, uint32_t (&pk)[64], float &mx, float &sum) {
         const float mc = m_used == -INFINITY ? 0.f : m_used * c;
-        if (need_mask) row_pass<CAP, true>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
-        else row_pass<CAP, false>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
+        if (need_mask) row_pass<CAP, true, F16>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
+        else row_pass<CAP, false, F16>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
       };
 
       for (int j = 0; j < n_tiles && !failed; j++) {
@@ -571,7 +574,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
       if (!failed && wait_bar_at(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag, 9)) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16 *orow = have ? p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
+        elem16 *orow = have ? p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
                                          (int64_t)(h * G + g) * kHeadSize
                                    : nullptr;
 #pragma unroll
@@ -583,10 +586,10 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               uint4 v;
-              v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+              v.x = pack2<F16>(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+              v.y = pack2<F16>(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+              v.z = pack2<F16>(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+              v.w = pack2<F16>(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
               *reinterpret_cast<uint4 *>(orow + ch * 32 + e) = v;
             }
           }
@@ -636,18 +639,26 @@ extern "C" int pa_debug_tile_timing(unsigned long long *out16, int reset) {
 int tile_queries_per_cta(int G) { return 2 * kQRows / G; }
 
 cudaError_t tile_configure() {
-  cudaError_t e = cudaFuncSetAttribute(tile_attention_tc_kernel<false>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(tile_attention_tc_kernel<true>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+  cudaError_t e = cudaSuccess;
+  auto set = [&](auto kernel) {
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+  };
+  set(tile_attention_tc_kernel<false, false>);
+  set(tile_attention_tc_kernel<true, false>);
+  set(tile_attention_tc_kernel<false, true>);
+  set(tile_attention_tc_kernel<true, true>);
+  return e;
 }
 
 cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
                                   cudaStream_t st) {
   if (num_work <= 0) return cudaSuccess;
-  if (p.softcap != 1.0f) tile_attention_tc_kernel<true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
-  else tile_attention_tc_kernel<false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  const bool cap = p.softcap != 1.0f, f16 = p.is_f16 != 0;
+  if (cap && f16) tile_attention_tc_kernel<true, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  else if (cap) tile_attention_tc_kernel<true, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  else if (f16) tile_attention_tc_kernel<false, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  else tile_attention_tc_kernel<false, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

@@ -43,6 +43,16 @@ static inline uint16_t f32_to_bf16(float f) {
   return (uint16_t)(u >> 16);
 }
 
+/* f16 bit pattern -> float (cache dtype 0); exact. */
+static inline float f16_to_f32(uint16_t h) {
+  _Float16 v;
+  memcpy(&v, &h, 2);
+  return (float)v;
+}
+static inline float elem_to_f32(uint16_t bits, int is_f16) {
+  return is_f16 ? f16_to_f32(bits) : bf16_to_f32(bits);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
@@ -145,7 +155,7 @@ static inline int64_t v_index(const int32_t *table, int64_t t, int h, int d,
 static void attend_row(float *o, const uint16_t *qp, const uint16_t *k_cache,
                        const uint16_t *v_cache, const int32_t *table, int n,
                        int h, int Hkv, int D, int BS, float scale,
-                       float softcap, double *logit, double *acc) {
+                       float softcap, double *logit, double *acc, int is_f16) {
   const int x = 8;
   if (n <= 0) {
     for (int d = 0; d < D; d++) o[d] = 0.f;
@@ -157,8 +167,8 @@ static void attend_row(float *o, const uint16_t *qp, const uint16_t *k_cache,
     double dot = 0.0;
     for (int c = 0; c < D / x; c++)
       for (int e = 0; e < x; e++)
-        dot += (double)bf16_to_f32(qp[c * x + e]) *
-               (double)bf16_to_f32(k_cache[kb + (int64_t)c * BS * x + e]);
+        dot += (double)elem_to_f32(qp[c * x + e], is_f16) *
+               (double)elem_to_f32(k_cache[kb + (int64_t)c * BS * x + e], is_f16);
     double l = dot * (double)scale;
     if (softcap != 1.0f) l = tanh(l / (double)softcap) * (double)softcap;
     logit[t] = l;
@@ -174,7 +184,7 @@ static void attend_row(float *o, const uint16_t *qp, const uint16_t *k_cache,
     const double p = logit[t];
     const int64_t vb = v_index(table, t, h, 0, Hkv, D, BS);
     for (int d = 0; d < D; d++)
-      acc[d] += p * (double)bf16_to_f32(v_cache[vb + (int64_t)d * BS]);
+      acc[d] += p * (double)elem_to_f32(v_cache[vb + (int64_t)d * BS], is_f16);
   }
   for (int d = 0; d < D; d++) o[d] = (float)(acc[d] / sum);
 }
@@ -196,15 +206,15 @@ static void attend_row(float *o, const uint16_t *qp, const uint16_t *k_cache,
  * fp64 rounding.  The Metal kernel's "+1e-6" in the normaliser and its
  * rounding of P to the storage type are deliberately not reproduced.
  * Output: fp32 [total_q, Hq, D].  cu_q_lens == NULL means one query/seq.   */
-void oracle_paged_attention_varlen(float *out, const uint16_t *q,
-                                   const uint16_t *k_cache,
-                                   const uint16_t *v_cache,
-                                   const int32_t *block_tables,
-                                   const int32_t *context_lens,
-                                   const int32_t *cu_q_lens, int S, int Hq,
-                                   int Hkv, int D, int BS, int MB,
-                                   int64_t q_stride, float scale,
-                                   float softcap) {
+void oracle_paged_attention_varlen_dt(float *out, const uint16_t *q,
+                                      const uint16_t *k_cache,
+                                      const uint16_t *v_cache,
+                                      const int32_t *block_tables,
+                                      const int32_t *context_lens,
+                                      const int32_t *cu_q_lens, int S, int Hq,
+                                      int Hkv, int D, int BS, int MB,
+                                      int64_t q_stride, float scale,
+                                      float softcap, int is_f16) {
   const int G = Hq / Hkv;
 #pragma omp parallel for collapse(2) schedule(dynamic, 1)
   for (int s = 0; s < S; s++) {
@@ -219,25 +229,38 @@ void oracle_paged_attention_varlen(float *out, const uint16_t *q,
         attend_row(out + ((int64_t)(q0 + j) * Hq + hq) * D,
                    q + (int64_t)(q0 + j) * q_stride + (int64_t)hq * D, k_cache,
                    v_cache, table, kv_len - q_len + j + 1, hq / G, Hkv, D, BS,
-                   scale, softcap, logit, acc);
+                   scale, softcap, logit, acc, is_f16);
       free(logit);
       free(acc);
     }
   }
+}
+/* bf16 inputs (cache dtype 1). */
+void oracle_paged_attention_varlen(float *out, const uint16_t *q,
+                                   const uint16_t *k_cache,
+                                   const uint16_t *v_cache,
+                                   const int32_t *block_tables,
+                                   const int32_t *context_lens,
+                                   const int32_t *cu_q_lens, int S, int Hq,
+                                   int Hkv, int D, int BS, int MB,
+                                   int64_t q_stride, float scale,
+                                   float softcap) {
+  oracle_paged_attention_varlen_dt(out, q, k_cache, v_cache, block_tables, context_lens, cu_q_lens,
+                                   S, Hq, Hkv, D, BS, MB, q_stride, scale, softcap, 0);
 }
 
 /* The same oracle restricted to a list of output rows, for spot checks at
  * sizes where the full result would take hours on a CPU.  rows = n_rows
  * triples (sequence, query index within the sequence, query head); out is
  * [n_rows, D] fp32 in list order.                                           */
-void oracle_paged_attention_rows(float *out, const int32_t *rows, int n_rows,
-                                 const uint16_t *q, const uint16_t *k_cache,
-                                 const uint16_t *v_cache,
-                                 const int32_t *block_tables,
-                                 const int32_t *context_lens,
-                                 const int32_t *cu_q_lens, int Hq, int Hkv,
-                                 int D, int BS, int MB, int64_t q_stride,
-                                 float scale, float softcap) {
+void oracle_paged_attention_rows_dt(float *out, const int32_t *rows, int n_rows,
+                                    const uint16_t *q, const uint16_t *k_cache,
+                                    const uint16_t *v_cache,
+                                    const int32_t *block_tables,
+                                    const int32_t *context_lens,
+                                    const int32_t *cu_q_lens, int Hq, int Hkv,
+                                    int D, int BS, int MB, int64_t q_stride,
+                                    float scale, float softcap, int is_f16) {
   const int G = Hq / Hkv;
 #pragma omp parallel for schedule(dynamic, 1)
   for (int r = 0; r < n_rows; r++) {
@@ -249,10 +272,21 @@ void oracle_paged_attention_rows(float *out, const int32_t *rows, int n_rows,
     double *acc = (double *)malloc(sizeof(double) * (size_t)D);
     attend_row(out + (int64_t)r * D, q + (int64_t)(q0 + j) * q_stride + (int64_t)hq * D,
                k_cache, v_cache, block_tables + (int64_t)s * MB,
-               kv_len - q_len + j + 1, hq / G, Hkv, D, BS, scale, softcap, logit, acc);
+               kv_len - q_len + j + 1, hq / G, Hkv, D, BS, scale, softcap, logit, acc, is_f16);
     free(logit);
     free(acc);
   }
+}
+void oracle_paged_attention_rows(float *out, const int32_t *rows, int n_rows,
+                                 const uint16_t *q, const uint16_t *k_cache,
+                                 const uint16_t *v_cache,
+                                 const int32_t *block_tables,
+                                 const int32_t *context_lens,
+                                 const int32_t *cu_q_lens, int Hq, int Hkv,
+                                 int D, int BS, int MB, int64_t q_stride,
+                                 float scale, float softcap) {
+  oracle_paged_attention_rows_dt(out, rows, n_rows, q, k_cache, v_cache, block_tables, context_lens,
+                                 cu_q_lens, Hq, Hkv, D, BS, MB, q_stride, scale, softcap, 0);
 }
 
 /* Dense causal attention over contiguous K/V ([S][kv_len][Hkv][D] packed with

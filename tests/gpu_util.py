@@ -4,12 +4,12 @@ import numpy as np
 import torch
 
 import paged_attn_b200 as pa
-from pa_testlib import BS, CANARY, D, X, bf16_to_f32
+from pa_testlib import BS, CANARY, D, X, bf16_to_f32, elems_to_f32
 
 
-def to_dev(bits: np.ndarray) -> torch.Tensor:
-    """uint16 bf16 bit patterns -> bf16 tensor on the device."""
-    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+def to_dev(bits: np.ndarray, f16: bool = False) -> torch.Tensor:
+    """uint16 bit patterns -> bf16 (or f16) tensor on the device."""
+    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.float16 if f16 else torch.bfloat16)
 
 
 def to_bits(t: torch.Tensor) -> np.ndarray:
@@ -32,13 +32,14 @@ class DeviceCase:
 
     def __init__(self, case, k_pool=None, v_pool=None):
         self.case = case
-        self.k_pool = to_dev(case.k_pool if k_pool is None else k_pool)
-        self.v_pool = to_dev(case.v_pool if v_pool is None else v_pool)
-        self.cache = pa.PagedCache(BS, case.NB, D, case.Hkv, key_pools=[self.k_pool],
-                                   value_pools=[self.v_pool])
-        self.q = to_dev(case.q)
-        self.k_new = to_dev(case.k_new)
-        self.v_new = to_dev(case.v_new)
+        f16 = getattr(case, "f16", False)
+        self.k_pool = to_dev(case.k_pool if k_pool is None else k_pool, f16)
+        self.v_pool = to_dev(case.v_pool if v_pool is None else v_pool, f16)
+        self.cache = pa.PagedCache(BS, case.NB, D, case.Hkv, dtype=0 if f16 else 1,
+                                   key_pools=[self.k_pool], value_pools=[self.v_pool])
+        self.q = to_dev(case.q, f16)
+        self.k_new = to_dev(case.k_new, f16)
+        self.v_new = to_dev(case.v_new, f16)
         self.slots = torch.from_numpy(case.slot_mapping).cuda()
         self.tables = torch.from_numpy(case.block_tables).cuda()
         self.lens = torch.from_numpy(case.kv_lens).cuda()
@@ -54,8 +55,9 @@ class DeviceCase:
 
     def attend(self, varlen=True, softcap=1.0):
         c = self.case
-        out = torch.full((max(c.total_q, 1), c.Hq, D), float("nan"), dtype=torch.bfloat16,
-                         device="cuda")
+        f16 = getattr(c, "f16", False)
+        out = torch.full((max(c.total_q, 1), c.Hq, D), float("nan"),
+                         dtype=torch.float16 if f16 else torch.bfloat16, device="cuda")
         if varlen:
             self.cache.varlen(out, self.q, self.tables, self.lens, c.cu_q, c.S, c.Hq, c.MB,
                               c.scale, self.ws, self.ws_bytes, softcap=softcap)
@@ -64,4 +66,4 @@ class DeviceCase:
                               self.ws, self.ws_bytes, softcap=softcap)
         torch.cuda.synchronize()
         self.cache.check_errors()
-        return bf16_to_f32(to_bits(out))[:c.total_q]
+        return elems_to_f32(to_bits(out), f16)[:c.total_q]

@@ -7,10 +7,10 @@ division, scores*scale, softmax, @V.  Multi-token sequences add the causal limit
 kv_len - q_len + j + 1.  It shares no index arithmetic with oracle/paged_oracle.c."""
 import numpy as np
 
-from pa_testlib import BS, D, X, bf16_to_f32
+from pa_testlib import BS, D, X, elems_to_f32
 
 
-def gather_sequence(k_pool, v_pool, table_row, kv_len):
+def gather_sequence(k_pool, v_pool, table_row, kv_len, f16=False):
     nb = (kv_len + BS - 1) // BS
     blocks = table_row[:nb]
     k = k_pool[blocks]                                  # [nb, Hkv, D/X, BS, X]
@@ -19,13 +19,13 @@ def gather_sequence(k_pool, v_pool, table_row, kv_len):
     v = v_pool[blocks]                                  # [nb, Hkv, D, BS]
     v = v.transpose(1, 0, 2, 3).transpose(0, 1, 3, 2)   # [Hkv, nb, BS, D]
     v = v.reshape(v.shape[0], nb * BS, D)[:, :kv_len]
-    return bf16_to_f32(np.ascontiguousarray(k)).astype(np.float64), \
-        bf16_to_f32(np.ascontiguousarray(v)).astype(np.float64)
+    return elems_to_f32(np.ascontiguousarray(k), f16).astype(np.float64), \
+        elems_to_f32(np.ascontiguousarray(v), f16).astype(np.float64)
 
 
 def paged_attention(q_bits, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv, scale,
-                    softcap=1.0):
-    q = bf16_to_f32(q_bits).astype(np.float64)
+                    softcap=1.0, f16=False):
+    q = elems_to_f32(q_bits, f16).astype(np.float64)
     out = np.zeros(q.shape, dtype=np.float64)
     G = Hq // Hkv
     for s in range(len(kv_lens)):
@@ -33,7 +33,7 @@ def paged_attention(q_bits, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv
         q0, q1 = int(cu_q[s]), int(cu_q[s + 1])
         if kv_len == 0 or q1 == q0:
             continue
-        k, v = gather_sequence(k_pool, v_pool, block_tables[s], kv_len)
+        k, v = gather_sequence(k_pool, v_pool, block_tables[s], kv_len, f16)
         for j in range(q1 - q0):
             n = kv_len - (q1 - q0) + j + 1
             if n <= 0:

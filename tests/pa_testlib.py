@@ -45,6 +45,9 @@ def oracle() -> C.CDLL:
     lib.oracle_paged_attention_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                                   i32, i32, i64, f32, f32]
     lib.oracle_paged_attention_varlen.restype = None
+    lib.oracle_paged_attention_varlen_dt.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                                     i32, i32, i64, f32, f32, i32]
+    lib.oracle_paged_attention_varlen_dt.restype = None
     lib.oracle_paged_attention_rows.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32,
                                                 i32, i32, i64, f32, f32]
     lib.oracle_paged_attention_rows.restype = None
@@ -89,12 +92,22 @@ def normal_bf16(shape, seed: int, stream: int) -> np.ndarray:
     return out
 
 
+def normal_f16(shape, seed: int, stream: int) -> np.ndarray:
+    """The same seeded values as f16 bit patterns (bf16 values are exact in f16 here)."""
+    return bf16_to_f32(normal_bf16(shape, seed, stream)).astype(np.float16).view(np.uint16)
+
+
+def elems_to_f32(bits: np.ndarray, f16: bool) -> np.ndarray:
+    return bits.view(np.float16).astype(np.float32) if f16 else bf16_to_f32(bits)
+
+
 # ---- case construction ---------------------------------------------------------------
 class Case:
     """One seeded workload: pool pre-filled with every sequence's prefix, the
     step's new tokens and queries held apart for the code under test."""
 
-    def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True):
+    def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True, f16=False):
+        self.f16 = f16
         self.S = len(kv_lens)
         self.Hq, self.Hkv, self.NB = Hq, Hkv, NB
         self.G = Hq // Hkv
@@ -116,12 +129,13 @@ class Case:
             pos += nblk[s]
         self.scale = 1.0 / math.sqrt(D)
         # tensors
-        self.q = normal_bf16((self.total_q, Hq, D), seed, 1)
+        gen = normal_f16 if f16 else normal_bf16
+        self.q = gen((self.total_q, Hq, D), seed, 1)
         tot_kv = int(self.kv_lens.sum())
         self.cu_kv = np.zeros(self.S + 1, dtype=np.int32)
         self.cu_kv[1:] = np.cumsum(self.kv_lens)
-        self.k_all = normal_bf16((tot_kv, Hkv, D), seed, 2)  # every token of every sequence
-        self.v_all = normal_bf16((tot_kv, Hkv, D), seed, 3)
+        self.k_all = gen((tot_kv, Hkv, D), seed, 2)  # every token of every sequence
+        self.v_all = gen((tot_kv, Hkv, D), seed, 3)
         slots_all = np.empty(tot_kv, dtype=np.int64)
         is_new = np.zeros(tot_kv, dtype=bool)
         for s in range(self.S):
@@ -158,10 +172,10 @@ def write_oracle(k_pool, v_pool, key, value, slots, Hkv, key_stride=None, value_
 def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np.ndarray:
     out = np.zeros((case.total_q, case.Hq, D), dtype=np.float32)
     cu = p(case.cu_q) if varlen else None
-    oracle().oracle_paged_attention_varlen(p(out), p(case.q), p(k_pool), p(v_pool),
-                                           p(case.block_tables), p(case.kv_lens), cu, case.S,
-                                           case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
-                                           case.scale, softcap)
+    oracle().oracle_paged_attention_varlen_dt(p(out), p(case.q), p(k_pool), p(v_pool),
+                                              p(case.block_tables), p(case.kv_lens), cu, case.S,
+                                              case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
+                                              case.scale, softcap, int(case.f16))
     return out
 
 

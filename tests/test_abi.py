@@ -50,7 +50,7 @@ def test_version_and_error_string():
     ("head_size", 100, 1),      # head 100 rejected
     ("num_blocks", 0, 1),
     ("dtype", 7, 1),
-    ("dtype", 0, 2),            # f16 accepted by the reference, not built here
+    ("dtype", 2, 2),            # f32 accepted by the reference, not built here
     ("block_size", 32, 2),      # valid in the reference, not built here
     ("head_size", 64, 2),
 ])

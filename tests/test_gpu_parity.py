@@ -81,6 +81,19 @@ def test_decode_wide_table_and_row_strides(cuda_device):
     assert (outs[:, case.Hq * D:] == 0).all(), "wrote outside the output rows"
 
 
+@pytest.mark.parametrize("kv,ql,Hq,Hkv", [
+    ([1, 15, 16, 17, 100, 4097, 700], [1] * 7, 32, 8),          # decode
+    ([37, 70, 21, 2000], [5, 5, 1, 3], 16, 4),                  # verify-shaped
+    ([640 + 200, 333, 77], [200, 333, 77], 32, 8),              # prefill chunks (tcgen05 path)
+])
+def test_f16_cache(cuda_device, kv, ql, Hq, Hkv):
+    # The reference's default cache dtype is f16 (dtype code 0,
+    # crates/mlx-core/src/transformer/paged_attention.rs:85-92).
+    case = Case(kv, ql, Hq, Hkv, 512, seed=90, f16=True)
+    got, ref = run_case(case)
+    print("f16", check_attention(got, ref, "f16 cache"))
+
+
 def test_write_edges(cuda_device):
     # negative slots skipped, ragged token count, untouched slots unchanged
     Hkv, NB, T = 8, 64, 37

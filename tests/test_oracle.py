@@ -167,3 +167,11 @@ def test_numpy_reference_agrees_on_random_case():
     ref = numpy_reference.paged_attention(case.q, k_pool, v_pool, case.block_tables, case.kv_lens,
                                           case.cu_q, case.Hq, case.Hkv, case.scale)
     np.testing.assert_allclose(attention_oracle(case, k_pool, v_pool), ref, rtol=0, atol=2e-6)
+
+
+def test_f16_inputs_against_numpy_reference():
+    case = Case([70, 33, 16, 5], [3, 1, 16, 5], 8, 2, 16, seed=23, f16=True)
+    k_pool, v_pool = case.pools_after_write()
+    ref = numpy_reference.paged_attention(case.q, k_pool, v_pool, case.block_tables, case.kv_lens,
+                                          case.cu_q, case.Hq, case.Hkv, case.scale, f16=True)
+    np.testing.assert_allclose(attention_oracle(case, k_pool, v_pool), ref, rtol=0, atol=2e-6)
