@@ -166,6 +166,32 @@ pa_status pa_copy_blocks(PagedAttnCache *cache, uint32_t layer_idx,
                          const int64_t *block_mapping, int64_t num_pairs,
                          void *cuda_stream);
 
+/* ---- swapping blocks to host memory ------------------------------------------
+ * CpuBlockCache + swap_out / swap_in of crates/mlx-paged-attn/src/metal/
+ * swap_blocks.rs:15-252 (PagedKVCache::swap_out / swap_in / create_cpu_cache,
+ * paged_kv_cache.rs:1542-1648).  The host copies live in pinned, device-mapped
+ * memory owned by the PaCpuBlockCache; one kernel moves all requested blocks of a
+ * layer over PCIe in each direction.  Like the reference, both calls return when the
+ * copy has completed, swap_out skips blocks that are already swapped, swap_in fails
+ * on a block that is not in the host cache ("Block N not found in CPU cache") and
+ * drops the host copies it restored.                                              */
+typedef struct PaCpuBlockCache PaCpuBlockCache;
+PaCpuBlockCache *pa_cpu_cache_create(const PagedAttnCache *cache);
+void pa_cpu_cache_free(PaCpuBlockCache *cpu);
+int32_t pa_cpu_cache_is_swapped(const PaCpuBlockCache *cpu, uint32_t block_id);
+size_t pa_cpu_cache_num_swapped(const PaCpuBlockCache *cpu);
+/* Host addresses of a swapped block's K and V bytes (borrowed), or PA_ERR_INVALID_ARG. */
+pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t block_id, void **key,
+                                  void **value);
+pa_status pa_swap_out(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *block_ids,
+                      size_t num_blocks, PaCpuBlockCache *cpu, void *cuda_stream);
+pa_status pa_swap_in(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *block_ids,
+                     size_t num_blocks, PaCpuBlockCache *cpu, void *cuda_stream);
+/* SwapBlocksParams::key_block_size / value_block_size (swap_blocks.rs:53-108):
+ * bytes of one block of one layer; use_fp8 halves them.                           */
+void pa_swap_block_bytes(uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                         int32_t use_fp8, uint64_t *key_bytes, uint64_t *value_bytes);
+
 /* Scratch the attention calls need, for any batch on this cache's device
  * (it depends only on the device's SM count and the head size).               */
 size_t pa_attention_workspace_bytes(const PagedAttnCache *cache);

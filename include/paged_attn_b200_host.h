@@ -193,6 +193,58 @@ void pa_sched_stats(const PaScheduler *s, PaSchedulerStats *out);
 /* 1 / 0 for a running sequence's prefill flag, -1 if it is not running */
 int32_t pa_sched_running_is_prefill(const PaScheduler *s, uint32_t seq_id);
 
+/* ---- hybrid scheduler: chunked prefill + speculative verify + decode in one batch ----
+ * No counterpart in the reference: its scheduler runs a whole prompt in one step and
+ * says chunked prefill is future work (scheduler.rs:237-242).  This one emits the mixed
+ * batches pa_paged_attention_varlen takes.  Per step and sequence: kind 0 = prefill
+ * chunk, 1 = decode (one token), 2 = verify (last token + draft tokens); q_len new
+ * tokens whose K/V the step writes at positions [kv_len - q_len, kv_len).           */
+typedef struct PaHybridConfig {
+  uint32_t max_batch_size, max_tokens_per_step, prefill_chunk_size, max_prefill_per_step;
+  uint32_t prioritize_decode, eos_token_id;
+} PaHybridConfig;
+void pa_hybrid_config_default(PaHybridConfig *out);
+typedef struct PaHybridScheduler PaHybridScheduler;
+PaHybridScheduler *pa_hybrid_create(uint32_t block_size, const PaHybridConfig *cfg_or_null);
+void pa_hybrid_destroy(PaHybridScheduler *s);
+void pa_hybrid_add_request(PaHybridScheduler *s, const char *request_id, const uint32_t *prompt_tokens,
+                           size_t n, uint32_t max_new_tokens, int32_t priority);
+/* draft tokens to verify at the sequence's next decode step */
+pa_status pa_hybrid_set_draft_tokens(PaHybridScheduler *s, uint32_t seq_id, const uint32_t *tokens, size_t n);
+/* returns the number of sequences in the batch (0 = nothing to run); the batch stays
+ * readable until the next call                                                       */
+uint32_t pa_hybrid_schedule_step(PaHybridScheduler *s, PaKvHost *kv);
+typedef struct PaHybridTotals {
+  uint32_t total_tokens, num_prefill, num_decode, num_verify;
+} PaHybridTotals;
+void pa_hybrid_batch_totals(const PaHybridScheduler *s, PaHybridTotals *out);
+pa_status pa_hybrid_batch_entry(const PaHybridScheduler *s, uint32_t i, uint32_t *seq_id, int32_t *kind,
+                                uint32_t *q_len, uint32_t *kv_len, int32_t *needs_sample);
+uint32_t pa_hybrid_batch_tokens(const PaHybridScheduler *s, uint32_t i, uint32_t *out, size_t cap);
+const char *pa_hybrid_batch_request_id(const PaHybridScheduler *s, uint32_t i);
+/* kernel arguments of the current batch: int32 tables [n, max_blocks_per_seq] zero
+ * padded, int32 context lens [n] (counting this step's tokens), int32 cu_q_lens [n+1],
+ * int64 slots [total_tokens]                                                          */
+pa_status pa_hybrid_batch_metadata(const PaHybridScheduler *s, const PaKvHost *kv, int32_t *block_tables,
+                                   int32_t *context_lens, int32_t *cu_q_lens, int64_t *slots,
+                                   size_t slots_cap, uint32_t *max_context_len);
+/* one record per entry with needs_sample: accepted draft tokens and the token sampled
+ * after them                                                                          */
+pa_status pa_hybrid_process_outputs(PaHybridScheduler *s, PaKvHost *kv, const uint32_t *seq_ids,
+                                    const uint32_t *num_accepted, const uint32_t *next_tokens,
+                                    const uint8_t *is_eos, size_t n);
+uint32_t pa_hybrid_take_completed(PaHybridScheduler *s);
+const char *pa_hybrid_completed_request_id(const PaHybridScheduler *s, uint32_t i);
+const char *pa_hybrid_completed_finish_reason(const PaHybridScheduler *s, uint32_t i);
+uint32_t pa_hybrid_completed_tokens(const PaHybridScheduler *s, uint32_t i, uint32_t *out, size_t cap,
+                                    uint32_t *total_tokens);
+int32_t pa_hybrid_is_empty(const PaHybridScheduler *s);
+uint32_t pa_hybrid_num_waiting(const PaHybridScheduler *s);
+uint32_t pa_hybrid_num_running(const PaHybridScheduler *s);
+/* truncate_sequence: drop the tail of a sequence, releasing emptied blocks (used for
+ * rejected draft tokens)                                                              */
+pa_status pa_kv_truncate_sequence(PaKvHost *kv, uint32_t seq_id, uint32_t new_num_tokens);
+
 #ifdef __cplusplus
 }
 #endif

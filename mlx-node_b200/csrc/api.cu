@@ -7,6 +7,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/paged_attn_b200.h"
@@ -321,6 +322,146 @@ pa_status pa_copy_blocks(PagedAttnCache *c, uint32_t layer, const int64_t *mappi
                                  c->cfg.num_blocks, c->err_dev,
                                  static_cast<cudaStream_t>(cuda_stream)));
   return PA_OK;
+}
+
+/* ---- swap ------------------------------------------------------------------------ */
+}  // extern "C"
+
+// Host copies of swapped blocks: slabs of pinned, device-mapped memory cut into
+// (K, V) slots; a free list; and a pinned argument area the swap kernel reads.
+struct PaCpuBlockCache {
+  int device = 0;
+  size_t block_bytes = 0;  // bytes of one block's K (== V) for one layer
+  static constexpr int kSlotsPerSlab = 64;
+  static constexpr int kMaxPerLaunch = 4096;
+  std::vector<char *> slabs;
+  std::vector<char *> free_slots;                    // each slot = K bytes then V bytes
+  std::unordered_map<uint32_t, char *> swapped;      // block id -> slot
+  char *args = nullptr;                              // pinned: ids | host_k ptrs | host_v ptrs
+};
+
+namespace {
+pa_status cpu_slot(PaCpuBlockCache *cpu, char **slot) {
+  if (cpu->free_slots.empty()) {
+    char *slab = nullptr;
+    PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&slab),
+                          2 * cpu->block_bytes * PaCpuBlockCache::kSlotsPerSlab,
+                          cudaHostAllocMapped | cudaHostAllocPortable));
+    cpu->slabs.push_back(slab);
+    for (int i = PaCpuBlockCache::kSlotsPerSlab - 1; i >= 0; i--)
+      cpu->free_slots.push_back(slab + (size_t)i * 2 * cpu->block_bytes);
+  }
+  *slot = cpu->free_slots.back();
+  cpu->free_slots.pop_back();
+  return PA_OK;
+}
+}  // namespace
+
+extern "C" {
+
+PaCpuBlockCache *pa_cpu_cache_create(const PagedAttnCache *c) {
+  if (!c) {
+    fail(PA_ERR_INVALID_ARG, "cache is null");
+    return nullptr;
+  }
+  PaCpuBlockCache *cpu = new (std::nothrow) PaCpuBlockCache();
+  if (!cpu) return nullptr;
+  cpu->device = c->device;
+  cpu->block_bytes = (size_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2;
+  return cpu;
+}
+void pa_cpu_cache_free(PaCpuBlockCache *cpu) {
+  if (!cpu) return;
+  DeviceGuard g(cpu->device);
+  for (char *s : cpu->slabs) cudaFreeHost(s);
+  if (cpu->args) cudaFreeHost(cpu->args);
+  delete cpu;
+}
+int32_t pa_cpu_cache_is_swapped(const PaCpuBlockCache *cpu, uint32_t id) {
+  return cpu && cpu->swapped.count(id) != 0;
+}
+size_t pa_cpu_cache_num_swapped(const PaCpuBlockCache *cpu) { return cpu ? cpu->swapped.size() : 0; }
+pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t id, void **key, void **value) {
+  if (!cpu || !key || !value) return fail(PA_ERR_INVALID_ARG, "null argument");
+  auto it = cpu->swapped.find(id);
+  if (it == cpu->swapped.end())
+    return fail(PA_ERR_INVALID_ARG, "Block " + std::to_string(id) + " not found in CPU cache");
+  *key = it->second;
+  *value = it->second + cpu->block_bytes;
+  return PA_OK;
+}
+void pa_swap_block_bytes(uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size, int32_t use_fp8,
+                         uint64_t *key_bytes, uint64_t *value_bytes) {
+  const uint64_t n = (uint64_t)num_kv_heads * head_size * block_size * (use_fp8 ? 1 : 2);
+  if (key_bytes) *key_bytes = n;
+  if (value_bytes) *value_bytes = n;
+}
+
+static pa_status swap_impl(PagedAttnCache *c, uint32_t layer, const uint32_t *ids, size_t n,
+                           PaCpuBlockCache *cpu, void *cuda_stream, bool to_host) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (!cpu) return fail(PA_ERR_INVALID_ARG, "cpu cache is null");
+  if (n == 0) return PA_OK;
+  if (!ids) return fail(PA_ERR_INVALID_ARG, "block_ids is null");
+  if (cpu->device != c->device ||
+      cpu->block_bytes != (size_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2)
+    return fail(PA_ERR_INVALID_ARG, "cpu cache was created for a different cache geometry");
+  DeviceGuard g(c->device);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  constexpr int kMax = PaCpuBlockCache::kMaxPerLaunch;
+  if (!cpu->args)
+    PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&cpu->args), (size_t)kMax * (4 + 8 + 8),
+                          cudaHostAllocMapped | cudaHostAllocPortable));
+  uint32_t *a_ids = reinterpret_cast<uint32_t *>(cpu->args);
+  char **a_k = reinterpret_cast<char **>(cpu->args + (size_t)kMax * 4);
+  char **a_v = a_k + kMax;
+  if (!to_host)  // every block must have a host copy before anything moves
+    for (size_t i = 0; i < n; i++)
+      if (!cpu->swapped.count(ids[i]))
+        return fail(PA_ERR_INVALID_ARG, "Block " + std::to_string(ids[i]) + " not found in CPU cache");
+  for (size_t base = 0; base < n; base += kMax) {
+    int m = 0;
+    for (size_t i = base; i < n && i < base + kMax; i++) {
+      const uint32_t id = ids[i];
+      if (id >= c->cfg.num_blocks) return fail(PA_ERR_OUT_OF_RANGE, "block id beyond num_blocks");
+      char *slot = nullptr;
+      if (to_host) {
+        if (cpu->swapped.count(id)) continue;  // already swapped out
+        st = cpu_slot(cpu, &slot);
+        if (st != PA_OK) return st;
+        cpu->swapped[id] = slot;
+      } else {
+        slot = cpu->swapped[id];
+      }
+      a_ids[m] = id;
+      a_k[m] = slot;
+      a_v[m] = slot + cpu->block_bytes;
+      m++;
+    }
+    PA_CUDA(pa::launch_swap_blocks(static_cast<pa::elem16 *>(c->k[layer]),
+                                   static_cast<pa::elem16 *>(c->v[layer]), a_ids, a_k, a_v, m,
+                                   (int64_t)cpu->block_bytes, to_host ? 1 : 0, c->cfg.num_blocks,
+                                   c->err_dev, stream));
+    PA_CUDA(cudaStreamSynchronize(stream));  // the argument area is reused; the reference blocks too
+  }
+  if (!to_host)
+    for (size_t i = 0; i < n; i++) {
+      auto it = cpu->swapped.find(ids[i]);
+      if (it != cpu->swapped.end()) {
+        cpu->free_slots.push_back(it->second);
+        cpu->swapped.erase(it);
+      }
+    }
+  return PA_OK;
+}
+pa_status pa_swap_out(PagedAttnCache *c, uint32_t layer, const uint32_t *ids, size_t n,
+                      PaCpuBlockCache *cpu, void *stream) {
+  return swap_impl(c, layer, ids, n, cpu, stream, true);
+}
+pa_status pa_swap_in(PagedAttnCache *c, uint32_t layer, const uint32_t *ids, size_t n,
+                     PaCpuBlockCache *cpu, void *stream) {
+  return swap_impl(c, layer, ids, n, cpu, stream, false);
 }
 
 size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {

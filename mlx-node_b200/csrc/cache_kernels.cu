@@ -138,4 +138,42 @@ cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
   return cudaGetLastError();
 }
 
+// Swap: one CTA per (block, 4 KB piece), 16 bytes per thread, K then V.  The host side
+// of each block is pinned memory mapped into the device's address space, so the kernel
+// itself moves the bytes over PCIe (one launch for any number of blocks).
+__global__ void __launch_bounds__(256)
+swap_blocks_kernel(elem16 *__restrict__ k_pool, elem16 *__restrict__ v_pool,
+                   const uint32_t *__restrict__ ids, char *const *__restrict__ host_k,
+                   char *const *__restrict__ host_v, int64_t bytes_per_block, int to_host,
+                   uint32_t num_blocks, unsigned *err) {
+  const uint32_t id = ids[blockIdx.x];
+  if (id >= num_blocks) {
+    if (threadIdx.x == 0) atomicOr(err, kErrBlockRange);
+    return;
+  }
+  const int64_t piece = (int64_t)blockIdx.y * 4096 + threadIdx.x * 16;
+  if (piece >= bytes_per_block) return;
+  char *kd = reinterpret_cast<char *>(k_pool) + (int64_t)id * bytes_per_block + piece;
+  char *vd = reinterpret_cast<char *>(v_pool) + (int64_t)id * bytes_per_block + piece;
+  char *kh = host_k[blockIdx.x] + piece, *vh = host_v[blockIdx.x] + piece;
+  if (to_host) {
+    *reinterpret_cast<uint4 *>(kh) = *reinterpret_cast<const uint4 *>(kd);
+    *reinterpret_cast<uint4 *>(vh) = *reinterpret_cast<const uint4 *>(vd);
+  } else {
+    *reinterpret_cast<uint4 *>(kd) = *reinterpret_cast<const uint4 *>(kh);
+    *reinterpret_cast<uint4 *>(vd) = *reinterpret_cast<const uint4 *>(vh);
+  }
+}
+
+cudaError_t launch_swap_blocks(elem16 *k_pool, elem16 *v_pool, const uint32_t *ids,
+                               char *const *host_k, char *const *host_v, int num, int64_t bytes_per_block,
+                               int to_host, uint32_t num_blocks, unsigned *err, cudaStream_t st) {
+  if (num <= 0) return cudaSuccess;
+  dim3 grid((unsigned)num, (unsigned)((bytes_per_block + 4095) / 4096));
+  swap_blocks_kernel<<<grid, 256, 0, st>>>(k_pool, v_pool, ids, host_k, host_v, bytes_per_block, to_host,
+                                           num_blocks, err);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
 }  // namespace pa

@@ -22,6 +22,13 @@ struct PaScheduler {
   PaScheduler(uint32_t bs, const SchedulerConfig &c) : s(bs, c) {}
 };
 
+struct PaHybridScheduler {
+  HybridScheduler s;
+  HybridBatch batch;
+  std::vector<CompletedSequence> done;
+  PaHybridScheduler(uint32_t bs, const HybridConfig &c) : s(bs, c) {}
+};
+
 namespace {
 pa_status err(const std::string &msg, pa_status code = PA_ERR_INVALID_ARG) { return pa::set_error(code, msg); }
 PagedAttentionConfig to_cfg(const PaHostConfig &c) {
@@ -402,6 +409,120 @@ void pa_sched_stats(const PaScheduler *s, PaSchedulerStats *out) {
 int32_t pa_sched_running_is_prefill(const PaScheduler *s, uint32_t seq_id) {
   const ActiveSequence *a = s ? s->s.running(seq_id) : nullptr;
   return a ? (a->is_prefill ? 1 : 0) : -1;
+}
+
+/* ---- hybrid scheduler ---- */
+void pa_hybrid_config_default(PaHybridConfig *out) {
+  if (!out) return;
+  const HybridConfig d;
+  *out = PaHybridConfig{d.max_batch_size, d.max_tokens_per_step, d.prefill_chunk_size, d.max_prefill_per_step,
+                        d.prioritize_decode ? 1u : 0u, d.eos_token_id};
+}
+PaHybridScheduler *pa_hybrid_create(uint32_t block_size, const PaHybridConfig *c) {
+  HybridConfig cfg;
+  if (c) {
+    cfg.max_batch_size = c->max_batch_size;
+    cfg.max_tokens_per_step = c->max_tokens_per_step;
+    cfg.prefill_chunk_size = c->prefill_chunk_size;
+    cfg.max_prefill_per_step = c->max_prefill_per_step;
+    cfg.prioritize_decode = c->prioritize_decode != 0;
+    cfg.eos_token_id = c->eos_token_id;
+  }
+  return new PaHybridScheduler(block_size, cfg);
+}
+void pa_hybrid_destroy(PaHybridScheduler *s) { delete s; }
+void pa_hybrid_add_request(PaHybridScheduler *s, const char *request_id, const uint32_t *tokens, size_t n,
+                           uint32_t max_new_tokens, int32_t priority) {
+  if (!s || !request_id) return;
+  PendingRequest r;
+  r.request_id = request_id;
+  if (tokens) r.prompt_tokens.assign(tokens, tokens + n);
+  r.max_new_tokens = max_new_tokens;
+  r.priority = priority;
+  s->s.add_request(std::move(r));
+}
+pa_status pa_hybrid_set_draft_tokens(PaHybridScheduler *s, uint32_t seq_id, const uint32_t *tokens, size_t n) {
+  if (!s || (n && !tokens)) return err("null argument");
+  return s->s.set_draft_tokens(seq_id, tokens, n) ? PA_OK : err("sequence is not running in decode");
+}
+uint32_t pa_hybrid_schedule_step(PaHybridScheduler *s, PaKvHost *kv) {
+  if (!s || !kv) return 0;
+  s->batch = HybridBatch();
+  std::string e;
+  if (!s->s.schedule_step(*kv->kv, &s->batch, &e)) return 0;
+  return (uint32_t)s->batch.entries.size();
+}
+void pa_hybrid_batch_totals(const PaHybridScheduler *s, PaHybridTotals *out) {
+  if (s && out)
+    *out = PaHybridTotals{s->batch.total_tokens, s->batch.num_prefill, s->batch.num_decode, s->batch.num_verify};
+}
+pa_status pa_hybrid_batch_entry(const PaHybridScheduler *s, uint32_t i, uint32_t *seq_id, int32_t *kind,
+                                uint32_t *q_len, uint32_t *kv_len, int32_t *needs_sample) {
+  if (!s || i >= s->batch.entries.size()) return err("batch index out of range");
+  const HybridEntry &e = s->batch.entries[i];
+  if (seq_id) *seq_id = e.seq_id;
+  if (kind) *kind = e.kind;
+  if (q_len) *q_len = e.q_len;
+  if (kv_len) *kv_len = e.kv_len;
+  if (needs_sample) *needs_sample = e.needs_sample ? 1 : 0;
+  return PA_OK;
+}
+uint32_t pa_hybrid_batch_tokens(const PaHybridScheduler *s, uint32_t i, uint32_t *out, size_t cap) {
+  if (!s || i >= s->batch.entries.size()) return 0;
+  return (uint32_t)copy_out(s->batch.entries[i].tokens, out, cap);
+}
+const char *pa_hybrid_batch_request_id(const PaHybridScheduler *s, uint32_t i) {
+  return (s && i < s->batch.entries.size()) ? s->batch.entries[i].request_id.c_str() : "";
+}
+pa_status pa_hybrid_batch_metadata(const PaHybridScheduler *s, const PaKvHost *kv, int32_t *tables,
+                                   int32_t *lens, int32_t *cu_q, int64_t *slots, size_t slots_cap,
+                                   uint32_t *max_ctx) {
+  if (!s || !kv || !tables || !lens || !cu_q || !slots) return err("null argument");
+  InputMetadata m;
+  std::vector<int32_t> cu;
+  std::string e;
+  if (!s->s.build_metadata(*kv->kv, s->batch, &m, &cu, &e)) return err(e);
+  if (m.slot_mappings.size() > slots_cap) return err("slot buffer too small");
+  copy_out(m.block_tables, tables, m.block_tables.size());
+  copy_out(m.context_lens, lens, m.context_lens.size());
+  copy_out(cu, cu_q, cu.size());
+  copy_out(m.slot_mappings, slots, slots_cap);
+  if (max_ctx) *max_ctx = m.max_context_len;
+  return PA_OK;
+}
+pa_status pa_hybrid_process_outputs(PaHybridScheduler *s, PaKvHost *kv, const uint32_t *seq_ids,
+                                    const uint32_t *num_accepted, const uint32_t *next_tokens,
+                                    const uint8_t *is_eos, size_t n) {
+  if (!s || !kv || (n && (!seq_ids || !next_tokens))) return err("null argument");
+  std::vector<HybridOutput> o;
+  for (size_t i = 0; i < n; i++)
+    o.push_back(HybridOutput{seq_ids[i], num_accepted ? num_accepted[i] : 0, next_tokens[i], is_eos && is_eos[i]});
+  std::string e;
+  if (!s->s.process_outputs(s->batch, o, *kv->kv, &e)) return err(e);
+  return PA_OK;
+}
+uint32_t pa_hybrid_take_completed(PaHybridScheduler *s) {
+  if (!s) return 0;
+  s->done = s->s.get_completed();
+  return (uint32_t)s->done.size();
+}
+const char *pa_hybrid_completed_request_id(const PaHybridScheduler *s, uint32_t i) {
+  return (s && i < s->done.size()) ? s->done[i].request_id.c_str() : "";
+}
+const char *pa_hybrid_completed_finish_reason(const PaHybridScheduler *s, uint32_t i) {
+  return (s && i < s->done.size()) ? s->done[i].finish_reason.c_str() : "";
+}
+uint32_t pa_hybrid_completed_tokens(const PaHybridScheduler *s, uint32_t i, uint32_t *out, size_t cap,
+                                    uint32_t *total) {
+  if (!s || i >= s->done.size()) return 0;
+  if (total) *total = s->done[i].total_tokens;
+  return (uint32_t)copy_out(s->done[i].generated_tokens, out, cap);
+}
+int32_t pa_hybrid_is_empty(const PaHybridScheduler *s) { return !s || s->s.is_empty(); }
+uint32_t pa_hybrid_num_waiting(const PaHybridScheduler *s) { return s ? s->s.num_waiting() : 0; }
+uint32_t pa_hybrid_num_running(const PaHybridScheduler *s) { return s ? s->s.num_running() : 0; }
+pa_status pa_kv_truncate_sequence(PaKvHost *kv, uint32_t seq_id, uint32_t n) {
+  KV_CALL(kv->kv->truncate_sequence(seq_id, n, &e));
 }
 
 }  // extern "C"

@@ -700,6 +700,231 @@ const ActiveSequence *ContinuousBatchingScheduler::running(uint32_t seq_id) cons
   return it == running_.end() ? nullptr : &it->second;
 }
 
+bool PagedKVCache::truncate_sequence(uint32_t seq_id, uint32_t new_num_tokens, std::string *error) {
+  SequenceBlockTable *t = table_.get(seq_id);
+  if (!t) {
+    *error = "Sequence " + std::to_string(seq_id) + " not found";
+    return false;
+  }
+  if (new_num_tokens > t->num_tokens()) {
+    *error = "truncate_sequence cannot grow a sequence";
+    return false;
+  }
+  const size_t keep = (new_num_tokens + cfg_.block_size - 1) / cfg_.block_size;
+  // rebuild the table with the kept blocks; release the rest
+  std::vector<BlockRef> blocks = t->blocks();
+  SequenceBlockTable fresh(seq_id, cfg_.block_size);
+  for (size_t i = 0; i < blocks.size(); i++) {
+    if (i < keep) {
+      fresh.add_block(blocks[i]);
+    } else {
+      if (blocks[i]->ref_count == 1) tracker_.remove_block(blocks[i]->block_id);
+      alloc_.free(blocks[i]);
+    }
+  }
+  fresh.set_num_tokens(new_num_tokens);
+  *t = fresh;
+  return true;
+}
+
+// ---- hybrid scheduler ------------------------------------------------------------------------------
+void HybridScheduler::add_request(PendingRequest r) {
+  auto pos = waiting_.begin();
+  while (pos != waiting_.end() && pos->priority >= r.priority) ++pos;
+  waiting_.insert(pos, std::move(r));
+}
+
+bool HybridScheduler::set_draft_tokens(uint32_t seq_id, const uint32_t *tokens, size_t n) {
+  auto it = running_.find(seq_id);
+  if (it == running_.end() || it->second.num_computed < it->second.prompt.size()) return false;
+  it->second.drafts.assign(tokens, tokens + n);
+  return true;
+}
+
+bool HybridScheduler::schedule_step(PagedKVCache &cache, HybridBatch *out, std::string *error) {
+  HybridBatch b;
+  size_t budget = cfg_.max_tokens_per_step;
+  auto add_decodes = [&]() -> bool {
+    for (auto &kv : running_) {
+      Seq &s = kv.second;
+      if (s.num_computed < s.prompt.size()) continue;  // still in prefill
+      if (b.entries.size() >= cfg_.max_batch_size) break;
+      uint32_t k = (uint32_t)s.drafts.size();
+      if (1 + k > budget) k = budget >= 1 ? (uint32_t)budget - 1 : 0;  // verify fewer drafts
+      if (budget < 1) break;
+      const uint32_t total = (uint32_t)(s.prompt.size() + s.generated.size());
+      if (k && !cache.extend_sequence(s.seq_id, k, error)) {
+        // pool exhausted: fall back to a plain decode step for this sequence
+        error->clear();
+        k = 0;
+      }
+      HybridEntry e;
+      e.seq_id = s.seq_id;
+      e.request_id = s.request_id;
+      e.kind = k ? kVerify : kDecode;
+      e.q_len = 1 + k;
+      e.kv_len = total + k;
+      e.needs_sample = true;
+      e.tokens.push_back(s.generated.back());
+      e.tokens.insert(e.tokens.end(), s.drafts.begin(), s.drafts.begin() + k);
+      s.drafts.resize(k);
+      budget -= e.q_len;
+      (k ? b.num_verify : b.num_decode)++;
+      b.entries.push_back(std::move(e));
+    }
+    return true;
+  };
+  auto add_prefills = [&]() {
+    // sequences already admitted and still in prefill, then new admissions
+    uint32_t in_prefill = 0;
+    auto chunk_for = [&](Seq &s) {
+      const uint32_t remaining = (uint32_t)s.prompt.size() - s.num_computed;
+      uint32_t chunk = cfg_.prefill_chunk_size ? std::min(remaining, cfg_.prefill_chunk_size) : remaining;
+      chunk = (uint32_t)std::min<size_t>(chunk, budget);
+      if (chunk == 0) return;
+      HybridEntry e;
+      e.seq_id = s.seq_id;
+      e.request_id = s.request_id;
+      e.kind = kPrefillChunk;
+      e.q_len = chunk;
+      e.kv_len = s.num_computed + chunk;
+      e.needs_sample = e.kv_len == s.prompt.size();
+      e.tokens.assign(s.prompt.begin() + s.num_computed, s.prompt.begin() + s.num_computed + chunk);
+      budget -= chunk;
+      b.num_prefill++;
+      b.entries.push_back(std::move(e));
+    };
+    for (auto &kv : running_) {
+      Seq &s = kv.second;
+      if (s.num_computed >= s.prompt.size()) continue;
+      if (b.entries.size() >= cfg_.max_batch_size || in_prefill >= cfg_.max_prefill_per_step || !budget) break;
+      chunk_for(s);
+      in_prefill++;
+    }
+    while (b.entries.size() < cfg_.max_batch_size && in_prefill < cfg_.max_prefill_per_step && budget &&
+           !waiting_.empty()) {
+      const PendingRequest &front = waiting_.front();
+      const uint32_t prompt_len = (uint32_t)front.prompt_tokens.size();
+      if (prompt_len == 0) {  // nothing to attend to: reject instead of looping
+        waiting_.pop_front();
+        continue;
+      }
+      if (!cache.can_allocate((prompt_len + block_size_ - 1) / block_size_)) break;
+      PendingRequest req = std::move(waiting_.front());
+      waiting_.pop_front();
+      uint32_t seq_id;
+      std::string err;
+      if (!cache.add_sequence(prompt_len, &seq_id, &err)) {
+        waiting_.push_front(std::move(req));
+        break;
+      }
+      Seq s;
+      s.seq_id = seq_id;
+      s.request_id = req.request_id;
+      s.prompt = std::move(req.prompt_tokens);
+      s.max_new_tokens = req.max_new_tokens;
+      auto ins = running_.emplace(seq_id, std::move(s));
+      chunk_for(ins.first->second);
+      in_prefill++;
+    }
+  };
+  if (cfg_.prioritize_decode) {
+    add_decodes();
+    add_prefills();
+  } else {
+    add_prefills();
+    add_decodes();
+  }
+  if (b.entries.empty()) return false;
+  b.total_tokens = 0;
+  for (const auto &e : b.entries) b.total_tokens += e.q_len;
+  *out = std::move(b);
+  return true;
+}
+
+bool HybridScheduler::build_metadata(const PagedKVCache &cache, const HybridBatch &batch, InputMetadata *meta,
+                                     std::vector<int32_t> *cu_q_lens, std::string *error) const {
+  InputMetadata m;
+  cu_q_lens->assign(1, 0);
+  const size_t mb = cache.max_blocks_per_seq();
+  bool all_prefill = true;
+  for (const HybridEntry &e : batch.entries) {
+    m.context_lens.push_back((int32_t)e.kv_len);
+    m.max_context_len = std::max(m.max_context_len, e.kv_len);
+    cu_q_lens->push_back(cu_q_lens->back() + (int32_t)e.q_len);
+    if (!cache.get_slot_mapping(e.seq_id, e.kv_len - e.q_len, e.q_len, &m.slot_mappings, error)) return false;
+    std::vector<std::vector<uint32_t>> t;
+    if (!cache.build_block_tables_batch(&e.seq_id, 1, &t, error)) return false;
+    if (t[0].size() > mb) {
+      *error = "sequence holds more blocks than max_seq_len allows";
+      return false;
+    }
+    for (uint32_t id : t[0]) m.block_tables.push_back((int32_t)id);
+    m.block_tables.insert(m.block_tables.end(), mb - t[0].size(), 0);
+    all_prefill = all_prefill && e.kind == kPrefillChunk;
+  }
+  m.is_prefill = all_prefill;
+  m.num_seqs = (uint32_t)batch.entries.size();
+  m.max_blocks_per_seq = (uint32_t)mb;
+  *meta = std::move(m);
+  return true;
+}
+
+bool HybridScheduler::process_outputs(const HybridBatch &batch, const std::vector<HybridOutput> &outputs,
+                                      PagedKVCache &cache, std::string *error) {
+  std::map<uint32_t, const HybridOutput *> by_seq;
+  for (const HybridOutput &o : outputs) by_seq[o.seq_id] = &o;
+  for (const HybridEntry &e : batch.entries) {
+    auto it = running_.find(e.seq_id);
+    if (it == running_.end()) continue;
+    Seq &s = it->second;
+    if (e.kind == kPrefillChunk) s.num_computed = e.kv_len;
+    if (!e.needs_sample) continue;
+    auto oi = by_seq.find(e.seq_id);
+    if (oi == by_seq.end()) {
+      *error = "no output for sequence " + std::to_string(e.seq_id);
+      return false;
+    }
+    const HybridOutput &o = *oi->second;
+    const uint32_t k = e.kind == kVerify ? e.q_len - 1 : 0;
+    const uint32_t a = std::min(o.num_accepted, k);
+    std::vector<uint32_t> fresh(s.drafts.begin(), s.drafts.begin() + a);
+    fresh.push_back(o.next_token);
+    s.drafts.clear();
+    bool stop = false, eos = false;
+    for (size_t i = 0; i < fresh.size(); i++) {
+      const uint32_t tok = fresh[i];
+      s.generated.push_back(tok);
+      const bool last = i + 1 == fresh.size();
+      if (tok == cfg_.eos_token_id || (last && o.is_eos)) { stop = eos = true; break; }
+      if (s.generated.size() >= s.max_new_tokens) { stop = true; break; }
+    }
+    // the pool must hold one slot per token of the sequence (the newest token's K/V is
+    // written by the next step): prompt + generated
+    const uint32_t want = (uint32_t)(s.prompt.size() + s.generated.size());
+    const uint32_t have = cache.sequence_num_tokens(e.seq_id);
+    if (want > have) {
+      if (!stop && !cache.extend_sequence(e.seq_id, want - have, error)) return false;
+    } else if (want < have) {
+      if (!cache.truncate_sequence(e.seq_id, want, error)) return false;
+    }
+    if (stop) {
+      const uint32_t gen = (uint32_t)s.generated.size();
+      completed_.push_back(CompletedSequence{s.request_id, std::move(s.generated), eos ? "stop" : "length",
+                                             (uint32_t)s.prompt.size() + gen});
+      running_.erase(it);
+      if (!cache.remove_sequence(e.seq_id, error)) return false;
+    }
+  }
+  return true;
+}
+
+std::vector<CompletedSequence> HybridScheduler::get_completed() {
+  std::vector<CompletedSequence> r;
+  r.swap(completed_);
+  return r;
+}
+
 // ---- kv_scale.rs:165-174 -------------------------------------------------------------------------
 float kv_compute_scale(float max_abs) { return max_abs < 1e-12f ? 1.0f : 448.0f / max_abs; }
 

@@ -213,6 +213,13 @@ class PagedKVCache {
   bool track_sequence_tokens(uint32_t seq_id, const uint32_t *tokens, size_t n, uint32_t start_pos,
                              std::string *error);
   bool get_sequence_tokens(uint32_t seq_id, std::vector<uint32_t> *out, std::string *error) const;
+  // Not in the reference: drop the tail of a sequence (rejected speculative tokens),
+  // releasing blocks that no longer hold a token.
+  bool truncate_sequence(uint32_t seq_id, uint32_t new_num_tokens, std::string *error);
+  uint32_t sequence_num_tokens(uint32_t seq_id) const {
+    const SequenceBlockTable *t = table_.get(seq_id);
+    return t ? t->num_tokens() : 0;
+  }
   TokenTracker &tracker() { return tracker_; }
   const TokenTracker &tracker() const { return tracker_; }
   BlockAllocator &allocator() { return alloc_; }
@@ -290,6 +297,74 @@ class ContinuousBatchingScheduler {
   std::map<uint32_t, ActiveSequence> running_;  // ordered by seq id: a deterministic batch order
   std::vector<CompletedSequence> completed_;
   SchedulerConfig cfg_;
+  uint32_t block_size_;
+};
+
+// ---- hybrid scheduler: chunked prefill + speculative verify + decode in one batch ----------
+// The reference scheduler runs a whole prompt in one step and has no multi-token decode
+// (scheduler.rs:237-242 says so).  This scheduler emits the mixed batches the variable-
+// length attention entry takes: per sequence q_len new tokens on top of its cached
+// prefix, with the slot mapping, context lengths (counting the new tokens) and
+// cu_q_lens the kernels need.  Ordering contract as in the reference: the step's K/V
+// are written first, then attention runs with context lengths that include them.
+struct HybridConfig {
+  uint32_t max_batch_size = 32;
+  uint32_t max_tokens_per_step = 4096;
+  uint32_t prefill_chunk_size = 1024;  // 0 = whole prompt in one step
+  uint32_t max_prefill_per_step = 1;   // sequences in prefill per step
+  bool prioritize_decode = true;
+  uint32_t eos_token_id = 151645;
+};
+enum HybridKind : int32_t { kPrefillChunk = 0, kDecode = 1, kVerify = 2 };
+struct HybridEntry {
+  uint32_t seq_id;
+  std::string request_id;
+  int32_t kind;
+  uint32_t q_len;    // new tokens this step
+  uint32_t kv_len;   // tokens in the pool after this step's write
+  bool needs_sample; // the caller samples after this step (false for a non-final prefill chunk)
+  std::vector<uint32_t> tokens;  // the q_len input tokens
+};
+struct HybridBatch {
+  std::vector<HybridEntry> entries;
+  uint32_t total_tokens = 0, num_prefill = 0, num_decode = 0, num_verify = 0;
+};
+struct HybridOutput {
+  uint32_t seq_id;
+  uint32_t num_accepted;  // accepted draft tokens (0 for prefill / plain decode)
+  uint32_t next_token;    // the token sampled after the accepted ones
+  bool is_eos;
+};
+class HybridScheduler {
+ public:
+  HybridScheduler(uint32_t block_size, const HybridConfig &cfg) : cfg_(cfg), block_size_(block_size) {}
+  void add_request(PendingRequest r);
+  // draft tokens to verify at the sequence's next decode step (consumed by it)
+  bool set_draft_tokens(uint32_t seq_id, const uint32_t *tokens, size_t n);
+  bool schedule_step(PagedKVCache &cache, HybridBatch *out, std::string *error);
+  // kernel arguments of the batch: tables [n, max_blocks_per_seq] zero padded, context
+  // lens [n], cu_q_lens [n+1], slots [total_tokens]
+  bool build_metadata(const PagedKVCache &cache, const HybridBatch &batch, InputMetadata *meta,
+                      std::vector<int32_t> *cu_q_lens, std::string *error) const;
+  bool process_outputs(const HybridBatch &batch, const std::vector<HybridOutput> &outputs, PagedKVCache &cache,
+                       std::string *error);
+  std::vector<CompletedSequence> get_completed();
+  bool is_empty() const { return waiting_.empty() && running_.empty(); }
+  uint32_t num_waiting() const { return (uint32_t)waiting_.size(); }
+  uint32_t num_running() const { return (uint32_t)running_.size(); }
+
+ private:
+  struct Seq {
+    uint32_t seq_id;
+    std::string request_id;
+    std::vector<uint32_t> prompt, generated, drafts;
+    uint32_t max_new_tokens;
+    uint32_t num_computed = 0;  // prompt tokens whose K/V are in the pool
+  };
+  std::deque<PendingRequest> waiting_;
+  std::map<uint32_t, Seq> running_;
+  std::vector<CompletedSequence> completed_;
+  HybridConfig cfg_;
   uint32_t block_size_;
 };
 

@@ -154,6 +154,11 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
 cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
                                const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
                                uint32_t num_blocks, unsigned *err, cudaStream_t st);
+// Block moves between the pools and per-block host (pinned, device-mapped) buffers.
+// to_host != 0: pool -> host.  ids/host_k/host_v are readable by the device.
+cudaError_t launch_swap_blocks(elem16 *k_pool, elem16 *v_pool, const uint32_t *ids,
+                               char *const *host_k, char *const *host_v, int num, int64_t bytes_per_block,
+                               int to_host, uint32_t num_blocks, unsigned *err, cudaStream_t st);
 // Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.
 cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st);
 size_t splitkv_workspace_bytes(int num_ctas);

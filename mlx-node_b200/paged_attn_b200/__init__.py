@@ -32,7 +32,9 @@ EXPORTED_SYMBOLS = [
     "pa_cache_create", "pa_cache_wrap", "pa_cache_free", "pa_cache_key_ptr", "pa_cache_value_ptr",
     "pa_cache_get_config", "pa_cache_check_errors", "pa_reshape_and_cache", "pa_copy_blocks",
     "pa_attention_workspace_bytes", "pa_paged_attention_decode", "pa_paged_attention_varlen",
-    "pa_paged_attention_decode_static",
+    "pa_paged_attention_decode_static", "pa_cpu_cache_create", "pa_cpu_cache_free",
+    "pa_cpu_cache_is_swapped", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
+    "pa_swap_in", "pa_swap_block_bytes",
     "pa_decode_step_host", "pa_kernel_launch_count",
 ]
 
@@ -88,6 +90,18 @@ def load_library() -> C.CDLL:
                                                      i64, f32, f32, vp]
     lib.pa_paged_attention_varlen.argtypes = [vp, u32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
                                               f32, f32, i32, vp, sz, vp]
+    lib.pa_cpu_cache_create.argtypes = [vp]
+    lib.pa_cpu_cache_create.restype = vp
+    lib.pa_cpu_cache_free.argtypes = [vp]
+    lib.pa_cpu_cache_free.restype = None
+    lib.pa_cpu_cache_is_swapped.argtypes = [vp, u32]
+    lib.pa_cpu_cache_num_swapped.argtypes = [vp]
+    lib.pa_cpu_cache_num_swapped.restype = sz
+    lib.pa_cpu_cache_block_ptrs.argtypes = [vp, u32, C.POINTER(vp), C.POINTER(vp)]
+    lib.pa_swap_out.argtypes = [vp, u32, C.POINTER(u32), sz, vp, vp]
+    lib.pa_swap_in.argtypes = [vp, u32, C.POINTER(u32), sz, vp, vp]
+    lib.pa_swap_block_bytes.argtypes = [u32, u32, u32, i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    lib.pa_swap_block_bytes.restype = None
     lib.pa_decode_step_host.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32]
     # tier 1
     lib.mlx_paged_attn_create_cache.argtypes = [C.POINTER(PagedAttnConfig)]
@@ -234,6 +248,18 @@ class PagedCache:
             out_stride or row, scale, softcap, max_context_len, _ptr(workspace), workspace_bytes,
             stream))
 
+    # -- swapping (PagedKVCache::create_cpu_cache / swap_out / swap_in) ----------------
+    def create_cpu_cache(self) -> "CpuBlockCache":
+        return CpuBlockCache(self)
+
+    def swap_out(self, block_ids, cpu: "CpuBlockCache", layer: int = 0, stream: int = 0) -> None:
+        ids = (C.c_uint32 * max(len(block_ids), 1))(*block_ids)
+        _check(self.lib.pa_swap_out(self.handle, layer, ids, len(block_ids), cpu.handle, stream))
+
+    def swap_in(self, block_ids, cpu: "CpuBlockCache", layer: int = 0, stream: int = 0) -> None:
+        ids = (C.c_uint32 * max(len(block_ids), 1))(*block_ids)
+        _check(self.lib.pa_swap_in(self.handle, layer, ids, len(block_ids), cpu.handle, stream))
+
     def decode_step_host(self, out_host, q_host, k_host, v_host, slots_host, tables_host,
                          lens_host, num_seqs: int, num_q_heads: int, max_blocks_per_seq: int,
                          scale: float, softcap: float = 1.0, layer: int = 0) -> None:
@@ -241,3 +267,30 @@ class PagedCache:
             self.handle, layer, _ptr(out_host), _ptr(q_host), _ptr(k_host), _ptr(v_host),
             _ptr(slots_host), _ptr(tables_host), _ptr(lens_host), num_seqs, num_q_heads,
             max_blocks_per_seq, scale, softcap))
+
+
+class CpuBlockCache:
+    """CpuBlockCache of crates/mlx-paged-attn/src/metal/swap_blocks.rs:15-52."""
+
+    def __init__(self, cache: PagedCache):
+        self.lib = cache.lib
+        self.handle = self.lib.pa_cpu_cache_create(cache.handle)
+        if not self.handle:
+            raise PagedAttnError(1, last_error())
+
+    def __del__(self):
+        try:
+            self.lib.pa_cpu_cache_free(self.handle)
+        except Exception:
+            pass
+
+    def is_swapped(self, block_id: int) -> bool:
+        return bool(self.lib.pa_cpu_cache_is_swapped(self.handle, block_id))
+
+    def num_swapped(self) -> int:
+        return int(self.lib.pa_cpu_cache_num_swapped(self.handle))
+
+    def block_ptrs(self, block_id: int):
+        k, v = C.c_void_p(), C.c_void_p()
+        _check(self.lib.pa_cpu_cache_block_ptrs(self.handle, block_id, C.byref(k), C.byref(v)))
+        return k.value, v.value

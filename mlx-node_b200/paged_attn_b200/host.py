@@ -40,6 +40,15 @@ class PaBatchTotals(C.Structure):
     _fields_ = [(n, u32) for n in ("total_tokens", "num_prefill", "num_decode")]
 
 
+class PaHybridConfig(C.Structure):
+    _fields_ = [(n, u32) for n in ("max_batch_size", "max_tokens_per_step", "prefill_chunk_size",
+                                   "max_prefill_per_step", "prioritize_decode", "eos_token_id")]
+
+
+class PaHybridTotals(C.Structure):
+    _fields_ = [(n, u32) for n in ("total_tokens", "num_prefill", "num_decode", "num_verify")]
+
+
 class PaSchedulerStats(C.Structure):
     _fields_ = [(n, u32) for n in ("num_waiting", "num_running", "num_completed", "num_prefill",
                                    "num_decode", "total_running_tokens")]
@@ -111,6 +120,24 @@ _SIGS = {
     "pa_sched_abort_request": (i32, [vp, vp, C.c_char_p, P(i32)]),
     "pa_sched_is_empty": (i32, [vp]), "pa_sched_stats": (None, [vp, P(PaSchedulerStats)]),
     "pa_sched_running_is_prefill": (i32, [vp, u32]),
+    "pa_hybrid_config_default": (None, [P(PaHybridConfig)]),
+    "pa_hybrid_create": (vp, [u32, P(PaHybridConfig)]), "pa_hybrid_destroy": (None, [vp]),
+    "pa_hybrid_add_request": (None, [vp, C.c_char_p, P(u32), sz, u32, i32]),
+    "pa_hybrid_set_draft_tokens": (i32, [vp, u32, P(u32), sz]),
+    "pa_hybrid_schedule_step": (u32, [vp, vp]),
+    "pa_hybrid_batch_totals": (None, [vp, P(PaHybridTotals)]),
+    "pa_hybrid_batch_entry": (i32, [vp, u32, P(u32), P(i32), P(u32), P(u32), P(i32)]),
+    "pa_hybrid_batch_tokens": (u32, [vp, u32, P(u32), sz]),
+    "pa_hybrid_batch_request_id": (C.c_char_p, [vp, u32]),
+    "pa_hybrid_batch_metadata": (i32, [vp, vp, P(i32), P(i32), P(i32), P(i64), sz, P(u32)]),
+    "pa_hybrid_process_outputs": (i32, [vp, vp, P(u32), P(u32), P(u32), P(u8), sz]),
+    "pa_hybrid_take_completed": (u32, [vp]),
+    "pa_hybrid_completed_request_id": (C.c_char_p, [vp, u32]),
+    "pa_hybrid_completed_finish_reason": (C.c_char_p, [vp, u32]),
+    "pa_hybrid_completed_tokens": (u32, [vp, u32, P(u32), sz, P(u32)]),
+    "pa_hybrid_is_empty": (i32, [vp]), "pa_hybrid_num_waiting": (u32, [vp]),
+    "pa_hybrid_num_running": (u32, [vp]),
+    "pa_kv_truncate_sequence": (i32, [vp, u32, u32]),
 }
 HOST_SYMBOLS = sorted(_SIGS)
 
@@ -347,6 +374,9 @@ class PagedKVCacheHost(_TrackerOps):
 
     def get_token_tracker_memory(self): return int(lib().pa_kv_tracker_memory(self.h))
 
+    def truncate_sequence(self, seq_id, new_num_tokens):
+        _check(lib().pa_kv_truncate_sequence(self.h, seq_id, new_num_tokens))
+
 
 class Scheduler:
     """ContinuousBatchingScheduler (crates/mlx-paged-attn/src/scheduler.rs)."""
@@ -423,3 +453,76 @@ class Scheduler:
     def num_running(self): return self.get_stats().num_running
     def num_completed(self): return self.get_stats().num_completed
     def running_is_prefill(self, seq_id): return lib().pa_sched_running_is_prefill(self.h, seq_id)
+
+
+class HybridScheduler:
+    """Chunked prefill + speculative verify + decode in one batch (no reference counterpart)."""
+    KINDS = {0: "prefill", 1: "decode", 2: "verify"}
+
+    def __init__(self, block_size, **cfg):
+        c = PaHybridConfig()
+        lib().pa_hybrid_config_default(C.byref(c))
+        for k, v in cfg.items():
+            setattr(c, k, int(v))
+        self.h = lib().pa_hybrid_create(block_size, C.byref(c))
+
+    def __del__(self):
+        lib().pa_hybrid_destroy(self.h)
+
+    def add_request(self, request_id, prompt_tokens, max_new_tokens, priority=0):
+        a, n = _arr(prompt_tokens)
+        lib().pa_hybrid_add_request(self.h, request_id.encode(), a, n, max_new_tokens, priority)
+
+    def set_draft_tokens(self, seq_id, tokens):
+        a, n = _arr(tokens)
+        _check(lib().pa_hybrid_set_draft_tokens(self.h, seq_id, a, n))
+
+    def schedule_step(self, cache: PagedKVCacheHost):
+        n = lib().pa_hybrid_schedule_step(self.h, cache.h)
+        if n == 0:
+            return None
+        t = PaHybridTotals()
+        lib().pa_hybrid_batch_totals(self.h, C.byref(t))
+        entries = []
+        for i in range(n):
+            sid, kind, ql, kv, ns = u32(), i32(), u32(), u32(), i32()
+            _check(lib().pa_hybrid_batch_entry(self.h, i, C.byref(sid), C.byref(kind), C.byref(ql),
+                                               C.byref(kv), C.byref(ns)))
+            buf = (u32 * max(ql.value, 1))()
+            lib().pa_hybrid_batch_tokens(self.h, i, buf, ql.value)
+            entries.append({"seq_id": int(sid.value), "kind": self.KINDS[kind.value], "q_len": int(ql.value),
+                            "kv_len": int(kv.value), "needs_sample": bool(ns.value),
+                            "tokens": list(buf[:ql.value]),
+                            "request_id": lib().pa_hybrid_batch_request_id(self.h, i).decode()})
+        mb = cache.get_max_blocks_per_seq()
+        tables, lens, cu = (i32 * (n * mb))(), (i32 * n)(), (i32 * (n + 1))()
+        slots, mx = (i64 * max(t.total_tokens, 1))(), u32()
+        _check(lib().pa_hybrid_batch_metadata(self.h, cache.h, tables, lens, cu, slots, t.total_tokens, C.byref(mx)))
+        return {"entries": entries, "total_tokens": t.total_tokens, "num_prefill": t.num_prefill,
+                "num_decode": t.num_decode, "num_verify": t.num_verify, "block_tables": list(tables),
+                "context_lens": list(lens), "cu_q_lens": list(cu), "slot_mapping": list(slots[:t.total_tokens]),
+                "max_blocks_per_seq": mb, "max_context_len": int(mx.value)}
+
+    def process_outputs(self, outputs, cache: PagedKVCacheHost):
+        """outputs: iterable of (seq_id, num_accepted, next_token, is_eos)."""
+        outputs = list(outputs)
+        s, n = _arr([o[0] for o in outputs])
+        a, _ = _arr([o[1] for o in outputs])
+        t, _ = _arr([o[2] for o in outputs])
+        e, _ = _arr([int(o[3]) for o in outputs], u8)
+        _check(lib().pa_hybrid_process_outputs(self.h, cache.h, s, a, t, e, n))
+
+    def get_completed(self):
+        n = lib().pa_hybrid_take_completed(self.h)
+        out = []
+        for i in range(n):
+            buf, total = (u32 * (1 << 16))(), u32()
+            k = lib().pa_hybrid_completed_tokens(self.h, i, buf, 1 << 16, C.byref(total))
+            out.append({"request_id": lib().pa_hybrid_completed_request_id(self.h, i).decode(),
+                        "finish_reason": lib().pa_hybrid_completed_finish_reason(self.h, i).decode(),
+                        "generated_tokens": list(buf[:k]), "total_tokens": int(total.value)})
+        return out
+
+    def is_empty(self): return bool(lib().pa_hybrid_is_empty(self.h))
+    def num_waiting(self): return int(lib().pa_hybrid_num_waiting(self.h))
+    def num_running(self): return int(lib().pa_hybrid_num_running(self.h))

@@ -86,3 +86,15 @@ def test_compute_fails_loudly_without_a_device():
         pytest.skip("a device is present")
     with pytest.raises(pa.PagedAttnError):
         pa.PagedCache(16, 8, 128, 2)
+
+
+def test_swap_block_sizes():
+    # crates/mlx-paged-attn/src/metal/swap_blocks.rs:265-312: 16384 B per block for 4 heads x 128 x 16
+    # in 16-bit storage, 8192 B with an fp8 cache
+    import ctypes as C
+    lib = pa.load_library()
+    k, v = C.c_uint64(), C.c_uint64()
+    lib.pa_swap_block_bytes(4, 128, 16, 0, C.byref(k), C.byref(v))
+    assert (k.value, v.value) == (16384, 16384)
+    lib.pa_swap_block_bytes(4, 128, 16, 1, C.byref(k), C.byref(v))
+    assert (k.value, v.value) == (8192, 8192)

@@ -149,6 +149,37 @@ def test_copy_blocks(cuda_device):
     assert (to_bits(kd) == k_pool).all() and (to_bits(vd) == v_pool).all()
 
 
+def test_swap_out_and_in(cuda_device):
+    # PagedKVCache::swap_out / swap_in (crates/mlx-paged-attn/src/paged_kv_cache.rs:1542-1637)
+    import ctypes as C
+    Hkv, NB = 8, 64
+    k_pool, v_pool = normal_bf16((NB, Hkv, D // X, BS, X), 71, 1), normal_bf16((NB, Hkv, D, BS), 71, 2)
+    kd, vd = to_dev(k_pool), to_dev(v_pool)
+    cache = pa.PagedCache(BS, NB, D, Hkv, key_pools=[kd], value_pools=[vd])
+    cpu = cache.create_cpu_cache()
+    assert cpu.num_swapped() == 0 and not cpu.is_swapped(0)
+    ids = [3, 17, 63, 0]
+    cache.swap_out(ids, cpu)
+    cache.swap_out([17], cpu)                      # already out: skipped
+    assert cpu.num_swapped() == 4 and cpu.is_swapped(63)
+    nbytes = Hkv * D * BS * 2
+    for b in ids:
+        kp, vp = cpu.block_ptrs(b)
+        assert C.string_at(kp, nbytes) == k_pool[b].tobytes()
+        assert C.string_at(vp, nbytes) == v_pool[b].tobytes()
+    # the device blocks are reused by someone else, then the originals come back
+    kd[torch.tensor(ids).cuda()] = 0
+    vd[torch.tensor(ids).cuda()] = 0
+    with pytest.raises(pa.PagedAttnError) as e:
+        cache.swap_in([3, 5], cpu)
+    assert "Block 5 not found in CPU cache" in str(e.value)
+    assert (to_bits(kd)[3] == 0).all()             # nothing moved by the failed call
+    cache.swap_in(ids, cpu)
+    cache.check_errors()
+    assert cpu.num_swapped() == 0
+    assert (to_bits(kd) == k_pool).all() and (to_bits(vd) == v_pool).all()
+
+
 def test_config1_full(cuda_device):
     # Qwen3-0.6B-shaped decode: the whole configuration against the whole oracle.
     kv, ql, Hq, Hkv, NB = config_lengths("c1")
