@@ -293,6 +293,7 @@ def main() -> None:
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     scale = 1.0 / math.sqrt(D)
     decode_only = bool((ql == 1).all())
+    kv_i32 = np.ascontiguousarray(kv.astype(np.int32))
     do_gather = args.gather and world > 1
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -302,7 +303,7 @@ def main() -> None:
             cache.decode(out, q, tables, lens, S, hq_l, MB, scale, ws, ws_bytes, stream=stream)
         else:
             cache.varlen(out, q, tables, lens, cu_q, S, hq_l, MB, scale, ws, ws_bytes,
-                         max_context_len=int(kv.max()), stream=stream)
+                         max_context_len=int(kv.max()), stream=stream, context_lens_host=kv_i32)
         if do_gather:
             sharding.gather_heads(out, world)
 
@@ -342,7 +343,7 @@ def main() -> None:
             cache.decode(out, q, tables, lens, S, hq_l, MB, scale, ws, ws_bytes, stream=stream)
         else:
             cache.varlen(out, q, tables, lens, cu_q, S, hq_l, MB, scale, ws, ws_bytes,
-                         max_context_len=int(kv.max()), stream=stream)
+                         max_context_len=int(kv.max()), stream=stream, context_lens_host=kv_i32)
     attn_ms = timed(attn_only, args.steps) / args.steps
 
     # end to end through the host-buffer entry: H2D of the step's inputs + kernels + D2H

@@ -257,14 +257,19 @@ pa_status pa_paged_attention_decode_static(PagedAttnCache *cache, uint32_t layer
  * and q_len_s = cu_q_lens[s+1]-cu_q_lens[s] >= 0 queries that occupy the last
  * q_len_s positions; query j attends keys [0, context_lens[s]-q_len_s+j].
  *   out, q        [total_q, num_q_heads, head_size] in the cache dtype, packed by sequence
- *   cu_q_lens     int32 [num_seqs+1] in HOST memory (the scheduler has it);
- *                 the library uploads what its kernels need
- *   max_context_len  upper bound of context_lens (0 = unknown)                */
+ *   cu_q_lens_host      int32 [num_seqs+1] in HOST memory (the scheduler has it);
+ *                       the library uploads what its kernels need
+ *   context_lens_host   optional host copy of context_lens (may be null).  With
+ *                       it, a batch that mixes long-query and short-query sequences
+ *                       runs its two kernels side by side on SM shares sized by
+ *                       their estimated work; without it they run back to back.
+ *   max_context_len     upper bound of context_lens (0 = unknown)              */
 pa_status pa_paged_attention_varlen(PagedAttnCache *cache, uint32_t layer_idx,
                                     void *out, const void *q,
                                     const int32_t *block_tables,
                                     const int32_t *context_lens,
-                                    const int32_t *cu_q_lens_host, int32_t num_seqs,
+                                    const int32_t *cu_q_lens_host,
+                                    const int32_t *context_lens_host, int32_t num_seqs,
                                     int32_t num_q_heads, int32_t max_blocks_per_seq,
                                     int64_t q_stride, int64_t out_stride, float scale,
                                     float softcap, int32_t max_context_len,

@@ -3,7 +3,9 @@
 // points and the host-buffer decode step.  No tensor-library types cross this
 // boundary and there is no CPU fallback: without a CUDA device every compute
 // entry fails with PA_ERR_CUDA.
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -71,6 +73,9 @@ struct PagedAttnCache {
   void *stage = nullptr;
   size_t stage_bytes = 0;
   cudaStream_t step_stream = nullptr;
+  // second stream and fork/join events for calls that run two kernels side by side
+  cudaStream_t aux_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 struct mlx_array {
@@ -80,6 +85,10 @@ struct mlx_array {
   size_t ndim = 0;
   int64_t shape[8] = {0};
   bool owns = false;
+  // set on the views mlx_paged_attn_get_key_cache / get_value_cache return, so that
+  // forward can run on the cache's own handle (error word, scratch) without setting one up
+  PagedAttnCache *owner = nullptr;
+  uint32_t layer = 0;
 };
 
 namespace {
@@ -128,6 +137,9 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
   PA_CUDA(cudaStreamCreateWithFlags(&c->step_stream, cudaStreamNonBlocking));
+  PA_CUDA(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+  PA_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+  PA_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   return PA_OK;
 }
 
@@ -253,6 +265,9 @@ pa_status pa_cache_free(PagedAttnCache *c) {
   if (c->meta) cudaFree(c->meta);
   if (c->stage) cudaFree(c->stage);
   if (c->step_stream) cudaStreamDestroy(c->step_stream);
+  if (c->aux_stream) cudaStreamDestroy(c->aux_stream);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   delete c;
   return PA_OK;
 }
@@ -471,7 +486,8 @@ size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {
 
 pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
                                     const int32_t *block_tables, const int32_t *context_lens,
-                                    const int32_t *cu_q_lens_host, int32_t num_seqs,
+                                    const int32_t *cu_q_lens_host,
+                                    const int32_t *context_lens_host, int32_t num_seqs,
                                     int32_t num_q_heads, int32_t max_blocks_per_seq,
                                     int64_t q_stride, int64_t out_stride, float scale,
                                     float softcap, int32_t max_context_len, void *workspace,
@@ -523,11 +539,16 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.err = c->err_dev;
   p.seq_base = 0;
   p.is_f16 = c->cfg.dtype == 0 ? 1 : 0;
+  p.early_trigger = 1;
 
   if (!cu_q_lens_host) {  // decode: one query per sequence
     p.min_cols = 1;
     p.max_cols = G;
-    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
+    int decode_ctas = c->num_sms;
+#ifdef PA_TILE_TIMING  // debug builds: study how bandwidth scales with the CTA count
+    if (const char *e = getenv("PA_DEBUG_SPLIT_CTAS")) decode_ctas = atoi(e);
+#endif
+    PA_CUDA(pa::launch_splitkv_attention(p, decode_ctas, stream));
     return PA_OK;
   }
 
@@ -539,20 +560,25 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   const int tile_q = pa::tile_queries_per_cta(G);
   bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
+  double tile_flops = 0.0, split_bytes = 0.0;  // work estimates, only with host context lengths
   for (int s = 0; s < num_seqs; s++) {
     const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
     if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
     if (ql == 0) continue;
+    const double kv = context_lens_host ? (double)context_lens_host[s] : 0.0;
     if (ql * G <= split_cols) {
       have_class[(ql * G - 1) / 8] = true;
+      split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * 2.0;
     } else {
       // Tiles of one (sequence, kv head) are neighbours in launch order so that they
       // share the head's KV blocks in L2; later tiles see more keys and go first.
       for (int h = 0; h < Hkv; h++)
         for (int qb = ((ql - 1) / tile_q) * tile_q; qb >= 0; qb -= tile_q)
           tiles.push_back(pa::TileWork{s, h, qb, ql - qb < tile_q ? ql - qb : tile_q});
+      tile_flops += 4.0 * c->cfg.head_size * num_q_heads * ql * (kv - 0.5 * ql);
     }
   }
+  const bool any_split = have_class[0] || have_class[1] || have_class[2];
   const size_t cu_bytes = ((size_t)(num_seqs + 1) * 4 + 255) & ~(size_t)255;
   const size_t need = cu_bytes + tiles.size() * sizeof(pa::TileWork);
   st = grow(&c->meta, &c->meta_bytes, need);
@@ -560,17 +586,62 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   PA_CUDA(cudaMemcpyAsync(c->meta, cu_q_lens_host, (size_t)(num_seqs + 1) * 4,
                           cudaMemcpyHostToDevice, stream));
   p.cu_q_lens = static_cast<const int32_t *>(c->meta);
-  if (!tiles.empty()) {
-    pa::TileWork *work_dev = reinterpret_cast<pa::TileWork *>(static_cast<char *>(c->meta) + cu_bytes);
+  pa::TileWork *work_dev = reinterpret_cast<pa::TileWork *>(static_cast<char *>(c->meta) + cu_bytes);
+  if (!tiles.empty())
     PA_CUDA(cudaMemcpyAsync(work_dev, tiles.data(), tiles.size() * sizeof(pa::TileWork),
                             cudaMemcpyHostToDevice, stream));
+
+  // A batch that holds both kinds of work runs them side by side: the tensor-bound tile
+  // kernel on a second stream, the memory-bound split-KV kernel on fewer CTAs.  The
+  // split is chosen from a small model measured on B200: split-KV streams about 70 GB/s
+  // per SM up to about 6 TB/s in total (100 SMs already saturate HBM); a tile CTA
+  // sustains about 0.9 PFLOP/s / 148 and tile CTAs run in waves over the SMs they get.
+  // Without host context lengths there is no estimate and the two run back to back.
+  int split_ctas = c->num_sms;
+  bool side_by_side = false;
+  if (!tiles.empty() && any_split && context_lens_host) {
+    const double t_cta = tile_flops / (double)tiles.size() / (0.9e15 / c->num_sms);
+    const double t_tile_alone = t_cta * (double)((tiles.size() + c->num_sms - 1) / c->num_sms);
+    const double t_split_alone = split_bytes / 6.0e12;
+    if (t_tile_alone > 20e-6 && t_split_alone > 20e-6) {
+      double best = 1e30;
+      int best_tile_sms = 0;
+      for (int n2 = 8; n2 <= c->num_sms - 32; n2++) {
+        const double bw = std::min(6.0e12, (c->num_sms - n2) * 70e9);
+        const double waves = (double)((tiles.size() + n2 - 1) / n2);
+        const double cost = std::max(split_bytes / bw, waves * t_cta);
+        if (cost < best - 1e-9) {
+          best = cost;
+          best_tile_sms = n2;
+        }
+      }
+      if (best_tile_sms > 0 && best < t_tile_alone + t_split_alone) {
+        split_ctas = c->num_sms - best_tile_sms;
+        side_by_side = true;
+      }
+    }
+  }
+  if (side_by_side) {
+    p.early_trigger = 0;
+    PA_CUDA(cudaEventRecord(c->ev_fork, stream));
+    PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
+  } else if (!tiles.empty()) {
     PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), stream));
   }
+  bool tile_launched = !side_by_side;
   for (int k = 0; k < 3; k++) {
     if (!have_class[k]) continue;
     p.min_cols = 8 * k + 1;
     p.max_cols = 8 * k + 8;
-    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream));
+    PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream));
+    if (!tile_launched) {  // after the first split-KV launch, so that it gets its SMs first
+      PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), c->aux_stream));
+      tile_launched = true;
+    }
+  }
+  if (side_by_side) {
+    PA_CUDA(cudaEventRecord(c->ev_join, c->aux_stream));
+    PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
   }
   return PA_OK;
 }
@@ -581,9 +652,9 @@ pa_status pa_paged_attention_decode(PagedAttnCache *c, uint32_t layer, void *out
                                     int32_t max_blocks_per_seq, int64_t q_stride,
                                     int64_t out_stride, float scale, float softcap,
                                     void *workspace, size_t workspace_bytes, void *cuda_stream) {
-  return pa_paged_attention_varlen(c, layer, out, q, block_tables, context_lens, nullptr, num_seqs,
-                                   num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale,
-                                   softcap, 0, workspace, workspace_bytes, cuda_stream);
+  return pa_paged_attention_varlen(c, layer, out, q, block_tables, context_lens, nullptr, nullptr,
+                                   num_seqs, num_q_heads, max_blocks_per_seq, q_stride, out_stride,
+                                   scale, softcap, 0, workspace, workspace_bytes, cuda_stream);
 }
 
 pa_status pa_paged_attention_decode_static(PagedAttnCache *c, uint32_t layer, void *out,
@@ -732,6 +803,8 @@ static mlx_array *pool_view(PagedAttnCache *c, uint32_t layer, bool key) {
   a->data = key ? c->k[layer] : c->v[layer];
   a->dtype = (int32_t)f.dtype;
   a->device = c->device;
+  a->owner = c;
+  a->layer = layer;
   if (key) {
     a->ndim = 5;
     const int64_t sh[5] = {f.num_blocks, f.num_kv_heads, f.head_size / 8, f.block_size, 8};
@@ -781,23 +854,26 @@ mlx_array *mlx_paged_attn_forward(mlx_array *q, mlx_array *kc, mlx_array *vc, ml
   PagedAttnConfig cfg{(uint32_t)vc->shape[3], (uint32_t)vc->shape[0], (uint32_t)vc->shape[2],
                       (uint32_t)vc->shape[1], 1, (uint32_t)q->dtype};
   void *kp = kc->data, *vp = vc->data;
-  // A transient handle over the caller's pools: this entry takes the pools as
-  // arrays, not the cache handle (crates/mlx-sys/src/lib.rs:782-791).
-  PagedAttnCache *c = nullptr;
-  if (pa_cache_wrap(&cfg, kc->device, &kp, &vp, &c) != PA_OK) return nullptr;
+  // This entry takes the pools as arrays, not the cache handle
+  // (crates/mlx-sys/src/lib.rs:782-791).  Views handed out by get_key_cache /
+  // get_value_cache remember their cache; for any other pair of arrays a transient
+  // handle is wrapped around the pools for the duration of the call.
+  const bool owned = kc->owner && kc->owner == vc->owner && kc->layer == vc->layer;
+  PagedAttnCache *c = owned ? kc->owner : nullptr;
+  const uint32_t layer = owned ? kc->layer : 0;
+  if (!owned && pa_cache_wrap(&cfg, kc->device, &kp, &vp, &c) != PA_OK) return nullptr;
   const int64_t S = q->shape[0], Hq = q->shape[1], D = q->shape[2];
   DeviceGuard g(c->device);
-  void *out = nullptr, *ws = nullptr;
-  const size_t ws_bytes = pa_attention_workspace_bytes(c);
+  void *out = nullptr;
   mlx_array *res = nullptr;
   cudaError_t e = cudaMalloc(&out, (size_t)(S * Hq * D * 2 > 0 ? S * Hq * D * 2 : 16));
-  if (e == cudaSuccess) e = cudaMalloc(&ws, ws_bytes);
   if (e != cudaSuccess) {
     cuda_fail(e, "forward: allocation");
-  } else if (pa_paged_attention_varlen(c, 0, out, q->data, static_cast<const int32_t *>(bt->data),
-                                       static_cast<const int32_t *>(cl->data), nullptr, (int32_t)S,
-                                       (int32_t)Hq, (int32_t)bt->shape[1], Hq * D, Hq * D, scale,
-                                       1.0f, (int32_t)max_context_len, ws, ws_bytes,
+  } else if (grow(&c->ws, &c->ws_bytes, pa_attention_workspace_bytes(c)) == PA_OK &&
+             pa_paged_attention_varlen(c, layer, out, q->data, static_cast<const int32_t *>(bt->data),
+                                       static_cast<const int32_t *>(cl->data), nullptr, nullptr,
+                                       (int32_t)S, (int32_t)Hq, (int32_t)bt->shape[1], Hq * D, Hq * D, scale,
+                                       1.0f, (int32_t)max_context_len, c->ws, c->ws_bytes,
                                        t_stream) == PA_OK &&
              cudaStreamSynchronize(t_stream) == cudaSuccess) {
     const int64_t sh[3] = {S, Hq, D};
@@ -809,8 +885,7 @@ mlx_array *mlx_paged_attn_forward(mlx_array *q, mlx_array *kc, mlx_array *vc, ml
     }
   }
   if (out) cudaFree(out);
-  if (ws) cudaFree(ws);
-  pa_cache_free(c);
+  if (!owned) pa_cache_free(c);
   return res;
 }
 

@@ -134,6 +134,7 @@ struct AttnParams {
   const int32_t *cu_q_lens;     // [S+1] device copy, or null: one query per sequence
   int S, Hq, Hkv, G, MB;
   int is_f16;  // element format: 1 = f16, 0 = bf16
+  int early_trigger;  // split-KV: let the merge grid become resident at once
   uint32_t num_blocks;  // pool size, for range checks
   int64_t q_stride, out_stride;
   float scale;    // logits multiplier

@@ -89,8 +89,10 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
   const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index, row within it
   const int S = p.S, Hkv = p.Hkv, G = p.G;
 
-  // The merge kernel may be scheduled now; it waits for this grid to finish.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The merge kernel may be scheduled now; it waits for this grid to finish.  Its CTAs
+  // then sit on every SM until this grid ends, holding registers, so the early trigger
+  // is skipped when another kernel is meant to use the SMs this grid leaves free.
+  if (p.early_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- per-launch prefix sum of block counts --------------------------------
   for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s);
   if (tid == 0) pre[0] = 0;

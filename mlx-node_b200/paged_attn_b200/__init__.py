@@ -88,7 +88,7 @@ def load_library() -> C.CDLL:
                                               f32, f32, vp, sz, vp]
     lib.pa_paged_attention_decode_static.argtypes = [vp, u32, vp, vp, vp, vp, i32, i32, i32, i64,
                                                      i64, f32, f32, vp]
-    lib.pa_paged_attention_varlen.argtypes = [vp, u32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
+    lib.pa_paged_attention_varlen.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
                                               f32, f32, i32, vp, sz, vp]
     lib.pa_cpu_cache_create.argtypes = [vp]
     lib.pa_cpu_cache_create.restype = vp
@@ -240,11 +240,11 @@ class PagedCache:
                num_q_heads: int, max_blocks_per_seq: int, scale: float, workspace,
                workspace_bytes: int, softcap: float = 1.0, max_context_len: int = 0,
                q_stride: int | None = None, out_stride: int | None = None, layer: int = 0,
-               stream: int = 0) -> None:
+               stream: int = 0, context_lens_host=None) -> None:
         row = num_q_heads * self.cfg.head_size
         _check(self.lib.pa_paged_attention_varlen(
             self.handle, layer, _ptr(out), _ptr(q), _ptr(block_tables), _ptr(context_lens),
-            _ptr(cu_q_lens_host), num_seqs, num_q_heads, max_blocks_per_seq, q_stride or row,
+            _ptr(cu_q_lens_host), _ptr(context_lens_host), num_seqs, num_q_heads, max_blocks_per_seq, q_stride or row,
             out_stride or row, scale, softcap, max_context_len, _ptr(workspace), workspace_bytes,
             stream))
 

@@ -53,14 +53,15 @@ class DeviceCase:
         self.cache.reshape_and_cache(self.k_new, self.v_new, self.slots, len(c.slot_mapping),
                                      c.Hkv * D, c.Hkv * D)
 
-    def attend(self, varlen=True, softcap=1.0):
+    def attend(self, varlen=True, softcap=1.0, host_lens=True):
         c = self.case
         f16 = getattr(c, "f16", False)
         out = torch.full((max(c.total_q, 1), c.Hq, D), float("nan"),
                          dtype=torch.float16 if f16 else torch.bfloat16, device="cuda")
         if varlen:
             self.cache.varlen(out, self.q, self.tables, self.lens, c.cu_q, c.S, c.Hq, c.MB,
-                              c.scale, self.ws, self.ws_bytes, softcap=softcap)
+                              c.scale, self.ws, self.ws_bytes, softcap=softcap,
+                              context_lens_host=c.kv_lens if host_lens else None)
         else:
             self.cache.decode(out, self.q, self.tables, self.lens, c.S, c.Hq, c.MB, c.scale,
                               self.ws, self.ws_bytes, softcap=softcap)

@@ -100,7 +100,8 @@ class FullCase:
         out = torch.full((self.total_q, self.Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
         if varlen:
             self.cache.varlen(out, self.q, self.tables, self.lens, self.cu_q, self.S, self.Hq, self.MB,
-                              self.scale, self.ws, self.ws.numel(), max_context_len=int(self.kv.max()))
+                              self.scale, self.ws, self.ws.numel(), max_context_len=int(self.kv.max()),
+                              context_lens_host=np.ascontiguousarray(self.kv.astype(np.int32)))
         else:
             self.cache.decode(out, self.q, self.tables, self.lens, self.S, self.Hq, self.MB, self.scale,
                               self.ws, self.ws.numel())

@@ -212,6 +212,10 @@ def test_mixed_batch_reduced(cuda_device):
     case = Case(kv, ql, 32, 8, 2048, seed=3)
     got, ref = run_case(case)
     print("mixed", check_attention(got, ref, "mixed batch"))
+    # without host context lengths the two kernels run back to back: same bits
+    dc = DeviceCase(case)
+    dc.write()
+    assert (dc.attend(host_lens=False) == got).all()
 
 
 def test_prefill_chunk_reduced(cuda_device):
