@@ -52,18 +52,18 @@ def workload_lengths(name: str, world: int):
     return config_lengths(name)
 
 
-def algorithmic_bytes(kv_lens, q_lens, Hq, Hkv) -> int:
+def algorithmic_bytes(kv_lens, q_lens, Hq, Hkv, kv_elem_bytes=2) -> int:
     """One pass over the live KV bytes (once per KV head, whatever the group size or the
     number of splits), the block-table entries and lengths, Q read and O written."""
     kv = int(np.sum(kv_lens))
     blocks = int(np.sum((np.asarray(kv_lens) + BS - 1) // BS))
     tq = int(np.sum(q_lens))
-    return kv * 2 * Hkv * D * 2 + blocks * 4 + len(kv_lens) * 4 + 2 * tq * Hq * D * 2
+    return kv * 2 * Hkv * D * kv_elem_bytes + blocks * 4 + len(kv_lens) * 4 + 2 * tq * Hq * D * 2
 
 
-def write_bytes(q_lens, Hkv) -> int:
+def write_bytes(q_lens, Hkv, kv_elem_bytes=2) -> int:
     t = int(np.sum(q_lens))
-    return t * (2 * Hkv * D * 2) * 2 + t * 8
+    return t * (2 * Hkv * D) * (2 + kv_elem_bytes) + t * 8
 
 
 def attention_flops(kv_lens, q_lens, Hq) -> int:
@@ -207,6 +207,10 @@ def main() -> None:
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--gather", action="store_true",
                     help="all-gather the head outputs over NCCL inside the step (N > 1)")
+    ap.add_argument("--fp8", action="store_true",
+                    help="E4M3 KV cache (one byte per element); decode workloads only")
+    ap.add_argument("--producer", action="store_true",
+                    help="the step's write becomes the fused QK-norm + rotary + KV-write launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--seqs", type=int, default=0, help="use only the first N sequences (small captures)")
@@ -271,9 +275,19 @@ def main() -> None:
             flat[i:i + n] = torch.randn(n, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
         return out
 
-    k_pool = torch.zeros(NB, hkv_l, D // 8, BS, 8, dtype=torch.bfloat16, device=dev)
-    v_pool = torch.zeros(NB, hkv_l, D, BS, dtype=torch.bfloat16, device=dev)
-    cache = pa.PagedCache(BS, NB, D, hkv_l, device=local_rank, key_pools=[k_pool], value_pools=[v_pool])
+    if args.fp8:
+        k_pool = torch.zeros(NB, hkv_l, D // 16, BS, 16, dtype=torch.uint8, device=dev)
+        v_pool = torch.zeros(NB, hkv_l, D, BS, dtype=torch.uint8, device=dev)
+    else:
+        k_pool = torch.zeros(NB, hkv_l, D // 8, BS, 8, dtype=torch.bfloat16, device=dev)
+        v_pool = torch.zeros(NB, hkv_l, D, BS, dtype=torch.bfloat16, device=dev)
+    cache = pa.PagedCache(BS, NB, D, hkv_l, device=local_rank, key_pools=[k_pool], value_pools=[v_pool],
+                          fp8=args.fp8)
+    if args.fp8:
+        cache.set_kv_scales(1.0 / 32, 1.0 / 32)  # N(0,1) values sit well inside +-240 * scale
+        # the wrapped pools were zero-filled above; the library's own writes switch the
+        # kernels back to exact decoding should a value ever overflow
+        cache.fp8_set_exact_decode(False)
     k_all = randn_bf16(int(kv.sum()), hkv_l, D)
     v_all = randn_bf16(int(kv.sum()), hkv_l, D)
     slots_all_d = torch.from_numpy(slots_all).to(dev)
@@ -297,8 +311,21 @@ def main() -> None:
     do_gather = args.gather and world > 1
     stream = torch.cuda.current_stream().cuda_stream
 
+    if args.producer:
+        # projections in, rotated queries out (separate buffer so every step does the same work)
+        q_raw = q
+        q = torch.empty_like(q_raw)
+        norm_w = torch.ones(D, dtype=torch.bfloat16, device=dev)
+        pos_h = np.concatenate([kv[s] - ql[s] + np.arange(ql[s]) for s in range(S)]).astype(np.int32)
+        positions = torch.from_numpy(pos_h).to(dev)
+
     def step():
-        cache.reshape_and_cache(k_new, v_new, slots, total_q, hkv_l * D, hkv_l * D, stream=stream)
+        if args.producer:
+            cache.qk_norm_rope_and_cache(q, q_raw, k_new, v_new, norm_w, norm_w, 1e-6, positions,
+                                         1.0e6, D, slots, total_q, hq_l, hq_l * D, hq_l * D,
+                                         hkv_l * D, hkv_l * D, stream=stream)
+        else:
+            cache.reshape_and_cache(k_new, v_new, slots, total_q, hkv_l * D, hkv_l * D, stream=stream)
         if decode_only:
             cache.decode(out, q, tables, lens, S, hq_l, MB, scale, ws, ws_bytes, stream=stream)
         else:
@@ -374,25 +401,35 @@ def main() -> None:
     clocks = sampler.stop() if rank == 0 else None
 
     # per-rank algorithmic work (this rank's heads)
-    kv_bytes = algorithmic_bytes(kv, ql, hq_l, hkv_l)
+    eb = 1 if args.fp8 else 2
+    kv_bytes = algorithmic_bytes(kv, ql, hq_l, hkv_l, eb)
     flops = attention_flops(kv, ql, hq_l)
     hbm_peak, tf_peak, peak_kind = measured_peaks()
     tensor_bound = args.workload == "c4"
     if tensor_bound:
         achieved = flops / (attn_ms * 1e-3) / 1e12
+        # ncu capture of one sequence of this workload (profiles/tile_attention_tc_kernel_c4_ncu.md):
+        # 61.1 MB of DRAM traffic per sequence per launch, scaled by the sequence count
         roof = {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
-                "frac": achieved / tf_peak, "traffic": None}
+                "frac": achieved / tf_peak, "traffic": int(61.1e6 * S * hkv_l / 8),
+                "traffic_source": "ncu dram bytes of a 1-sequence capture x sequences"}
     else:
         achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
+        # ncu capture of a 16-sequence case of this workload
+        # (profiles/splitkv_kernel_c2_16seq_ncu_full.md): DRAM read+write = 1.021 x the
+        # algorithmic bytes; traffic grows in proportion with the units processed
+        traffic = None if (args.fp8 or not decode_only) else int(1.021 * kv_bytes)
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak, "traffic": None}
+                "frac": achieved / hbm_peak, "traffic": traffic,
+                "traffic_source": "ncu dram bytes of a 16-sequence capture, scaled by algorithmic bytes"
+                if traffic else None}
     roof.update({"kernel": "tile_attention" if tensor_bound else "splitkv_kernel (+ merge)",
                  "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)" if peak_kind == "measured"
                  else "fallback", "kernel_ms": attn_ms, "algorithmic_bytes": kv_bytes,
                  "algorithmic_flops": flops, "per": "rank"})
 
     cpu_base = None
-    if rank == 0 and world == 1 and decode_only and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and decode_only and not args.no_cpu_baseline and not args.fp8:
         cpu_base = cpu_baseline_and_spot_check(kv, ql, Hq, Hkv, tables_h, k_pool, v_pool, q, out,
                                                scale)
     if rank == 0:
@@ -405,9 +442,13 @@ def main() -> None:
             "config": workload_config(args.workload, world, kv, ql, Hq, Hkv),
             "roofline": roof, "cpu_baseline": cpu_base, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
-            "step_bytes": kv_bytes + write_bytes(ql, hkv_l),
-            "step_gbs": (kv_bytes + write_bytes(ql, hkv_l)) / (ms_per_step * 1e-3) / 1e9,
+            "step_bytes": kv_bytes + write_bytes(ql, hkv_l, eb),
+            "step_gbs": (kv_bytes + write_bytes(ql, hkv_l, eb)) / (ms_per_step * 1e-3) / 1e9,
         }
+        if args.fp8:
+            line["config"]["kv_cache"] = "E4M3 bytes, scales 1/32; q, out and the written k, v bf16"
+        if args.producer:
+            line["config"]["producer"] = "QK norm + rotary embedding fused into the KV write launch"
         if do_gather:
             line["config"]["gather"] = "NCCL all_gather of head outputs inside the step"
         print(json.dumps(line))

@@ -140,6 +140,41 @@ pa_status pa_cache_free(PagedAttnCache *cache);
 void *pa_cache_key_ptr(PagedAttnCache *cache, uint32_t layer_idx);
 void *pa_cache_value_ptr(PagedAttnCache *cache, uint32_t layer_idx);
 pa_status pa_cache_get_config(const PagedAttnCache *cache, PagedAttnConfig *out);
+/* FP8 (E4M3) KV cache: PagedAttentionConfig::use_fp8_cache
+ * (crates/mlx-paged-attn/src/config.rs:23-26, 87-88) as CacheEngine::initialize lays
+ * it out (crates/mlx-paged-attn/src/cache_engine.rs:66-90): one byte per element,
+ * key pool [num_blocks, num_kv_heads, head_size/16, block_size, 16], value pool
+ * [num_blocks, num_kv_heads, head_size, block_size].  config->dtype (0 f16, 1 bf16)
+ * is then the type of the queries, outputs and of the keys/values given to
+ * pa_reshape_and_cache.  The byte format is the reference's
+ * (crates/mlx-paged-attn/metal/float8.metal:11-33, 63-121; largest finite value
+ * 240).  The write stores encode(T(x / scale)) (reshape_and_cache.metal:88-92), the
+ * attention reads decode(byte) * scale (paged_attention.metal:569-571, 920-929,
+ * 1063-1071) with the per-layer scales below (KvScaleManager::k_scale / v_scale,
+ * crates/mlx-paged-attn/src/metal/kv_scale.rs:90-97; default 1).  Decode and
+ * multi-token sequences of up to 24 / (query heads per kv head) tokens are built;
+ * longer chunks return PA_ERR_UNSUPPORTED with an FP8 cache.                       */
+pa_status pa_cache_create_fp8(const PagedAttnConfig *config, int32_t device,
+                              PagedAttnCache **out_cache);
+pa_status pa_cache_wrap_fp8(const PagedAttnConfig *config, int32_t device,
+                            void *const *key_ptrs, void *const *value_ptrs,
+                            PagedAttnCache **out_cache);
+int32_t pa_cache_is_fp8(const PagedAttnCache *cache);
+pa_status pa_cache_set_kv_scales(PagedAttnCache *cache, uint32_t layer_idx, float k_scale,
+                                 float v_scale);
+pa_status pa_cache_get_kv_scales(const PagedAttnCache *cache, uint32_t layer_idx,
+                                 float *k_scale, float *v_scale);
+/* The attention kernels decode FP8 bytes in one of two ways.  The exact one reads a
+ * byte with exponent field 15 as infinity or NaN, as the cache format defines; the
+ * fast one is valid while the pools hold no such byte.  A cache made by
+ * pa_cache_create_fp8 starts fast (zero-filled pools) and switches to exact by
+ * itself when a write produces such a byte (overflow of x/scale, infinity or NaN
+ * going in).  A cache made by pa_cache_wrap_fp8 starts exact, because the contents
+ * of the caller's memory are unknown; on = 0 is the caller's statement that the
+ * pools hold no exponent-15 byte, on = 1 forces the exact variant.  Synchronous
+ * (one 4-byte copy); no reference counterpart.                                   */
+pa_status pa_cache_fp8_set_exact_decode(PagedAttnCache *cache, int32_t on);
+
 /* Synchronises `stream` and reports, then clears, the error word the kernels
  * of this cache write instead of trapping (out-of-range block id or slot,
  * a bounded wait that ran out).                                               */
@@ -157,6 +192,35 @@ pa_status pa_reshape_and_cache(PagedAttnCache *cache, uint32_t layer_idx,
                                const int64_t *slot_mapping, int64_t num_tokens,
                                int64_t key_stride, int64_t value_stride,
                                void *cuda_stream);
+
+/* Producer of the write + attend pair: per-head RMS norm of the projected queries
+ * and keys, rotary embedding at each token's own position, and the KV block write,
+ * one launch for all tokens.  Replaces the per-sequence loop of
+ * Attention::compute_qkv_paged_decode
+ * (crates/mlx-core/src/transformer/attention.rs:637-691), which runs steps 3-5 of
+ * mlx_fused_attention_qkv (crates/mlx-sys/src/mlx.cpp:1343-1365: fast::rms_norm per
+ * head, then fast::rope with traditional = false, scale 1, offset = the sequence's
+ * position) once per sequence and stacks the results, followed by
+ * PagedAttentionLayer::update_cache
+ * (crates/mlx-core/src/transformer/block.rs:224-226).
+ * q, k, v: the projection outputs [num_tokens, heads, head_size] in the cache dtype
+ * (row strides in elements); q_out receives the normalised, rotated queries and may
+ * be q itself; the normalised, rotated keys and the values go to the pool at
+ * slot_mapping (same skipping and reporting as pa_reshape_and_cache) and nowhere
+ * else.  q_norm_weight / k_norm_weight: [head_size] in the cache dtype, or null for
+ * no norm.  positions: int32 [num_tokens] on the device.  rope_dims: even, <=
+ * head_size; elements beyond it pass through.  The angle of frequency i is
+ * float(position) * float(pow(rope_base, -i / (rope_dims/2))).                    */
+pa_status pa_qk_norm_rope_and_cache(PagedAttnCache *cache, uint32_t layer_idx,
+                                    void *q_out, const void *q, const void *k,
+                                    const void *v, const void *q_norm_weight,
+                                    const void *k_norm_weight, float eps,
+                                    const int32_t *positions, float rope_base,
+                                    uint32_t rope_dims, const int64_t *slot_mapping,
+                                    int64_t num_tokens, int32_t num_q_heads,
+                                    int64_t q_stride, int64_t q_out_stride,
+                                    int64_t k_stride, int64_t v_stride,
+                                    void *cuda_stream);
 
 /* Copy-on-write block copy.  dispatch_copy_blocks_raw
  * (crates/mlx-paged-attn/src/metal/copy_blocks.rs:96-99) over

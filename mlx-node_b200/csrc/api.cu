@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <cmath>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -63,7 +64,14 @@ struct PagedAttnCache {
   bool owns = false;
   int num_sms = 0;
   std::vector<void *> k, v;
+  // FP8 (E4M3) pools: one byte per element; cfg.dtype is then the type of q, out and of
+  // the keys and values handed to the write.  Per-layer dequantisation factors.
+  bool fp8 = false;
+  std::vector<float> k_scale, v_scale;
   unsigned *err_dev = nullptr;
+  // FP8: device word next to the error word, non-zero once a pool may hold a byte with
+  // exponent field 15 (infinity / NaN in the cache format)
+  unsigned *fp8_special() const { return err_dev + 16; }
   // scratch owned by the handle: attention workspace for tier 1 / the host step,
   // per-call metadata (cu_q_lens copy, tile work list), host-step staging
   void *ws = nullptr;
@@ -121,8 +129,11 @@ pa_status validate_config(const PagedAttnConfig *c) {
   return PA_OK;
 }
 
-size_t layer_bytes(const PagedAttnConfig &c) {
-  return (size_t)c.num_blocks * c.num_kv_heads * c.head_size * c.block_size * 2;
+size_t layer_bytes(const PagedAttnConfig &c, bool fp8) {
+  return (size_t)c.num_blocks * c.num_kv_heads * c.head_size * c.block_size * (fp8 ? 1 : 2);
+}
+int64_t block_bytes_of(const PagedAttnCache *c) {  // K (or V) bytes of one block, all heads
+  return (int64_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * (c->fp8 ? 1 : 2);
 }
 
 pa_status finish_create(PagedAttnCache *c) {
@@ -182,7 +193,57 @@ pa_status pa_set_stream(void *cuda_stream) {
   return PA_OK;
 }
 
+static pa_status cache_create_impl(const PagedAttnConfig *config, int32_t device, bool fp8,
+                                   PagedAttnCache **out);
+static pa_status cache_wrap_impl(const PagedAttnConfig *config, int32_t device, bool fp8,
+                                 void *const *key_ptrs, void *const *value_ptrs,
+                                 PagedAttnCache **out);
+
 pa_status pa_cache_create(const PagedAttnConfig *config, int32_t device, PagedAttnCache **out) {
+  return cache_create_impl(config, device, false, out);
+}
+pa_status pa_cache_create_fp8(const PagedAttnConfig *config, int32_t device, PagedAttnCache **out) {
+  return cache_create_impl(config, device, true, out);
+}
+pa_status pa_cache_wrap(const PagedAttnConfig *config, int32_t device, void *const *key_ptrs,
+                        void *const *value_ptrs, PagedAttnCache **out) {
+  return cache_wrap_impl(config, device, false, key_ptrs, value_ptrs, out);
+}
+pa_status pa_cache_wrap_fp8(const PagedAttnConfig *config, int32_t device, void *const *key_ptrs,
+                            void *const *value_ptrs, PagedAttnCache **out) {
+  return cache_wrap_impl(config, device, true, key_ptrs, value_ptrs, out);
+}
+int32_t pa_cache_is_fp8(const PagedAttnCache *c) { return c && c->fp8 ? 1 : 0; }
+pa_status pa_cache_set_kv_scales(PagedAttnCache *c, uint32_t layer, float k_scale, float v_scale) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (!c->fp8) return fail(PA_ERR_INVALID_ARG, "scales apply to an FP8 cache only");
+  if (!(k_scale > 0.f) || !(v_scale > 0.f) || std::isinf(k_scale) || std::isinf(v_scale))
+    return fail(PA_ERR_INVALID_ARG, "scales must be finite and > 0");
+  c->k_scale[layer] = k_scale;
+  c->v_scale[layer] = v_scale;
+  return PA_OK;
+}
+pa_status pa_cache_fp8_set_exact_decode(PagedAttnCache *c, int32_t on) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  if (!c->fp8) return fail(PA_ERR_INVALID_ARG, "not an FP8 cache");
+  DeviceGuard g(c->device);
+  const unsigned word = on ? 1u : 0u;
+  PA_CUDA(cudaMemcpy(c->fp8_special(), &word, sizeof(word), cudaMemcpyHostToDevice));
+  return PA_OK;
+}
+pa_status pa_cache_get_kv_scales(const PagedAttnCache *c, uint32_t layer, float *k_scale,
+                                 float *v_scale) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (!k_scale || !v_scale) return fail(PA_ERR_INVALID_ARG, "null argument");
+  *k_scale = c->fp8 ? c->k_scale[layer] : 1.f;
+  *v_scale = c->fp8 ? c->v_scale[layer] : 1.f;
+  return PA_OK;
+}
+
+static pa_status cache_create_impl(const PagedAttnConfig *config, int32_t device, bool fp8,
+                                   PagedAttnCache **out) {
   if (!out) return fail(PA_ERR_INVALID_ARG, "out_cache is null");
   *out = nullptr;
   pa_status st = validate_config(config);
@@ -194,7 +255,10 @@ pa_status pa_cache_create(const PagedAttnConfig *config, int32_t device, PagedAt
   c->cfg = *config;
   c->device = device;
   c->owns = true;
-  const size_t bytes = layer_bytes(*config);
+  c->fp8 = fp8;
+  c->k_scale.assign(config->num_layers, 1.f);
+  c->v_scale.assign(config->num_layers, 1.f);
+  const size_t bytes = layer_bytes(*config, fp8);
   for (uint32_t i = 0; i < config->num_layers; i++) {
     void *kp = nullptr, *vp = nullptr;
     cudaError_t e = cudaMalloc(&kp, bytes);
@@ -222,8 +286,9 @@ pa_status pa_cache_create(const PagedAttnConfig *config, int32_t device, PagedAt
   return PA_OK;
 }
 
-pa_status pa_cache_wrap(const PagedAttnConfig *config, int32_t device, void *const *key_ptrs,
-                        void *const *value_ptrs, PagedAttnCache **out) {
+static pa_status cache_wrap_impl(const PagedAttnConfig *config, int32_t device, bool fp8,
+                                 void *const *key_ptrs, void *const *value_ptrs,
+                                 PagedAttnCache **out) {
   if (!out) return fail(PA_ERR_INVALID_ARG, "out_cache is null");
   *out = nullptr;
   pa_status st = validate_config(config);
@@ -241,9 +306,13 @@ pa_status pa_cache_wrap(const PagedAttnConfig *config, int32_t device, void *con
   c->cfg = *config;
   c->device = device;
   c->owns = false;
+  c->fp8 = fp8;
+  c->k_scale.assign(config->num_layers, 1.f);
+  c->v_scale.assign(config->num_layers, 1.f);
   c->k.assign(key_ptrs, key_ptrs + config->num_layers);
   c->v.assign(value_ptrs, value_ptrs + config->num_layers);
   st = finish_create(c);
+  if (st == PA_OK && fp8) st = pa_cache_fp8_set_exact_decode(c, 1);  // contents unknown
   if (st != PA_OK) {
     std::string keep = t_err;
     pa_cache_free(c);
@@ -315,11 +384,82 @@ pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *ke
     return fail(PA_ERR_INVALID_ARG, "key/value must be 16-byte aligned");
   if (num_tokens > ((int64_t)1 << 34)) return fail(PA_ERR_INVALID_ARG, "num_tokens too large");
   DeviceGuard g(c->device);
+  if (c->fp8) {
+    PA_CUDA(pa::launch_reshape_and_cache_fp8(
+        static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
+        static_cast<uint8_t *>(c->k[layer]), static_cast<uint8_t *>(c->v[layer]), slot_mapping,
+        num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads, c->cfg.num_blocks,
+        c->k_scale[layer], c->v_scale[layer], c->cfg.dtype == 0, c->err_dev, c->fp8_special(),
+        static_cast<cudaStream_t>(cuda_stream)));
+    return PA_OK;
+  }
   PA_CUDA(pa::launch_reshape_and_cache(
       static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
       static_cast<pa::elem16 *>(c->k[layer]), static_cast<pa::elem16 *>(c->v[layer]),
       slot_mapping, num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads,
       c->cfg.num_blocks, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
+  return PA_OK;
+}
+
+pa_status pa_qk_norm_rope_and_cache(PagedAttnCache *c, uint32_t layer, void *q_out, const void *q,
+                                    const void *k, const void *v, const void *q_norm_weight,
+                                    const void *k_norm_weight, float eps,
+                                    const int32_t *positions, float rope_base,
+                                    uint32_t rope_dims, const int64_t *slot_mapping,
+                                    int64_t num_tokens, int32_t num_q_heads, int64_t q_stride,
+                                    int64_t q_out_stride, int64_t k_stride, int64_t v_stride,
+                                    void *cuda_stream) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_tokens < 0) return fail(PA_ERR_INVALID_ARG, "num_tokens < 0");
+  if (num_tokens == 0) return PA_OK;
+  if (!q_out || !q || !k || !v || !positions || !slot_mapping)
+    return fail(PA_ERR_INVALID_ARG, "null tensor pointer");
+  const int Hkv = (int)c->cfg.num_kv_heads, D = (int)c->cfg.head_size;
+  if (num_q_heads <= 0 || num_q_heads % Hkv)
+    return fail(PA_ERR_INVALID_ARG, "num_q_heads must be a positive multiple of num_kv_heads");
+  if (rope_dims > (uint32_t)D || (rope_dims & 1))
+    return fail(PA_ERR_INVALID_ARG, "rope_dims must be even and <= head_size");
+  if (!(rope_base > 0.f) || !(eps >= 0.f)) return fail(PA_ERR_INVALID_ARG, "bad rope_base or eps");
+  const int64_t q_row = (int64_t)num_q_heads * D, kv_row = (int64_t)Hkv * D;
+  if (q_stride < q_row || q_out_stride < q_row || k_stride < kv_row || v_stride < kv_row ||
+      ((q_stride | q_out_stride | k_stride | v_stride) & 7))
+    return fail(PA_ERR_INVALID_ARG, "row strides must cover a row and be multiples of 8");
+  if (!aligned16(q) || !aligned16(q_out) || !aligned16(k) || !aligned16(v) ||
+      (q_norm_weight && !aligned16(q_norm_weight)) || (k_norm_weight && !aligned16(k_norm_weight)))
+    return fail(PA_ERR_INVALID_ARG, "tensors must be 16-byte aligned");
+  if (num_tokens > ((int64_t)1 << 34)) return fail(PA_ERR_INVALID_ARG, "num_tokens too large");
+  if (c->fp8)
+    return fail(PA_ERR_UNSUPPORTED, "the fused producer writes 16-bit pools; with an FP8 cache "
+                                    "rotate into a buffer and call pa_reshape_and_cache");
+  pa::ProducerParams p{};
+  p.q_in = static_cast<const pa::elem16 *>(q);
+  p.q_out = static_cast<pa::elem16 *>(q_out);
+  p.k = static_cast<const pa::elem16 *>(k);
+  p.v = static_cast<const pa::elem16 *>(v);
+  p.q_norm_w = static_cast<const pa::elem16 *>(q_norm_weight);
+  p.k_norm_w = static_cast<const pa::elem16 *>(k_norm_weight);
+  p.positions = positions;
+  p.slot_mapping = slot_mapping;
+  p.k_pool = static_cast<pa::elem16 *>(c->k[layer]);
+  p.v_pool = static_cast<pa::elem16 *>(c->v[layer]);
+  p.num_tokens = num_tokens;
+  p.q_stride = q_stride;
+  p.q_out_stride = q_out_stride;
+  p.k_stride = k_stride;
+  p.v_stride = v_stride;
+  p.Hq = num_q_heads;
+  p.Hkv = Hkv;
+  p.rope_dims = (int)rope_dims;
+  p.num_blocks = c->cfg.num_blocks;
+  p.eps = eps;
+  p.err = c->err_dev;
+  const int half = (int)rope_dims / 2;
+  for (int i = 0; i < half; i++)
+    p.inv_freq[i] = (float)std::pow((double)rope_base, -(double)i / (double)half);
+  DeviceGuard g(c->device);
+  PA_CUDA(pa::launch_qk_norm_rope_cache(p, c->cfg.dtype == 0, c->num_sms,
+                                        static_cast<cudaStream_t>(cuda_stream)));
   return PA_OK;
 }
 
@@ -331,7 +471,7 @@ pa_status pa_copy_blocks(PagedAttnCache *c, uint32_t layer, const int64_t *mappi
   if (num_pairs == 0) return PA_OK;
   if (!mapping) return fail(PA_ERR_INVALID_ARG, "block_mapping is null");
   DeviceGuard g(c->device);
-  const int64_t bpb = (int64_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2;
+  const int64_t bpb = block_bytes_of(c);
   PA_CUDA(pa::launch_copy_blocks(static_cast<pa::elem16 *>(c->k[layer]),
                                  static_cast<pa::elem16 *>(c->v[layer]), mapping, num_pairs, bpb,
                                  c->cfg.num_blocks, c->err_dev,
@@ -382,7 +522,7 @@ PaCpuBlockCache *pa_cpu_cache_create(const PagedAttnCache *c) {
   PaCpuBlockCache *cpu = new (std::nothrow) PaCpuBlockCache();
   if (!cpu) return nullptr;
   cpu->device = c->device;
-  cpu->block_bytes = (size_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2;
+  cpu->block_bytes = (size_t)block_bytes_of(c);
   return cpu;
 }
 void pa_cpu_cache_free(PaCpuBlockCache *cpu) {
@@ -420,7 +560,7 @@ static pa_status swap_impl(PagedAttnCache *c, uint32_t layer, const uint32_t *id
   if (n == 0) return PA_OK;
   if (!ids) return fail(PA_ERR_INVALID_ARG, "block_ids is null");
   if (cpu->device != c->device ||
-      cpu->block_bytes != (size_t)c->cfg.num_kv_heads * c->cfg.head_size * c->cfg.block_size * 2)
+      cpu->block_bytes != (size_t)block_bytes_of(c))
     return fail(PA_ERR_INVALID_ARG, "cpu cache was created for a different cache geometry");
   DeviceGuard g(c->device);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
@@ -539,6 +679,10 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.err = c->err_dev;
   p.seq_base = 0;
   p.is_f16 = c->cfg.dtype == 0 ? 1 : 0;
+  p.is_fp8 = c->fp8 ? 1 : 0;
+  p.k_scale = c->fp8 ? c->k_scale[layer] : 1.f;
+  p.v_scale = c->fp8 ? c->v_scale[layer] : 1.f;
+  p.fp8_special = c->fp8_special();
   p.early_trigger = 1;
 
   if (!cu_q_lens_host) {  // decode: one query per sequence
@@ -568,8 +712,13 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
     const double kv = context_lens_host ? (double)context_lens_host[s] : 0.0;
     if (ql * G <= split_cols) {
       have_class[(ql * G - 1) / 8] = true;
-      split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * 2.0;
+      split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
     } else {
+      if (c->fp8)
+        return fail(PA_ERR_UNSUPPORTED,
+                    "with an FP8 cache a sequence may hold at most " +
+                        std::to_string(split_cols / G) + " query tokens per call (the tile "
+                        "kernel for long chunks reads 16-bit pools only)");
       // Tiles of one (sequence, kv head) are neighbours in launch order so that they
       // share the head's KV blocks in L2; later tiles see more keys and go first.
       for (int h = 0; h < Hkv; h++)

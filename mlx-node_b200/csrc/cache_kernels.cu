@@ -104,6 +104,153 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
   return cudaGetLastError();
 }
 
+// ---- FP8 (E4M3) cache write -----------------------------------------------------
+// Encoder of the reference's byte format, crates/mlx-paged-attn/metal/float8.metal:63-121:
+// bias 7, exponent field 15 is infinity / NaN (largest finite value 240).  Normal range:
+// round to nearest even, overflow to the infinity code.  Below it: magnitudes under 2^-9
+// become zero, the rest round half up, and a
+// value that would round up to the smallest normal number comes out as zero (the result is
+// masked to the three mantissa bits).  Inputs of magnitude 256 and above miss the normal
+// range test and take the below-normal branch as well; for magnitudes below 16384 that
+// yields the low three bits of a shifted mantissa, which is kept as is so that the bytes
+// match; above, where the reference's shift count turns negative, the infinity code.
+__device__ __forceinline__ uint32_t fp8_e4m3_encode_ref(float f) {
+  const uint32_t bits = __float_as_uint(f);
+  const uint32_t s = (bits >> 31) << 7, a = bits & 0x7FFFFFFFu;
+  if (a >= 0x7F800000u) return s | 0x78u | (a != 0x7F800000u);
+  const int e8 = (int)(a >> 23) - 120;
+  const uint32_t m = a & 0x7FFFFFu;
+  if (e8 >= 1 && e8 <= 14) {
+    uint32_t mant = m >> 20;
+    mant += ((m >> 19) & 1u) & (((m & 0x7FFFFu) != 0u) | (mant & 1u));
+    uint32_t e = (uint32_t)e8;
+    if (mant >> 3) {
+      mant = 0;
+      if (++e > 14u) return s | 0x78u;
+    }
+    return s | (e << 3) | mant;
+  }
+  if (e8 < -2) return s;
+  const int rshift = 21 - e8;
+  if (rshift < 1) return s | 0x78u;
+  return s | ((((0x800000u | m) + (1u << (rshift - 1))) >> rshift) & 7u);
+}
+
+// Eight 16-bit elements (one uint4) -> eight bytes: x / scale in fp32 (IEEE division),
+// rounded to the input type, then encoded
+// (crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:88-92).
+template <bool F16>
+__device__ __forceinline__ uint2 quantise8(uint4 v, float scale) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const uint32_t bits16 = (w[i >> 1] >> ((i & 1) * 16)) & 0xffffu;
+    float x;
+    if (F16) asm("cvt.f32.f16 %0, %1;" : "=f"(x) : "h"((uint16_t)bits16));
+    else x = __uint_as_float(bits16 << 16);
+    const uint32_t r16 = to_elem<F16>(__fdiv_rn(x, scale));
+    float y;
+    if (F16) asm("cvt.f32.f16 %0, %1;" : "=f"(y) : "h"((uint16_t)r16));
+    else y = __uint_as_float(r16 << 16);
+    out[i >> 2] |= fp8_e4m3_encode_ref(y) << ((i & 3) * 8);
+  }
+  return make_uint2(out[0], out[1]);
+}
+
+// Same decomposition as reshape_and_cache_kernel; the pools hold bytes, K as
+// [block][head][D/16][BS][16] and V as [block][head][D][BS]
+// (crates/mlx-paged-attn/src/cache_engine.rs:66-90).
+template <bool F16>
+__global__ void __launch_bounds__(256)
+reshape_and_cache_fp8_kernel(const elem16 *__restrict__ key, const elem16 *__restrict__ value,
+                             uint8_t *__restrict__ k_pool, uint8_t *__restrict__ v_pool,
+                             const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
+                             int64_t key_stride, int64_t value_stride, int Hkv,
+                             uint32_t num_blocks, float k_scale, float v_scale, unsigned *err,
+                             unsigned *special_flag) {
+  __shared__ uint2 k_s[kTokPerCta][kHeadSize / 8];                   // 16 x 128 B
+  __shared__ __align__(8) uint8_t v_s[kTokPerCta][kHeadSize + 8];    // padded rows
+  __shared__ int64_t slot_s[kTokPerCta];
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int h = blockIdx.y;
+  const int64_t t0 = (int64_t)blockIdx.x * kTokPerCta;
+  const int tid = threadIdx.x;
+  const int64_t n_slots = (int64_t)num_blocks * kBlockSize;
+  if (tid < kTokPerCta) {
+    int64_t s = -1;
+    if (t0 + tid < num_tokens) {
+      s = slot_mapping[t0 + tid];
+      if (s >= n_slots) {
+        atomicOr(err, kErrSlotRange);
+        s = -1;
+      }
+    }
+    slot_s[tid] = s;
+  }
+  {
+    const int tok = tid >> 4, piece = tid & 15;
+    if (t0 + tok < num_tokens) {
+      const uint4 kv = *reinterpret_cast<const uint4 *>(key + (t0 + tok) * key_stride +
+                                                        (int64_t)h * kHeadSize + piece * 8);
+      const uint4 vv = *reinterpret_cast<const uint4 *>(value + (t0 + tok) * value_stride +
+                                                        (int64_t)h * kHeadSize + piece * 8);
+      const uint2 kq = quantise8<F16>(kv, k_scale), vq = quantise8<F16>(vv, v_scale);
+      k_s[tok][piece] = kq;
+      *reinterpret_cast<uint2 *>(&v_s[tok][piece * 8]) = vq;
+      // An exponent-15 byte (overflow, infinity or NaN going in) switches the attention
+      // kernels of this cache to their exact decoding variant.  Tokens whose slot is
+      // skipped count too; the flag only ever errs on the slow side.
+      auto has15 = [](uint32_t w) { return (((w & 0x78787878u) + 0x08080808u) & 0x80808080u) != 0u; };
+      if (has15(kq.x) | has15(kq.y) | has15(vq.x) | has15(vq.y)) atomicOr(special_flag, 1u);
+    }
+  }
+  __syncthreads();
+  constexpr int kChunk8 = kHeadSize * kBlockSize;  // bytes per (block, head) chunk
+  if (tid < 128) {  // K: 16 bytes of (token, d/16)
+    const int tok = tid & 15, c = tid >> 4;
+    const int64_t slot = slot_s[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kBlockSize;
+      const int off = (int)(slot % kBlockSize);
+      uint8_t *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunk8 + c * (kBlockSize * 16) + off * 16;
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(k_s[tok][2 * c].x, k_s[tok][2 * c].y,
+                                                   k_s[tok][2 * c + 1].x, k_s[tok][2 * c + 1].y);
+    }
+  }
+  for (int e = tid; e < kTokPerCta * kHeadSize; e += 256) {
+    const int tok = e & 15, d = e >> 4;
+    const int64_t slot = slot_s[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kBlockSize;
+      const int off = (int)(slot % kBlockSize);
+      v_pool[(blk * Hkv + h) * (int64_t)kChunk8 + d * kBlockSize + off] = v_s[tok][d];
+    }
+  }
+}
+
+cudaError_t launch_reshape_and_cache_fp8(const elem16 *key, const elem16 *value, uint8_t *k_pool,
+                                         uint8_t *v_pool, const int64_t *slot_mapping,
+                                         int64_t num_tokens, int64_t key_stride,
+                                         int64_t value_stride, int Hkv, uint32_t num_blocks,
+                                         float k_scale, float v_scale, bool f16, unsigned *err,
+                                         unsigned *special_flag, cudaStream_t st) {
+  if (num_tokens <= 0) return cudaSuccess;
+  const int64_t groups = (num_tokens + kTokPerCta - 1) / kTokPerCta;
+  dim3 grid((unsigned)groups, (unsigned)Hkv);
+  if (f16)
+    reshape_and_cache_fp8_kernel<true><<<grid, 256, 0, st>>>(
+        key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride, value_stride, Hkv,
+        num_blocks, k_scale, v_scale, err, special_flag);
+  else
+    reshape_and_cache_fp8_kernel<false><<<grid, 256, 0, st>>>(
+        key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride, value_stride, Hkv,
+        num_blocks, k_scale, v_scale, err, special_flag);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
 // One CTA per (pair, 4 KB piece): K piece then V piece, 16 bytes per thread.
 // Pairs are independent unless a destination is also a source of a later pair;
 // the reference processes pairs in parallel as well (one threadgroup per pair).

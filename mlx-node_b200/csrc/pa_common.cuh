@@ -134,6 +134,9 @@ struct AttnParams {
   const int32_t *cu_q_lens;     // [S+1] device copy, or null: one query per sequence
   int S, Hq, Hkv, G, MB;
   int is_f16;  // element format: 1 = f16, 0 = bf16
+  int is_fp8;  // pools hold E4M3 bytes (split-KV kernels only); is_f16 is then the q/out format
+  float k_scale, v_scale;  // FP8 dequantisation factors; 1 otherwise
+  const unsigned *fp8_special;  // FP8: non-zero once the pools may hold an exponent-15 byte
   int early_trigger;  // split-KV: let the merge grid become resident at once
   uint32_t num_blocks;  // pool size, for range checks
   int64_t q_stride, out_stride;
@@ -146,12 +149,40 @@ struct AttnParams {
   int max_cols;
 };
 
+// Producer (QK norm + rotary embedding + KV write) launch parameters.
+struct ProducerParams {
+  const elem16 *q_in;      // [T, Hq, 128] projected queries
+  elem16 *q_out;           // rotated queries; may alias q_in
+  const elem16 *k;         // [T, Hkv, 128] projected keys
+  const elem16 *v;         // [T, Hkv, 128] projected values
+  const elem16 *q_norm_w;  // [128] or null: no query norm
+  const elem16 *k_norm_w;  // [128] or null: no key norm
+  const int32_t *positions;     // [T] rotary position of each token
+  const int64_t *slot_mapping;  // [T] pool slot of each token (< 0: not written)
+  elem16 *k_pool, *v_pool;
+  int64_t num_tokens, q_stride, q_out_stride, k_stride, v_stride;
+  int tok_per_cta;         // 1..16, chosen by the launcher
+  int Hq, Hkv, rope_dims;  // rope_dims even, <= 128; elements beyond pass through
+  uint32_t num_blocks;
+  float eps;
+  unsigned *err;
+  float inv_freq[kHeadSize / 2];  // base^(-i/(rope_dims/2)), computed on the host
+};
+
 // Host-side launchers (defined next to their kernels).
+cudaError_t launch_qk_norm_rope_cache(const ProducerParams &p, bool f16, int num_sms,
+                                      cudaStream_t st);
 cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
                                      elem16 *k_pool, elem16 *v_pool,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
                                      uint32_t num_blocks, unsigned *err, cudaStream_t st);
+cudaError_t launch_reshape_and_cache_fp8(const elem16 *key, const elem16 *value, uint8_t *k_pool,
+                                         uint8_t *v_pool, const int64_t *slot_mapping,
+                                         int64_t num_tokens, int64_t key_stride,
+                                         int64_t value_stride, int Hkv, uint32_t num_blocks,
+                                         float k_scale, float v_scale, bool f16, unsigned *err,
+                                         unsigned *special_flag, cudaStream_t st);
 cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
                                const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
                                uint32_t num_blocks, unsigned *err, cudaStream_t st);

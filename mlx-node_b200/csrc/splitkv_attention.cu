@@ -36,6 +36,7 @@
 // S^T accumulators with one movmatrix transpose per 8x8 tile.  Online softmax in
 // fp32 with exp2; column maxima by warp shuffles.
 #include <mutex>
+#include <type_traits>
 
 #include "pa_common.cuh"
 
@@ -46,12 +47,15 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxSeqsPerLaunch = 2048;
-constexpr int kStageBytes = 2 * kChunkBytes;
 constexpr int kMaxNT = 3;  // up to 24 columns per item
 
-template <int NT>
+// FP8: an E4M3 cache, one byte per element; a unit is a 2 KB K chunk laid out
+// [D/16][BS][16] plus a 2 KB V chunk [D][BS], and the ring holds twice as many stages.
+template <int NT, bool FP8 = false>
 struct Cfg {
-  static constexpr int kStages = NT == 1 ? 3 : 2;
+  static constexpr int kChunk = FP8 ? kChunkBytes / 2 : kChunkBytes;  // bytes of one K or V chunk
+  static constexpr int kStageBytes = 2 * kChunk;
+  static constexpr int kStages = (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1);
   static constexpr int kRegs = 36 * NT;  // per thread: 32NT accumulators, 2NT maxima, 2NT sums
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
   static constexpr int kMergeBytes = (kWarps / 2) * kRegs * 32 * 4;
@@ -73,10 +77,45 @@ __device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
   return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
 }
 
-template <int NT, bool F16>
+// Four cache bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3) holding value / 256,
+// by integer operations only: with the byte in the high half of a 16-bit lane, sign
+// stays at bit 15 and the seven exponent/mantissa bits move down one place, which reads
+// as an f16 with the E4M3 exponent field taken at bias 15 instead of 7 (subnormals
+// included); the factor 2^8 is folded into the scales.  (The conversion instruction
+// cvt.rn.f16x2.e4m3x2 measured about four times slower than this in this kernel.)
+// The cache format (crates/mlx-paged-attn/metal/float8.metal:11-33) reads exponent
+// field 15 as infinity (mantissa 0) or NaN; EXACT restores that by raising the f16
+// exponent field from 15 to 31.  The fast variant is used while the cache is known to
+// hold no such byte.
+template <bool EXACT>
+__device__ __forceinline__ void fp8x4_to_f16(uint32_t w, uint32_t &lo, uint32_t &hi) {
+  const uint32_t xa = __byte_perm(w, 0u, 0x1404u);  // b1 << 24 | b0 << 8
+  const uint32_t xb = __byte_perm(w, 0u, 0x3424u);  // b3 << 24 | b2 << 8
+  lo = ((xa & 0x7F007F00u) >> 1) | (xa & 0x80008000u);
+  hi = ((xb & 0x7F007F00u) >> 1) | (xb & 0x80008000u);
+  if (EXACT) {
+    lo |= ((lo & 0x3C003C00u) + 0x04000400u) & 0x40004000u;
+    hi |= ((hi & 0x3C003C00u) + 0x04000400u) & 0x40004000u;
+  }
+}
+constexpr float kFp8Unbias = 256.f;  // the factor the conversion above leaves out
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+  return pack2<true>(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+// FP8 path: row r of a 16-token MMA tile holds token fp8_row_token(r) of the block, so
+// that the token pairs a thread gets from one 32-bit piece of a V row (tokens 4t..4t+3)
+// are the pairs its P^T fragment holds.
+__device__ __forceinline__ int fp8_row_token(int r) {
+  return 4 * ((r & 7) >> 1) + 2 * (r >> 3) + (r & 1);
+}
+
+template <int NT, bool F16, bool FP8>
 __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p) {
-  using C = Cfg<NT>;
+  using C = Cfg<NT, FP8>;
   constexpr int NST = C::kStages;
+  constexpr int kStageBytes = C::kStageBytes;
+  constexpr int kChunk = C::kChunk;
+  constexpr bool MF16 = F16 || FP8;  // operand type of the MMAs
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t *ring = smem;
   float *merge_buf = reinterpret_cast<float *>(smem + C::kRingBytes);
@@ -152,6 +191,10 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
   // pool (and the workspace and output rows a previous call may still be reading or
   // writing) must not be touched before the predecessor has completed.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // FP8: one pass of the main loop is compiled per decoding variant; which one runs is
+  // decided by a device word the cache write sets when it produces an exponent-15 byte.
+  auto main_loop = [&](auto exact_tag) {
+    constexpr bool EXACT = decltype(exact_tag)::value;
   const uint32_t ring_w = smem_u32(ring) + warp * NST * kStageBytes;
   const uint32_t bar_w = smem_u32(&bars[warp * NST]);
   uint32_t cur_ids = lookup(lane), nxt_ids = lookup(32 + lane);
@@ -166,8 +209,10 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
       const int st = ji % NST;
       const uint32_t bar = bar_w + st * 8, dst = ring_w + st * kStageBytes;
       mbar_expect_tx(bar, kStageBytes);
-      bulk_g2s(dst, p.k_pool + (size_t)chunk * kChunkElems, kChunkBytes, bar);
-      bulk_g2s(dst + kChunkBytes, p.v_pool + (size_t)chunk * kChunkElems, kChunkBytes, bar);
+      bulk_g2s(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk, kChunk,
+               bar);
+      bulk_g2s(dst + kChunk, reinterpret_cast<const uint8_t *>(p.v_pool) + (size_t)chunk * kChunk,
+               kChunk, bar);
     }
     ji++;
   };
@@ -175,7 +220,10 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
 
   int jc = 0;          // units consumed by this warp
   bool dead = false;   // a wait ran out: stop touching data, keep the barriers balanced
-  const float sc_log2 = p.scale * kLog2e;
+  // k_scale: FP8 dequantisation (with the conversion's missing 2^8), else 1
+  const float qk_scale = p.scale * p.k_scale * (FP8 ? kFp8Unbias : 1.f);
+  const float v_unscale = p.v_scale * (FP8 ? kFp8Unbias : 1.f);
+  const float sc_log2 = qk_scale * kLog2e;
   const bool use_cap = p.softcap != 1.0f;
 
   // ---- walk the segments of [lo, hi) -----------------------------------------
@@ -209,8 +257,16 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
             p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-          qf[nt][j][0] = __ldg(qp + 8 * j + tig);
-          qf[nt][j][1] = __ldg(qp + 8 * j + 4 + tig);
+          if (FP8) {
+            // k-slots {2tig, 2tig+1, 2tig+8, 2tig+9} of step j carry d = 16j + 4tig .. +3,
+            // the four bytes a thread gets from one 16-byte K row piece
+            const uint2 w = __ldg(reinterpret_cast<const uint2 *>(qp) + 4 * j + tig);
+            qf[nt][j][0] = F16 ? w.x : bf16x2_to_f16x2(w.x);
+            qf[nt][j][1] = F16 ? w.y : bf16x2_to_f16x2(w.y);
+          } else {
+            qf[nt][j][0] = __ldg(qp + 8 * j + tig);
+            qf[nt][j][1] = __ldg(qp + 8 * j + 4 + tig);
+          }
         }
       } else {
 #pragma unroll
@@ -247,20 +303,40 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         }
       }
       if (!dead) {
-        const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunkBytes;
+        const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunk;
         float sacc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
           for (int i = 0; i < 4; i++) sacc[nt][i] = 0.f;
+        if (FP8) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          uint32_t af[4];
-          ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
+          for (int jj = 0; jj < 4; jj++) {
+            // matrices: (rows 0-7, step 2jj), (rows 8-15, step 2jj), then the same of step 2jj+1;
+            // a row of a matrix is the 16 bytes (one whole k-step) of one token
+            uint32_t r[4];
+            ldmatrix_x4(r, ks + (2 * jj + (mi >> 1)) * 256 + fp8_row_token((mi & 1) * 8 + mr) * 16);
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++) mma_16816<F16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
+            for (int hf = 0; hf < 2; hf++) {
+              uint32_t af[4];
+              fp8x4_to_f16<EXACT>(r[2 * hf], af[0], af[2]);
+              fp8x4_to_f16<EXACT>(r[2 * hf + 1], af[1], af[3]);
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++)
+                mma_16816<MF16>(sacc[nt], af, qf[nt][2 * jj + hf][0], qf[nt][2 * jj + hf][1]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            uint32_t af[4];
+            ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
+          }
         }
-        const int tok0 = blk * kBlockSize + gid, tok1 = tok0 + 8;
+        const int tok0 = blk * kBlockSize + (FP8 ? fp8_row_token(gid) : gid);
+        const int tok1 = FP8 ? tok0 + 2 : tok0 + 8;
         const bool need_mask = (blk + 1) * kBlockSize > min_lim;
         float alpha[NT][2];
 #pragma unroll
@@ -268,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             float x = sacc[nt][i];
-            if (use_cap) x = tanhf(x * p.scale / p.softcap) * p.softcap * kLog2e;
+            if (use_cap) x = tanhf(x * qk_scale / p.softcap) * p.softcap * kLog2e;
             else x *= sc_log2;
             sacc[nt][i] = x;
           }
@@ -299,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         uint32_t pb[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-          pb[nt][0] = movmatrix_trans(pack2<F16>(sacc[nt][0], sacc[nt][1]));
-          pb[nt][1] = movmatrix_trans(pack2<F16>(sacc[nt][2], sacc[nt][3]));
+          pb[nt][0] = movmatrix_trans(pack2<MF16>(sacc[nt][0], sacc[nt][1]));
+          pb[nt][1] = movmatrix_trans(pack2<MF16>(sacc[nt][2], sacc[nt][3]));
         }
         // Tokens past the context in the last block may hold anything (NaN
         // included) and 0*NaN is NaN: clear them in the V fragments
@@ -308,22 +384,52 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         const int valid = kv_len - blk * kBlockSize;  // >= 1
         uint32_t vmask[2] = {0xffffffffu, 0xffffffffu};
         if (valid < kBlockSize) {
+          if (FP8) {  // one byte per token; a thread's piece holds tokens 4tig .. 4tig+3
+            vmask[0] = 0u;
 #pragma unroll
-          for (int hh = 0; hh < 2; hh++) {
-            const int t = hh * 8 + 2 * tig;
-            vmask[hh] = (t < valid ? 0x0000ffffu : 0u) | (t + 1 < valid ? 0xffff0000u : 0u);
+            for (int i = 0; i < 4; i++)
+              if (4 * tig + i < valid) vmask[0] |= 0xffu << (8 * i);
+          } else {
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+              const int t = hh * 8 + 2 * tig;
+              vmask[hh] = (t < valid ? 0x0000ffffu : 0u) | (t + 1 < valid ? 0xffff0000u : 0u);
+            }
           }
         }
+        if (FP8) {
 #pragma unroll
-        for (int mt = 0; mt < 8; mt++) {
-          uint32_t vf[4];
-          ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
-          vf[0] &= vmask[0]; vf[1] &= vmask[0]; vf[2] &= vmask[1]; vf[3] &= vmask[1];
+          for (int mm = 0; mm < 4; mm++) {
+            // matrices: d rows 0-7 and 8-15 of m-tile 2mm, then of m-tile 2mm+1; a row is
+            // the 16 tokens of one head dimension
+            uint32_t r[4];
+            ldmatrix_x4(r, vs + (32 * mm + (mi >> 1) * 16 + (mi & 1) * 8 + mr) * 16);
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
-            o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
-            mma_16816<F16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+            for (int hf = 0; hf < 2; hf++) {
+              const int mt = 2 * mm + hf;
+              uint32_t vf[4];
+              fp8x4_to_f16<EXACT>(r[2 * hf] & vmask[0], vf[0], vf[2]);
+              fp8x4_to_f16<EXACT>(r[2 * hf + 1] & vmask[0], vf[1], vf[3]);
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) {
+                o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
+                o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
+                mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int mt = 0; mt < 8; mt++) {
+            uint32_t vf[4];
+            ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
+            vf[0] &= vmask[0]; vf[1] &= vmask[0]; vf[2] &= vmask[1]; vf[3] &= vmask[1];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
+              o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
+              mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+            }
           }
         }
       }
@@ -395,7 +501,8 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
 #pragma unroll
           for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) dst[((mt * NT + nt) * 4 + i) * 32] = o[mt][nt][i];
+            for (int i = 0; i < 4; i++)
+              dst[((mt * NT + nt) * 4 + i) * 32] = FP8 ? o[mt][nt][i] * v_unscale : o[mt][nt][i];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -411,7 +518,8 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
             const int col = nt * 8 + 2 * tig + c;
             if (col < ncols) {
               const int qj = col / G, g = col - qj * G;
-              const float inv = l[nt][c] > 0.f ? 1.f / l[nt][c] : 0.f;
+              float inv = l[nt][c] > 0.f ? 1.f / l[nt][c] : 0.f;
+              if (FP8) inv *= v_unscale;
               elem16 *op = p.out + (int64_t)(q0 + qj) * p.out_stride +
                                   (int64_t)(h * G + g) * kHeadSize;
 #pragma unroll
@@ -432,6 +540,13 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
       do { s++; } while (s < S && pre[s + 1] == pre[s]);
     }
     if (s < S) nb = pre[s + 1] - pre[s];
+  }
+  };
+  if constexpr (FP8) {
+    if (*p.fp8_special != 0u) main_loop(std::true_type{});
+    else main_loop(std::false_type{});
+  } else {
+    main_loop(std::false_type{});
   }
 }
 
@@ -552,11 +667,17 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 template <int NT>
 cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
-  const cudaError_t e =
-      p.is_f16 ? launch_dependent(splitkv_kernel<NT, true>, dim3(num_ctas), dim3(kThreads),
-                                  Cfg<NT>::kSmemBytes, st, p)
-               : launch_dependent(splitkv_kernel<NT, false>, dim3(num_ctas), dim3(kThreads),
-                                  Cfg<NT>::kSmemBytes, st, p);
+  cudaError_t e;
+  if (p.is_fp8)
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, true>, dim3(num_ctas), dim3(kThreads),
+                                    Cfg<NT, true>::kSmemBytes, st, p)
+                 : launch_dependent(splitkv_kernel<NT, false, true>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT, true>::kSmemBytes, st, p);
+  else
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false>, dim3(num_ctas), dim3(kThreads),
+                                    Cfg<NT>::kSmemBytes, st, p)
+                 : launch_dependent(splitkv_kernel<NT, false, false>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT>::kSmemBytes, st, p);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return e;
 }
@@ -598,11 +719,18 @@ size_t splitkv_workspace_bytes(int num_ctas) {
 
 template <int NT>
 static cudaError_t configure_nt() {
-  cudaError_t e = cudaFuncSetAttribute(splitkv_kernel<NT, false>,
+  cudaError_t e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(splitkv_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Cfg<NT>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, false, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, true>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, true>::kSmemBytes);
+  return e;
 }
 
 cudaError_t splitkv_configure() {

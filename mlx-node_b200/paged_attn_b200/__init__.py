@@ -31,6 +31,8 @@ EXPORTED_SYMBOLS = [
     "mlx_array_shape", "mlx_array_dtype", "mlx_array_delete", "pa_set_device", "pa_set_stream",
     "pa_cache_create", "pa_cache_wrap", "pa_cache_free", "pa_cache_key_ptr", "pa_cache_value_ptr",
     "pa_cache_get_config", "pa_cache_check_errors", "pa_reshape_and_cache", "pa_copy_blocks",
+    "pa_qk_norm_rope_and_cache", "pa_cache_create_fp8", "pa_cache_wrap_fp8", "pa_cache_is_fp8",
+    "pa_cache_set_kv_scales", "pa_cache_get_kv_scales", "pa_cache_fp8_set_exact_decode",
     "pa_attention_workspace_bytes", "pa_paged_attention_decode", "pa_paged_attention_varlen",
     "pa_paged_attention_decode_static", "pa_cpu_cache_create", "pa_cpu_cache_free",
     "pa_cpu_cache_is_swapped", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
@@ -73,6 +75,12 @@ def load_library() -> C.CDLL:
     lib.pa_cache_create.argtypes = [C.POINTER(PagedAttnConfig), i32, C.POINTER(vp)]
     lib.pa_cache_wrap.argtypes = [C.POINTER(PagedAttnConfig), i32, C.POINTER(vp), C.POINTER(vp),
                                   C.POINTER(vp)]
+    lib.pa_cache_create_fp8.argtypes = lib.pa_cache_create.argtypes
+    lib.pa_cache_wrap_fp8.argtypes = lib.pa_cache_wrap.argtypes
+    lib.pa_cache_is_fp8.argtypes = [vp]
+    lib.pa_cache_set_kv_scales.argtypes = [vp, u32, f32, f32]
+    lib.pa_cache_get_kv_scales.argtypes = [vp, u32, C.POINTER(f32), C.POINTER(f32)]
+    lib.pa_cache_fp8_set_exact_decode.argtypes = [vp, i32]
     lib.pa_cache_free.argtypes = [vp]
     lib.pa_cache_key_ptr.argtypes = [vp, u32]
     lib.pa_cache_key_ptr.restype = vp
@@ -102,6 +110,8 @@ def load_library() -> C.CDLL:
     lib.pa_swap_in.argtypes = [vp, u32, C.POINTER(u32), sz, vp, vp]
     lib.pa_swap_block_bytes.argtypes = [u32, u32, u32, i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     lib.pa_swap_block_bytes.restype = None
+    lib.pa_qk_norm_rope_and_cache.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, f32, vp, f32, u32, vp,
+                                              i64, i32, i64, i64, i64, i64, vp]
     lib.pa_decode_step_host.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32]
     # tier 1
     lib.mlx_paged_attn_create_cache.argtypes = [C.POINTER(PagedAttnConfig)]
@@ -169,19 +179,33 @@ class PagedCache:
 
     def __init__(self, block_size: int, num_blocks: int, head_size: int, num_kv_heads: int,
                  num_layers: int = 1, dtype: int = 1, device: int = 0, key_pools=None,
-                 value_pools=None):
+                 value_pools=None, fp8: bool = False):
         self.lib = load_library()
         self.cfg = PagedAttnConfig(block_size, num_blocks, head_size, num_kv_heads, num_layers, dtype)
         self.device = device
         self.handle = C.c_void_p()
         self._keep = (key_pools, value_pools)
+        self.fp8 = fp8
+        create = self.lib.pa_cache_create_fp8 if fp8 else self.lib.pa_cache_create
+        wrap = self.lib.pa_cache_wrap_fp8 if fp8 else self.lib.pa_cache_wrap
         if key_pools is None:
-            _check(self.lib.pa_cache_create(C.byref(self.cfg), device, C.byref(self.handle)))
+            _check(create(C.byref(self.cfg), device, C.byref(self.handle)))
         else:
             kp = (C.c_void_p * num_layers)(*[_ptr(t) for t in key_pools])
             vp = (C.c_void_p * num_layers)(*[_ptr(t) for t in value_pools])
-            _check(self.lib.pa_cache_wrap(C.byref(self.cfg), device, kp, vp, C.byref(self.handle)))
+            _check(wrap(C.byref(self.cfg), device, kp, vp, C.byref(self.handle)))
         self._ws = None
+
+    def set_kv_scales(self, k_scale: float, v_scale: float, layer: int = 0) -> None:
+        _check(self.lib.pa_cache_set_kv_scales(self.handle, layer, k_scale, v_scale))
+
+    def fp8_set_exact_decode(self, on: bool) -> None:
+        _check(self.lib.pa_cache_fp8_set_exact_decode(self.handle, int(on)))
+
+    def kv_scales(self, layer: int = 0):
+        k, v = C.c_float(), C.c_float()
+        _check(self.lib.pa_cache_get_kv_scales(self.handle, layer, C.byref(k), C.byref(v)))
+        return k.value, v.value
 
     def close(self) -> None:
         if self.handle:
@@ -211,6 +235,18 @@ class PagedCache:
         _check(self.lib.pa_reshape_and_cache(self.handle, layer, _ptr(key), _ptr(value),
                                              _ptr(slot_mapping), num_tokens, key_stride,
                                              value_stride, stream))
+
+    def qk_norm_rope_and_cache(self, q_out, q, k, v, q_norm_weight, k_norm_weight, eps: float,
+                               positions, rope_base: float, rope_dims: int, slot_mapping,
+                               num_tokens: int, num_q_heads: int, q_stride: int, q_out_stride: int,
+                               k_stride: int, v_stride: int, layer: int = 0, stream: int = 0) -> None:
+        """QK norm + rotary embedding + KV write in one launch (weights may be None)."""
+        _check(self.lib.pa_qk_norm_rope_and_cache(
+            self.handle, layer, _ptr(q_out), _ptr(q), _ptr(k), _ptr(v),
+            _ptr(q_norm_weight) if q_norm_weight is not None else None,
+            _ptr(k_norm_weight) if k_norm_weight is not None else None, eps, _ptr(positions),
+            rope_base, rope_dims, _ptr(slot_mapping), num_tokens, num_q_heads, q_stride,
+            q_out_stride, k_stride, v_stride, stream))
 
     def copy_blocks(self, block_mapping, num_pairs: int, layer: int = 0, stream: int = 0) -> None:
         _check(self.lib.pa_copy_blocks(self.handle, layer, _ptr(block_mapping), num_pairs, stream))

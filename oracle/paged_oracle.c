@@ -459,3 +459,249 @@ void oracle_fill_normal_bf16(uint16_t *dst, int64_t n, uint64_t seed,
     dst[i] = f32_to_bf16((float)z);
   }
 }
+
+/* ------------------------------------------------------------------------- *
+ * Producer of the write + attend pair: per-head RMS norm, then rotary
+ * embedding at each token's position.  Restates steps 3 and 5 of
+ * mlx_fused_attention_qkv (crates/mlx-sys/src/mlx.cpp:1343-1365) as they act on
+ * one token at offset `positions[t]` (the per-sequence call of
+ * crates/mlx-core/src/transformer/attention.rs:658-664), using the published
+ * arithmetic of MLX's fast::rms_norm (w * T(x * rsqrt(mean(x^2) + eps))) and
+ * fast::rope with traditional = false, scale 1: element i < dims/2 pairs with
+ * i + dims/2, angle = float(position) * inv_freq[i],
+ *   out[i]          = x[i] cos - x[i + dims/2] sin,
+ *   out[i + dims/2] = x[i] sin + x[i + dims/2] cos,
+ * elements >= dims unchanged.  MLX itself is an absent third-party dependency
+ * (git submodule crates/mlx-sys/mlx, no pinned version in the tree).
+ *
+ * The mean of squares, the reciprocal square root and the trigonometric
+ * functions are evaluated in double here; the rounding points (normalised value
+ * to T, times weight to T, rotated value to T) and the fp32 angle are the
+ * reference's.  `bound[t,h,d]` (optional) receives |a| + |b| of the rotated
+ * pair after the norm: a difference of one unit in the last place of either
+ * operand moves the result by at most 2^-8 (bf16) or 2^-11 (f16) of it.
+ * x: [T, H, D] with row stride `stride` elements; w: [D] or NULL; out like x
+ * (contiguous [T, H, D]).
+ * ------------------------------------------------------------------------- */
+static inline uint16_t f32_to_f16(float f) {
+  _Float16 v = (_Float16)f;
+  uint16_t h;
+  memcpy(&h, &v, 2);
+  return h;
+}
+static inline uint16_t f32_to_elem(float f, int is_f16) {
+  return is_f16 ? f32_to_f16(f) : f32_to_bf16(f);
+}
+
+void oracle_qk_norm_rope(uint16_t *out, float *bound, const uint16_t *x, int64_t stride,
+                         const uint16_t *w, double eps, const int32_t *positions,
+                         double rope_base, int rope_dims, int64_t T, int H, int D,
+                         int is_f16) {
+  const int half = rope_dims / 2;
+  float *inv_freq = (float *)malloc(sizeof(float) * (half > 0 ? half : 1));
+  for (int i = 0; i < half; i++)
+    inv_freq[i] = (float)pow(rope_base, -(double)i / (double)half);
+#pragma omp parallel for schedule(static)
+  for (int64_t t = 0; t < T; t++) {
+    double *y = (double *)malloc(sizeof(double) * D);
+    for (int h = 0; h < H; h++) {
+      const uint16_t *xp = x + t * stride + (int64_t)h * D;
+      if (w) {
+        double ss = 0.0;
+        for (int d = 0; d < D; d++) {
+          const double v = elem_to_f32(xp[d], is_f16);
+          ss += v * v;
+        }
+        const double inv = 1.0 / sqrt(ss / D + eps);
+        for (int d = 0; d < D; d++) {
+          const float n = elem_to_f32(f32_to_elem((float)(elem_to_f32(xp[d], is_f16) * inv), is_f16), is_f16);
+          y[d] = elem_to_f32(f32_to_elem(n * elem_to_f32(w[d], is_f16), is_f16), is_f16);
+        }
+      } else {
+        for (int d = 0; d < D; d++) y[d] = elem_to_f32(xp[d], is_f16);
+      }
+      uint16_t *op = out + (t * H + h) * (int64_t)D;
+      float *bp = bound ? bound + (t * H + h) * (int64_t)D : NULL;
+      for (int i = 0; i < half; i++) {
+        const float theta = (float)positions[t] * inv_freq[i];
+        const double c = cos((double)theta), s = sin((double)theta);
+        const double a = y[i], b = y[i + half];
+        op[i] = f32_to_elem((float)(a * c - b * s), is_f16);
+        op[i + half] = f32_to_elem((float)(a * s + b * c), is_f16);
+        if (bp) bp[i] = bp[i + half] = (float)(fabs(a) + fabs(b));
+      }
+      for (int d = 2 * half; d < D; d++) {
+        op[d] = f32_to_elem((float)y[d], is_f16);
+        if (bp) bp[d] = 0.f;
+      }
+    }
+    free(y);
+  }
+  free(inv_freq);
+}
+
+/* ------------------------------------------------------------------------- *
+ * FP8 (E4M3) KV cache.  The pools hold one byte per element, x = 16
+ * (crates/mlx-paged-attn/src/cache_engine.rs:66-76): key cache
+ * [num_blocks, num_kv_heads, head_size/16, block_size, 16], value cache
+ * [num_blocks, num_kv_heads, head_size, block_size].
+ *
+ * The byte format is the reference's own, not the OCP "FN" variant
+ * (crates/mlx-paged-attn/metal/float8.metal:11-33 decode, :63-121 encode):
+ * bias 7; exponent field 15 decodes to infinity (mantissa 0) or NaN, so the
+ * largest finite value is 1.75 * 2^7 = 240.  The encoder rounds the normal
+ * range to nearest even and lets it overflow to the infinity code; below the
+ * normal range magnitudes under 2^-9 become zero, the rest round half up, and a value that would round up to the
+ * smallest normal number is returned as zero (the mantissa is masked to three
+ * bits with the exponent field left at 0).  Inputs with an unbiased exponent
+ * of 8 or more (|x| >= 256) are not in its normal range test and fall into
+ * the same below-normal branch; for 256 <= |x| < 16384 that branch yields the
+ * low three bits of a shifted mantissa, which is restated as is; from 16384 up
+ * the reference's shift count is negative (undefined there) and the infinity
+ * code is produced here instead.
+ * ------------------------------------------------------------------------- */
+float oracle_fp8_e4m3_decode(uint8_t v) {
+  const unsigned s = v >> 7, e = (v >> 3) & 0xF, m = v & 7;
+  float val;
+  if (e == 0) val = ldexpf((float)m / 8.f, -6);
+  else if (e == 0xF) val = m ? NAN : INFINITY;
+  else val = ldexpf(1.f + (float)m / 8.f, (int)e - 7);
+  return s ? -val : val;
+}
+
+uint8_t oracle_fp8_e4m3_encode(float f) {
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  const uint32_t s = bits >> 31, a = bits & 0x7FFFFFFFu;
+  if (a >= 0x7F800000u) return (uint8_t)((s << 7) | 0x78u | (a != 0x7F800000u));
+  const int e8 = (int)(a >> 23) - 127 + 7;
+  const uint32_t m = a & 0x7FFFFFu;
+  if (e8 >= 1 && e8 <= 14) {
+    uint32_t mant = m >> 20;
+    const uint32_t half = (m >> 19) & 1u, rest = (m & 0x7FFFFu) != 0u;
+    mant += half & (rest | (mant & 1u));
+    int e = e8;
+    if (mant >> 3) {
+      mant = 0;
+      if (++e > 14) return (uint8_t)((s << 7) | 0x78u);
+    }
+    return (uint8_t)((s << 7) | ((uint32_t)e << 3) | (mant & 7u));
+  }
+  if (e8 < -2) return (uint8_t)(s << 7);
+  const int rshift = (1 - e8) + 20;
+  if (rshift < 1) return (uint8_t)((s << 7) | 0x78u);
+  const uint32_t rounded = ((0x800000u | m) + (1u << (rshift - 1))) >> rshift;
+  return (uint8_t)((s << 7) | (rounded & 7u));
+}
+
+/* KV block write into an FP8 cache.
+ * crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:58-97, the
+ * USE_FP8_SCALES branch (:88-92): the element is divided by the scale in fp32,
+ * rounded to the input type, and encoded.  Index formulas as in
+ * oracle_reshape_and_cache with x = 16.                                      */
+void oracle_reshape_and_cache_fp8(const uint16_t *key, const uint16_t *value,
+                                  uint8_t *key_cache, uint8_t *value_cache,
+                                  const int64_t *slot_mapping, int64_t num_tokens,
+                                  int64_t key_stride, int64_t value_stride,
+                                  int num_heads, int head_size, int block_size,
+                                  float k_scale, float v_scale, int is_f16) {
+  const int x = 16;
+  for (int64_t token_idx = 0; token_idx < num_tokens; token_idx++) {
+    const int64_t slot_idx = slot_mapping[token_idx];
+    if (slot_idx < 0) continue;
+    const int64_t block_idx = slot_idx / block_size;
+    const int64_t block_offset = slot_idx % block_size;
+    const int n = num_heads * head_size;
+    for (int i = 0; i < n; i++) {
+      const int head_idx = i / head_size, head_offset = i % head_size;
+      const int x_idx = head_offset / x, x_offset = head_offset % x;
+      const int64_t tgt_key_idx =
+          block_idx * num_heads * (head_size / x) * block_size * x +
+          (int64_t)head_idx * (head_size / x) * block_size * x +
+          (int64_t)x_idx * block_size * x + block_offset * x + x_offset;
+      const int64_t tgt_value_idx =
+          block_idx * num_heads * head_size * block_size +
+          (int64_t)head_idx * head_size * block_size +
+          (int64_t)head_offset * block_size + block_offset;
+      const float kq = elem_to_f32(key[token_idx * key_stride + i], is_f16) / k_scale;
+      const float vq = elem_to_f32(value[token_idx * value_stride + i], is_f16) / v_scale;
+      key_cache[tgt_key_idx] =
+          oracle_fp8_e4m3_encode(elem_to_f32(f32_to_elem(kq, is_f16), is_f16));
+      value_cache[tgt_value_idx] =
+          oracle_fp8_e4m3_encode(elem_to_f32(f32_to_elem(vq, is_f16), is_f16));
+    }
+  }
+}
+
+/* Attention over an FP8 cache: element = decode(byte) * scale
+ * (crates/mlx-paged-attn/metal/attention/paged_attention.metal:569-571,
+ * used at :920-929 for K and :1063-1071 for V), everything else as
+ * oracle_paged_attention_varlen_dt, in fp64.  The reference rounds each
+ * dequantised element to the query type before use; that rounding is a
+ * precision loss of its kernel and is not reproduced.                       */
+static void attend_row_fp8(float *o, const uint16_t *qp, const uint8_t *k_cache,
+                           const uint8_t *v_cache, const int32_t *table, int n,
+                           int h, int Hkv, int D, int BS, float scale, float softcap,
+                           double *logit, double *acc, int is_f16, float k_scale,
+                           float v_scale) {
+  const int x = 16;
+  if (n <= 0) {
+    for (int d = 0; d < D; d++) o[d] = 0.f;
+    return;
+  }
+  double mx = -INFINITY;
+  for (int t = 0; t < n; t++) {
+    const int64_t kb = k_index(table, t, h, 0, Hkv, D, BS, x);
+    double dot = 0.0;
+    for (int c = 0; c < D / x; c++)
+      for (int e = 0; e < x; e++)
+        dot += (double)elem_to_f32(qp[c * x + e], is_f16) *
+               ((double)oracle_fp8_e4m3_decode(k_cache[kb + (int64_t)c * BS * x + e]) *
+                (double)k_scale);
+    double l = dot * (double)scale;
+    if (softcap != 1.0f) l = tanh(l / (double)softcap) * (double)softcap;
+    logit[t] = l;
+    if (l > mx) mx = l;
+  }
+  double sum = 0.0;
+  for (int t = 0; t < n; t++) {
+    logit[t] = exp(logit[t] - mx);
+    sum += logit[t];
+  }
+  for (int d = 0; d < D; d++) acc[d] = 0.0;
+  for (int t = 0; t < n; t++) {
+    const double p = logit[t];
+    const int64_t vb = v_index(table, t, h, 0, Hkv, D, BS);
+    for (int d = 0; d < D; d++)
+      acc[d] += p * ((double)oracle_fp8_e4m3_decode(v_cache[vb + (int64_t)d * BS]) *
+                     (double)v_scale);
+  }
+  for (int d = 0; d < D; d++) o[d] = (float)(acc[d] / sum);
+}
+
+void oracle_paged_attention_varlen_fp8(float *out, const uint16_t *q, const uint8_t *k_cache,
+                                       const uint8_t *v_cache, const int32_t *block_tables,
+                                       const int32_t *context_lens, const int32_t *cu_q_lens,
+                                       int S, int Hq, int Hkv, int D, int BS, int MB,
+                                       int64_t q_stride, float scale, float softcap,
+                                       int is_f16, float k_scale, float v_scale) {
+  const int G = Hq / Hkv;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+  for (int s = 0; s < S; s++) {
+    for (int hq = 0; hq < Hq; hq++) {
+      const int q0 = cu_q_lens ? cu_q_lens[s] : s;
+      const int q_len = cu_q_lens ? cu_q_lens[s + 1] - cu_q_lens[s] : 1;
+      const int kv_len = context_lens[s];
+      const int32_t *table = block_tables + (int64_t)s * MB;
+      double *logit = (double *)malloc(sizeof(double) * (size_t)(kv_len > 0 ? kv_len : 1));
+      double *acc = (double *)malloc(sizeof(double) * (size_t)D);
+      for (int j = 0; j < q_len; j++)
+        attend_row_fp8(out + ((int64_t)(q0 + j) * Hq + hq) * D,
+                       q + (int64_t)(q0 + j) * q_stride + (int64_t)hq * D, k_cache, v_cache,
+                       table, kv_len - q_len + j + 1, hq / G, Hkv, D, BS, scale, softcap,
+                       logit, acc, is_f16, k_scale, v_scale);
+      free(logit);
+      free(acc);
+    }
+  }
+}

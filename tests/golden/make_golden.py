@@ -32,6 +32,31 @@ CASES = {
 }
 
 
+# Producer (QK norm + rotary embedding) fixtures: name -> (T, H, seed, rope_base, rope_dims,
+# eps, with_weight, f16).  Positions are seeded, spread over [0, 40000).
+PRODUCER_CASES = {
+    "producer_bf16_norm": (19, 6, 21, 1.0e6, 128, 1e-6, True, False),
+    "producer_bf16_partial": (7, 3, 22, 1.0e4, 64, 1e-5, True, False),
+    "producer_f16_nonorm": (9, 4, 23, 1.0e6, 128, 1e-6, False, True),
+}
+
+
+def build_producer(name):
+    """Seeded producer inputs: x [T, H, 128], weight [128] (or None), positions [T]."""
+    from pa_testlib import normal_bf16, normal_f16, bf16_to_f32, f32_to_bf16
+    T, H, seed, base, dims, eps, with_w, f16 = PRODUCER_CASES[name]
+    gen = normal_f16 if f16 else normal_bf16
+    x = gen((T, H, 128), seed, 1)
+    w = None
+    if with_w:
+        wf = 1.0 + 0.25 * bf16_to_f32(normal_bf16((128,), seed, 2))
+        w = wf.astype(np.float16).view(np.uint16) if f16 else f32_to_bf16(wf)
+    rng = np.random.Generator(np.random.PCG64(seed))
+    pos = rng.integers(0, 40000, size=T).astype(np.int32)
+    pos[0] = 0
+    return dict(x=x, w=w, pos=pos, base=base, dims=dims, eps=eps, f16=f16)
+
+
 def digest(*arrays) -> str:
     h = hashlib.sha256()
     for a in arrays:
@@ -67,6 +92,13 @@ def main():
             inputs_sha256=digest(case.q, case.k_all, case.v_all, case.block_tables),
             pools_sha256=digest(k_exp, v_exp), k_pool_block0=k_exp[case.block_tables[0, 0]],
             v_pool_block0=v_exp[case.block_tables[0, 0]], out=out, out_softcap30=out_cap)
+        print(name, out.shape)
+    for name in PRODUCER_CASES:
+        c = build_producer(name)
+        out = numpy_reference.qk_norm_rope(c["x"], c["w"], c["eps"], c["pos"], c["base"], c["dims"],
+                                           f16=c["f16"]).astype(np.float32)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"),
+                            inputs_sha256=digest(c["x"], c["pos"]), out=out)
         print(name, out.shape)
 
 

@@ -46,3 +46,34 @@ def paged_attention(q_bits, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv
                 w = np.exp(logits - logits.max())
                 out[q0 + j, hq] = (w / w.sum()) @ v[h, :n]
     return out
+
+
+def qk_norm_rope(x_bits, weight_bits, eps, positions, rope_base, rope_dims, f16=False):
+    """Independent numpy statement of the producer (RMS norm per head, then rotary
+    embedding with traditional = false, scale 1; crates/mlx-sys/src/mlx.cpp:1343-1365
+    applied to one token per sequence at its own offset,
+    crates/mlx-core/src/transformer/attention.rs:658-664), vectorised over tokens and
+    heads, float64 inside, the 16-bit rounding points of MLX's kernels kept.  Returns the
+    rotated values as float64 rounded to the 16-bit type."""
+    def rnd(a):
+        a32 = a.astype(np.float32)
+        if f16:
+            return a32.astype(np.float16).astype(np.float64)
+        u = a32.view(np.uint32).astype(np.uint64)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32) << 16
+        return r.astype(np.uint32).view(np.float32).astype(np.float64)
+
+    x = elems_to_f32(x_bits, f16).astype(np.float64)          # [T, H, D]
+    if weight_bits is not None:
+        w = elems_to_f32(weight_bits, f16).astype(np.float64)
+        inv = 1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
+        x = rnd(rnd(x * inv) * w)
+    half = rope_dims // 2
+    inv_freq = np.power(np.float64(rope_base), -np.arange(half) / half).astype(np.float32)
+    theta = (np.asarray(positions, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float64)
+    c, s_ = np.cos(theta)[:, None, :], np.sin(theta)[:, None, :]
+    a, b = x[..., :half], x[..., half:2 * half]
+    out = x.copy()
+    out[..., :half] = a * c - b * s_
+    out[..., half:2 * half] = a * s_ + b * c
+    return rnd(out)

@@ -58,6 +58,19 @@ def oracle() -> C.CDLL:
     lib.baseline_mlx_paged_forward.restype = i32
     lib.oracle_fill_normal_bf16.argtypes = [vp, i64, C.c_uint64, C.c_uint64, i64]
     lib.oracle_fill_normal_bf16.restype = None
+    lib.oracle_fp8_e4m3_decode.argtypes = [C.c_uint8]
+    lib.oracle_fp8_e4m3_decode.restype = f32
+    lib.oracle_fp8_e4m3_encode.argtypes = [f32]
+    lib.oracle_fp8_e4m3_encode.restype = C.c_uint8
+    lib.oracle_reshape_and_cache_fp8.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32,
+                                                 f32, f32, i32]
+    lib.oracle_reshape_and_cache_fp8.restype = None
+    lib.oracle_paged_attention_varlen_fp8.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                                      i32, i32, i64, f32, f32, i32, f32, f32]
+    lib.oracle_paged_attention_varlen_fp8.restype = None
+    lib.oracle_qk_norm_rope.argtypes = [vp, vp, vp, i64, vp, C.c_double, vp, C.c_double, i32, i64,
+                                        i32, i32, i32]
+    lib.oracle_qk_norm_rope.restype = None
     lib.oracle_f32_to_bf16.argtypes = [vp, vp, i64]
     lib.oracle_f32_to_bf16.restype = None
     lib.oracle_bf16_to_f32.argtypes = [vp, vp, i64]
@@ -188,6 +201,64 @@ def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, 
                                          p(cu_q) if cu_q is not None else None, Hq, Hkv, D, BS, MB,
                                          Hq * D, scale, softcap)
     return out
+
+
+# ---- FP8 (E4M3) cache ----------------------------------------------------------------
+X8 = 16  # elements per 16-byte piece of the FP8 key pool
+
+
+def fp8_pools(NB, Hkv, fill=0):
+    return (np.full((NB, Hkv, D // X8, BS, X8), fill, dtype=np.uint8),
+            np.full((NB, Hkv, D, BS), fill, dtype=np.uint8))
+
+
+def write_oracle_fp8(k_pool8, v_pool8, key, value, slots, Hkv, k_scale, v_scale, f16=False):
+    n = len(slots)
+    if n:
+        oracle().oracle_reshape_and_cache_fp8(p(key), p(value), p(k_pool8), p(v_pool8), p(slots), n,
+                                              Hkv * D, Hkv * D, Hkv, D, BS, k_scale, v_scale, int(f16))
+
+
+def attention_oracle_fp8(case, k_pool8, v_pool8, k_scale, v_scale, softcap=1.0, varlen=True):
+    out = np.zeros((case.total_q, case.Hq, D), dtype=np.float32)
+    cu = p(case.cu_q) if varlen else None
+    oracle().oracle_paged_attention_varlen_fp8(p(out), p(case.q), p(k_pool8), p(v_pool8),
+                                               p(case.block_tables), p(case.kv_lens), cu, case.S,
+                                               case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
+                                               case.scale, softcap, int(case.f16), k_scale, v_scale)
+    return out
+
+
+def qk_norm_rope_oracle(x_bits, weight_bits, eps, positions, rope_base, rope_dims, f16=False):
+    """Oracle for the producer on x [T, H, D]: returns (rotated bits, per-element bound base
+    |a|+|b| of the rotated pair)."""
+    T, H, _ = x_bits.shape
+    x_bits = np.ascontiguousarray(x_bits)
+    out = np.empty_like(x_bits)
+    bound = np.empty(x_bits.shape, dtype=np.float32)
+    positions = np.ascontiguousarray(positions, dtype=np.int32)
+    oracle().oracle_qk_norm_rope(p(out), p(bound), p(x_bits), H * D,
+                                 p(weight_bits) if weight_bits is not None else None, eps,
+                                 p(positions), rope_base, rope_dims, T, H, D, int(f16))
+    return out, bound
+
+
+def check_rotated(got_bits, ref_bits, bound, f16, what=""):
+    """The producer's fp32 steps (mean of squares, reciprocal square root, sine and
+    cosine) are evaluated by different routines on the two sides, so a value that sits
+    on a rounding boundary can land one unit in the last place apart after the norm and
+    carry that through the rotation: |a-b| <= 2^-7 (bf16) / 2^-10 (f16) of the pair's
+    magnitude |a|+|b|, and at least 99 % of the elements identical."""
+    got = elems_to_f32(got_bits, f16).astype(np.float64)
+    ref = elems_to_f32(ref_bits, f16).astype(np.float64)
+    ulp = 2.0 ** (-10 if f16 else -7)
+    floor = np.maximum(bound.astype(np.float64), np.abs(ref))
+    bad = np.abs(got - ref) > ulp * floor + 1e-30
+    same = float((got_bits == ref_bits).mean())
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements beyond one unit in the last place; " \
+                          f"worst {np.abs(got - ref).max()}"
+    assert same >= 0.99, f"{what}: only {same:.4f} of the elements identical"
+    return same
 
 
 # ---- parity rule ------------------------------------------------------------------------

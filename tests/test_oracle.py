@@ -175,3 +175,46 @@ def test_f16_inputs_against_numpy_reference():
     ref = numpy_reference.paged_attention(case.q, k_pool, v_pool, case.block_tables, case.kv_lens,
                                           case.cu_q, case.Hq, case.Hkv, case.scale, f16=True)
     np.testing.assert_allclose(attention_oracle(case, k_pool, v_pool), ref, rtol=0, atol=2e-6)
+
+
+@pytest.mark.parametrize("name", sorted(make_golden.PRODUCER_CASES))
+def test_producer_oracle_matches_golden(name):
+    """QK norm + rotary embedding: the C oracle against the numpy-made fixture."""
+    from pa_testlib import check_rotated, elems_to_f32, qk_norm_rope_oracle
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    c = make_golden.build_producer(name)
+    assert make_golden.digest(c["x"], c["pos"]) == str(g["inputs_sha256"]), "seeded inputs changed"
+    bits, bound = qk_norm_rope_oracle(c["x"], c["w"], c["eps"], c["pos"], c["base"], c["dims"],
+                                      f16=c["f16"])
+    exp = g["out"]
+    exp_bits = exp.astype(np.float16).view(np.uint16) if c["f16"] else f32_to_bf16(exp)
+    assert (elems_to_f32(exp_bits, c["f16"]) == exp).all()
+    same = check_rotated(bits, exp_bits, bound, c["f16"], name)
+    assert same >= 0.999
+    # position 0 rotates by nothing: with no norm the row passes through bit for bit
+    if c["w"] is None:
+        assert (bits[0] == c["x"][0]).all()
+    # elements beyond rope_dims are only normalised
+    if c["dims"] < D:
+        ref = numpy_reference.qk_norm_rope(c["x"], c["w"], c["eps"], np.zeros_like(c["pos"]),
+                                           c["base"], c["dims"], f16=c["f16"])
+        assert (elems_to_f32(bits, c["f16"])[..., c["dims"]:] == ref[..., c["dims"]:]).mean() >= 0.999
+
+
+def test_producer_rotation_preserves_pair_norm_and_composes():
+    """Size-independent properties: a rotation keeps a^2+b^2 of every pair (to rounding),
+    and rotating by position p is the same as what the attention logits need:
+    <rot(q,p), rot(k,p')> depends on p-p' only (checked for equal positions)."""
+    from pa_testlib import elems_to_f32, qk_norm_rope_oracle
+    x = normal_bf16((33, 2, D), 5, 1)
+    pos = np.arange(33, dtype=np.int32) * 977
+    bits, _ = qk_norm_rope_oracle(x, None, 1e-6, pos, 1e6, D)
+    a, r = bf16_to_f32(x).astype(np.float64), bf16_to_f32(bits).astype(np.float64)
+    n_in = a[..., :64] ** 2 + a[..., 64:] ** 2
+    n_out = r[..., :64] ** 2 + r[..., 64:] ** 2
+    np.testing.assert_allclose(n_out, n_in, rtol=2 ** -6, atol=1e-3)
+    y = normal_bf16((33, 2, D), 6, 1)
+    ybits, _ = qk_norm_rope_oracle(y, None, 1e-6, pos, 1e6, D)
+    dot_in = (a * bf16_to_f32(y)).sum(-1)
+    dot_out = (r * bf16_to_f32(ybits)).sum(-1)
+    np.testing.assert_allclose(dot_out, dot_in, atol=0.25)
