@@ -69,6 +69,9 @@ struct PagedAttnCache {
   bool fp8 = false;
   std::vector<float> k_scale, v_scale;
   unsigned *err_dev = nullptr;
+  // pinned, device-mapped copy of the error word, written by the last kernel of an
+  // attention call, so that the host-buffer step reads it without a copy of its own
+  unsigned *err_host = nullptr, *err_host_dev = nullptr;
   // FP8: device word next to the error word, non-zero once a pool may hold a byte with
   // exponent field 15 (infinity / NaN in the cache format)
   unsigned *fp8_special() const { return err_dev + 16; }
@@ -145,6 +148,10 @@ pa_status finish_create(PagedAttnCache *c) {
   c->num_sms = sms;
   PA_CUDA(cudaMalloc(&c->err_dev, 256));
   PA_CUDA(cudaMemset(c->err_dev, 0, 256));
+  PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), 64,
+                        cudaHostAllocMapped | cudaHostAllocPortable));
+  *c->err_host = 0;
+  PA_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->err_host_dev), c->err_host, 0));
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
   PA_CUDA(cudaStreamCreateWithFlags(&c->step_stream, cudaStreamNonBlocking));
@@ -330,6 +337,7 @@ pa_status pa_cache_free(PagedAttnCache *c) {
     for (void *p : c->v) cudaFree(p);
   }
   if (c->err_dev) cudaFree(c->err_dev);
+  if (c->err_host) cudaFreeHost(c->err_host);
   if (c->ws) cudaFree(c->ws);
   if (c->meta) cudaFree(c->meta);
   if (c->stage) cudaFree(c->stage);
@@ -677,6 +685,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.softcap = softcap;
   p.ws = static_cast<float *>(workspace);
   p.err = c->err_dev;
+  p.err_mirror = c->err_host_dev;
   p.seq_base = 0;
   p.is_f16 = c->cfg.dtype == 0 ? 1 : 0;
   p.is_fp8 = c->fp8 ? 1 : 0;
@@ -854,14 +863,39 @@ pa_status pa_decode_step_host(PagedAttnCache *c, uint32_t layer, void *out_host,
   if (st != PA_OK) return st;
   char *base = static_cast<char *>(c->stage);
   cudaStream_t s = c->step_stream;
-  PA_CUDA(cudaMemcpyAsync(base + o_q, q_host, q_b, cudaMemcpyHostToDevice, s));
-  PA_CUDA(cudaMemcpyAsync(base + o_k, k_host, kv_b, cudaMemcpyHostToDevice, s));
-  PA_CUDA(cudaMemcpyAsync(base + o_v, v_host, kv_b, cudaMemcpyHostToDevice, s));
-  PA_CUDA(cudaMemcpyAsync(base + o_sl, slots_host, sl_b, cudaMemcpyHostToDevice, s));
-  PA_CUDA(cudaMemcpyAsync(base + o_tb, tables_host, tb_b, cudaMemcpyHostToDevice, s));
-  PA_CUDA(cudaMemcpyAsync(base + o_ln, lens_host, ln_b, cudaMemcpyHostToDevice, s));
-  st = pa_reshape_and_cache(c, layer, base + o_k, base + o_v,
-                            reinterpret_cast<const int64_t *>(base + o_sl), num_seqs,
+  // Pinned, device-mapped host buffers (cudaHostAlloc / cudaHostRegister, which is what
+  // frameworks' pinned tensors are) are read by the kernels themselves: the KV write takes
+  // k, v and the slots straight from host memory and one ingest launch brings q, the
+  // tables and the lengths over, instead of six DMA operations in a row.  Anything else
+  // (pageable memory) goes through cudaMemcpyAsync.
+  auto mapped = [](const void *h) -> const void * {
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, h) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+  };
+  const void *q_m = mapped(q_host), *k_m = mapped(k_host), *v_m = mapped(v_host),
+             *sl_m = mapped(slots_host), *tb_m = mapped(tables_host), *ln_m = mapped(lens_host);
+  const bool zero_copy = q_m && k_m && v_m && sl_m && tb_m && ln_m && aligned16(q_m) &&
+                         aligned16(k_m) && aligned16(v_m) && aligned16(tb_m) && aligned16(ln_m);
+  const void *k_src = base + o_k, *v_src = base + o_v, *sl_src = base + o_sl;
+  if (zero_copy) {
+    pa::StageCopy sc{{q_m, tb_m, ln_m}, {base + o_q, base + o_tb, base + o_ln}, {q_b, tb_b, ln_b}};
+    PA_CUDA(pa::launch_stage_copy(sc, s));
+    k_src = k_m;
+    v_src = v_m;
+    sl_src = sl_m;
+  } else {
+    PA_CUDA(cudaMemcpyAsync(base + o_q, q_host, q_b, cudaMemcpyHostToDevice, s));
+    PA_CUDA(cudaMemcpyAsync(base + o_k, k_host, kv_b, cudaMemcpyHostToDevice, s));
+    PA_CUDA(cudaMemcpyAsync(base + o_v, v_host, kv_b, cudaMemcpyHostToDevice, s));
+    PA_CUDA(cudaMemcpyAsync(base + o_sl, slots_host, sl_b, cudaMemcpyHostToDevice, s));
+    PA_CUDA(cudaMemcpyAsync(base + o_tb, tables_host, tb_b, cudaMemcpyHostToDevice, s));
+    PA_CUDA(cudaMemcpyAsync(base + o_ln, lens_host, ln_b, cudaMemcpyHostToDevice, s));
+  }
+  st = pa_reshape_and_cache(c, layer, k_src, v_src, static_cast<const int64_t *>(sl_src), num_seqs,
                             (int64_t)(Hkv * D), (int64_t)(Hkv * D), s);
   if (st != PA_OK) return st;
   st = pa_paged_attention_decode(c, layer, base + o_out, base + o_q,
@@ -871,10 +905,9 @@ pa_status pa_decode_step_host(PagedAttnCache *c, uint32_t layer, void *out_host,
                                  (int64_t)(num_q_heads * D), scale, softcap, c->ws, c->ws_bytes, s);
   if (st != PA_OK) return st;
   PA_CUDA(cudaMemcpyAsync(out_host, base + o_out, q_b, cudaMemcpyDeviceToHost, s));
-  unsigned word = 0;
-  PA_CUDA(cudaMemcpyAsync(&word, c->err_dev, sizeof(word), cudaMemcpyDeviceToHost, s));
   PA_CUDA(cudaStreamSynchronize(s));
-  if (word != 0) return pa_cache_check_errors(c, s);
+  // the merge kernel left a copy of the error word in host-visible memory
+  if (*reinterpret_cast<volatile unsigned *>(c->err_host) != 0) return pa_cache_check_errors(c, s);
   return PA_OK;
 }
 

@@ -3,6 +3,8 @@
 // Semantics: crates/mlx-paged-attn/metal/cache/reshape_and_cache.metal:58-97 and
 // crates/mlx-paged-attn/metal/cache/copy_blocks.metal:6-36.  Both are pure
 // index arithmetic over 16-bit patterns, so results are bit-exact.
+#include <algorithm>
+
 #include "pa_common.cuh"
 
 namespace pa {
@@ -281,6 +283,34 @@ cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
   dim3 grid((unsigned)num_pairs, (unsigned)((bytes_per_block + 4095) / 4096));
   copy_blocks_kernel<<<grid, 256, 0, st>>>(k_pool, v_pool, mapping, bytes_per_block, num_blocks,
                                            err);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+// Ingest of a step's small inputs from pinned host memory: up to three segments copied
+// by one launch, the device reading the host pages over PCIe itself (one launch instead
+// of one DMA operation per buffer).  Segment sizes are multiples of 4 bytes.
+__global__ void __launch_bounds__(256)
+stage_copy_kernel(StageCopy a) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+#pragma unroll
+  for (int k = 0; k < 3; k++) {
+    const size_t n16 = a.bytes[k] / 16, tail = (a.bytes[k] % 16) / 4;
+    const uint4 *s16 = static_cast<const uint4 *>(a.src[k]);
+    uint4 *d16 = static_cast<uint4 *>(a.dst[k]);
+    for (size_t i = tid; i < n16; i += nthreads) d16[i] = s16[i];
+    if (tid < tail)
+      static_cast<uint32_t *>(a.dst[k])[n16 * 4 + tid] =
+          static_cast<const uint32_t *>(a.src[k])[n16 * 4 + tid];
+  }
+}
+
+cudaError_t launch_stage_copy(const StageCopy &a, cudaStream_t st) {
+  size_t total = 0;
+  for (int k = 0; k < 3; k++) total += a.bytes[k] / 16 + 1;
+  const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 1024);
+  stage_copy_kernel<<<blocks, 256, 0, st>>>(a);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

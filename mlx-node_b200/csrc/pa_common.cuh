@@ -144,6 +144,7 @@ struct AttnParams {
   float softcap;  // 1.0f = off
   float *ws;      // partial results, slot layout described in decode.cu
   unsigned *err;  // error word
+  unsigned *err_mirror;  // null, or a host-visible word the merge kernel copies `err` to
   int seq_base;   // first sequence this launch covers
   int min_cols;   // a sequence is taken by the split-KV launch iff min_cols <= q_len*G <= max_cols
   int max_cols;
@@ -191,6 +192,14 @@ cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
 cudaError_t launch_swap_blocks(elem16 *k_pool, elem16 *v_pool, const uint32_t *ids,
                                char *const *host_k, char *const *host_v, int num, int64_t bytes_per_block,
                                int to_host, uint32_t num_blocks, unsigned *err, cudaStream_t st);
+// Up to three host->device (or any) copies in one launch; sizes multiples of 4 bytes,
+// sources and destinations 16-byte aligned.
+struct StageCopy {
+  const void *src[3];
+  void *dst[3];
+  size_t bytes[3];
+};
+cudaError_t launch_stage_copy(const StageCopy &a, cudaStream_t st);
 // Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.
 cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st);
 size_t splitkv_workspace_bytes(int num_ctas);

@@ -594,6 +594,9 @@ splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
   const int c_last = nb ? (int)((U1 * num_ctas - 1) / W) : 0;
   // everything below depends on what the main kernel wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // every kernel that can set an error bit in this call has finished by now
+  if (p.err_mirror && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
+    *p.err_mirror = *reinterpret_cast<volatile unsigned *>(p.err);
   if (!ours) return;
   if (nb == 0) {  // empty context: zero rows (crates/mlx-sys/src/mlx.cpp:4084-4088)
     for (int col = threadIdx.y; col < ncols; col += kMergeCols) {

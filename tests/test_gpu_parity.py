@@ -305,3 +305,31 @@ def test_decode_step_from_host_buffers(cuda_device):
     k_ref, v_ref = case.pools_after_write()
     assert (to_bits(dc.k_pool) == k_ref).all() and (to_bits(dc.v_pool) == v_ref).all()
     check_attention(bf16_to_f32(out), attention_oracle(case, k_ref, v_ref), "host step")
+
+
+def test_decode_step_from_pinned_host_buffers(cuda_device):
+    """Pinned (device-mapped) buffers take the path where the kernels read host memory
+    themselves; results and error reporting must be the same as with pageable memory."""
+    case = Case([513, 64, 2000, 31, 17, 4096], [1] * 6, 32, 8, 512, seed=14)
+    dc = DeviceCase(case)
+    pin = lambda a: torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).pin_memory()
+    q, k, v = pin(case.q), pin(case.k_new), pin(case.v_new)
+    slots, tables, lens = pin(case.slot_mapping), pin(case.block_tables), pin(case.kv_lens)
+    out = torch.zeros(case.S, case.Hq, D, dtype=torch.int16).pin_memory()
+    for _ in range(2):  # twice: the second call reuses the staging area
+        out.zero_()
+        dc.cache.decode_step_host(out, q, k, v, slots, tables, lens, case.S, case.Hq, case.MB,
+                                  case.scale)
+        k_ref, v_ref = case.pools_after_write()
+        assert (to_bits(dc.k_pool) == k_ref).all() and (to_bits(dc.v_pool) == v_ref).all()
+        check_attention(bf16_to_f32(out.numpy().view(np.uint16)),
+                        attention_oracle(case, k_ref, v_ref), "pinned host step")
+    # an out-of-range block id is reported by the same call
+    bad = tables.clone().pin_memory()
+    bad[2, 0] = case.NB + 5
+    with pytest.raises(pa.PagedAttnError) as e:
+        dc.cache.decode_step_host(out, q, k, v, slots, bad, lens, case.S, case.Hq, case.MB,
+                                  case.scale)
+    assert e.value.status == 4
+    dc.cache.decode_step_host(out, q, k, v, slots, tables, lens, case.S, case.Hq, case.MB,
+                              case.scale)  # and the handle stays usable
