@@ -629,7 +629,8 @@ pa_status pa_swap_in(PagedAttnCache *c, uint32_t layer, const uint32_t *ids, siz
 
 size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {
   if (!c) return 0;
-  return pa::splitkv_workspace_bytes(c->num_sms);
+  // an FP8 cache may run its narrow kernel with two CTAs per SM
+  return pa::splitkv_workspace_bytes(c->num_sms * (c->fp8 ? 2 : 1));
 }
 
 pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
@@ -658,7 +659,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   if (q_stride < row || out_stride < row || (q_stride & 7) || (out_stride & 7))
     return fail(PA_ERR_INVALID_ARG, "q/out stride must be >= num_q_heads*head_size and a multiple of 8");
   if (!aligned16(q) || !aligned16(out)) return fail(PA_ERR_INVALID_ARG, "q/out must be 16-byte aligned");
-  if (!workspace || workspace_bytes < pa_attention_workspace_bytes(c) ||
+  if (!workspace || workspace_bytes < pa::splitkv_workspace_bytes(c->num_sms) ||
       (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return fail(PA_ERR_INVALID_ARG, "workspace missing, too small or not 256-byte aligned");
   if (!(scale > 0.f) || !(softcap > 0.f)) return fail(PA_ERR_INVALID_ARG, "scale and softcap must be > 0");
@@ -684,6 +685,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.scale = scale;
   p.softcap = softcap;
   p.ws = static_cast<float *>(workspace);
+  p.ws_ctas = (int)std::min<size_t>(workspace_bytes / pa::splitkv_workspace_bytes(1), 1u << 20);
   p.err = c->err_dev;
   p.err_mirror = c->err_host_dev;
   p.seq_base = 0;

@@ -142,7 +142,8 @@ struct AttnParams {
   int64_t q_stride, out_stride;
   float scale;    // logits multiplier
   float softcap;  // 1.0f = off
-  float *ws;      // partial results, slot layout described in decode.cu
+  float *ws;      // partial results, two slots per CTA (layout: splitkv_attention.cu)
+  int ws_ctas;    // CTAs the workspace has slots for
   unsigned *err;  // error word
   unsigned *err_mirror;  // null, or a host-visible word the merge kernel copies `err` to
   int seq_base;   // first sequence this launch covers

@@ -55,7 +55,11 @@ template <int NT, bool FP8 = false>
 struct Cfg {
   static constexpr int kChunk = FP8 ? kChunkBytes / 2 : kChunkBytes;  // bytes of one K or V chunk
   static constexpr int kStageBytes = 2 * kChunk;
-  static constexpr int kStages = (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1);
+  // The narrow FP8 variant runs two CTAs per SM (its per-unit work is latency-bound, so
+  // it wants 16 warps per SM; 128 registers per thread allow it): two 4 KB stages per
+  // warp there, otherwise the ring keeps its byte size and holds twice as many stages.
+  static constexpr int kCtasPerSm = (FP8 && NT == 1) ? 2 : 1;
+  static constexpr int kStages = kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1);
   static constexpr int kRegs = 36 * NT;  // per thread: 32NT accumulators, 2NT maxima, 2NT sums
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
   static constexpr int kMergeBytes = (kWarps / 2) * kRegs * 32 * 4;
@@ -99,9 +103,65 @@ __device__ __forceinline__ void fp8x4_to_f16(uint32_t w, uint32_t &lo, uint32_t 
   }
 }
 constexpr float kFp8Unbias = 256.f;  // the factor the conversion above leaves out
+
+// D(16x8,f32) += A(16x32,row) * B(32x8,col), both operands E4M3 bytes.  The tensor cores
+// read exponent field 15 as finite values (the OCP variant of the format); every other
+// byte means the same as in the cache format, so this path serves the fast variant only.
+__device__ __forceinline__ void mma_fp8_16832(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Four floats -> four E4M3 bytes (x0 in the low byte), round to nearest, saturating.
+__device__ __forceinline__ uint32_t pack_e4m3x4(float x0, float x1, float x2, float x3) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(x1), "f"(x0));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(x3), "f"(x2));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ float f16lo_to_float(uint32_t h2) {
+  float f;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((uint16_t)(h2 & 0xffffu)));
+  return f;
+}
+__device__ __forceinline__ float f16hi_to_float(uint32_t h2) {
+  float f;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((uint16_t)(h2 >> 16)));
+  return f;
+}
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
   return pack2<true>(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
+// A operand E4M3 (cache bytes), B operand E5M2 (probabilities).
+__device__ __forceinline__ void mma_fp8_16832_e5m2(float (&d)[4], const uint32_t (&a)[4],
+                                                   uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e5m2.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// An f16 pair rounded (to nearest even) to E5M2 precision, i.e. to its high bytes; the
+// result is still an f16 pair, with zero low bytes.
+__device__ __forceinline__ uint32_t f16x2_round_e5m2(uint32_t h) {
+  return (h + 0x007F007Fu + ((h >> 8) & 0x00010001u)) & 0xFF00FF00u;
+}
+__device__ __forceinline__ uint32_t f16x2_sub(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// Fast FP8 variant: MMA row r holds token 4*((r&7)>>1) + 2*(r&1) + (r>>3), so that one
+// movmatrix of the packed probabilities yields, per thread, the four tokens 4t..4t+3 of
+// one column - the order of the bytes in a V row piece.
+__device__ __forceinline__ int fp8_row_token_fast(int r) {
+  return 4 * ((r & 7) >> 1) + 2 * (r & 1) + (r >> 3);
+}
+constexpr float kPScale = 16384.f;  // probabilities are scaled by 2^14 before they become E5M2
+
 // FP8 path: row r of a 16-token MMA tile holds token fp8_row_token(r) of the block, so
 // that the token pairs a thread gets from one 32-bit piece of a V row (tokens 4t..4t+3)
 // are the pairs its P^T fragment holds.
@@ -110,7 +170,8 @@ __device__ __forceinline__ int fp8_row_token(int r) {
 }
 
 template <int NT, bool F16, bool FP8>
-__global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
+splitkv_kernel(const AttnParams p) {
   using C = Cfg<NT, FP8>;
   constexpr int NST = C::kStages;
   constexpr int kStageBytes = C::kStageBytes;
@@ -222,7 +283,9 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
   bool dead = false;   // a wait ran out: stop touching data, keep the barriers balanced
   // k_scale: FP8 dequantisation (with the conversion's missing 2^8), else 1
   const float qk_scale = p.scale * p.k_scale * (FP8 ? kFp8Unbias : 1.f);
-  const float v_unscale = p.v_scale * (FP8 ? kFp8Unbias : 1.f);
+  // fast FP8 variant: V bytes at face value, probabilities scaled by 2^14
+  const float v_unscale =
+      p.v_scale * (FP8 ? (EXACT ? kFp8Unbias : 1.f / kPScale) : 1.f);
   const float sc_log2 = qk_scale * kLog2e;
   const bool use_cap = p.softcap != 1.0f;
 
@@ -246,15 +309,64 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
     const int ncols = q_len * G;
 
     // Q^T B-fragments: column nt*8+gid, k = 16j + 2tig (+8).
+    // FP8 fast variant: S = K.Q^T runs on the FP8 tensor-core path straight from the
+    // cache bytes.  The query row is scaled by a power of two (largest element into
+    // [64, 128)) and split into two E4M3 numbers per element, hi = rn(q') and
+    // lo = rn(q' - hi), which together carry eight significant bits (all of a bf16 query);
+    // qf[.][0..3] hold hi and qf[.][4..7] lo of the four 32-wide steps, and the power of
+    // two comes back out in the column's logit scale.
+    constexpr bool QK8 = FP8 && !EXACT;
     uint32_t qf[NT][8][2];
     int lim[NT][2];  // keys visible to columns nt*8 + 2tig + {0,1}
+    float col_lin[NT][2];  // S accumulator -> logit, for columns nt*8 + 2tig + {0,1}
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
       const int col = nt * 8 + gid;
-      if (col < ncols) {
-        const int qj = col / G, g = col - qj * G;
-        const uint32_t *qp = reinterpret_cast<const uint32_t *>(
-            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
+      int q_exp = 0;  // QK8: the row was multiplied by 2^q_exp
+      const bool have_col = col < ncols;
+      const int qj = have_col ? col / G : 0, g = have_col ? col - qj * G : 0;
+      const uint32_t *qp = reinterpret_cast<const uint32_t *>(
+          p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
+      if (QK8) {
+        // step s: b0 carries d = 32s + 4tig .. +3, b1 carries d = 32s + 16 + 4tig .. +3.
+        // Every lane runs this block (columns beyond the item carry zeros): the shuffles
+        // below need the whole warp.
+        float qv[8][4];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          uint2 w = make_uint2(0u, 0u);
+          if (have_col) w = __ldg(reinterpret_cast<const uint2 *>(qp) + 4 * j + tig);
+          if (F16) {
+            qv[j][0] = f16lo_to_float(w.x); qv[j][1] = f16hi_to_float(w.x);
+            qv[j][2] = f16lo_to_float(w.y); qv[j][3] = f16hi_to_float(w.y);
+          } else {
+            qv[j][0] = __uint_as_float(w.x << 16); qv[j][1] = __uint_as_float(w.x & 0xffff0000u);
+            qv[j][2] = __uint_as_float(w.y << 16); qv[j][3] = __uint_as_float(w.y & 0xffff0000u);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; i++) amax = fmaxf(amax, fabsf(qv[j][i]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+        q_exp = (ex == 0 || ex == 255) ? 0 : min(133 - ex, 120);
+        const float up = __uint_as_float((uint32_t)(q_exp + 127) << 23);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float x0 = qv[j][0] * up, x1 = qv[j][1] * up, x2 = qv[j][2] * up,
+                      x3 = qv[j][3] * up;
+          const uint32_t hi8 = pack_e4m3x4(x0, x1, x2, x3);
+          uint32_t ha, hb;
+          fp8x4_to_f16<false>(hi8, ha, hb);
+          const uint32_t lo8 = pack_e4m3x4(x0 - f16lo_to_float(ha) * kFp8Unbias,
+                                           x1 - f16hi_to_float(ha) * kFp8Unbias,
+                                           x2 - f16lo_to_float(hb) * kFp8Unbias,
+                                           x3 - f16hi_to_float(hb) * kFp8Unbias);
+          qf[nt][j >> 1][j & 1] = hi8;
+          qf[nt][4 + (j >> 1)][j & 1] = lo8;
+        }
+      } else if (have_col) {
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           if (FP8) {
@@ -276,6 +388,12 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
       for (int c = 0; c < 2; c++) {
         const int cc = nt * 8 + 2 * tig + c;
         lim[nt][c] = cc < ncols ? kv_len - q_len + cc / G + 1 : 0;
+        if (QK8) {
+          // the exponent of column 2tig+c sits with the threads whose gid is that column;
+          // in the fast variant the K bytes are taken at face value (no 2^8 left out)
+          const int e = __shfl_sync(0xffffffffu, q_exp, (2 * tig + c) * 4);
+          col_lin[nt][c] = p.scale * p.k_scale * __uint_as_float((uint32_t)(127 - e) << 23);
+        }
       }
     }
     const int min_lim = kv_len - q_len + 1;
@@ -309,7 +427,32 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
           for (int i = 0; i < 4; i++) sacc[nt][i] = 0.f;
-        if (FP8) {
+        if (QK8) {
+          float slo[NT][4];
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) slo[nt][i] = 0.f;
+#pragma unroll
+          for (int st32 = 0; st32 < 4; st32++) {
+            // one 32-wide step: 16-byte row pieces of chunks 2s and 2s+1, rows 0-7 and 8-15,
+            // land in the registers in the order the A operand wants them
+            uint32_t r[4];
+            ldmatrix_x4(r, ks + (2 * st32 + (mi >> 1)) * 256 +
+                               fp8_row_token_fast((mi & 1) * 8 + mr) * 16);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              mma_fp8_16832(sacc[nt], r, qf[nt][st32][0], qf[nt][st32][1]);
+              // a second accumulator halves the dependent chain (not for the widest
+              // variant, which has no registers to spare)
+              mma_fp8_16832(NT < 3 ? slo[nt] : sacc[nt], r, qf[nt][4 + st32][0], qf[nt][4 + st32][1]);
+            }
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) sacc[nt][i] += slo[nt][i];
+        } else if (FP8) {
 #pragma unroll
           for (int jj = 0; jj < 4; jj++) {
             // matrices: (rows 0-7, step 2jj), (rows 8-15, step 2jj), then the same of step 2jj+1;
@@ -335,8 +478,9 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
             for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
           }
         }
-        const int tok0 = blk * kBlockSize + (FP8 ? fp8_row_token(gid) : gid);
-        const int tok1 = FP8 ? tok0 + 2 : tok0 + 8;
+        const int tok0 =
+            blk * kBlockSize + (QK8 ? fp8_row_token_fast(gid) : FP8 ? fp8_row_token(gid) : gid);
+        const int tok1 = QK8 ? tok0 + 1 : FP8 ? tok0 + 2 : tok0 + 8;
         const bool need_mask = (blk + 1) * kBlockSize > min_lim;
         float alpha[NT][2];
 #pragma unroll
@@ -344,8 +488,15 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             float x = sacc[nt][i];
-            if (use_cap) x = tanhf(x * qk_scale / p.softcap) * p.softcap * kLog2e;
-            else x *= sc_log2;
+            if (QK8) {
+              x *= col_lin[nt][i & 1];
+              if (use_cap) x = tanhf(x / p.softcap) * p.softcap;
+              x *= kLog2e;
+            } else if (use_cap) {
+              x = tanhf(x * qk_scale / p.softcap) * p.softcap * kLog2e;
+            } else {
+              x *= sc_log2;
+            }
             sacc[nt][i] = x;
           }
           if (need_mask) {
@@ -375,8 +526,24 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
         uint32_t pb[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-          pb[nt][0] = movmatrix_trans(pack2<MF16>(sacc[nt][0], sacc[nt][1]));
-          pb[nt][1] = movmatrix_trans(pack2<MF16>(sacc[nt][2], sacc[nt][3]));
+          if (QK8) {
+            // P as two E5M2 numbers per element, hi = rn(p) and lo = rn(p - hi) (six
+            // significant bits together, the exponent range of f16), in the byte order
+            // [row gid | row gid+8] x [column 2tig, 2tig+1]: after the transpose a thread
+            // holds the four tokens 4tig..4tig+3 of column gid.  pb[.][0] feeds k-slots
+            // 0-15 (hi), pb[.][1] k-slots 16-31 (lo) of one 32-wide MMA whose A operand
+            // repeats the V piece.
+            const uint32_t ha = pack2<true>(sacc[nt][0] * kPScale, sacc[nt][2] * kPScale);
+            const uint32_t hb = pack2<true>(sacc[nt][1] * kPScale, sacc[nt][3] * kPScale);
+            const uint32_t ha_hi = f16x2_round_e5m2(ha), hb_hi = f16x2_round_e5m2(hb);
+            const uint32_t ha_lo = f16x2_round_e5m2(f16x2_sub(ha, ha_hi));
+            const uint32_t hb_lo = f16x2_round_e5m2(f16x2_sub(hb, hb_hi));
+            pb[nt][0] = movmatrix_trans(__byte_perm(ha_hi, hb_hi, 0x7531u));
+            pb[nt][1] = movmatrix_trans(__byte_perm(ha_lo, hb_lo, 0x7531u));
+          } else {
+            pb[nt][0] = movmatrix_trans(pack2<MF16>(sacc[nt][0], sacc[nt][1]));
+            pb[nt][1] = movmatrix_trans(pack2<MF16>(sacc[nt][2], sacc[nt][3]));
+          }
         }
         // Tokens past the context in the last block may hold anything (NaN
         // included) and 0*NaN is NaN: clear them in the V fragments
@@ -408,13 +575,19 @@ __global__ void __launch_bounds__(kThreads, 1) splitkv_kernel(const AttnParams p
             for (int hf = 0; hf < 2; hf++) {
               const int mt = 2 * mm + hf;
               uint32_t vf[4];
-              fp8x4_to_f16<EXACT>(r[2 * hf] & vmask[0], vf[0], vf[2]);
-              fp8x4_to_f16<EXACT>(r[2 * hf + 1] & vmask[0], vf[1], vf[3]);
+              if (QK8) {  // the V bytes are the operand: k-slots 0-15 and 16-31 both hold them
+                vf[0] = vf[2] = r[2 * hf] & vmask[0];
+                vf[1] = vf[3] = r[2 * hf + 1] & vmask[0];
+              } else {
+                fp8x4_to_f16<EXACT>(r[2 * hf] & vmask[0], vf[0], vf[2]);
+                fp8x4_to_f16<EXACT>(r[2 * hf + 1] & vmask[0], vf[1], vf[3]);
+              }
 #pragma unroll
               for (int nt = 0; nt < NT; nt++) {
                 o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
                 o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
-                mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+                if (QK8) mma_fp8_16832_e5m2(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+                else mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
               }
             }
           }
@@ -743,9 +916,13 @@ cudaError_t splitkv_configure() {
   return e;
 }
 
-cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_ctas, cudaStream_t st) {
+cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, cudaStream_t st) {
   // Width of the kernel: enough 8-column tiles for the widest item it may meet.
   const int nt = (p_in.max_cols + 7) / 8;
+  // CTAs: one per SM the caller grants, two for the variant built to share an SM, as far
+  // as the workspace has partial-result slots for them.
+  int num_ctas = num_sms_used;
+  if (p_in.is_fp8 && nt <= 1 && 2 * num_sms_used <= p_in.ws_ctas) num_ctas = 2 * num_sms_used;
   for (int base = 0; base < p_in.S; base += kMaxSeqsPerLaunch) {
     AttnParams p = p_in;
     p.seq_base = p_in.seq_base + base;

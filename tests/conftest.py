@@ -13,6 +13,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+def pytest_collection_modifyitems(config, items):
+    """A GPU test that stops making progress ends its process after two minutes instead
+    of holding the device until an outer limit does (pytest-timeout, thread method: the
+    main thread may be blocked inside a CUDA call, where a signal would not be seen)."""
+    if not config.pluginmanager.hasplugin("timeout"):
+        return
+    for item in items:
+        if item.get_closest_marker("gpu") and not item.get_closest_marker("timeout"):
+            item.add_marker(pytest.mark.timeout(120, method="thread"))
+
+
 @pytest.fixture(scope="session")
 def cuda_device():
     import torch
