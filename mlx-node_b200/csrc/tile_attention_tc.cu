@@ -220,24 +220,24 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return true;
 }
 
-// One pass over a row's 128 logits of the current KV tile (thread = row): probabilities
-// against the reference maximum (mc = m_used*c) packed to bf16 pairs in pk, the raw row
-// maximum and the row sum.  The whole row is fetched from TMEM with four loads in flight
-// at once (one latency instead of several), which is why the softmax warps raise their
-// register budget.  MASK and CAP are compile-time so the common loop is five
-// instructions per element with no branches.
+// One pass over a row's 128 logits of the current KV tile (thread = row), which the caller
+// holds in registers (fetched from TMEM with four loads in flight at once: one latency
+// instead of several, which is why the softmax warps raise their register budget):
+// probabilities against the reference maximum (mc = m_used*c), the raw row maximum and the
+// row sum.  Each 32-column chunk's probabilities are packed to 16-bit pairs and stored to
+// TMEM (over the first 64 columns of S, whose values live in registers by now) as soon as
+// they exist, so that the stores run under the arithmetic of the next chunk.  MASK and
+// CAP are compile-time so the common loop is five instructions per element, no branches.
 template <bool CAP, bool MASK, bool F16>
-__device__ __forceinline__ void row_pass(uint32_t s_t, float c, float mc, int lim, int tok0,
-                                         float cap_in, float cap_out, uint32_t (&pk)[64],
-                                         float &mx_out, float &sum_out) {
+__device__ __forceinline__ void row_pass(uint32_t s_t, const uint32_t (&s0)[32],
+                                         const uint32_t (&s1)[32], const uint32_t (&s2)[32],
+                                         const uint32_t (&s3)[32], float c, float mc, int lim,
+                                         int tok0, float cap_in, float cap_out, float &mx_out,
+                                         float &sum_out) {
   float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
   float sma[4] = {0.f, 0.f, 0.f, 0.f};
-  uint32_t s0[32], s1[32], s2[32], s3[32];
-  tmem_ld32(s_t, s0);
-  tmem_ld32(s_t + 32, s1);
-  tmem_ld32(s_t + 64, s2);
-  tmem_ld32(s_t + 96, s3);
-  auto process32 = [&](const uint32_t (&r)[32], int col0, uint32_t *dst) {
+  auto process32 = [&](const uint32_t (&r)[32], int col0) {
+    uint32_t t16[16];
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
       float x0 = __uint_as_float(r[e]), x1 = __uint_as_float(r[e + 1]);
@@ -252,17 +252,14 @@ __device__ __forceinline__ void row_pass(uint32_t s_t, float c, float mc, int li
       mxa[(e >> 1) & 3] = fmaxf(mxa[(e >> 1) & 3], fmaxf(x0, x1));
       const float p0 = fast_exp2(fmaf(x0, c, -mc)), p1 = fast_exp2(fmaf(x1, c, -mc));
       sma[(e >> 1) & 3] += p0 + p1;
-      dst[e >> 1] = pack2<F16>(p0, p1);
+      t16[e >> 1] = pack2<F16>(p0, p1);
     }
+    tmem_st16(s_t + (col0 >> 1), t16);
   };
-  tmem_wait_ld32(s0);  // waits for all four loads
-  process32(s0, 0, &pk[0]);
-  tmem_wait_ld32(s1);  // already complete: ties s1 to the wait
-  process32(s1, 32, &pk[16]);
-  tmem_wait_ld32(s2);
-  process32(s2, 64, &pk[32]);
-  tmem_wait_ld32(s3);
-  process32(s3, 96, &pk[48]);
+  process32(s0, 0);
+  process32(s1, 32);
+  process32(s2, 64);
+  process32(s3, 96);
   mx_out = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
   sum_out = (sma[0] + sma[1]) + (sma[2] + sma[3]);
 }
@@ -515,10 +512,16 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
       // soft-capping: x -> tanh(x*scale/cap)*cap/scale, so that x*c is the capped logit
       const float cap_in = p.scale / p.softcap, cap_out = p.softcap / p.scale;
       float m_used = -INFINITY, l = 0.f;
-      auto pass = [&](bool need_mask, int tok0, uint32_t (&pk)[64], float &mx, float &sum) {
+#ifdef PA_TILE_TIMING
+      long long dbg_pass = 0, dbg_store = 0;
+#endif
+      uint32_t s0[32], s1[32], s2[32], s3[32];  // the row's logits of the current tile
+      auto pass = [&](bool need_mask, int tok0, float &mx, float &sum) {
         const float mc = m_used == -INFINITY ? 0.f : m_used * c;
-        if (need_mask) row_pass<CAP, true, F16>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
-        else row_pass<CAP, false, F16>(s_t, c, mc, lim, tok0, cap_in, cap_out, pk, mx, sum);
+        if (need_mask)
+          row_pass<CAP, true, F16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
+        else
+          row_pass<CAP, false, F16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
       };
 
       for (int j = 0; j < n_tiles && !failed; j++) {
@@ -526,11 +529,26 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         tc_fence_after();
         const bool need_mask = (j + 1) * kTileTok > warp_min_lim;
         const int tok0 = j * kTileTok;
-        uint32_t pk[64];
         float mx, sum;
+        tmem_ld32(s_t, s0);
+        tmem_ld32(s_t + 32, s1);
+        tmem_ld32(s_t + 64, s2);
+        tmem_ld32(s_t + 96, s3);
+        tmem_wait_ld32(s0);  // waits for all four loads
+        tmem_wait_ld32(s1);  // already complete: these tie the registers to the wait
+        tmem_wait_ld32(s2);
+        tmem_wait_ld32(s3);
+#ifdef PA_TILE_TIMING
+        const long long t_pass0 = clock64();
+#endif
         // Optimistic pass against the maximum carried from earlier tiles (for the first
-        // tile: against 0, result discarded unless the logits happen to be small).
-        pass(need_mask, tok0, pk, mx, sum);
+        // tile: against 0, result discarded unless the logits happen to be small).  It
+        // already writes P; a second pass, from the same registers, overwrites it.
+        pass(need_mask, tok0, mx, sum);
+#ifdef PA_TILE_TIMING
+        const long long t_pass1 = clock64();
+        dbg_pass += t_pass1 - t_pass0;
+#endif
         // stale-maximum rule: move the reference only when it would grow by > 2^8
         const bool grew = mx > m_used && !((mx - m_used) * c <= 8.f);
         if (__any_sync(0xffffffffu, grew)) {
@@ -555,21 +573,23 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
             tmem_wait_st();
           }
           l *= factor;
-          pass(need_mask, tok0, pk, mx, sum);
+          pass(need_mask, tok0, mx, sum);
         }
         l += sum;
-        // bf16 P over the first 64 columns of S (every logit of the row has been read)
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-          uint32_t t16[16];
-#pragma unroll
-          for (int e = 0; e < 16; e++) t16[e] = pk[ch * 16 + e];
-          tmem_st16(s_t + ch * 16, t16);
-        }
+        // P (16-bit) now covers the first 64 columns of S
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + i));
+#ifdef PA_TILE_TIMING
+        dbg_store += clock64() - t_pass1;
+#endif
       }
+#ifdef PA_TILE_TIMING
+      if (lane == 0) {
+        atomicAdd(&g_tile_timing[13], (unsigned long long)dbg_pass);
+        atomicAdd(&g_tile_timing[14], (unsigned long long)dbg_store);
+      }
+#endif
       // epilogue: O / l -> bf16 rows
       if (!failed && wait_bar_at(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag, 9)) {
         tc_fence_after();
