@@ -323,14 +323,14 @@ splitkv_kernel(const AttnParams p) {
     for (int nt = 0; nt < NT; nt++) {
       const int col = nt * 8 + gid;
       int q_exp = 0;  // QK8: the row was multiplied by 2^q_exp
-      const bool have_col = col < ncols;
-      const int qj = have_col ? col / G : 0, g = have_col ? col - qj * G : 0;
-      const uint32_t *qp = reinterpret_cast<const uint32_t *>(
-          p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
       if (QK8) {
         // step s: b0 carries d = 32s + 4tig .. +3, b1 carries d = 32s + 16 + 4tig .. +3.
         // Every lane runs this block (columns beyond the item carry zeros): the shuffles
         // below need the whole warp.
+        const bool have_col = col < ncols;
+        const int qj = have_col ? col / G : 0, g = have_col ? col - qj * G : 0;
+        const uint32_t *qp = reinterpret_cast<const uint32_t *>(
+            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
         float qv[8][4];
         float amax = 0.f;
 #pragma unroll
@@ -366,7 +366,10 @@ splitkv_kernel(const AttnParams p) {
           qf[nt][j >> 1][j & 1] = hi8;
           qf[nt][4 + (j >> 1)][j & 1] = lo8;
         }
-      } else if (have_col) {
+      } else if (col < ncols) {
+        const int qj = col / G, g = col - qj * G;
+        const uint32_t *qp = reinterpret_cast<const uint32_t *>(
+            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           if (FP8) {
@@ -410,19 +413,9 @@ splitkv_kernel(const AttnParams p) {
         for (int i = 0; i < 4; i++) o[mt][nt][i] = 0.f;
     }
 
-    for (int k = a + ((warp - a) & (kWarps - 1)); k < a + seglen; k += kWarps) {
-      const int blk = b0 + (k - a);
-      const int st = jc % NST;
-      if (!dead) {
-        const bool ok = mbar_wait_bounded(bar_w + st * 8, (jc / NST) & 1);
-        if (!__all_sync(0xffffffffu, ok)) {
-          dead = true;
-          if (lane == 0) atomicOr(p.err, kErrTimeout);
-        }
-      }
-      if (!dead) {
-        const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunk;
-        float sacc[NT][4];
+    // S^T = K.Q^T of the unit in ring stage `st`
+    auto s_phase = [&](int st, float (&sacc)[NT][4]) {
+        const uint32_t ks = ring_w + st * kStageBytes;
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -478,6 +471,10 @@ splitkv_kernel(const AttnParams p) {
             for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
           }
         }
+    };
+    // softmax of the unit's logits and O^T += V^T.P^T, V from ring stage `st`
+    auto finish = [&](int st, int blk, float (&sacc)[NT][4]) {
+        const uint32_t vs = ring_w + st * kStageBytes + kChunk;
         const int tok0 =
             blk * kBlockSize + (QK8 ? fp8_row_token_fast(gid) : FP8 ? fp8_row_token(gid) : gid);
         const int tok1 = QK8 ? tok0 + 1 : FP8 ? tok0 + 2 : tok0 + 8;
@@ -605,10 +602,61 @@ splitkv_kernel(const AttnParams p) {
             }
           }
         }
+    };
+    // Waits for the next unit of this warp; false once a wait has run out.
+    auto wait_unit = [&](int j) {
+      const bool ok = mbar_wait_bounded(bar_w + (j % NST) * 8, (j / NST) & 1);
+      if (!__all_sync(0xffffffffu, ok)) {
+        dead = true;
+        if (lane == 0) atomicOr(p.err, kErrTimeout);
       }
-      __syncwarp();
-      jc++;
-      if (ji < n_w) issue();
+      return !dead;
+    };
+    // The warp's units of this segment, software-pipelined: the logits of unit i+1 are
+    // computed in the same straight-line block as the softmax and P.V of unit i, so that
+    // the two dependency chains fill each other's latencies.  Two units are then held at
+    // once, so a third ring stage is needed for a copy to be in flight meanwhile; the
+    // two-stage variant takes its units one at a time.
+    constexpr bool kPipelined = NST >= 3;
+    if constexpr (!kPipelined) {
+      for (int k = a + ((warp - a) & (kWarps - 1)); k < a + seglen; k += kWarps) {
+        if (!dead && wait_unit(jc)) {
+          float s_cur[NT][4];
+          s_phase(jc % NST, s_cur);
+          finish(jc % NST, b0 + (k - a), s_cur);
+        }
+        __syncwarp();
+        jc++;
+        if (ji < n_w) issue();
+      }
+    } else {
+      int k = a + ((warp - a) & (kWarps - 1));
+      const int k_end = a + seglen;
+      float s_cur[NT][4];
+      bool cur_ok = false;
+      if (k < k_end && !dead && wait_unit(jc)) {
+        s_phase(jc % NST, s_cur);
+        cur_ok = true;
+      }
+      while (k < k_end) {
+        const int kn = k + kWarps;
+        if (cur_ok && kn < k_end && wait_unit(jc + 1)) {
+          float s_next[NT][4];
+          s_phase((jc + 1) % NST, s_next);
+          finish(jc % NST, b0 + (k - a), s_cur);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) s_cur[nt][i] = s_next[nt][i];
+        } else {
+          if (cur_ok && !dead) finish(jc % NST, b0 + (k - a), s_cur);
+          cur_ok = false;
+        }
+        __syncwarp();
+        jc++;
+        if (ji < n_w) issue();
+        k = kn;
+      }
     }
 
     // ---- combine the eight warps' partials (fixed tree order) -----------------
