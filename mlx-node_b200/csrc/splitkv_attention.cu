@@ -34,7 +34,15 @@
 // for K as the A operand, and V's [D][BS] is A-operand order for V^T, so both
 // tiles are consumed straight from the raw 4 KB chunks.  P^T is produced from the
 // S^T accumulators with one movmatrix transpose per 8x8 tile.  Online softmax in
-// fp32 with exp2; column maxima by warp shuffles.
+// fp32 with exp2; column maxima by warp shuffles.  Where the ring has three stages the
+// loop over a warp's units is software-pipelined: the logits of the next unit are
+// computed next to the softmax and P.V of the current one, so that the two dependency
+// chains (ldmatrix -> MMA chain, and max -> exp2 -> movmatrix -> MMA) overlap.
+//
+// FP8 (E4M3) pools: the same kernel on 2 KB chunks, with the products either on the FP8
+// tensor-core path straight from the cache bytes or, when the cache may hold bytes that
+// the tensor cores read differently from the cache format, on f16 after an integer
+// conversion; see the comments at fp8x4_to_f16 and in the main loop.
 #include <mutex>
 #include <type_traits>
 

@@ -228,6 +228,32 @@ def test_prefill_chunk_reduced(cuda_device):
     print("prefill", check_attention(got, ref, "prefill chunk"))
 
 
+def test_more_sequences_than_one_launch_covers(cuda_device):
+    """The split-KV kernel keeps per-launch prefix sums for 2048 sequences; a larger batch is
+    cut into several launches that share the workspace one after the other."""
+    rng = np.random.Generator(np.random.PCG64(41))
+    S = 2048 + 77
+    kv = rng.integers(0, 40, size=S)          # includes empty contexts
+    kv[5] = 700                                 # and one item that is split across CTAs
+    ql = (kv > 0).astype(np.int64)
+    case = Case(kv, ql, 8, 2, 4096, seed=41)
+    case.q = normal_bf16((S, 8, D), 41, 7)      # one query per sequence, empty ones included
+    case.total_q = S
+    case.cu_q = np.arange(S + 1, dtype=np.int32)
+    got, ref = run_case(case, varlen=False)
+    assert (got[kv == 0] == 0).all()
+    check_attention(got, ref, "2125 sequences")
+
+
+def test_fewer_units_than_ctas(cuda_device):
+    """Three one-block sequences: most CTAs own nothing, the merge kernel must skip them."""
+    case = Case([3, 16, 9], [1, 1, 1], 4, 1, 8, seed=42)
+    got, ref = run_case(case, varlen=False)
+    check_attention(got, ref, "tiny batch")
+    got_v, ref_v = run_case(Case([3, 16, 9], [2, 1, 3], 4, 1, 8, seed=43))
+    check_attention(got_v, ref_v, "tiny varlen batch")
+
+
 def test_determinism_and_placement_invariance(cuda_device):
     # Same logical KV under two physical placements: outputs must be bit-identical,
     # and two runs of the same call must be bit-identical.
