@@ -68,6 +68,7 @@ struct PagedAttnCache {
   // the keys and values handed to the write.  Per-layer dequantisation factors.
   bool fp8 = false;
   std::vector<float> k_scale, v_scale;
+  std::vector<pa::TensorMapBlob> v_maps;  // per layer: tensor map of the V pool (16-bit pools)
   unsigned *err_dev = nullptr;
   // pinned, device-mapped copy of the error word, written by the last kernel of an
   // attention call, so that the host-buffer step reads it without a copy of its own
@@ -154,6 +155,12 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->err_host_dev), c->err_host, 0));
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
+  if (!c->fp8) {
+    c->v_maps.resize(c->cfg.num_layers);
+    for (uint32_t i = 0; i < c->cfg.num_layers; i++)
+      PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
+                                    (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads));
+  }
   PA_CUDA(cudaStreamCreateWithFlags(&c->step_stream, cudaStreamNonBlocking));
   PA_CUDA(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
   PA_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
@@ -786,7 +793,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
     PA_CUDA(cudaEventRecord(c->ev_fork, stream));
     PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
   } else if (!tiles.empty()) {
-    PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), stream));
+    PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), &c->v_maps[layer], stream));
   }
   bool tile_launched = !side_by_side;
   for (int k = 0; k < 3; k++) {
@@ -795,7 +802,8 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
     p.max_cols = 8 * k + 8;
     PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream));
     if (!tile_launched) {  // after the first split-KV launch, so that it gets its SMs first
-      PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), c->aux_stream));
+      PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), &c->v_maps[layer],
+                                        c->aux_stream));
       tile_launched = true;
     }
   }

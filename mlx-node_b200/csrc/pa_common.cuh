@@ -216,8 +216,13 @@ struct TileWork {
   int32_t q_begin;   // first query (within the sequence) of this tile
   int32_t q_count;   // queries in this tile
 };
+// An encoded tensor map (opaque 128 bytes; what the driver calls CUtensorMap).
+struct alignas(64) TensorMapBlob {
+  unsigned char bytes[128];
+};
+cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks);
 cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
-                                  cudaStream_t st);
+                                  const TensorMapBlob *v_map, cudaStream_t st);
 cudaError_t tile_configure();
 int tile_queries_per_cta(int G);
 

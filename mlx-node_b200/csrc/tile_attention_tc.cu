@@ -34,6 +34,8 @@
 //
 // Every wait is bounded; on expiry the CTA raises the error word, every role
 // leaves its loop, in-flight copies are drained and TMEM is freed.
+#include <cuda.h>
+
 #include "pa_common.cuh"
 
 namespace pa {
@@ -53,7 +55,20 @@ constexpr int kRegsSoftmax = 200, kRegsOther = 56;
 
 // barrier slots
 enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9,
-       B_PREADY = 11, B_PVDONE = 13 };
+       B_PREADY = 11, B_PVDONE = 13, B_VTAIL = 15 };
+
+// One V block (128 head dimensions x 16 tokens) through the tensor map of the V pool
+// {16 tokens, 128 rows, chunk}: the 32-byte swizzle of the map lays the rows out as the
+// MMA descriptor of v_block_desc expects them.  This CTA's shared memory only; a chunk
+// index beyond the pool reads as zeros.  x and y are always 0.
+__device__ __forceinline__ void tma_load_v_block(uint32_t dst, const CUtensorMap *map, int chunk,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(chunk), "r"(bar)
+      : "memory");
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
@@ -196,11 +211,20 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int u) {
 #ifdef PA_TILE_TIMING
 // Debug builds only: cycles each role spends waiting, summed over CTAs.
 __device__ unsigned long long g_tile_timing[16];
+__device__ unsigned long long g_trace[3 * 2048];
+// event trace of CTA 0 (debug builds): one list per traced warp, plain stores,
+// (clock << 8) | event id; slot 0 = MMA warp, 1 / 2 = first softmax warp of tile 0 / 1
+#define PA_TRACE(slot, id)                                                              \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 2048)                      \
+      g_trace[(slot) * 2048 + tr_n++] = ((unsigned long long)clock64() << 8) | (unsigned)(id); \
+  } while (0)
 #define PA_T0() const long long t_dbg0 = clock64()
 #define PA_T1(slot) atomicAdd(&g_tile_timing[slot], (unsigned long long)(clock64() - t_dbg0))
 #else
 #define PA_T0()
 #define PA_T1(slot)
+#define PA_TRACE(slot, id)
 #endif
 
 // Wait that gives up when the budget runs out or another role has raised the flag.
@@ -280,7 +304,8 @@ __device__ __forceinline__ bool wait_bar_at(uint32_t bar, uint32_t parity, volat
 
 template <bool CAP, bool F16>
 __global__ void __launch_bounds__(kTcThreads, 1)
-tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) {
+tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
+                         const __grid_constant__ CUtensorMap v_map) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -294,6 +319,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef PA_TILE_TIMING
   const long long t_cta0 = clock64();
+  int tr_n = 0;
 #endif
   const TileWork w = work[blockIdx.x];
   const int seq = w.seq, h = w.kv_head, G = p.G;
@@ -317,14 +343,15 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
   if (tid == 0) {
     mbar_init(bar(B_QFULL), 128);
     for (int s = 0; s < 2; s++) {
-      mbar_init(bar(B_KFULL + s), 128);
-      mbar_init(bar(B_VFULL + s), 128);
+      mbar_init(bar(B_KFULL + s), 128);  // every producer thread, after its pieces landed
+      mbar_init(bar(B_VFULL + s), 2);    // "bytes announced" and "tail of the last block cleared"
       mbar_init(bar(B_KEMPTY + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
       mbar_init(bar(B_SFULL + s), 1);
       mbar_init(bar(B_PREADY + s), 128);
       mbar_init(bar(B_PVDONE + s), 1);
     }
+    mbar_init(bar(B_VTAIL), 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -367,76 +394,96 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         cp_async16(q_s + (tile * 2 + (c >> 3)) * kSlab + sw128_off(r, c & 7), src, have ? 16u : 0u);
       }
       cp_async_commit();
-      // half-tiles: even = K(j), odd = V(j)
-      auto issue_half = [&](int hf) {
-        const int j = hf >> 1;
-        const bool is_v = hf & 1;
-        const uint32_t stage = (is_v ? v_s : k_s) + (j & 1) * kStage;
+      // K tiles: 16-byte cp.async pieces, every thread its share, published with a proxy
+      // fence and one arrival per thread.  A K block is sixteen 256-byte runs that go to
+      // sixteen different places (chunk order [d/8][tok][8] -> tile order
+      // [d/8][block][tok][8]); as 256-byte bulk copies they measured slower than this.
+      auto issue_k = [&](int j) {
+        const uint32_t stage = k_s + (j & 1) * kStage;
         for (int bb = 0; bb < 2; bb++) {
           const int b = pw * 2 + bb;           // block within the tile
           const int gb = j * 8 + b;            // block within the sequence
           const bool have = gb < nblk;
           const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
-          const elem16 *src = (is_v ? p.v_pool : p.k_pool) + chunk * kChunkElems;
+          const elem16 *src = p.k_pool + chunk * kChunkElems;
 #pragma unroll
           for (int it = 0; it < 8; it++) {
             const int e = it * 32 + lane;  // 16-byte piece of the 4 KB chunk, in memory order
-            if (!is_v) {
-              // K chunk [c][t][8] -> [c][block][t][8]: 256-byte runs stay contiguous
-              const int c = e >> 4, t = e & 15;
-              cp_async16(stage + c * 2048 + b * 256 + t * 16, src + e * 8, have ? 16u : 0u);
-            } else {
-              // V chunk [d][16 tok] stays in place; the 32-byte swizzle swaps the two
-              // 16-byte halves of rows 4..7 of every 8-row group
-              const int d = e >> 1, hh = e & 1;
-              cp_async16(stage + b * 4096 + d * 32 + ((hh ^ ((d >> 2) & 1)) << 4), src + e * 8,
-                         have ? 16u : 0u);
-            }
+            const int c = e >> 4, t = e & 15;
+            cp_async16(stage + c * 2048 + b * 256 + t * 16, src + e * 8, have ? 16u : 0u);
           }
         }
         cp_async_commit();
       };
-      // Tokens past the context inside the last block may hold anything; P is 0 there
-      // but 0*NaN is NaN, so clear those V columns once the copy has landed.
-      auto scrub_v_tail = [&](int j) {
-        const int last_gb = (kv_len - 1) >> 4;
-        const int valid = kv_len - last_gb * kBlockSize;
-        if (valid >= kBlockSize || (last_gb >> 3) != j) return;
-        const int b = last_gb & 7;
-        if ((b >> 1) != pw) return;
-        uint8_t *vgen = gen + kQBytes + 2 * kStage + (j & 1) * kStage + b * 4096;
-        for (int d = lane; d < 128; d += 32)
-          for (int t = valid; t < kBlockSize; t++)
-            *reinterpret_cast<uint16_t *>(vgen + d * 32 + ((((t >> 3) ^ (d >> 2)) & 1) << 4) +
-                                          (t & 7) * 2) = 0;
-      };
-      auto land = [&](int hf) {  // copies of half-tile hf (and Q before the first) are complete
-        __syncwarp();  // every lane's pieces of the warp's two blocks have landed
-        if (hf & 1) scrub_v_tail(hf >> 1);
+      auto land_k = [&](int j) {  // this thread's pieces of K(j) (and of Q before K(0)) are in
+        __syncwarp();
         fence_proxy_async();
-        if (hf == 0) mbar_arrive(bar(B_QFULL));
-        mbar_arrive(bar(((hf & 1) ? B_VFULL : B_KFULL) + ((hf >> 1) & 1)));
+        if (j == 0) mbar_arrive(bar(B_QFULL));
+        mbar_arrive(bar(B_KFULL + (j & 1)));
       };
-      const int n_half = 2 * n_tiles;
-      for (int hf = 0; hf < n_half && !failed; hf++) {
-        const int j = hf >> 1;
-        if (j >= 2) {
-          const uint32_t eb = bar(((hf & 1) ? B_VEMPTY : B_KEMPTY) + (j & 1));
-          if (!wait_bar_at(eb, ((j >> 1) - 1) & 1, abort_flag, 0)) {
-            failed = true;
-            break;
+      // V tiles come in through the copy engine: one tensor-map copy of 4 KB per block (the
+      // map's 32-byte swizzle is the layout the MMA reads), eight per tile, completion
+      // counted in bytes on the tile's "full" barrier.
+      // Tokens past the context inside the last block may hold anything; P is 0 there but
+      // 0*NaN is NaN, so that block lands on a barrier of its own and its stray columns are
+      // cleared before the tile is published.
+      const int last_gb = (kv_len - 1) >> 4;
+      const int last_valid = kv_len - last_gb * kBlockSize;
+      const bool have_tail = last_valid < kBlockSize && last_gb < nblk;
+      const int total_chunks = (int)p.num_blocks * p.Hkv;
+      for (int j = 0; j < n_tiles && !failed; j++) {
+        const int nb_here = min(8, nblk - j * 8);  // blocks of this tile that exist
+        if (j >= 2 && !wait_bar_at(bar(B_KEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+          failed = true;
+          break;
+        }
+        // Published as soon as it has landed (the producers have time to wait here): a
+        // tile announced only after the next one could be issued would be held back by the
+        // release of that next tile's stage.
+        issue_k(j);
+        {
+          PA_T0();
+          cp_async_wait<0>();
+          if (lane == 0) PA_T1(10);
+        }
+        land_k(j);
+        if (j >= 2 && !wait_bar_at(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+          failed = true;
+          break;
+        }
+        {
+          const uint32_t vfull = bar(B_VFULL + (j & 1));
+          const int tail_b = (have_tail && (last_gb >> 3) == j) ? (last_gb & 7) : -1;
+          if (pt == 0) mbar_expect_tx(vfull, (uint32_t)(tail_b >= 0 ? 7 : 8) * kChunkBytes);
+          if (pt < 8) {
+            const int b = pt;
+            const int chunk = b < nb_here ? (int)block_id(j * 8 + b) * p.Hkv + h : total_chunks;
+            const uint32_t dst = v_s + (j & 1) * kStage + b * 4096;
+            if (b == tail_b) {
+              mbar_expect_tx(bar(B_VTAIL), kChunkBytes);
+              tma_load_v_block(dst, &v_map, chunk, bar(B_VTAIL));
+            } else {
+              tma_load_v_block(dst, &v_map, chunk, vfull);
+            }
+          }
+          if (pw == 1) {  // second arrival: nothing left to clear in this tile
+            if (tail_b >= 0) {
+              if (!wait_bar_at(bar(B_VTAIL), 0, abort_flag, 0)) {
+                failed = true;
+                break;
+              }
+              uint8_t *vgen = gen + kQBytes + 2 * kStage + (j & 1) * kStage + tail_b * 4096;
+              for (int d = lane; d < 128; d += 32)
+                for (int t = last_valid; t < kBlockSize; t++)
+                  *reinterpret_cast<uint16_t *>(vgen + d * 32 + ((((t >> 3) ^ (d >> 2)) & 1) << 4) +
+                                                (t & 7) * 2) = 0;
+              fence_proxy_async();
+              __syncwarp();
+            }
+            if (lane == 0) mbar_arrive(vfull);
           }
         }
-        issue_half(hf);
-        if (hf > 0) {
-          PA_T0();
-          cp_async_wait<1>();
-          if (lane == 0) PA_T1(10);
-          land(hf - 1);
-        }
       }
-      cp_async_wait<0>();
-      if (!failed) land(n_half - 1);
     } else if (warp >= 12) {
       // =========================== MMA issuer ========================================
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
@@ -481,11 +528,14 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
               break;
             }
             for (int i = 0; i < 2; i++) {
+              PA_TRACE(0, 10 + i);
               if (!wait_bar_at(bar(B_PREADY + i), j & 1, abort_flag, 4 + i)) { failed = true; break; }
+              PA_TRACE(0, 12 + i);
               tc_fence_after();
               issue_pv(i, j);
               if (i == 1 && leader) tc_commit(bar(B_VEMPTY + (j & 1)));
               if (more) issue_s(i, j + 1);
+              PA_TRACE(0, 14 + i);
             }
             if (more && !failed && leader) tc_commit(bar(B_KEMPTY + ((j + 1) & 1)));
             __syncwarp();
@@ -526,6 +576,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
 
       for (int j = 0; j < n_tiles && !failed; j++) {
         if (!wait_bar_at(bar(B_SFULL + i), j & 1, abort_flag, 6 + i)) { failed = true; break; }
+        if ((warp & 3) == 0) PA_TRACE(1 + i, 20 + i);
         tc_fence_after();
         const bool need_mask = (j + 1) * kTileTok > warp_min_lim;
         const int tok0 = j * kTileTok;
@@ -538,6 +589,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         tmem_wait_ld32(s1);  // already complete: these tie the registers to the wait
         tmem_wait_ld32(s2);
         tmem_wait_ld32(s3);
+        if ((warp & 3) == 0) PA_TRACE(1 + i, 22 + i);
 #ifdef PA_TILE_TIMING
         const long long t_pass0 = clock64();
 #endif
@@ -549,6 +601,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         const long long t_pass1 = clock64();
         dbg_pass += t_pass1 - t_pass0;
 #endif
+        if ((warp & 3) == 0) PA_TRACE(1 + i, 24 + i);
         // stale-maximum rule: move the reference only when it would grow by > 2^8
         const bool grew = mx > m_used && !((mx - m_used) * c <= 8.f);
         if (__any_sync(0xffffffffu, grew)) {
@@ -580,6 +633,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + i));
+        if ((warp & 3) == 0) PA_TRACE(1 + i, 26 + i);
 #ifdef PA_TILE_TIMING
         dbg_store += clock64() - t_pass1;
 #endif
@@ -646,6 +700,14 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work) 
 }  // namespace
 
 #ifdef PA_TILE_TIMING
+extern "C" int pa_debug_tile_trace(unsigned long long *out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 3 * 2048);
+  if (e == cudaSuccess && reset) {
+    static unsigned long long z[3 * 2048];
+    e = cudaMemcpyToSymbol(g_trace, z, sizeof(z));
+  }
+  return (int)e;
+}
 extern "C" int pa_debug_tile_timing(unsigned long long *out16, int reset) {
   cudaError_t e = cudaMemcpyFromSymbol(out16, g_tile_timing, sizeof(unsigned long long) * 16);
   if (e == cudaSuccess && reset) {
@@ -671,14 +733,41 @@ cudaError_t tile_configure() {
   return e;
 }
 
+// Tensor map of one V pool: 16-bit elements, {16 tokens, 128 head dimensions, chunks},
+// box = one (block, kv head) chunk, 32-byte swizzle.  The encoder is a driver entry point,
+// fetched through the runtime so that the library does not link against the driver.
+cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks) {
+  static_assert(sizeof(CUtensorMap) == sizeof(TensorMapBlob), "tensor map size");
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return e;
+  if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+  const cuuint64_t dims[3] = {16, 128, num_chunks};
+  const cuuint64_t strides[2] = {32, 4096};
+  const cuuint32_t box[3] = {16, 128, 1}, elem_strides[3] = {1, 1, 1};
+  const CUresult r = reinterpret_cast<EncodeFn>(fn)(
+      reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT16, 3,
+      const_cast<void *>(v_pool), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
-                                  cudaStream_t st) {
+                                  const TensorMapBlob *v_map, cudaStream_t st) {
   if (num_work <= 0) return cudaSuccess;
+  if (!v_map) return cudaErrorInvalidValue;
+  const CUtensorMap &m = *reinterpret_cast<const CUtensorMap *>(v_map);
   const bool cap = p.softcap != 1.0f, f16 = p.is_f16 != 0;
-  if (cap && f16) tile_attention_tc_kernel<true, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
-  else if (cap) tile_attention_tc_kernel<true, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
-  else if (f16) tile_attention_tc_kernel<false, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
-  else tile_attention_tc_kernel<false, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev);
+  if (cap && f16) tile_attention_tc_kernel<true, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
+  else if (cap) tile_attention_tc_kernel<true, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
+  else if (f16) tile_attention_tc_kernel<false, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
+  else tile_attention_tc_kernel<false, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }
