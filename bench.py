@@ -189,12 +189,21 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
+def l2_statement(kv, hkv_local, kv_elem_bytes=2):
+    """Whether one step's KV bytes per GPU exceed the L2 (no flush is done between steps)."""
+    step = int(np.sum(kv)) * 2 * hkv_local * D * kv_elem_bytes
+    if step > L2_BYTES:
+        return f"inputs larger than L2 ({step / 1e6:.0f} MB of KV per step and GPU, L2 126 MB)"
+    return (f"working set {step / 1e6:.0f} MB fits in the 126 MB L2 and nothing flushes it: "
+            "L2-resident timing, reported for latency only")
+
+
 def workload_config(name, world, kv, ql, Hq, Hkv):
     return {"workload": f"{name}: {len(kv)} sequences, {Hq} query / {Hkv} kv heads, head {D}, "
                         f"block {BS}, {int(np.sum(ql))} query tokens over {int(np.sum(kv))} cached "
                         f"tokens; step = KV write + paged attention",
             "sharding": f"kv heads split {world} ways, batch x{world}" if world > 1 else "single GPU",
-            "l2": "inputs larger than L2" }
+            "l2": l2_statement(kv, Hkv // max(world, 1))}
 
 
 # ---------------------------------------------------------------------------------------
@@ -418,7 +427,8 @@ def main() -> None:
         # ncu capture of a 16-sequence case of this workload
         # (profiles/splitkv_kernel_c2_16seq_ncu_full.md): DRAM read+write = 1.021 x the
         # algorithmic bytes; traffic grows in proportion with the units processed
-        traffic = None if (args.fp8 or not decode_only) else int(1.021 * kv_bytes)
+        # (FP8: profiles/splitkv_kernel_fp8.md, read + write = 1.047 x the algorithmic bytes)
+        traffic = None if not decode_only else int((1.047 if args.fp8 else 1.021) * kv_bytes)
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "traffic": traffic,
                 "traffic_source": "ncu dram bytes of a 16-sequence capture, scaled by algorithmic bytes"
@@ -447,6 +457,8 @@ def main() -> None:
         }
         if args.fp8:
             line["config"]["kv_cache"] = "E4M3 bytes, scales 1/32; q, out and the written k, v bf16"
+            line["config"]["l2"] = l2_statement(kv, hkv_l, 1)
+            line["dtype"] = "e4m3 cache, bf16 queries and output, fp32 accumulation"
         if args.producer:
             line["config"]["producer"] = "QK norm + rotary embedding fused into the KV write launch"
         if do_gather:

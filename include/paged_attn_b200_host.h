@@ -42,6 +42,19 @@ uint64_t pa_compute_token_hash(const uint32_t *tokens, size_t n);
 /* KvScaleManager::compute_scale, metal/kv_scale.rs:165-174. */
 float pa_kv_compute_scale(float max_abs);
 
+/* KV-head sharding over the GPUs of one box (no counterpart in the reference, which
+ * runs on one device): rank r of `world` owns kv heads [kv_begin, kv_end) and the
+ * query heads [q_begin, q_end) that map onto them (kv_head = q_head / G,
+ * crates/mlx-paged-attn/metal/attention/paged_attention.metal:837-840).  Its pools
+ * are [num_blocks, kv_end - kv_begin, ...] with the same block ids on every rank;
+ * pointing `out` of an attention call at column q_begin * head_size of a
+ * [tokens, num_q_heads, head_size] buffer with out_stride = num_q_heads * head_size
+ * places the rank's heads where a gathered result has them.
+ * PA_ERR_INVALID_ARG when the heads do not split `world` ways.                      */
+pa_status pa_shard_head_ranges(int32_t rank, int32_t world, int32_t num_q_heads,
+                               int32_t num_kv_heads, int32_t *kv_begin, int32_t *kv_end,
+                               int32_t *q_begin, int32_t *q_end);
+
 /* ---- BlockAllocator, block_allocator.rs:62-236 ---------------------------------- */
 typedef struct PaAllocator PaAllocator;
 PaAllocator *pa_alloc_create(uint32_t num_blocks, uint32_t block_size);

@@ -67,6 +67,20 @@ uint32_t pa_host_config_num_blocks(const PaHostConfig *cfg) { return cfg ? to_cf
 uint64_t pa_hash_tokens(const uint32_t *tokens, size_t n, uint64_t parent) { return hash_tokens(tokens, n, parent); }
 uint64_t pa_compute_token_hash(const uint32_t *tokens, size_t n) { return compute_token_hash(tokens, n); }
 float pa_kv_compute_scale(float max_abs) { return kv_compute_scale(max_abs); }
+pa_status pa_shard_head_ranges(int32_t rank, int32_t world, int32_t num_q_heads, int32_t num_kv_heads,
+                               int32_t *kv_begin, int32_t *kv_end, int32_t *q_begin, int32_t *q_end) {
+  if (!kv_begin || !kv_end || !q_begin || !q_end) return err("null output pointer");
+  if (world < 1 || rank < 0 || rank >= world) return err("bad rank/world");
+  if (num_kv_heads < 1 || num_q_heads < 1 || num_q_heads % num_kv_heads)
+    return err("query heads must be a positive multiple of kv heads");
+  if (num_kv_heads % world) return err("kv heads do not split this many ways");
+  const int32_t n = num_kv_heads / world, g = num_q_heads / num_kv_heads;
+  *kv_begin = rank * n;
+  *kv_end = (rank + 1) * n;
+  *q_begin = *kv_begin * g;
+  *q_end = *kv_end * g;
+  return PA_OK;
+}
 
 /* ---- allocator ---- */
 PaAllocator *pa_alloc_create(uint32_t num_blocks, uint32_t block_size) { return new PaAllocator(num_blocks, block_size); }

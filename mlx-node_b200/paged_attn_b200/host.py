@@ -61,6 +61,8 @@ _SIGS = {
     "pa_hash_tokens": (u64, [P(u32), sz, u64]),
     "pa_compute_token_hash": (u64, [P(u32), sz]),
     "pa_kv_compute_scale": (f32, [f32]),
+    "pa_shard_head_ranges": (i32, [i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32),
+                                   C.POINTER(i32)]),
     "pa_alloc_create": (vp, [u32, u32]), "pa_alloc_destroy": (None, [vp]),
     "pa_alloc_allocate": (i64, [vp]), "pa_alloc_release": (i32, [vp, u32]),
     "pa_alloc_incref": (i32, [vp, u32]), "pa_alloc_ref_count": (i64, [vp, u32]),

@@ -62,3 +62,26 @@ def test_shard_ranges():
         sharding.kv_head_range(0, 3, 8)
     with pytest.raises(ValueError):
         sharding.kv_head_range(2, 2, 8)
+
+
+def test_shard_head_ranges_c_abi_matches_python():
+    """The C ABI helper and the Python mirror give the same head ranges, and refuse the
+    same splits."""
+    import ctypes as C
+
+    from paged_attn_b200 import PagedAttnError, sharding
+    from paged_attn_b200.host import lib
+    l = lib()
+    for world in (1, 2, 4, 8):
+        for hq, hkv in ((32, 8), (64, 8), (16, 8), (8, 8)):
+            for rank in range(world):
+                out = [C.c_int32() for _ in range(4)]
+                rc = l.pa_shard_head_ranges(rank, world, hq, hkv, *[C.byref(o) for o in out])
+                assert rc == 0
+                assert (out[0].value, out[1].value) == sharding.kv_head_range(rank, world, hkv)
+                assert (out[2].value, out[3].value) == sharding.q_head_range(rank, world, hq, hkv)
+    out = [C.c_int32() for _ in range(4)]
+    refs = [C.byref(o) for o in out]
+    assert l.pa_shard_head_ranges(0, 3, 32, 8, *refs) == 1      # 8 heads do not split 3 ways
+    assert l.pa_shard_head_ranges(2, 2, 32, 8, *refs) == 1      # rank out of range
+    assert l.pa_shard_head_ranges(0, 2, 30, 8, *refs) == 1      # 30 is not a multiple of 8
