@@ -723,6 +723,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
   double tile_flops = 0.0, split_bytes = 0.0;  // work estimates, only with host context lengths
+  bool long_fp8 = false;  // FP8 cache and a chunk too long for the split-KV kernel
   for (int s = 0; s < num_seqs; s++) {
     const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
     if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
@@ -732,11 +733,10 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       have_class[(ql * G - 1) / 8] = true;
       split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
     } else {
-      if (c->fp8)
-        return fail(PA_ERR_UNSUPPORTED,
-                    "with an FP8 cache a sequence may hold at most " +
-                        std::to_string(split_cols / G) + " query tokens per call (the tile "
-                        "kernel for long chunks reads 16-bit pools only)");
+      if (c->fp8) {  // served below as several shorter sequences
+        long_fp8 = true;
+        continue;
+      }
       // Tiles of one (sequence, kv head) are neighbours in launch order so that they
       // share the head's KV blocks in L2; later tiles see more keys and go first.
       for (int h = 0; h < Hkv; h++)
@@ -745,15 +745,58 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       tile_flops += 4.0 * c->cfg.head_size * num_q_heads * ql * (kv - 0.5 * ql);
     }
   }
+  // The tile kernel reads 16-bit pools only.  With an FP8 cache a longer chunk is handed
+  // to the split-KV kernel as consecutive pieces of at most 24/G query tokens, each a
+  // sequence of its own with the same block-table row and the context length that ends
+  // at its last query: the same results (the KV of the chunk's sequence is read once per
+  // piece, from L2 mostly), at the price of that re-reading.
+  std::vector<int32_t> v_cu, v_ctx, v_row;
+  if (long_fp8) {
+    if (!context_lens_host)
+      return fail(PA_ERR_INVALID_ARG,
+                  "with an FP8 cache, chunks of more than " + std::to_string(split_cols / G) +
+                      " query tokens need context_lens_host");
+    const int piece = split_cols / G;
+    v_cu.push_back(0);
+    have_class[0] = have_class[1] = have_class[2] = false;
+    split_bytes = 0.0;
+    for (int s = 0; s < num_seqs; s++) {
+      const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
+      const int kv_len = context_lens_host[s];
+      for (int qa = 0; qa < ql || qa == 0; qa += piece) {
+        const int qb = std::min(ql, qa + piece);
+        v_cu.push_back(v_cu.back() + (qb - qa));
+        v_ctx.push_back(ql ? kv_len - ql + qb : kv_len);
+        v_row.push_back(s);
+        if (qb > qa) {
+          have_class[((qb - qa) * G - 1) / 8] = true;
+          split_bytes += (double)v_ctx.back() * 2.0 * Hkv * c->cfg.head_size;
+        }
+        if (ql == 0) break;
+      }
+    }
+  }
+  const int num_items = long_fp8 ? (int)v_row.size() : num_seqs;
   const bool any_split = have_class[0] || have_class[1] || have_class[2];
-  const size_t cu_bytes = ((size_t)(num_seqs + 1) * 4 + 255) & ~(size_t)255;
-  const size_t need = cu_bytes + tiles.size() * sizeof(pa::TileWork);
+  const size_t cu_bytes = ((size_t)(num_items + 1) * 4 + 255) & ~(size_t)255;
+  const size_t vx_bytes = long_fp8 ? (((size_t)num_items * 4 + 255) & ~(size_t)255) : 0;
+  const size_t need = cu_bytes + 2 * vx_bytes + tiles.size() * sizeof(pa::TileWork);
   st = grow(&c->meta, &c->meta_bytes, need);
   if (st != PA_OK) return st;
-  PA_CUDA(cudaMemcpyAsync(c->meta, cu_q_lens_host, (size_t)(num_seqs + 1) * 4,
+  char *meta = static_cast<char *>(c->meta);
+  PA_CUDA(cudaMemcpyAsync(meta, long_fp8 ? v_cu.data() : cu_q_lens_host, (size_t)(num_items + 1) * 4,
                           cudaMemcpyHostToDevice, stream));
-  p.cu_q_lens = static_cast<const int32_t *>(c->meta);
-  pa::TileWork *work_dev = reinterpret_cast<pa::TileWork *>(static_cast<char *>(c->meta) + cu_bytes);
+  p.cu_q_lens = reinterpret_cast<const int32_t *>(meta);
+  if (long_fp8) {
+    PA_CUDA(cudaMemcpyAsync(meta + cu_bytes, v_ctx.data(), (size_t)num_items * 4,
+                            cudaMemcpyHostToDevice, stream));
+    PA_CUDA(cudaMemcpyAsync(meta + cu_bytes + vx_bytes, v_row.data(), (size_t)num_items * 4,
+                            cudaMemcpyHostToDevice, stream));
+    p.context_lens = reinterpret_cast<const int32_t *>(meta + cu_bytes);
+    p.seq_row = reinterpret_cast<const int32_t *>(meta + cu_bytes + vx_bytes);
+    p.S = num_items;
+  }
+  pa::TileWork *work_dev = reinterpret_cast<pa::TileWork *>(meta + cu_bytes + 2 * vx_bytes);
   if (!tiles.empty())
     PA_CUDA(cudaMemcpyAsync(work_dev, tiles.data(), tiles.size() * sizeof(pa::TileWork),
                             cudaMemcpyHostToDevice, stream));

@@ -132,6 +132,8 @@ struct AttnParams {
   const int32_t *block_tables;  // [S, MB]
   const int32_t *context_lens;  // [S]
   const int32_t *cu_q_lens;     // [S+1] device copy, or null: one query per sequence
+  const int32_t *seq_row;       // null, or [S]: block-table row of each sequence (when a long
+                                // chunk is served as several shorter sequences)
   int S, Hq, Hkv, G, MB;
   int is_f16;  // element format: 1 = f16, 0 = bf16
   int is_fp8;  // pools hold E4M3 bytes (split-KV kernels only); is_f16 is then the q/out format

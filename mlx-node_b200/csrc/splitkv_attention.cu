@@ -248,7 +248,8 @@ splitkv_kernel(const AttnParams p) {
     const int r = (int)(u - (long long)Hkv * pre[s]);
     const int nb = pre[s + 1] - pre[s];
     const int h = r / nb, b = r - h * nb;
-    uint32_t id = (uint32_t)p.block_tables[(long long)(p.seq_base + s) * p.MB + b];
+    const int row = p.seq_row ? p.seq_row[p.seq_base + s] : p.seq_base + s;
+    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + b];
     if (id >= p.num_blocks) {
       atomicOr(p.err, kErrBlockRange);
       id = 0;

@@ -200,12 +200,21 @@ def test_fp8_overflow_in_a_write_switches_to_exact_decoding(cuda_device):
     check_attention(np.where(fin, got, 0), np.where(fin, ref, 0), "finite part")
 
 
-def test_fp8_long_chunk_is_refused(cuda_device):
-    case = Case([200], [100], 8, 2, 16, seed=86)
-    dc = Fp8DeviceCase(case, 1.0, 1.0)
+def test_fp8_long_chunks_run_as_pieces(cuda_device):
+    """The tile kernel reads 16-bit pools only; with an FP8 cache a prefill chunk is served
+    by the split-KV kernel in pieces of 24/G query tokens.  Same results as the oracle on
+    the whole chunk; a decode and an empty sequence ride along."""
+    case = Case([200, 64, 33, 700], [100, 30, 1, 0], 8, 2, 128, seed=86)
+    got, ref = run(case, 0.5, 0.5)
+    check_attention(got, ref, "fp8 chunk in pieces")
+    # the piece boundaries need the context lengths on the host
+    dc = Fp8DeviceCase(case, 0.5, 0.5, exact=False)
+    dc.write_and_check()
+    out = torch.zeros((case.total_q, case.Hq, D), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(pa.PagedAttnError) as e:
-        dc.attend()
-    assert e.value.status == 2
+        dc.cache.varlen(out, dc.q, dc.tables, dc.lens, case.cu_q, case.S, case.Hq, case.MB,
+                        case.scale, dc.ws, dc.ws_bytes)
+    assert e.value.status == 1
 
 
 def test_fp8_copy_blocks_and_swap(cuda_device):
