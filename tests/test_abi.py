@@ -98,3 +98,24 @@ def test_swap_block_sizes():
     assert (k.value, v.value) == (16384, 16384)
     lib.pa_swap_block_bytes(4, 128, 16, 1, C.byref(k), C.byref(v))
     assert (k.value, v.value) == (8192, 8192)
+
+
+def test_plain_c_program_links_and_runs(tmp_path):
+    """The headers are C (not only C++) and the shared object is usable from a C program
+    without Python in between; only entry points that need no GPU are called."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cc = shutil.which("gcc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    libdir = os.path.join(root, "mlx-node_b200")
+    exe = str(tmp_path / "c_abi_host_smoke")
+    subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-I", os.path.join(root, "include"),
+                    os.path.join(root, "tests", "c_abi_host_smoke.c"), "-o", exe, "-L", libdir,
+                    "-lpaged_attn_b200", f"-Wl,-rpath,{libdir}"], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    words = r.stdout.split()
+    assert words[0] == "version" and int(words[1]) >= 100
+    assert words[-5:] == ["shard", "4", "8", "16", "32"] and words[words.index("hash") + 1] == "1"
