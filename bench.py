@@ -214,8 +214,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--gather", action="store_true",
-                    help="all-gather the head outputs over NCCL inside the step (N > 1)")
+    ap.add_argument("--gather", nargs="?", const="nccl", default=None, choices=["nccl", "peer"],
+                    help="all-gather the head outputs inside the step (N > 1): over NCCL, or "
+                         "'peer' = the library's stores into the other ranks' buffers "
+                         "(symmetric memory), checked once against NCCL")
     ap.add_argument("--fp8", action="store_true",
                     help="E4M3 KV cache (one byte per element); decode workloads only")
     ap.add_argument("--producer", action="store_true",
@@ -317,7 +319,20 @@ def main() -> None:
     scale = 1.0 / math.sqrt(D)
     decode_only = bool((ql == 1).all())
     kv_i32 = np.ascontiguousarray(kv.astype(np.int32))
-    do_gather = args.gather and world > 1
+    do_gather = args.gather is not None and world > 1
+    peer = None
+    if do_gather and args.gather == "peer":
+        import torch.distributed._symmetric_memory as symm_mem
+        # two full-width output buffers (alternating, so that a rank never overwrites what a
+        # slower rank is still reading) and the flag words, all in symmetric memory
+        fulls = [symm_mem.empty((total_q, Hq, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        flag_t = symm_mem.empty((64,), dtype=torch.int32, device=dev)
+        flag_t.zero_()
+        hd = [symm_mem.rendezvous(t, dist.group.WORLD) for t in fulls]
+        hf = symm_mem.rendezvous(flag_t, dist.group.WORLD)
+        dist.barrier()
+        peer = {"fulls": fulls, "out_ptrs": [[int(p) for p in h.buffer_ptrs] for h in hd],
+                "flag_ptrs": [int(p) for p in hf.buffer_ptrs], "epoch": 0}
     stream = torch.cuda.current_stream().cuda_stream
 
     if args.producer:
@@ -340,7 +355,12 @@ def main() -> None:
         else:
             cache.varlen(out, q, tables, lens, cu_q, S, hq_l, MB, scale, ws, ws_bytes,
                          max_context_len=int(kv.max()), stream=stream, context_lens_host=kv_i32)
-        if do_gather:
+        if do_gather and peer is not None:
+            peer["epoch"] += 1
+            k = peer["epoch"] & 1
+            cache.gather_heads_peer_store(out, total_q, hq_l, world, rank, peer["out_ptrs"][k],
+                                          peer["flag_ptrs"], peer["epoch"], stream=stream)
+        elif do_gather:
             sharding.gather_heads(out, world)
 
     def barrier():
@@ -365,6 +385,15 @@ def main() -> None:
     for _ in range(args.warmup):
         step()
     cache.check_errors(stream)
+    if peer is not None:
+        torch.cuda.synchronize()
+        ref_full = sharding.gather_heads(out, world)
+        got_full = peer["fulls"][peer["epoch"] & 1]
+        same = torch.equal(ref_full.view(torch.int16), got_full.view(torch.int16))
+        flag = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        peer["checked"] = bool(flag.item())
+        dist.barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -462,7 +491,10 @@ def main() -> None:
         if args.producer:
             line["config"]["producer"] = "QK norm + rotary embedding fused into the KV write launch"
         if do_gather:
-            line["config"]["gather"] = "NCCL all_gather of head outputs inside the step"
+            line["config"]["gather"] = (
+                "stores into every rank's buffer over NVLink + one flag per rank pair, inside the "
+                "step; equal to an NCCL all_gather of the same outputs: " + str(peer["checked"])
+                if peer is not None else "NCCL all_gather of head outputs inside the step")
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

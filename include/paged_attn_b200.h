@@ -252,6 +252,30 @@ pa_status pa_swap_out(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t 
                       size_t num_blocks, PaCpuBlockCache *cpu, void *cuda_stream);
 pa_status pa_swap_in(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *block_ids,
                      size_t num_blocks, PaCpuBlockCache *cpu, void *cuda_stream);
+/* All-gather of head outputs over peer memory, for KV-head sharding across the GPUs
+ * of one box when a consumer needs every head on every rank (no counterpart in the
+ * reference, which runs on one device).  Rank `rank` holds local_out
+ * [num_tokens, heads_local, head_size]; peer_out[w] is rank w's
+ * [num_tokens, world * heads_local, head_size] buffer and peer_flags[w] its `world`
+ * flag words (zero before the first call), both addressable from this GPU (peer access
+ * in one process, or symmetric-memory / IPC mappings across processes).  The call
+ * stores this rank's heads into every buffer with plain 16-byte stores, publishes
+ * flag[rank] = epoch in every rank's flag words, and then, if `wait` is non-zero, waits
+ * on `stream` (about a second at most; a missing writer is reported as PA_ERR_TIMEOUT by
+ * pa_cache_check_errors) until all `world` flags of this rank have reached `epoch`;
+ * pa_gather_heads_wait is that wait on its own, for a caller that wants to put work
+ * between the two.
+ * Use epoch = 1, 2, 3, ... for successive calls; every rank must make the same calls.
+ * Before an output buffer is reused as a peer_out target, all ranks must have consumed
+ * its previous contents (alternate two buffers, or separate the steps by a barrier). */
+pa_status pa_gather_heads_peer_store(PagedAttnCache *cache, const void *local_out,
+                                     int64_t num_tokens, int32_t heads_local, int32_t world,
+                                     int32_t rank, void *const *peer_out,
+                                     uint32_t *const *peer_flags, uint32_t epoch,
+                                     int32_t wait, void *cuda_stream);
+pa_status pa_gather_heads_wait(PagedAttnCache *cache, const uint32_t *my_flags, int32_t world,
+                               uint32_t epoch, void *cuda_stream);
+
 /* SwapBlocksParams::key_block_size / value_block_size (swap_blocks.rs:53-108):
  * bytes of one block of one layer; use_fp8 halves them.                           */
 void pa_swap_block_bytes(uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,

@@ -494,6 +494,49 @@ pa_status pa_copy_blocks(PagedAttnCache *c, uint32_t layer, const int64_t *mappi
   return PA_OK;
 }
 
+pa_status pa_gather_heads_peer_store(PagedAttnCache *c, const void *local_out, int64_t num_tokens,
+                                     int32_t heads_local, int32_t world, int32_t rank,
+                                     void *const *peer_out, uint32_t *const *peer_flags,
+                                     uint32_t epoch, int32_t wait, void *cuda_stream) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  if (world < 1 || world > pa::kMaxPeers || rank < 0 || rank >= world)
+    return fail(PA_ERR_INVALID_ARG, "world must be 1..8 and 0 <= rank < world");
+  if (num_tokens < 0 || heads_local <= 0) return fail(PA_ERR_INVALID_ARG, "bad sizes");
+  if (!local_out || !peer_out || !peer_flags) return fail(PA_ERR_INVALID_ARG, "null pointer");
+  pa::PeerGather a{};
+  a.local_out = local_out;
+  for (int w = 0; w < world; w++) {
+    if (!peer_out[w] || !peer_flags[w] || !aligned16(peer_out[w]))
+      return fail(PA_ERR_INVALID_ARG, "peer buffers must be non-null and 16-byte aligned");
+    a.peer_out[w] = peer_out[w];
+    a.peer_flags[w] = peer_flags[w];
+  }
+  if (!aligned16(local_out)) return fail(PA_ERR_INVALID_ARG, "local_out must be 16-byte aligned");
+  a.counter = c->err_dev + 32;  // a zeroed word of the handle, next to the error word
+  a.num_tokens = num_tokens;
+  a.row_bytes_local = heads_local * (int32_t)c->cfg.head_size * 2;
+  a.world = world;
+  a.rank = rank;
+  a.epoch = epoch;
+  DeviceGuard g(c->device);
+  PA_CUDA(pa::launch_peer_gather(a, static_cast<cudaStream_t>(cuda_stream)));
+  if (wait)
+    PA_CUDA(pa::launch_peer_wait(peer_flags[rank], world, epoch, c->err_dev,
+                                 static_cast<cudaStream_t>(cuda_stream)));
+  return PA_OK;
+}
+
+pa_status pa_gather_heads_wait(PagedAttnCache *c, const uint32_t *my_flags, int32_t world,
+                               uint32_t epoch, void *cuda_stream) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  if (!my_flags || world < 1 || world > pa::kMaxPeers)
+    return fail(PA_ERR_INVALID_ARG, "flags null or world not in 1..8");
+  DeviceGuard g(c->device);
+  PA_CUDA(pa::launch_peer_wait(my_flags, world, epoch, c->err_dev,
+                               static_cast<cudaStream_t>(cuda_stream)));
+  return PA_OK;
+}
+
 /* ---- swap ------------------------------------------------------------------------ */
 }  // extern "C"
 

@@ -315,6 +315,78 @@ cudaError_t launch_stage_copy(const StageCopy &a, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+// ---- head gather over peer memory ------------------------------------------------
+// With the KV heads sharded over the GPUs of a box, rank r holds out[:, r*hl:(r+1)*hl, :].
+// A consumer that wants every head on every rank gets them by plain 16-byte stores into
+// each rank's full-width buffer (peer pointers: NVLink through NVSwitch), followed by one
+// flag per (writer, reader) pair written with release semantics at system scope once all
+// of the writer's stores are out.  No library collective, no multicast.
+__global__ void __launch_bounds__(256)
+scatter_heads_kernel(PeerGather a) {
+  const size_t vec_local = (size_t)a.row_bytes_local / 16;   // 16-byte vectors per local row
+  const size_t vec_full = vec_local * a.world;
+  const size_t total = (size_t)a.num_tokens * vec_local * a.world;
+  const uint4 *src = static_cast<const uint4 *>(a.local_out);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t per_peer = (size_t)a.num_tokens * vec_local;
+    const int w = (int)(i / per_peer);
+    const size_t r = i - (size_t)w * per_peer;
+    const size_t t = r / vec_local, v = r - t * vec_local;
+    static_cast<uint4 *>(a.peer_out[w])[t * vec_full + (size_t)a.rank * vec_local + v] = src[r];
+  }
+  // last block out publishes: every block fences its stores, then counts itself
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned last;
+  if (threadIdx.x == 0) last = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+  __syncthreads();
+  if (last) {
+    if (threadIdx.x < (unsigned)a.world) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x] + a.rank),
+                   "r"(a.epoch)
+                   : "memory");
+    }
+    if (threadIdx.x == 0) *a.counter = 0u;
+  }
+}
+
+// Reader side: until every writer's flag has reached `epoch`, for about a second at most;
+// a flag that never comes sets the time-out bit instead of hanging the stream.
+__global__ void wait_heads_kernel(const unsigned *my_flags, int world, unsigned epoch, unsigned *err) {
+  const int w = threadIdx.x;
+  if (w >= world) return;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + w) : "memory");
+    if ((int)(v - epoch) >= 0) return;
+    if (clock64() - t0 > (1ll << 31)) {
+      atomicOr(err, kErrTimeout);
+      return;
+    }
+  }
+}
+
+cudaError_t launch_peer_wait(const unsigned *my_flags, int world, unsigned epoch, unsigned *err,
+                             cudaStream_t st) {
+  wait_heads_kernel<<<1, 32, 0, st>>>(my_flags, world, epoch, err);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_gather(const PeerGather &a, cudaStream_t st) {
+  const size_t total = (size_t)a.num_tokens * (a.row_bytes_local / 16) * a.world;
+  if (total) {
+    const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 296);
+    scatter_heads_kernel<<<blocks, 256, 0, st>>>(a);
+    __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+    return cudaGetLastError();
+  }
+  return cudaSuccess;
+}
+
 // Swap: one CTA per (block, 4 KB piece), 16 bytes per thread, K then V.  The host side
 // of each block is pinned memory mapped into the device's address space, so the kernel
 // itself moves the bytes over PCIe (one launch for any number of blocks).

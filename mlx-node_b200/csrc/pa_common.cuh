@@ -203,6 +203,21 @@ struct StageCopy {
   size_t bytes[3];
 };
 cudaError_t launch_stage_copy(const StageCopy &a, cudaStream_t st);
+// Head gather over peer memory (cache_kernels.cu).
+constexpr int kMaxPeers = 8;
+struct PeerGather {
+  const void *local_out;          // [num_tokens, row_bytes_local] contiguous
+  void *peer_out[kMaxPeers];      // every rank's [num_tokens, world * row_bytes_local] buffer
+  unsigned *peer_flags[kMaxPeers];  // every rank's flag words, one per writer
+  unsigned *counter;              // zero-initialised device word of the caller
+  int64_t num_tokens;
+  int32_t row_bytes_local;        // heads_local * head_size * 2, a multiple of 16
+  int32_t world, rank;
+  unsigned epoch;
+};
+cudaError_t launch_peer_gather(const PeerGather &a, cudaStream_t st);
+cudaError_t launch_peer_wait(const unsigned *my_flags, int world, unsigned epoch, unsigned *err,
+                             cudaStream_t st);
 // Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.
 cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st);
 size_t splitkv_workspace_bytes(int num_ctas);

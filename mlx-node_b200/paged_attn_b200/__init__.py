@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = [
     "pa_cache_get_config", "pa_cache_check_errors", "pa_reshape_and_cache", "pa_copy_blocks",
     "pa_qk_norm_rope_and_cache", "pa_cache_create_fp8", "pa_cache_wrap_fp8", "pa_cache_is_fp8",
     "pa_cache_set_kv_scales", "pa_cache_get_kv_scales", "pa_cache_fp8_set_exact_decode",
+    "pa_gather_heads_peer_store", "pa_gather_heads_wait",
     "pa_attention_workspace_bytes", "pa_paged_attention_decode", "pa_paged_attention_varlen",
     "pa_paged_attention_decode_static", "pa_cpu_cache_create", "pa_cpu_cache_free",
     "pa_cpu_cache_is_swapped", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
@@ -81,6 +82,9 @@ def load_library() -> C.CDLL:
     lib.pa_cache_set_kv_scales.argtypes = [vp, u32, f32, f32]
     lib.pa_cache_get_kv_scales.argtypes = [vp, u32, C.POINTER(f32), C.POINTER(f32)]
     lib.pa_cache_fp8_set_exact_decode.argtypes = [vp, i32]
+    lib.pa_gather_heads_peer_store.argtypes = [vp, vp, i64, i32, i32, i32, C.POINTER(vp), C.POINTER(vp),
+                                               u32, i32, vp]
+    lib.pa_gather_heads_wait.argtypes = [vp, vp, i32, u32, vp]
     lib.pa_cache_free.argtypes = [vp]
     lib.pa_cache_key_ptr.argtypes = [vp, u32]
     lib.pa_cache_key_ptr.restype = vp
@@ -198,6 +202,20 @@ class PagedCache:
 
     def set_kv_scales(self, k_scale: float, v_scale: float, layer: int = 0) -> None:
         _check(self.lib.pa_cache_set_kv_scales(self.handle, layer, k_scale, v_scale))
+
+    def gather_heads_peer_store(self, local_out, num_tokens: int, heads_local: int, world: int,
+                                rank: int, peer_out_ptrs, peer_flag_ptrs, epoch: int,
+                                wait: bool = True, stream: int = 0) -> None:
+        """Stores this rank's heads into every rank's full-width buffer and (wait=True) waits
+        for the others (peer pointers as integers)."""
+        outs = (C.c_void_p * world)(*[int(x) for x in peer_out_ptrs])
+        flags = (C.c_void_p * world)(*[int(x) for x in peer_flag_ptrs])
+        _check(self.lib.pa_gather_heads_peer_store(self.handle, _ptr(local_out), num_tokens,
+                                                   heads_local, world, rank, outs, flags, epoch,
+                                                   int(wait), stream))
+
+    def gather_heads_wait(self, my_flags, world: int, epoch: int, stream: int = 0) -> None:
+        _check(self.lib.pa_gather_heads_wait(self.handle, _ptr(my_flags), world, epoch, stream))
 
     def fp8_set_exact_decode(self, on: bool) -> None:
         _check(self.lib.pa_cache_fp8_set_exact_decode(self.handle, int(on)))
