@@ -39,10 +39,11 @@
 // computed next to the softmax and P.V of the current one, so that the two dependency
 // chains (ldmatrix -> MMA chain, and max -> exp2 -> movmatrix -> MMA) overlap.
 //
-// FP8 (E4M3) pools: the same kernel on 2 KB chunks, with the products either on the FP8
-// tensor-core path straight from the cache bytes or, when the cache may hold bytes that
-// the tensor cores read differently from the cache format, on f16 after an integer
-// conversion; see the comments at fp8x4_to_f16 and in the main loop.
+// FP8 (E4M3) pools: the same kernel on 2 KB chunks.  K.Q^T runs on the FP8 tensor-core
+// path straight from the cache bytes (queries split into two E4M3 numbers) unless the
+// cache may hold bytes that the tensor cores read differently from the cache format; then,
+// and always for V^T.P^T, the bytes become f16 by integer operations; see the comments at
+// fp8x4_to_f16 and in the main loop.
 #include <mutex>
 #include <type_traits>
 
@@ -143,33 +144,6 @@ __device__ __forceinline__ float f16hi_to_float(uint32_t h2) {
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
   return pack2<true>(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
-// A operand E4M3 (cache bytes), B operand E5M2 (probabilities).
-__device__ __forceinline__ void mma_fp8_16832_e5m2(float (&d)[4], const uint32_t (&a)[4],
-                                                   uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e5m2.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-      "{%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// An f16 pair rounded (to nearest even) to E5M2 precision, i.e. to its high bytes; the
-// result is still an f16 pair, with zero low bytes.
-__device__ __forceinline__ uint32_t f16x2_round_e5m2(uint32_t h) {
-  return (h + 0x007F007Fu + ((h >> 8) & 0x00010001u)) & 0xFF00FF00u;
-}
-__device__ __forceinline__ uint32_t f16x2_sub(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-// Fast FP8 variant: MMA row r holds token 4*((r&7)>>1) + 2*(r&1) + (r>>3), so that one
-// movmatrix of the packed probabilities yields, per thread, the four tokens 4t..4t+3 of
-// one column - the order of the bytes in a V row piece.
-__device__ __forceinline__ int fp8_row_token_fast(int r) {
-  return 4 * ((r & 7) >> 1) + 2 * (r & 1) + (r >> 3);
-}
-constexpr float kPScale = 16384.f;  // probabilities are scaled by 2^14 before they become E5M2
-
 // FP8 path: row r of a 16-token MMA tile holds token fp8_row_token(r) of the block, so
 // that the token pairs a thread gets from one 32-bit piece of a V row (tokens 4t..4t+3)
 // are the pairs its P^T fragment holds.
@@ -292,9 +266,7 @@ splitkv_kernel(const AttnParams p) {
   bool dead = false;   // a wait ran out: stop touching data, keep the barriers balanced
   // k_scale: FP8 dequantisation (with the conversion's missing 2^8), else 1
   const float qk_scale = p.scale * p.k_scale * (FP8 ? kFp8Unbias : 1.f);
-  // fast FP8 variant: V bytes at face value, probabilities scaled by 2^14
-  const float v_unscale =
-      p.v_scale * (FP8 ? (EXACT ? kFp8Unbias : 1.f / kPScale) : 1.f);
+  const float v_unscale = p.v_scale * (FP8 ? kFp8Unbias : 1.f);
   const float sc_log2 = qk_scale * kLog2e;
   const bool use_cap = p.softcap != 1.0f;
 
@@ -440,8 +412,7 @@ splitkv_kernel(const AttnParams p) {
             // one 32-wide step: 16-byte row pieces of chunks 2s and 2s+1, rows 0-7 and 8-15,
             // land in the registers in the order the A operand wants them
             uint32_t r[4];
-            ldmatrix_x4(r, ks + (2 * st32 + (mi >> 1)) * 256 +
-                               fp8_row_token_fast((mi & 1) * 8 + mr) * 16);
+            ldmatrix_x4(r, ks + (2 * st32 + (mi >> 1)) * 256 + fp8_row_token((mi & 1) * 8 + mr) * 16);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
               mma_fp8_16832(sacc[nt], r, qf[nt][st32][0], qf[nt][st32][1]);
@@ -484,9 +455,8 @@ splitkv_kernel(const AttnParams p) {
     // softmax of the unit's logits and O^T += V^T.P^T, V from ring stage `st`
     auto finish = [&](int st, int blk, float (&sacc)[NT][4]) {
         const uint32_t vs = ring_w + st * kStageBytes + kChunk;
-        const int tok0 =
-            blk * kBlockSize + (QK8 ? fp8_row_token_fast(gid) : FP8 ? fp8_row_token(gid) : gid);
-        const int tok1 = QK8 ? tok0 + 1 : FP8 ? tok0 + 2 : tok0 + 8;
+        const int tok0 = blk * kBlockSize + (FP8 ? fp8_row_token(gid) : gid);
+        const int tok1 = FP8 ? tok0 + 2 : tok0 + 8;
         const bool need_mask = (blk + 1) * kBlockSize > min_lim;
         float alpha[NT][2];
 #pragma unroll
@@ -532,24 +502,8 @@ splitkv_kernel(const AttnParams p) {
         uint32_t pb[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-          if (QK8) {
-            // P as two E5M2 numbers per element, hi = rn(p) and lo = rn(p - hi) (six
-            // significant bits together, the exponent range of f16), in the byte order
-            // [row gid | row gid+8] x [column 2tig, 2tig+1]: after the transpose a thread
-            // holds the four tokens 4tig..4tig+3 of column gid.  pb[.][0] feeds k-slots
-            // 0-15 (hi), pb[.][1] k-slots 16-31 (lo) of one 32-wide MMA whose A operand
-            // repeats the V piece.
-            const uint32_t ha = pack2<true>(sacc[nt][0] * kPScale, sacc[nt][2] * kPScale);
-            const uint32_t hb = pack2<true>(sacc[nt][1] * kPScale, sacc[nt][3] * kPScale);
-            const uint32_t ha_hi = f16x2_round_e5m2(ha), hb_hi = f16x2_round_e5m2(hb);
-            const uint32_t ha_lo = f16x2_round_e5m2(f16x2_sub(ha, ha_hi));
-            const uint32_t hb_lo = f16x2_round_e5m2(f16x2_sub(hb, hb_hi));
-            pb[nt][0] = movmatrix_trans(__byte_perm(ha_hi, hb_hi, 0x7531u));
-            pb[nt][1] = movmatrix_trans(__byte_perm(ha_lo, hb_lo, 0x7531u));
-          } else {
-            pb[nt][0] = movmatrix_trans(pack2<MF16>(sacc[nt][0], sacc[nt][1]));
-            pb[nt][1] = movmatrix_trans(pack2<MF16>(sacc[nt][2], sacc[nt][3]));
-          }
+          pb[nt][0] = movmatrix_trans(pack2<MF16>(sacc[nt][0], sacc[nt][1]));
+          pb[nt][1] = movmatrix_trans(pack2<MF16>(sacc[nt][2], sacc[nt][3]));
         }
         // Tokens past the context in the last block may hold anything (NaN
         // included) and 0*NaN is NaN: clear them in the V fragments
@@ -581,19 +535,13 @@ splitkv_kernel(const AttnParams p) {
             for (int hf = 0; hf < 2; hf++) {
               const int mt = 2 * mm + hf;
               uint32_t vf[4];
-              if (QK8) {  // the V bytes are the operand: k-slots 0-15 and 16-31 both hold them
-                vf[0] = vf[2] = r[2 * hf] & vmask[0];
-                vf[1] = vf[3] = r[2 * hf + 1] & vmask[0];
-              } else {
-                fp8x4_to_f16<EXACT>(r[2 * hf] & vmask[0], vf[0], vf[2]);
-                fp8x4_to_f16<EXACT>(r[2 * hf + 1] & vmask[0], vf[1], vf[3]);
-              }
+              fp8x4_to_f16<EXACT>(r[2 * hf] & vmask[0], vf[0], vf[2]);
+              fp8x4_to_f16<EXACT>(r[2 * hf + 1] & vmask[0], vf[1], vf[3]);
 #pragma unroll
               for (int nt = 0; nt < NT; nt++) {
                 o[mt][nt][0] *= alpha[nt][0]; o[mt][nt][1] *= alpha[nt][1];
                 o[mt][nt][2] *= alpha[nt][0]; o[mt][nt][3] *= alpha[nt][1];
-                if (QK8) mma_fp8_16832_e5m2(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
-                else mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
+                mma_16816<MF16>(o[mt][nt], vf, pb[nt][0], pb[nt][1]);
               }
             }
           }

@@ -10,7 +10,8 @@ import torch
 import paged_attn_b200 as pa
 from gpu_util import to_bits, to_dev
 from paged_attn_b200.host import HybridScheduler, PagedKVCacheHost, host_config
-from pa_testlib import BS, D, X, bf16_to_f32, check_attention, normal_bf16
+from pa_testlib import (BS, D, X, X8, bf16_to_f32, check_attention, fp8_pools, normal_bf16, oracle,
+                        write_oracle_fp8)
 
 pytestmark = pytest.mark.gpu
 
@@ -27,7 +28,20 @@ def dense_rows(q, k, v, positions, G, scale):
     return out
 
 
-def test_scheduler_drives_the_kernels(cuda_device):
+def through_fp8(x_bits, scale):
+    """[L, Hkv, D] bf16 bits -> float64 values as an FP8 cache with this scale holds them
+    (written by the oracle into a scratch pool, decoded by the format's table)."""
+    L, Hkv, _ = x_bits.shape
+    nb = (L + BS - 1) // BS
+    k8, v8 = fp8_pools(nb, Hkv)
+    write_oracle_fp8(k8, v8, x_bits, x_bits, np.arange(L, dtype=np.int64), Hkv, scale, scale)
+    table = np.array([oracle().oracle_fp8_e4m3_decode(c) for c in range(256)], dtype=np.float64)
+    vals = table[v8] * scale                       # [nb, Hkv, D, BS]
+    return vals.transpose(0, 3, 1, 2).reshape(nb * BS, Hkv, D)[:L]
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_scheduler_drives_the_kernels(cuda_device, fp8):
     Hq, Hkv, L = 16, 4, 400
     G = Hq // Hkv
     rng = np.random.Generator(np.random.PCG64(5))
@@ -35,9 +49,19 @@ def test_scheduler_drives_the_kernels(cuda_device):
                       max_seq_len=512)
     kv_host = PagedKVCacheHost(cfg)
     NB = kv_host.total_blocks()
-    k_pool = torch.zeros(NB, Hkv, D // X, BS, X, dtype=torch.bfloat16, device="cuda")
-    v_pool = torch.zeros(NB, Hkv, D, BS, dtype=torch.bfloat16, device="cuda")
-    cache = pa.PagedCache(BS, NB, D, Hkv, key_pools=[k_pool], value_pools=[v_pool])
+    kv_scale = 1.0 / 16
+    if fp8:
+        # prefill chunks of 64 tokens are longer than one split-KV piece (24/G = 6 tokens):
+        # this run also covers the chunk-in-pieces path and its host context lengths
+        k_pool = torch.zeros(NB, Hkv, D // X8, BS, X8, dtype=torch.uint8, device="cuda")
+        v_pool = torch.zeros(NB, Hkv, D, BS, dtype=torch.uint8, device="cuda")
+    else:
+        k_pool = torch.zeros(NB, Hkv, D // X, BS, X, dtype=torch.bfloat16, device="cuda")
+        v_pool = torch.zeros(NB, Hkv, D, BS, dtype=torch.bfloat16, device="cuda")
+    cache = pa.PagedCache(BS, NB, D, Hkv, key_pools=[k_pool], value_pools=[v_pool], fp8=fp8)
+    if fp8:
+        cache.set_kv_scales(kv_scale, kv_scale)
+        cache.fp8_set_exact_decode(False)   # zero-filled pools, in-range values
     ws = torch.empty(cache.workspace_bytes(), dtype=torch.uint8, device="cuda")
     sched = HybridScheduler(BS, prefill_chunk_size=64, max_tokens_per_step=160, max_prefill_per_step=2,
                             max_batch_size=8, eos_token_id=1 << 30)
@@ -49,6 +73,13 @@ def test_scheduler_drives_the_kernels(cuda_device):
         true_k[name] = normal_bf16((L, Hkv, D), 100 + i, 2)
         true_v[name] = normal_bf16((L, Hkv, D), 100 + i, 3)
         junk_k[name] = normal_bf16((L, Hkv, D), 100 + i, 4)
+    # what the cache holds of the true keys and values
+    if fp8:
+        held_k = {n: through_fp8(true_k[n], kv_scale) for n in prompts}
+        held_v = {n: through_fp8(true_v[n], kv_scale) for n in prompts}
+    else:
+        held_k = {n: bf16_to_f32(true_k[n]).astype(np.float64) for n in prompts}
+        held_v = {n: bf16_to_f32(true_v[n]).astype(np.float64) for n in prompts}
     scale = 1.0 / np.sqrt(D)
     checked, kinds, steps = 0, set(), 0
     while not sched.is_empty() and steps < 200:
@@ -84,15 +115,15 @@ def test_scheduler_drives_the_kernels(cuda_device):
         cu = np.asarray(b["cu_q_lens"], dtype=np.int32)
         cache.reshape_and_cache(to_dev(k), to_dev(v), slots, total, Hkv * D, Hkv * D)
         cache.varlen(out, to_dev(q), tables, lens, cu, n, Hq, b["max_blocks_per_seq"], scale, ws, ws.numel(),
-                     max_context_len=b["max_context_len"])
+                     max_context_len=b["max_context_len"],
+                     context_lens_host=np.asarray(b["context_lens"], dtype=np.int32) if fp8 else None)
         torch.cuda.synchronize()
         cache.check_errors()
         got = bf16_to_f32(to_bits(out))
         for name in {kname for _, kname, _ in keep}:
             rows = [(r, p_) for r, kname, p_ in keep if kname == name]
-            ref = dense_rows(bf16_to_f32(true_q[name]).astype(np.float64),
-                             bf16_to_f32(true_k[name]).astype(np.float64),
-                             bf16_to_f32(true_v[name]).astype(np.float64), [p_ for _, p_ in rows], G, scale)
+            ref = dense_rows(bf16_to_f32(true_q[name]).astype(np.float64), held_k[name],
+                             held_v[name], [p_ for _, p_ in rows], G, scale)
             check_attention(np.stack([got[r] for r, _ in rows]), ref, f"step {steps} {name}")
             checked += len(rows)
         sched.process_outputs(outputs, kv_host)
