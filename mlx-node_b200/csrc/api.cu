@@ -868,6 +868,16 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
           best_tile_sms = n2;
         }
       }
+#ifdef PA_DEBUG_TUNE  // debug builds: sweep the split by hand
+      if (const char *e = getenv("PA_DEBUG_TILE_SMS")) {
+        best_tile_sms = atoi(e);
+        best = 0.0;
+        if (getenv("PA_DEBUG_VERBOSE")) fprintf(stderr, "tile_sms forced to %d\n", best_tile_sms);
+      } else if (getenv("PA_DEBUG_VERBOSE")) {
+        fprintf(stderr, "model picks tile_sms %d (cost %.1f us, alone %.1f + %.1f us)\n", best_tile_sms,
+                best * 1e6, t_tile_alone * 1e6, t_split_alone * 1e6);
+      }
+#endif
       if (best_tile_sms > 0 && best < t_tile_alone + t_split_alone) {
         split_ctas = c->num_sms - best_tile_sms;
         side_by_side = true;
