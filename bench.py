@@ -153,7 +153,7 @@ def run_reference(args, rank: int, world: int) -> None:
     n_s = min(len(kv), max(cores, 8))
     kv_s, ql_s = kv[:n_s], ql[:n_s]
     nb = int(((kv_s + BS - 1) // BS).sum())
-    case = Case(kv_s, ql_s, Hq, Hkv, nb + 8, seed=0)
+    case = Case(kv_s, ql_s, Hq, Hkv, nb + 8, seed=0, bs=BS)
     k_pool, v_pool = case.k_pool, case.v_pool
     k_pool[k_pool == 0x7FFF] = 0
     v_pool[v_pool == 0x7FFF] = 0
@@ -226,7 +226,11 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--seqs", type=int, default=0, help="use only the first N sequences (small captures)")
     ap.add_argument("--pool-blocks", type=int, default=0, help="override the pool size in blocks")
+    ap.add_argument("--block-size", type=int, default=16, choices=[16, 32],
+                    help="tokens per pool block (the configurations are quoted on 16)")
     args = ap.parse_args()
+    global BS
+    BS = args.block_size
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -249,6 +253,8 @@ def main() -> None:
     kv, ql, Hq, Hkv, NB = workload_lengths(args.workload, world)
     if args.seqs:
         kv, ql = kv[:args.seqs], ql[:args.seqs]
+    if BS != 16:  # the same pool bytes in larger blocks
+        NB = max(NB * 16 // BS, int(((kv + BS - 1) // BS).sum()))
     if args.pool_blocks:
         NB = args.pool_blocks
     assert int(((kv + BS - 1) // BS).sum()) <= NB

@@ -69,6 +69,11 @@ struct PagedAttnCache {
   bool fp8 = false;
   std::vector<float> k_scale, v_scale;
   std::vector<pa::TensorMapBlob> v_maps;  // per layer: tensor map of the V pool (16-bit pools)
+  // 32-token blocks: log2(block_size / 16) = 1 and, per layer, the maps that fetch one
+  // 16-token unit of a chunk for the split-KV kernel
+  int bs_shift = 0;
+  std::vector<pa::UnitMaps> unit_maps;
+  const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift ? &unit_maps[layer] : nullptr; }
   unsigned *err_dev = nullptr;
   // pinned, device-mapped copy of the error word, written by the last kernel of an
   // attention call, so that the host-buffer step reads it without a copy of its own
@@ -128,8 +133,11 @@ pa_status validate_config(const PagedAttnConfig *c) {
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
   if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
-  if (c->head_size != pa::kHeadSize || c->block_size != pa::kBlockSize)
-    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 with block_size 16 is built");
+  if (c->head_size != pa::kHeadSize || (c->block_size != 16 && c->block_size != 32))
+    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 with block_size 16 or 32 is built");
+  // with 32-token blocks a unit is addressed as 2 * (block * heads + head) + half in 32 bits
+  if (c->block_size == 32 && (uint64_t)c->num_blocks * c->num_kv_heads >= (1ull << 31))
+    return fail(PA_ERR_INVALID_ARG, "num_blocks * num_kv_heads must be below 2^31 with block_size 32");
   return PA_OK;
 }
 
@@ -147,6 +155,7 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, c->device));
   if (major != 10) return fail(PA_ERR_UNSUPPORTED, "this library is built for sm_100a only");
   c->num_sms = sms;
+  c->bs_shift = c->cfg.block_size == 32 ? 1 : 0;
   PA_CUDA(cudaMalloc(&c->err_dev, 256));
   PA_CUDA(cudaMemset(c->err_dev, 0, 256));
   PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), 64,
@@ -159,7 +168,15 @@ pa_status finish_create(PagedAttnCache *c) {
     c->v_maps.resize(c->cfg.num_layers);
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
-                                    (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads));
+                                    (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
+                                    (int)c->cfg.block_size));
+  }
+  if (c->bs_shift) {
+    c->unit_maps.resize(c->cfg.num_layers);
+    for (uint32_t i = 0; i < c->cfg.num_layers; i++)
+      PA_CUDA(pa::encode_unit_maps(&c->unit_maps[i], c->k[i], c->v[i],
+                                   (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
+                                   (int)c->cfg.block_size, c->fp8));
   }
   PA_CUDA(cudaStreamCreateWithFlags(&c->step_stream, cudaStreamNonBlocking));
   PA_CUDA(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
@@ -404,7 +421,7 @@ pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *ke
         static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
         static_cast<uint8_t *>(c->k[layer]), static_cast<uint8_t *>(c->v[layer]), slot_mapping,
         num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads, c->cfg.num_blocks,
-        c->k_scale[layer], c->v_scale[layer], c->cfg.dtype == 0, c->err_dev, c->fp8_special(),
+        c->bs_shift, c->k_scale[layer], c->v_scale[layer], c->cfg.dtype == 0, c->err_dev, c->fp8_special(),
         static_cast<cudaStream_t>(cuda_stream)));
     return PA_OK;
   }
@@ -412,7 +429,7 @@ pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *ke
       static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
       static_cast<pa::elem16 *>(c->k[layer]), static_cast<pa::elem16 *>(c->v[layer]),
       slot_mapping, num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads,
-      c->cfg.num_blocks, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
+      c->cfg.num_blocks, c->bs_shift, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
   return PA_OK;
 }
 
@@ -467,6 +484,7 @@ pa_status pa_qk_norm_rope_and_cache(PagedAttnCache *c, uint32_t layer, void *q_o
   p.Hkv = Hkv;
   p.rope_dims = (int)rope_dims;
   p.num_blocks = c->cfg.num_blocks;
+  p.bs_shift = c->bs_shift;
   p.eps = eps;
   p.err = c->err_dev;
   const int half = (int)rope_dims / 2;
@@ -729,6 +747,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.Hkv = Hkv;
   p.G = G;
   p.MB = max_blocks_per_seq;
+  p.bs_shift = c->bs_shift;
   p.num_blocks = c->cfg.num_blocks;
   p.q_stride = q_stride;
   p.out_stride = out_stride;
@@ -753,7 +772,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
 #ifdef PA_TILE_TIMING  // debug builds: study how bandwidth scales with the CTA count
     if (const char *e = getenv("PA_DEBUG_SPLIT_CTAS")) decode_ctas = atoi(e);
 #endif
-    PA_CUDA(pa::launch_splitkv_attention(p, decode_ctas, stream));
+    PA_CUDA(pa::launch_splitkv_attention(p, decode_ctas, stream, c->unit_map(layer)));
     return PA_OK;
   }
 
@@ -896,7 +915,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
     if (!have_class[k]) continue;
     p.min_cols = 8 * k + 1;
     p.max_cols = 8 * k + 8;
-    PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream));
+    PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream, c->unit_map(layer)));
     if (!tile_launched) {  // after the first split-KV launch, so that it gets its SMs first
       PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), &c->v_maps[layer],
                                         c->aux_stream));

@@ -26,7 +26,7 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
                          elem16 *__restrict__ k_pool, elem16 *__restrict__ v_pool,
                          const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
                          int64_t key_stride, int64_t value_stride, int Hkv, uint32_t num_blocks,
-                         unsigned *err) {
+                         int bs_shift, unsigned *err) {
   __shared__ uint4 k_s[kTokPerCta][kHeadSize / 8];                 // 16 x 256 B
   __shared__ __align__(16) uint16_t v_s[kTokPerCta][kHeadSize + kVPad];
   __shared__ int64_t slot_s[kTokPerCta];
@@ -37,7 +37,8 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
   const int h = blockIdx.y;
   const int64_t t0 = (int64_t)blockIdx.x * kTokPerCta;
   const int tid = threadIdx.x;
-  const int64_t n_slots = (int64_t)num_blocks * kBlockSize;
+  const int bs_log = 4 + bs_shift, bs = 1 << bs_log;  // tokens of a pool block
+  const int64_t n_slots = (int64_t)num_blocks << bs_log;
 
   if (tid < kTokPerCta) {
     int64_t s = -1;
@@ -70,9 +71,9 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
     const int tok = tid & 15, c = tid >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      elem16 *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunkElems + c * (kBlockSize * 8) +
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      elem16 *dst = k_pool + (((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) + c * (bs * 8) +
                            off * 8;
       *reinterpret_cast<uint4 *>(dst) = k_s[tok][c];
     }
@@ -82,10 +83,10 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
     const int tok = e & 15, d = e >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      reinterpret_cast<uint16_t *>(v_pool)[(blk * Hkv + h) * (int64_t)kChunkElems +
-                                           d * kBlockSize + off] = v_s[tok][d];
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      reinterpret_cast<uint16_t *>(v_pool)[(((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) +
+                                           d * bs + off] = v_s[tok][d];
     }
   }
 }
@@ -94,14 +95,15 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
                                      elem16 *k_pool, elem16 *v_pool,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
-                                     uint32_t num_blocks, unsigned *err, cudaStream_t st) {
+                                     uint32_t num_blocks, int bs_shift, unsigned *err,
+                                     cudaStream_t st) {
   if (num_tokens <= 0) return cudaSuccess;
   const int64_t groups = (num_tokens + kTokPerCta - 1) / kTokPerCta;
   // grid.x is 31-bit; a write of more than 2^31*16 tokens is not a real call.
   dim3 grid((unsigned)groups, (unsigned)Hkv);
   reshape_and_cache_kernel<<<grid, 256, 0, st>>>(key, value, k_pool, v_pool, slot_mapping,
                                                  num_tokens, key_stride, value_stride, Hkv,
-                                                 num_blocks, err);
+                                                 num_blocks, bs_shift, err);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }
@@ -169,8 +171,8 @@ reshape_and_cache_fp8_kernel(const elem16 *__restrict__ key, const elem16 *__res
                              uint8_t *__restrict__ k_pool, uint8_t *__restrict__ v_pool,
                              const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
                              int64_t key_stride, int64_t value_stride, int Hkv,
-                             uint32_t num_blocks, float k_scale, float v_scale, unsigned *err,
-                             unsigned *special_flag) {
+                             uint32_t num_blocks, int bs_shift, float k_scale, float v_scale,
+                             unsigned *err, unsigned *special_flag) {
   __shared__ uint2 k_s[kTokPerCta][kHeadSize / 8];                   // 16 x 128 B
   __shared__ __align__(8) uint8_t v_s[kTokPerCta][kHeadSize + 8];    // padded rows
   __shared__ int64_t slot_s[kTokPerCta];
@@ -179,7 +181,8 @@ reshape_and_cache_fp8_kernel(const elem16 *__restrict__ key, const elem16 *__res
   const int h = blockIdx.y;
   const int64_t t0 = (int64_t)blockIdx.x * kTokPerCta;
   const int tid = threadIdx.x;
-  const int64_t n_slots = (int64_t)num_blocks * kBlockSize;
+  const int bs_log = 4 + bs_shift, bs = 1 << bs_log;  // tokens of a pool block
+  const int64_t n_slots = (int64_t)num_blocks << bs_log;
   if (tid < kTokPerCta) {
     int64_t s = -1;
     if (t0 + tid < num_tokens) {
@@ -209,14 +212,15 @@ reshape_and_cache_fp8_kernel(const elem16 *__restrict__ key, const elem16 *__res
     }
   }
   __syncthreads();
-  constexpr int kChunk8 = kHeadSize * kBlockSize;  // bytes per (block, head) chunk
+  // a (block, head) chunk is kHeadSize * bs bytes
   if (tid < 128) {  // K: 16 bytes of (token, d/16)
     const int tok = tid & 15, c = tid >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      uint8_t *dst = k_pool + (blk * Hkv + h) * (int64_t)kChunk8 + c * (kBlockSize * 16) + off * 16;
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      uint8_t *dst = k_pool + (((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) + c * (bs * 16) +
+                     off * 16;
       *reinterpret_cast<uint4 *>(dst) = make_uint4(k_s[tok][2 * c].x, k_s[tok][2 * c].y,
                                                    k_s[tok][2 * c + 1].x, k_s[tok][2 * c + 1].y);
     }
@@ -225,9 +229,9 @@ reshape_and_cache_fp8_kernel(const elem16 *__restrict__ key, const elem16 *__res
     const int tok = e & 15, d = e >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      v_pool[(blk * Hkv + h) * (int64_t)kChunk8 + d * kBlockSize + off] = v_s[tok][d];
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      v_pool[(((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) + d * bs + off] = v_s[tok][d];
     }
   }
 }
@@ -236,19 +240,19 @@ cudaError_t launch_reshape_and_cache_fp8(const elem16 *key, const elem16 *value,
                                          uint8_t *v_pool, const int64_t *slot_mapping,
                                          int64_t num_tokens, int64_t key_stride,
                                          int64_t value_stride, int Hkv, uint32_t num_blocks,
-                                         float k_scale, float v_scale, bool f16, unsigned *err,
-                                         unsigned *special_flag, cudaStream_t st) {
+                                         int bs_shift, float k_scale, float v_scale, bool f16,
+                                         unsigned *err, unsigned *special_flag, cudaStream_t st) {
   if (num_tokens <= 0) return cudaSuccess;
   const int64_t groups = (num_tokens + kTokPerCta - 1) / kTokPerCta;
   dim3 grid((unsigned)groups, (unsigned)Hkv);
   if (f16)
     reshape_and_cache_fp8_kernel<true><<<grid, 256, 0, st>>>(
         key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride, value_stride, Hkv,
-        num_blocks, k_scale, v_scale, err, special_flag);
+        num_blocks, bs_shift, k_scale, v_scale, err, special_flag);
   else
     reshape_and_cache_fp8_kernel<false><<<grid, 256, 0, st>>>(
         key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride, value_stride, Hkv,
-        num_blocks, k_scale, v_scale, err, special_flag);
+        num_blocks, bs_shift, k_scale, v_scale, err, special_flag);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

@@ -10,13 +10,16 @@ namespace pa {
 // never interpret it; the attention kernels are compiled for both formats.
 using elem16 = uint16_t;
 
-// Fixed geometry of the tuned path: head size 128, 16-token blocks, 16-bit elements.
-// One (block, kv head) pair is a contiguous 4 KB K chunk laid out
-// [D/8][BS][8] and a contiguous 4 KB V chunk laid out [D][BS]
+// Fixed geometry of the tuned path: head size 128, 16-bit elements, and a working unit of
+// 16 tokens.  One (block, kv head) pair of the pool is a contiguous K chunk laid out
+// [D/8][BS][8] and a contiguous V chunk laid out [D][BS]
 // (crates/mlx-paged-attn/src/paged_kv_cache.rs:1129-1136: kv_head_stride = D*BS).
+// With BS = 16 a chunk is one unit (4 KB of K, 4 KB of V, each contiguous); with BS = 32 it
+// holds two units interleaved (tokens 0-15 and 16-31 of every row) and the kernels fetch
+// a unit with a tensor-map copy.  `bs_shift` below is log2(BS / 16).
 constexpr int kHeadSize = 128;
-constexpr int kBlockSize = 16;
-constexpr int kChunkBytes = kHeadSize * kBlockSize * 2;  // 4096
+constexpr int kBlockSize = 16;                           // tokens of a unit
+constexpr int kChunkBytes = kHeadSize * kBlockSize * 2;  // 4096: K (or V) bytes of a unit
 constexpr int kChunkElems = kHeadSize * kBlockSize;      // 2048
 
 // Error word bits written by kernels instead of trapping.
@@ -135,6 +138,7 @@ struct AttnParams {
   const int32_t *seq_row;       // null, or [S]: block-table row of each sequence (when a long
                                 // chunk is served as several shorter sequences)
   int S, Hq, Hkv, G, MB;
+  int bs_shift;  // 0: 16-token pool blocks, 1: 32-token pool blocks (MB counts pool blocks)
   int is_f16;  // element format: 1 = f16, 0 = bf16
   int is_fp8;  // pools hold E4M3 bytes (split-KV kernels only); is_f16 is then the q/out format
   float k_scale, v_scale;  // FP8 dequantisation factors; 1 otherwise
@@ -166,6 +170,7 @@ struct ProducerParams {
   elem16 *k_pool, *v_pool;
   int64_t num_tokens, q_stride, q_out_stride, k_stride, v_stride;
   int tok_per_cta;         // 1..16, chosen by the launcher
+  int bs_shift;            // 0: 16-token pool blocks, 1: 32-token pool blocks
   int Hq, Hkv, rope_dims;  // rope_dims even, <= 128; elements beyond pass through
   uint32_t num_blocks;
   float eps;
@@ -180,13 +185,14 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
                                      elem16 *k_pool, elem16 *v_pool,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
-                                     uint32_t num_blocks, unsigned *err, cudaStream_t st);
+                                     uint32_t num_blocks, int bs_shift, unsigned *err,
+                                     cudaStream_t st);
 cudaError_t launch_reshape_and_cache_fp8(const elem16 *key, const elem16 *value, uint8_t *k_pool,
                                          uint8_t *v_pool, const int64_t *slot_mapping,
                                          int64_t num_tokens, int64_t key_stride,
                                          int64_t value_stride, int Hkv, uint32_t num_blocks,
-                                         float k_scale, float v_scale, bool f16, unsigned *err,
-                                         unsigned *special_flag, cudaStream_t st);
+                                         int bs_shift, float k_scale, float v_scale, bool f16,
+                                         unsigned *err, unsigned *special_flag, cudaStream_t st);
 cudaError_t launch_copy_blocks(elem16 *k_pool, elem16 *v_pool,
                                const int64_t *mapping, int64_t num_pairs, int64_t bytes_per_block,
                                uint32_t num_blocks, unsigned *err, cudaStream_t st);
@@ -218,8 +224,21 @@ struct PeerGather {
 cudaError_t launch_peer_gather(const PeerGather &a, cudaStream_t st);
 cudaError_t launch_peer_wait(const unsigned *my_flags, int world, unsigned epoch, unsigned *err,
                              cudaStream_t st);
+// An encoded tensor map (opaque 128 bytes; what the driver calls CUtensorMap).
+struct alignas(64) TensorMapBlob {
+  unsigned char bytes[128];
+};
+// Maps over the K and the V pool of one layer that fetch one 16-token unit of a
+// (block, kv head) chunk; what the split-KV kernel needs when bs_shift != 0.
+struct alignas(64) UnitMaps {
+  TensorMapBlob k, v;
+};
+cudaError_t encode_unit_maps(UnitMaps *out, const void *k_pool, const void *v_pool,
+                             uint64_t num_chunks, int block_size, bool fp8);
 // Split-KV kernel over every sequence whose q_len*G <= p.max_cols, then the merge.
-cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st);
+// `maps` may be null when p.bs_shift == 0.
+cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStream_t st,
+                                     const UnitMaps *maps = nullptr);
 size_t splitkv_workspace_bytes(int num_ctas);
 int splitkv_max_cols();
 cudaError_t splitkv_configure();  // opt-in shared memory sizes, once per device
@@ -233,11 +252,8 @@ struct TileWork {
   int32_t q_begin;   // first query (within the sequence) of this tile
   int32_t q_count;   // queries in this tile
 };
-// An encoded tensor map (opaque 128 bytes; what the driver calls CUtensorMap).
-struct alignas(64) TensorMapBlob {
-  unsigned char bytes[128];
-};
-cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks);
+cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks,
+                              int block_size);
 cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
                                   const TensorMapBlob *v_map, cudaStream_t st);
 cudaError_t tile_configure();

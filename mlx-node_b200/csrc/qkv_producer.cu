@@ -54,7 +54,8 @@ qk_norm_rope_cache_kernel(const ProducerParams p) {
   // batches so that the rows spread over more SMs
   const int n_tok = (int)min((int64_t)p.tok_per_cta, p.num_tokens - t0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t n_slots = (int64_t)p.num_blocks * kBlockSize;
+  const int bs_log = 4 + p.bs_shift, bs = 1 << bs_log;  // tokens of a pool block
+  const int64_t n_slots = (int64_t)p.num_blocks << bs_log;
   const int half = p.rope_dims >> 1;
   const int G = p.Hq / p.Hkv;
 
@@ -150,9 +151,9 @@ qk_norm_rope_cache_kernel(const ProducerParams p) {
     const int tok = tid & 15, c = tid >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      elem16 *dst = p.k_pool + (blk * p.Hkv + h) * (int64_t)kChunkElems + c * (kBlockSize * 8) +
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      elem16 *dst = p.k_pool + (((blk * p.Hkv + h) * (int64_t)kHeadSize) << bs_log) + c * (bs * 8) +
                     off * 8;
       *reinterpret_cast<uint4 *>(dst) = k_s[tok][c];
     }
@@ -161,10 +162,10 @@ qk_norm_rope_cache_kernel(const ProducerParams p) {
     const int tok = e & 15, d = e >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
-      const int64_t blk = slot / kBlockSize;
-      const int off = (int)(slot % kBlockSize);
-      reinterpret_cast<uint16_t *>(p.v_pool)[(blk * p.Hkv + h) * (int64_t)kChunkElems +
-                                             d * kBlockSize + off] = v_s[tok][d];
+      const int64_t blk = slot >> bs_log;
+      const int off = (int)(slot & (bs - 1));
+      reinterpret_cast<uint16_t *>(p.v_pool)[(((blk * p.Hkv + h) * (int64_t)kHeadSize) << bs_log) +
+                                             d * bs + off] = v_s[tok][d];
     }
   }
 }

@@ -39,11 +39,20 @@
 // computed next to the softmax and P.V of the current one, so that the two dependency
 // chains (ldmatrix -> MMA chain, and max -> exp2 -> movmatrix -> MMA) overlap.
 //
+// 32-token pool blocks (p.bs_shift = 1): the unit stays 16 tokens.  A (block, kv head)
+// chunk then holds two units interleaved row by row, and a unit comes in through two
+// tensor-map copies (a [D/8] x 256 B box of the K chunk, a [D] x 32 B box of the V chunk)
+// that land in the ring stage in exactly the layout of a 16-token chunk; everything after
+// the copy is the same code.
+//
 // FP8 (E4M3) pools: the same kernel on 2 KB chunks.  K.Q^T runs on the FP8 tensor-core
 // path straight from the cache bytes (queries split into two E4M3 numbers) unless the
 // cache may hold bytes that the tensor cores read differently from the cache format; then,
 // and always for V^T.P^T, the bytes become f16 by integer operations; see the comments at
 // fp8x4_to_f16 and in the main loop.
+#include <cuda.h>
+
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -151,9 +160,24 @@ __device__ __forceinline__ int fp8_row_token(int r) {
   return 4 * ((r & 7) >> 1) + 2 * (r >> 3) + (r & 1);
 }
 
+// The K and V maps of encode_unit_maps as the kernel parameter they have to be.
+struct KvMaps {
+  CUtensorMap k, v;
+};
+// One unit through a tensor map {x: elements of a chunk row, y: row, z: chunk}; x0 picks
+// the unit within the row (a multiple of 16 bytes).  This CTA's shared memory only.
+__device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap *map, int x0, int chunk,
+                                              uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x0), "r"(0), "r"(chunk), "r"(bar)
+      : "memory");
+}
+
 template <int NT, bool F16, bool FP8>
 __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
-splitkv_kernel(const AttnParams p) {
+splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   using C = Cfg<NT, FP8>;
   constexpr int NST = C::kStages;
   constexpr int kStageBytes = C::kStageBytes;
@@ -214,7 +238,8 @@ splitkv_kernel(const AttnParams p) {
     }
     return a;
   };
-  // Pool chunk index (block id * Hkv + kv head) of this warp's j-th unit.
+  // Pool chunk index (block id * Hkv + kv head) of this warp's j-th unit; with 32-token
+  // blocks, twice that plus the unit's place in the chunk.
   auto lookup = [&](int j) -> uint32_t {
     if (j >= n_w) return 0u;
     const long long u = lo + warp + (long long)kWarps * j;
@@ -223,12 +248,13 @@ splitkv_kernel(const AttnParams p) {
     const int nb = pre[s + 1] - pre[s];
     const int h = r / nb, b = r - h * nb;
     const int row = p.seq_row ? p.seq_row[p.seq_base + s] : p.seq_base + s;
-    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + b];
+    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + (b >> p.bs_shift)];
     if (id >= p.num_blocks) {
       atomicOr(p.err, kErrBlockRange);
       id = 0;
     }
-    return id * (uint32_t)Hkv + (uint32_t)h;
+    const uint32_t chunk = id * (uint32_t)Hkv + (uint32_t)h;
+    return p.bs_shift ? 2u * chunk + (uint32_t)(b & 1) : chunk;
   };
 
   // This grid may have started while the KV write before it was still running: the
@@ -253,10 +279,17 @@ splitkv_kernel(const AttnParams p) {
       const int st = ji % NST;
       const uint32_t bar = bar_w + st * 8, dst = ring_w + st * kStageBytes;
       mbar_expect_tx(bar, kStageBytes);
-      bulk_g2s(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk, kChunk,
-               bar);
-      bulk_g2s(dst + kChunk, reinterpret_cast<const uint8_t *>(p.v_pool) + (size_t)chunk * kChunk,
-               kChunk, bar);
+      if (p.bs_shift) {
+        // elements of a K row per unit: 16 tokens x 8 (16-bit) or x 16 (bytes); of a V row: 16
+        const int unit = (int)(chunk & 1u), ch = (int)(chunk >> 1);
+        tma_load_unit(dst, &maps.k, unit * (FP8 ? 256 : 128), ch, bar);
+        tma_load_unit(dst + kChunk, &maps.v, unit * 16, ch, bar);
+      } else {
+        bulk_g2s(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk, kChunk,
+                 bar);
+        bulk_g2s(dst + kChunk, reinterpret_cast<const uint8_t *>(p.v_pool) + (size_t)chunk * kChunk,
+                 kChunk, bar);
+      }
     }
     ji++;
   };
@@ -847,18 +880,18 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 }
 
 template <int NT>
-cudaError_t launch_nt(const AttnParams &p, int num_ctas, cudaStream_t st) {
+cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cudaStream_t st) {
   cudaError_t e;
   if (p.is_fp8)
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, true>, dim3(num_ctas), dim3(kThreads),
-                                    Cfg<NT, true>::kSmemBytes, st, p)
+                                    Cfg<NT, true>::kSmemBytes, st, p, maps)
                  : launch_dependent(splitkv_kernel<NT, false, true>, dim3(num_ctas),
-                                    dim3(kThreads), Cfg<NT, true>::kSmemBytes, st, p);
+                                    dim3(kThreads), Cfg<NT, true>::kSmemBytes, st, p, maps);
   else
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false>, dim3(num_ctas), dim3(kThreads),
-                                    Cfg<NT>::kSmemBytes, st, p)
+                                    Cfg<NT>::kSmemBytes, st, p, maps)
                  : launch_dependent(splitkv_kernel<NT, false, false>, dim3(num_ctas),
-                                    dim3(kThreads), Cfg<NT>::kSmemBytes, st, p);
+                                    dim3(kThreads), Cfg<NT>::kSmemBytes, st, p, maps);
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return e;
 }
@@ -921,7 +954,58 @@ cudaError_t splitkv_configure() {
   return e;
 }
 
-cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, cudaStream_t st) {
+// Tensor maps that fetch one 16-token unit out of a (block, kv head) chunk of `block_size`
+// tokens: K as {block_size * 8 elements (16-bit) or block_size * 16 (bytes), D/8 or D/16
+// rows, chunk}, box {one unit, every row}; V as {block_size, D, chunk}, box {16, D}.  No
+// swizzle: the box arrives in shared memory row after row, which is the layout of a
+// 16-token chunk.
+cudaError_t encode_unit_maps(UnitMaps *out, const void *k_pool, const void *v_pool,
+                             uint64_t num_chunks, int block_size, bool fp8) {
+  static_assert(sizeof(CUtensorMap) == sizeof(TensorMapBlob), "tensor map size");
+  static_assert(sizeof(KvMaps) == sizeof(UnitMaps), "map pair size");
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return e;
+  if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+  const uint64_t esz = fp8 ? 1 : 2;
+  const uint64_t k_group = fp8 ? 16 : 8;  // elements of one token in a K row
+  const cuuint32_t ones[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  const uint64_t chunk_bytes = (uint64_t)kHeadSize * block_size * esz;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)block_size * k_group, kHeadSize / k_group, num_chunks};
+    const cuuint64_t strides[2] = {(cuuint64_t)block_size * k_group * esz, chunk_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)(kBlockSize * k_group), (cuuint32_t)(kHeadSize / k_group), 1};
+    const CUresult r = reinterpret_cast<EncodeFn>(fn)(
+        reinterpret_cast<CUtensorMap *>(&out->k), dt, 3, const_cast<void *>(k_pool), dims, strides,
+        box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  }
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)block_size, kHeadSize, num_chunks};
+    const cuuint64_t strides[2] = {(cuuint64_t)block_size * esz, chunk_bytes};
+    const cuuint32_t box[3] = {kBlockSize, kHeadSize, 1};
+    const CUresult r = reinterpret_cast<EncodeFn>(fn)(
+        reinterpret_cast<CUtensorMap *>(&out->v), dt, 3, const_cast<void *>(v_pool), dims, strides,
+        box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, cudaStream_t st,
+                                     const UnitMaps *unit_maps) {
+  if (p_in.bs_shift != 0 && !unit_maps) return cudaErrorInvalidValue;
+  KvMaps maps;
+  if (unit_maps) memcpy(&maps, unit_maps, sizeof(maps));
+  else memset(&maps, 0, sizeof(maps));
   // Width of the kernel: enough 8-column tiles for the widest item it may meet.
   const int nt = (p_in.max_cols + 7) / 8;
   // CTAs: one per SM the caller grants, two for the variant built to share an SM, as far
@@ -933,9 +1017,9 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
     p.seq_base = p_in.seq_base + base;
     p.S = min(kMaxSeqsPerLaunch, p_in.S - base);
     cudaError_t e;
-    if (nt <= 1) e = launch_nt<1>(p, num_ctas, st);
-    else if (nt == 2) e = launch_nt<2>(p, num_ctas, st);
-    else e = launch_nt<3>(p, num_ctas, st);
+    if (nt <= 1) e = launch_nt<1>(p, maps, num_ctas, st);
+    else if (nt == 2) e = launch_nt<2>(p, maps, num_ctas, st);
+    else e = launch_nt<3>(p, maps, num_ctas, st);
     if (e != cudaSuccess) return e;
     e = launch_dependent(splitkv_merge_kernel, dim3((unsigned)p.S, (unsigned)p.Hkv),
                          dim3(128, kMergeCols), 0, st, p, num_ctas, nt <= 1 ? 1 : (nt == 2 ? 2 : 3));

@@ -60,13 +60,14 @@ enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFUL
 // One V block (128 head dimensions x 16 tokens) through the tensor map of the V pool
 // {16 tokens, 128 rows, chunk}: the 32-byte swizzle of the map lays the rows out as the
 // MMA descriptor of v_block_desc expects them.  This CTA's shared memory only; a chunk
-// index beyond the pool reads as zeros.  x and y are always 0.
-__device__ __forceinline__ void tma_load_v_block(uint32_t dst, const CUtensorMap *map, int chunk,
-                                                 uint32_t bar) {
+// index beyond the pool reads as zeros.  y is always 0; x0 is 0, or 16 for the second
+// half of a 32-token pool block (32 bytes into the row).
+__device__ __forceinline__ void tma_load_v_block(uint32_t dst, const CUtensorMap *map, int x0,
+                                                 int chunk, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(chunk), "r"(bar)
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x0), "r"(0), "r"(chunk), "r"(bar)
       : "memory");
 }
 
@@ -332,8 +333,11 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
   const int32_t *table = p.block_tables + (int64_t)seq * p.MB;
 
   // ---- set-up ---------------------------------------------------------------------
+  // "block" below is a 16-token unit; with 32-token pool blocks (sh = 1) two consecutive
+  // units share a table entry and a pool chunk
+  const int sh = p.bs_shift;
   for (int i = tid; i < nblk && i < kTblCap; i += kTcThreads) {
-    uint32_t id = (uint32_t)table[i];
+    uint32_t id = (uint32_t)table[i >> sh];
     if (id >= p.num_blocks) {
       atomicOr(p.err, kErrBlockRange);
       id = 0;
@@ -374,7 +378,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       const int pw = warp - 8;
       auto block_id = [&](int b) -> uint32_t {
         if (b < kTblCap) return (uint32_t)tbl[b];
-        uint32_t id = (uint32_t)table[b];
+        uint32_t id = (uint32_t)table[b >> sh];
         if (id >= p.num_blocks) {
           atomicOr(p.err, kErrBlockRange);
           id = 0;
@@ -405,12 +409,14 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           const int gb = j * 8 + b;            // block within the sequence
           const bool have = gb < nblk;
           const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
-          const elem16 *src = p.k_pool + chunk * kChunkElems;
+          // rows of the chunk are (16 << sh) tokens long; the unit starts (gb & sh) * 16 tokens in
+          const elem16 *src = p.k_pool + ((chunk * kChunkElems) << sh) + (gb & sh) * 128;
 #pragma unroll
           for (int it = 0; it < 8; it++) {
-            const int e = it * 32 + lane;  // 16-byte piece of the 4 KB chunk, in memory order
+            const int e = it * 32 + lane;  // 16-byte piece of the unit's 4 KB, in memory order
             const int c = e >> 4, t = e & 15;
-            cp_async16(stage + c * 2048 + b * 256 + t * 16, src + e * 8, have ? 16u : 0u);
+            cp_async16(stage + c * 2048 + b * 256 + t * 16, src + ((c * 128) << sh) + t * 8,
+                       have ? 16u : 0u);
           }
         }
         cp_async_commit();
@@ -458,12 +464,13 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           if (pt < 8) {
             const int b = pt;
             const int chunk = b < nb_here ? (int)block_id(j * 8 + b) * p.Hkv + h : total_chunks;
+            const int x0 = (b & sh) * 16;  // j * 8 is even: the unit's half is b's low bit
             const uint32_t dst = v_s + (j & 1) * kStage + b * 4096;
             if (b == tail_b) {
               mbar_expect_tx(bar(B_VTAIL), kChunkBytes);
-              tma_load_v_block(dst, &v_map, chunk, bar(B_VTAIL));
+              tma_load_v_block(dst, &v_map, x0, chunk, bar(B_VTAIL));
             } else {
-              tma_load_v_block(dst, &v_map, chunk, vfull);
+              tma_load_v_block(dst, &v_map, x0, chunk, vfull);
             }
           }
           if (pw == 1) {  // second arrival: nothing left to clear in this tile
@@ -736,7 +743,8 @@ cudaError_t tile_configure() {
 // Tensor map of one V pool: 16-bit elements, {16 tokens, 128 head dimensions, chunks},
 // box = one (block, kv head) chunk, 32-byte swizzle.  The encoder is a driver entry point,
 // fetched through the runtime so that the library does not link against the driver.
-cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks) {
+cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t num_chunks,
+                              int block_size) {
   static_assert(sizeof(CUtensorMap) == sizeof(TensorMapBlob), "tensor map size");
   using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -747,8 +755,8 @@ cudaError_t tile_encode_v_map(TensorMapBlob *out, const void *v_pool, uint64_t n
   cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
   if (e != cudaSuccess) return e;
   if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
-  const cuuint64_t dims[3] = {16, 128, num_chunks};
-  const cuuint64_t strides[2] = {32, 4096};
+  const cuuint64_t dims[3] = {(cuuint64_t)block_size, 128, num_chunks};
+  const cuuint64_t strides[2] = {(cuuint64_t)block_size * 2, (cuuint64_t)block_size * 256};
   const cuuint32_t box[3] = {16, 128, 1}, elem_strides[3] = {1, 1, 1};
   const CUresult r = reinterpret_cast<EncodeFn>(fn)(
       reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT16, 3,

@@ -35,7 +35,7 @@ class DeviceCase:
         f16 = getattr(case, "f16", False)
         self.k_pool = to_dev(case.k_pool if k_pool is None else k_pool, f16)
         self.v_pool = to_dev(case.v_pool if v_pool is None else v_pool, f16)
-        self.cache = pa.PagedCache(BS, case.NB, D, case.Hkv, dtype=0 if f16 else 1,
+        self.cache = pa.PagedCache(getattr(case, "bs", BS), case.NB, D, case.Hkv, dtype=0 if f16 else 1,
                                    key_pools=[self.k_pool], value_pools=[self.v_pool])
         self.q = to_dev(case.q, f16)
         self.k_new = to_dev(case.k_new, f16)

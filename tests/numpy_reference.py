@@ -7,10 +7,11 @@ division, scores*scale, softmax, @V.  Multi-token sequences add the causal limit
 kv_len - q_len + j + 1.  It shares no index arithmetic with oracle/paged_oracle.c."""
 import numpy as np
 
-from pa_testlib import BS, D, X, elems_to_f32
+from pa_testlib import D, X, elems_to_f32
 
 
 def gather_sequence(k_pool, v_pool, table_row, kv_len, f16=False):
+    BS = v_pool.shape[3]  # tokens per pool block
     nb = (kv_len + BS - 1) // BS
     blocks = table_row[:nb]
     k = k_pool[blocks]                                  # [nb, Hkv, D/X, BS, X]

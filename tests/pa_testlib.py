@@ -119,8 +119,10 @@ class Case:
     """One seeded workload: pool pre-filled with every sequence's prefix, the
     step's new tokens and queries held apart for the code under test."""
 
-    def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True, f16=False):
+    def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True, f16=False,
+                 bs=BS):
         self.f16 = f16
+        self.bs = bs  # tokens per pool block (16 or 32)
         self.S = len(kv_lens)
         self.Hq, self.Hkv, self.NB = Hq, Hkv, NB
         self.G = Hq // Hkv
@@ -130,7 +132,7 @@ class Case:
         self.cu_q = np.zeros(self.S + 1, dtype=np.int32)
         self.cu_q[1:] = np.cumsum(self.q_lens)
         self.total_q = int(self.cu_q[-1])
-        nblk = (self.kv_lens + BS - 1) // BS
+        nblk = (self.kv_lens + bs - 1) // bs
         assert int(nblk.sum()) <= NB, "pool too small"
         rng = np.random.Generator(np.random.PCG64(seed))
         perm = rng.permutation(NB).astype(np.int32)
@@ -154,14 +156,14 @@ class Case:
         for s in range(self.S):
             t = np.arange(self.kv_lens[s])
             slots_all[self.cu_kv[s]:self.cu_kv[s + 1]] = (
-                self.block_tables[s, t // BS].astype(np.int64) * BS + t % BS)
+                self.block_tables[s, t // bs].astype(np.int64) * bs + t % bs)
             is_new[self.cu_kv[s + 1] - self.q_lens[s]:self.cu_kv[s + 1]] = True
         self.slots_all = slots_all
         self.k_new = np.ascontiguousarray(self.k_all[is_new])
         self.v_new = np.ascontiguousarray(self.v_all[is_new])
         self.slot_mapping = np.ascontiguousarray(slots_all[is_new])
-        self.k_pool = np.full((NB, Hkv, D // X, BS, X), CANARY, dtype=np.uint16)
-        self.v_pool = np.full((NB, Hkv, D, BS), CANARY, dtype=np.uint16)
+        self.k_pool = np.full((NB, Hkv, D // X, bs, X), CANARY, dtype=np.uint16)
+        self.v_pool = np.full((NB, Hkv, D, bs), CANARY, dtype=np.uint16)
         if prefill:
             old = ~is_new
             write_oracle(self.k_pool, self.v_pool, np.ascontiguousarray(self.k_all[old]),
@@ -179,7 +181,8 @@ def write_oracle(k_pool, v_pool, key, value, slots, Hkv, key_stride=None, value_
     if n == 0:
         return
     oracle().oracle_reshape_and_cache(p(key), p(value), p(k_pool), p(v_pool), p(slots), n,
-                                      key_stride or Hkv * D, value_stride or Hkv * D, Hkv, D, BS, X)
+                                      key_stride or Hkv * D, value_stride or Hkv * D, Hkv, D,
+                                      k_pool.shape[3], X)
 
 
 def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np.ndarray:
@@ -187,8 +190,8 @@ def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np
     cu = p(case.cu_q) if varlen else None
     oracle().oracle_paged_attention_varlen_dt(p(out), p(case.q), p(k_pool), p(v_pool),
                                               p(case.block_tables), p(case.kv_lens), cu, case.S,
-                                              case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
-                                              case.scale, softcap, int(case.f16))
+                                              case.Hq, case.Hkv, D, k_pool.shape[3], case.MB,
+                                              case.Hq * D, case.scale, softcap, int(case.f16))
     return out
 
 
@@ -198,7 +201,8 @@ def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, 
     out = np.zeros((len(rows), D), dtype=np.float32)
     oracle().oracle_paged_attention_rows(p(out), p(rows), len(rows), p(q), p(k_pool), p(v_pool),
                                          p(block_tables), p(kv_lens),
-                                         p(cu_q) if cu_q is not None else None, Hq, Hkv, D, BS, MB,
+                                         p(cu_q) if cu_q is not None else None, Hq, Hkv, D,
+                                         k_pool.shape[3], MB,
                                          Hq * D, scale, softcap)
     return out
 
@@ -207,16 +211,17 @@ def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, 
 X8 = 16  # elements per 16-byte piece of the FP8 key pool
 
 
-def fp8_pools(NB, Hkv, fill=0):
-    return (np.full((NB, Hkv, D // X8, BS, X8), fill, dtype=np.uint8),
-            np.full((NB, Hkv, D, BS), fill, dtype=np.uint8))
+def fp8_pools(NB, Hkv, fill=0, bs=BS):
+    return (np.full((NB, Hkv, D // X8, bs, X8), fill, dtype=np.uint8),
+            np.full((NB, Hkv, D, bs), fill, dtype=np.uint8))
 
 
 def write_oracle_fp8(k_pool8, v_pool8, key, value, slots, Hkv, k_scale, v_scale, f16=False):
     n = len(slots)
     if n:
         oracle().oracle_reshape_and_cache_fp8(p(key), p(value), p(k_pool8), p(v_pool8), p(slots), n,
-                                              Hkv * D, Hkv * D, Hkv, D, BS, k_scale, v_scale, int(f16))
+                                              Hkv * D, Hkv * D, Hkv, D, k_pool8.shape[3], k_scale,
+                                              v_scale, int(f16))
 
 
 def attention_oracle_fp8(case, k_pool8, v_pool8, k_scale, v_scale, softcap=1.0, varlen=True):
@@ -224,8 +229,9 @@ def attention_oracle_fp8(case, k_pool8, v_pool8, k_scale, v_scale, softcap=1.0, 
     cu = p(case.cu_q) if varlen else None
     oracle().oracle_paged_attention_varlen_fp8(p(out), p(case.q), p(k_pool8), p(v_pool8),
                                                p(case.block_tables), p(case.kv_lens), cu, case.S,
-                                               case.Hq, case.Hkv, D, BS, case.MB, case.Hq * D,
-                                               case.scale, softcap, int(case.f16), k_scale, v_scale)
+                                               case.Hq, case.Hkv, D, k_pool8.shape[3], case.MB,
+                                               case.Hq * D, case.scale, softcap, int(case.f16), k_scale,
+                                               v_scale)
     return out
 
 

@@ -22,7 +22,7 @@ class Fp8DeviceCase:
         in-range values."""
         self.case, self.ks, self.vs = case, k_scale, v_scale
         if k8 is None:
-            k8, v8 = fp8_pools(case.NB, case.Hkv, fill=0x7F)   # NaN codes where nothing was written
+            k8, v8 = fp8_pools(case.NB, case.Hkv, fill=0x7F, bs=case.bs)  # NaN codes where nothing was written
             old = np.ones(len(case.slots_all), dtype=bool)
             for s in range(case.S):
                 old[case.cu_kv[s + 1] - case.q_lens[s]:case.cu_kv[s + 1]] = False
@@ -33,7 +33,7 @@ class Fp8DeviceCase:
         self.k8_host, self.v8_host = k8, v8
         self.k_pool = torch.from_numpy(k8).cuda()
         self.v_pool = torch.from_numpy(v8).cuda()
-        self.cache = pa.PagedCache(BS, case.NB, D, case.Hkv, dtype=0 if case.f16 else 1,
+        self.cache = pa.PagedCache(case.bs, case.NB, D, case.Hkv, dtype=0 if case.f16 else 1,
                                    key_pools=[self.k_pool], value_pools=[self.v_pool], fp8=True)
         self.cache.set_kv_scales(k_scale, v_scale)
         if not exact:

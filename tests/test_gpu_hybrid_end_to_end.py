@@ -40,12 +40,13 @@ def through_fp8(x_bits, scale):
     return vals.transpose(0, 3, 1, 2).reshape(nb * BS, Hkv, D)[:L]
 
 
+@pytest.mark.parametrize("bs", [16, 32])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_scheduler_drives_the_kernels(cuda_device, fp8):
+def test_scheduler_drives_the_kernels(cuda_device, fp8, bs):
     Hq, Hkv, L = 16, 4, 400
     G = Hq // Hkv
     rng = np.random.Generator(np.random.PCG64(5))
-    cfg = host_config(block_size=BS, gpu_memory_mb=256, head_size=D, num_kv_heads=Hkv, num_layers=1,
+    cfg = host_config(block_size=bs, gpu_memory_mb=256, head_size=D, num_kv_heads=Hkv, num_layers=1,
                       max_seq_len=512)
     kv_host = PagedKVCacheHost(cfg)
     NB = kv_host.total_blocks()
@@ -53,17 +54,17 @@ def test_scheduler_drives_the_kernels(cuda_device, fp8):
     if fp8:
         # prefill chunks of 64 tokens are longer than one split-KV piece (24/G = 6 tokens):
         # this run also covers the chunk-in-pieces path and its host context lengths
-        k_pool = torch.zeros(NB, Hkv, D // X8, BS, X8, dtype=torch.uint8, device="cuda")
-        v_pool = torch.zeros(NB, Hkv, D, BS, dtype=torch.uint8, device="cuda")
+        k_pool = torch.zeros(NB, Hkv, D // X8, bs, X8, dtype=torch.uint8, device="cuda")
+        v_pool = torch.zeros(NB, Hkv, D, bs, dtype=torch.uint8, device="cuda")
     else:
-        k_pool = torch.zeros(NB, Hkv, D // X, BS, X, dtype=torch.bfloat16, device="cuda")
-        v_pool = torch.zeros(NB, Hkv, D, BS, dtype=torch.bfloat16, device="cuda")
-    cache = pa.PagedCache(BS, NB, D, Hkv, key_pools=[k_pool], value_pools=[v_pool], fp8=fp8)
+        k_pool = torch.zeros(NB, Hkv, D // X, bs, X, dtype=torch.bfloat16, device="cuda")
+        v_pool = torch.zeros(NB, Hkv, D, bs, dtype=torch.bfloat16, device="cuda")
+    cache = pa.PagedCache(bs, NB, D, Hkv, key_pools=[k_pool], value_pools=[v_pool], fp8=fp8)
     if fp8:
         cache.set_kv_scales(kv_scale, kv_scale)
         cache.fp8_set_exact_decode(False)   # zero-filled pools, in-range values
     ws = torch.empty(cache.workspace_bytes(), dtype=torch.uint8, device="cuda")
-    sched = HybridScheduler(BS, prefill_chunk_size=64, max_tokens_per_step=160, max_prefill_per_step=2,
+    sched = HybridScheduler(bs, prefill_chunk_size=64, max_tokens_per_step=160, max_prefill_per_step=2,
                             max_batch_size=8, eos_token_id=1 << 30)
     prompts = {"r0": 20, "r1": 150, "r2": 300, "r3": 65, "r4": 33}
     true_q, true_k, true_v, junk_k = {}, {}, {}, {}

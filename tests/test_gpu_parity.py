@@ -12,7 +12,8 @@ import paged_attn_b200 as pa
 from golden import make_golden
 from gpu_util import DeviceCase, device_view, to_bits, to_dev
 from pa_testlib import (BS, CANARY, D, X, Case, attention_oracle, attention_oracle_rows,
-                        bf16_to_f32, check_attention, config_lengths, normal_bf16, oracle, p)
+                        bf16_to_f32, check_attention, config_lengths, normal_bf16, oracle, p,
+                        write_oracle)
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -252,6 +253,41 @@ def test_fewer_units_than_ctas(cuda_device):
     check_attention(got, ref, "tiny batch")
     got_v, ref_v = run_case(Case([3, 16, 9], [2, 1, 3], 4, 1, 8, seed=43))
     check_attention(got_v, ref_v, "tiny varlen batch")
+
+
+def test_layers_of_a_library_owned_cache_are_independent(cuda_device):
+    """pa_cache_create allocates zero-filled pools per layer; a write and an attention call
+    on one layer neither read nor disturb the others."""
+    L = 3
+    cases = [Case([70, 33, 129], [1, 1, 1], 8, 2, 32, seed=50 + i, prefill=False) for i in range(L)]
+    cache = pa.PagedCache(BS, 32, D, 2, num_layers=L)
+    ws = torch.empty(cache.workspace_bytes(), dtype=torch.uint8, device="cuda")
+    for i, c in enumerate(cases):
+        k_view = device_view(cache.key_ptr(i), (c.NB, c.Hkv, D // X, BS, X))
+        assert (k_view.view(torch.int16) == 0).all(), "pools start zero-filled"
+        slots = torch.from_numpy(c.slots_all).cuda()
+        cache.reshape_and_cache(to_dev(c.k_all), to_dev(c.v_all), slots, len(c.slots_all),
+                                c.Hkv * D, c.Hkv * D, layer=i)
+    torch.cuda.synchronize()
+    for i, c in enumerate(cases):
+        k_ref = np.zeros_like(c.k_pool)
+        v_ref = np.zeros_like(c.v_pool)
+        write_oracle(k_ref, v_ref, c.k_all, c.v_all, c.slots_all, c.Hkv)
+        k_got = to_bits(device_view(cache.key_ptr(i), k_ref.shape))
+        v_got = to_bits(device_view(cache.value_ptr(i), v_ref.shape))
+        assert (k_got == k_ref).all() and (v_got == v_ref).all(), f"layer {i} pools"
+        out = torch.full((c.S, c.Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        cache.decode(out, to_dev(c.q), torch.from_numpy(c.block_tables).cuda(),
+                     torch.from_numpy(c.kv_lens).cuda(), c.S, c.Hq, c.MB, c.scale, ws, ws.numel(),
+                     layer=i)
+        torch.cuda.synchronize()
+        cache.check_errors()
+        check_attention(bf16_to_f32(to_bits(out)), attention_oracle(c, k_ref, v_ref, varlen=False),
+                        f"layer {i}")
+    with pytest.raises(pa.PagedAttnError):
+        cache.decode(out, to_dev(cases[0].q), torch.from_numpy(cases[0].block_tables).cuda(),
+                     torch.from_numpy(cases[0].kv_lens).cuda(), 3, 8, cases[0].MB, 0.1, ws, ws.numel(),
+                     layer=L)
 
 
 def test_determinism_and_placement_invariance(cuda_device):
