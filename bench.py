@@ -226,7 +226,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--seqs", type=int, default=0, help="use only the first N sequences (small captures)")
     ap.add_argument("--pool-blocks", type=int, default=0, help="override the pool size in blocks")
-    ap.add_argument("--block-size", type=int, default=16, choices=[16, 32],
+    ap.add_argument("--block-size", type=int, default=16, choices=[8, 16, 32],
                     help="tokens per pool block (the configurations are quoted on 16)")
     args = ap.parse_args()
     global BS

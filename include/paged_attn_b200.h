@@ -60,9 +60,10 @@ int32_t pa_version(void);
 /* ---- configuration and cache handle -------------------------------------- */
 /* Same six u32 fields as the reference (crates/mlx-sys/src/lib.rs:690-705,
  * crates/mlx-sys/src/mlx.cpp:3796-3803). dtype: 0 f16, 1 bf16, 2 f32.
- * Built: head_size 128 with block_size 16 or 32 (the model's and the config's
- * defaults, crates/mlx-paged-attn/src/config.rs:128) and dtype 0 or 1; other
- * values the reference accepts return PA_ERR_UNSUPPORTED.                     */
+ * Built: head_size 128 with every block size the reference accepts (8, 16, 32;
+ * crates/mlx-paged-attn/src/config.rs:40-45) and dtype 0 or 1; the other head
+ * sizes and dtype 2 return PA_ERR_UNSUPPORTED.  An FP8 cache needs block_size
+ * 16 or 32, as in the reference (config.rs:71-76).                            */
 typedef struct PagedAttnConfig {
   uint32_t block_size;
   uint32_t num_blocks;

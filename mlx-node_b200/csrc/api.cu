@@ -69,11 +69,13 @@ struct PagedAttnCache {
   bool fp8 = false;
   std::vector<float> k_scale, v_scale;
   std::vector<pa::TensorMapBlob> v_maps;  // per layer: tensor map of the V pool (16-bit pools)
-  // 32-token blocks: log2(block_size / 16) = 1 and, per layer, the maps that fetch one
-  // 16-token unit of a chunk for the split-KV kernel
+  // log2(block_size / 16): -1, 0 or 1.  32-token blocks: per layer, the maps that fetch
+  // one 16-token unit of a chunk for the split-KV kernel
   int bs_shift = 0;
   std::vector<pa::UnitMaps> unit_maps;
-  const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift ? &unit_maps[layer] : nullptr; }
+  const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift > 0 ? &unit_maps[layer] : nullptr; }
+  // the tcgen05 tile kernel reads 16-bit pools of 16- or 32-token blocks
+  bool has_tile_kernel() const { return !fp8 && bs_shift >= 0; }
   unsigned *err_dev = nullptr;
   // pinned, device-mapped copy of the error word, written by the last kernel of an
   // attention call, so that the host-buffer step reads it without a copy of its own
@@ -133,8 +135,8 @@ pa_status validate_config(const PagedAttnConfig *c) {
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
   if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
-  if (c->head_size != pa::kHeadSize || (c->block_size != 16 && c->block_size != 32))
-    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 with block_size 16 or 32 is built");
+  if (c->head_size != pa::kHeadSize)
+    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 is built");
   // with 32-token blocks a unit is addressed as 2 * (block * heads + head) + half in 32 bits
   if (c->block_size == 32 && (uint64_t)c->num_blocks * c->num_kv_heads >= (1ull << 31))
     return fail(PA_ERR_INVALID_ARG, "num_blocks * num_kv_heads must be below 2^31 with block_size 32");
@@ -155,7 +157,7 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, c->device));
   if (major != 10) return fail(PA_ERR_UNSUPPORTED, "this library is built for sm_100a only");
   c->num_sms = sms;
-  c->bs_shift = c->cfg.block_size == 32 ? 1 : 0;
+  c->bs_shift = c->cfg.block_size == 32 ? 1 : (c->cfg.block_size == 8 ? -1 : 0);
   PA_CUDA(cudaMalloc(&c->err_dev, 256));
   PA_CUDA(cudaMemset(c->err_dev, 0, 256));
   PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), 64,
@@ -164,14 +166,14 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->err_host_dev), c->err_host, 0));
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
-  if (!c->fp8) {
+  if (!c->fp8 && c->bs_shift >= 0) {  // what the tile kernel reads
     c->v_maps.resize(c->cfg.num_layers);
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
                                     (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
                                     (int)c->cfg.block_size));
   }
-  if (c->bs_shift) {
+  if (c->bs_shift > 0) {
     c->unit_maps.resize(c->cfg.num_layers);
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::encode_unit_maps(&c->unit_maps[i], c->k[i], c->v[i],
@@ -279,6 +281,8 @@ static pa_status cache_create_impl(const PagedAttnConfig *config, int32_t device
   *out = nullptr;
   pa_status st = validate_config(config);
   if (st != PA_OK) return st;
+  if (fp8 && config->block_size == 8)  // crates/mlx-paged-attn/src/config.rs:71-76
+    return fail(PA_ERR_INVALID_ARG, "FP8 cache requires block_size 16 or 32 for optimal alignment.");
   DeviceGuard g(device);
   if (!g.ok) return fail(PA_ERR_CUDA, "cannot select device");
   PagedAttnCache *c = new (std::nothrow) PagedAttnCache();
@@ -324,6 +328,8 @@ static pa_status cache_wrap_impl(const PagedAttnConfig *config, int32_t device, 
   *out = nullptr;
   pa_status st = validate_config(config);
   if (st != PA_OK) return st;
+  if (fp8 && config->block_size == 8)  // crates/mlx-paged-attn/src/config.rs:71-76
+    return fail(PA_ERR_INVALID_ARG, "FP8 cache requires block_size 16 or 32 for optimal alignment.");
   if (!key_ptrs || !value_ptrs) return fail(PA_ERR_INVALID_ARG, "pool pointer arrays are null");
   for (uint32_t i = 0; i < config->num_layers; i++) {
     if (!key_ptrs[i] || !value_ptrs[i]) return fail(PA_ERR_INVALID_ARG, "a pool pointer is null");
@@ -785,7 +791,9 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
   double tile_flops = 0.0, split_bytes = 0.0;  // work estimates, only with host context lengths
-  bool long_fp8 = false;  // FP8 cache and a chunk too long for the split-KV kernel
+  // a chunk too long for the split-KV kernel on a cache the tile kernel does not read
+  // (FP8 pools, 8-token blocks)
+  bool long_fp8 = false;
   for (int s = 0; s < num_seqs; s++) {
     const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
     if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
@@ -795,7 +803,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       have_class[(ql * G - 1) / 8] = true;
       split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
     } else {
-      if (c->fp8) {  // served below as several shorter sequences
+      if (!c->has_tile_kernel()) {  // served below as several shorter sequences
         long_fp8 = true;
         continue;
       }
@@ -807,8 +815,8 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       tile_flops += 4.0 * c->cfg.head_size * num_q_heads * ql * (kv - 0.5 * ql);
     }
   }
-  // The tile kernel reads 16-bit pools only.  With an FP8 cache a longer chunk is handed
-  // to the split-KV kernel as consecutive pieces of at most 24/G query tokens, each a
+  // The tile kernel reads 16-bit pools of 16- or 32-token blocks only.  With an FP8 cache
+  // or 8-token blocks a longer chunk is handed to the split-KV kernel as consecutive pieces of at most 24/G query tokens, each a
   // sequence of its own with the same block-table row and the context length that ends
   // at its last query: the same results (the KV of the chunk's sequence is read once per
   // piece, from L2 mostly), at the price of that re-reading.
@@ -816,8 +824,8 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   if (long_fp8) {
     if (!context_lens_host)
       return fail(PA_ERR_INVALID_ARG,
-                  "with an FP8 cache, chunks of more than " + std::to_string(split_cols / G) +
-                      " query tokens need context_lens_host");
+                  "with an FP8 cache or 8-token blocks, chunks of more than " +
+                      std::to_string(split_cols / G) + " query tokens need context_lens_host");
     const int piece = split_cols / G;
     v_cu.push_back(0);
     have_class[0] = have_class[1] = have_class[2] = false;
@@ -832,7 +840,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
         v_row.push_back(s);
         if (qb > qa) {
           have_class[((qb - qa) * G - 1) / 8] = true;
-          split_bytes += (double)v_ctx.back() * 2.0 * Hkv * c->cfg.head_size;
+          split_bytes += (double)v_ctx.back() * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
         }
         if (ql == 0) break;
       }

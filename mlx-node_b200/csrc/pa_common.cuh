@@ -16,7 +16,8 @@ using elem16 = uint16_t;
 // (crates/mlx-paged-attn/src/paged_kv_cache.rs:1129-1136: kv_head_stride = D*BS).
 // With BS = 16 a chunk is one unit (4 KB of K, 4 KB of V, each contiguous); with BS = 32 it
 // holds two units interleaved (tokens 0-15 and 16-31 of every row) and the kernels fetch
-// a unit with a tensor-map copy.  `bs_shift` below is log2(BS / 16).
+// a unit with a tensor-map copy; with BS = 8 a unit is two chunks of 2 KB.  `bs_shift`
+// below is log2(BS / 16).
 constexpr int kHeadSize = 128;
 constexpr int kBlockSize = 16;                           // tokens of a unit
 constexpr int kChunkBytes = kHeadSize * kBlockSize * 2;  // 4096: K (or V) bytes of a unit
@@ -138,7 +139,7 @@ struct AttnParams {
   const int32_t *seq_row;       // null, or [S]: block-table row of each sequence (when a long
                                 // chunk is served as several shorter sequences)
   int S, Hq, Hkv, G, MB;
-  int bs_shift;  // 0: 16-token pool blocks, 1: 32-token pool blocks (MB counts pool blocks)
+  int bs_shift;  // log2(pool block size / 16): 0, 1 (32 tokens) or -1 (8 tokens); MB counts pool blocks
   int is_f16;  // element format: 1 = f16, 0 = bf16
   int is_fp8;  // pools hold E4M3 bytes (split-KV kernels only); is_f16 is then the q/out format
   float k_scale, v_scale;  // FP8 dequantisation factors; 1 otherwise
@@ -170,7 +171,7 @@ struct ProducerParams {
   elem16 *k_pool, *v_pool;
   int64_t num_tokens, q_stride, q_out_stride, k_stride, v_stride;
   int tok_per_cta;         // 1..16, chosen by the launcher
-  int bs_shift;            // 0: 16-token pool blocks, 1: 32-token pool blocks
+  int bs_shift;            // log2(pool block size / 16): -1, 0 or 1
   int Hq, Hkv, rope_dims;  // rope_dims even, <= 128; elements beyond pass through
   uint32_t num_blocks;
   float eps;

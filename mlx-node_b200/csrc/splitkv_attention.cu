@@ -45,6 +45,13 @@
 // that land in the ring stage in exactly the layout of a 16-token chunk; everything after
 // the copy is the same code.
 //
+// 8-token pool blocks (p.bs_shift = -1, template flag B8; 16-bit pools): a unit is two pool
+// blocks with ids of their own, four 2 KB bulk copies into the stage (K of the first block,
+// K of the second, V of the first, V of the second), and the ldmatrix addresses take the
+// token half from the 2 KB sub-chunk instead of from the row.  Block ids are looked up 16
+// units at a time, lane 2i and 2i+1 holding the two blocks of unit i; a last unit of eight
+// tokens or fewer has no second block and copies half the bytes.
+//
 // FP8 (E4M3) pools: the same kernel on 2 KB chunks.  K.Q^T runs on the FP8 tensor-core
 // path straight from the cache bytes (queries split into two E4M3 numbers) unless the
 // cache may hold bytes that the tensor cores read differently from the cache format; then,
@@ -175,9 +182,12 @@ __device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap *m
       : "memory");
 }
 
-template <int NT, bool F16, bool FP8>
+constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool block
+
+template <int NT, bool F16, bool FP8, bool B8 = false>
 __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
+  static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
   using C = Cfg<NT, FP8>;
   constexpr int NST = C::kStages;
   constexpr int kStageBytes = C::kStageBytes;
@@ -240,7 +250,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   };
   // Pool chunk index (block id * Hkv + kv head) of this warp's j-th unit; with 32-token
   // blocks, twice that plus the unit's place in the chunk.
-  auto lookup = [&](int j) -> uint32_t {
+  // B8: the argument is 2 * j + (0: first, 1: second pool block of the unit).
+  auto lookup = [&](int jj) -> uint32_t {
+    const int j = B8 ? jj >> 1 : jj;
     if (j >= n_w) return 0u;
     const long long u = lo + warp + (long long)kWarps * j;
     const int s = seq_of(u);
@@ -248,13 +260,20 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     const int nb = pre[s + 1] - pre[s];
     const int h = r / nb, b = r - h * nb;
     const int row = p.seq_row ? p.seq_row[p.seq_base + s] : p.seq_base + s;
-    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + (b >> p.bs_shift)];
+    int col;  // block-table column
+    if (B8) {
+      col = 2 * b + (jj & 1);
+      if (col * 8 >= p.context_lens[p.seq_base + s]) return kNoBlock;
+    } else {
+      col = b >> p.bs_shift;
+    }
+    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + col];
     if (id >= p.num_blocks) {
       atomicOr(p.err, kErrBlockRange);
       id = 0;
     }
     const uint32_t chunk = id * (uint32_t)Hkv + (uint32_t)h;
-    return p.bs_shift ? 2u * chunk + (uint32_t)(b & 1) : chunk;
+    return (!B8 && p.bs_shift) ? 2u * chunk + (uint32_t)(b & 1) : chunk;
   };
 
   // This grid may have started while the KV write before it was still running: the
@@ -269,22 +288,38 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   const uint32_t bar_w = smem_u32(&bars[warp * NST]);
   uint32_t cur_ids = lookup(lane), nxt_ids = lookup(32 + lane);
   int ji = 0;  // units issued by this warp
+  constexpr int kBatch = B8 ? 16 : 32;  // units per lookup
   auto issue = [&]() {  // whole warp calls; lane 0 issues unit ji
-    if ((ji & 31) == 0 && ji > 0) {
+    if ((ji & (kBatch - 1)) == 0 && ji > 0) {
       cur_ids = nxt_ids;
-      nxt_ids = lookup(ji + 32 + lane);
+      nxt_ids = lookup((B8 ? 2 : 1) * (ji + kBatch) + lane);
     }
-    const uint32_t chunk = __shfl_sync(0xffffffffu, cur_ids, ji & 31);
+    const uint32_t chunk = __shfl_sync(0xffffffffu, cur_ids, B8 ? 2 * (ji & 15) : ji & 31);
+    uint32_t chunk_b = 0u;
+    if (B8) chunk_b = __shfl_sync(0xffffffffu, cur_ids, 2 * (ji & 15) + 1);
     if (lane == 0) {
       const int st = ji % NST;
       const uint32_t bar = bar_w + st * 8, dst = ring_w + st * kStageBytes;
-      mbar_expect_tx(bar, kStageBytes);
-      if (p.bs_shift) {
+      if (B8) {
+        // stage: K of the first block | K of the second | V of the first | V of the second
+        const uint8_t *kp = reinterpret_cast<const uint8_t *>(p.k_pool);
+        const uint8_t *vp = reinterpret_cast<const uint8_t *>(p.v_pool);
+        const bool two = chunk_b != kNoBlock;
+        mbar_expect_tx(bar, two ? kStageBytes : kStageBytes / 2);
+        bulk_g2s(dst, kp + (size_t)chunk * (kChunk / 2), kChunk / 2, bar);
+        bulk_g2s(dst + kChunk, vp + (size_t)chunk * (kChunk / 2), kChunk / 2, bar);
+        if (two) {
+          bulk_g2s(dst + kChunk / 2, kp + (size_t)chunk_b * (kChunk / 2), kChunk / 2, bar);
+          bulk_g2s(dst + kChunk + kChunk / 2, vp + (size_t)chunk_b * (kChunk / 2), kChunk / 2, bar);
+        }
+      } else if (p.bs_shift) {
         // elements of a K row per unit: 16 tokens x 8 (16-bit) or x 16 (bytes); of a V row: 16
         const int unit = (int)(chunk & 1u), ch = (int)(chunk >> 1);
+        mbar_expect_tx(bar, kStageBytes);
         tma_load_unit(dst, &maps.k, unit * (FP8 ? 256 : 128), ch, bar);
         tma_load_unit(dst + kChunk, &maps.v, unit * 16, ch, bar);
       } else {
+        mbar_expect_tx(bar, kStageBytes);
         bulk_g2s(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk, kChunk,
                  bar);
         bulk_g2s(dst + kChunk, reinterpret_cast<const uint8_t *>(p.v_pool) + (size_t)chunk * kChunk,
@@ -479,7 +514,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
 #pragma unroll
           for (int j = 0; j < 8; j++) {
             uint32_t af[4];
-            ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
+            // B8: tokens 0-7 and 8-15 sit in the two 2 KB sub-chunks, rows of 8 tokens
+            if (B8) ldmatrix_x4(af, ks + (mi & 1) * 2048 + (2 * j + (mi >> 1)) * 128 + mr * 16);
+            else ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
           }
@@ -582,7 +619,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
 #pragma unroll
           for (int mt = 0; mt < 8; mt++) {
             uint32_t vf[4];
-            ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
+            if (B8) ldmatrix_x4(vf, vs + (mi >> 1) * 2048 + (16 * mt + (mi & 1) * 8 + mr) * 16);
+            else ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
             vf[0] &= vmask[0]; vf[1] &= vmask[0]; vf[2] &= vmask[1]; vf[3] &= vmask[1];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -887,6 +925,11 @@ cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cud
                                     Cfg<NT, true>::kSmemBytes, st, p, maps)
                  : launch_dependent(splitkv_kernel<NT, false, true>, dim3(num_ctas),
                                     dim3(kThreads), Cfg<NT, true>::kSmemBytes, st, p, maps);
+  else if (p.bs_shift < 0)
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, true>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT>::kSmemBytes, st, p, maps)
+                 : launch_dependent(splitkv_kernel<NT, false, false, true>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT>::kSmemBytes, st, p, maps);
   else
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false>, dim3(num_ctas), dim3(kThreads),
                                     Cfg<NT>::kSmemBytes, st, p, maps)
@@ -937,6 +980,12 @@ static cudaError_t configure_nt() {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, false, true>,
@@ -1002,7 +1051,8 @@ cudaError_t encode_unit_maps(UnitMaps *out, const void *k_pool, const void *v_po
 
 cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, cudaStream_t st,
                                      const UnitMaps *unit_maps) {
-  if (p_in.bs_shift != 0 && !unit_maps) return cudaErrorInvalidValue;
+  if (p_in.bs_shift > 0 && !unit_maps) return cudaErrorInvalidValue;
+  if (p_in.bs_shift < 0 && p_in.is_fp8) return cudaErrorInvalidValue;
   KvMaps maps;
   if (unit_maps) memcpy(&maps, unit_maps, sizeof(maps));
   else memset(&maps, 0, sizeof(maps));

@@ -51,7 +51,6 @@ def test_version_and_error_string():
     ("num_blocks", 0, 1),
     ("dtype", 7, 1),
     ("dtype", 2, 2),            # f32 accepted by the reference, not built here
-    ("block_size", 8, 2),       # valid in the reference, not built here
     ("head_size", 64, 2),
 ])
 def test_config_validation_needs_no_device(field, value, status):

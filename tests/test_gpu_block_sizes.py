@@ -1,9 +1,9 @@
-"""GPU parity tests with 32-token pool blocks, the default block size of
-PagedAttentionConfig (crates/mlx-paged-attn/src/config.rs:128): the KV write bit-exact,
-decode / verify / chunked-prefill attention within the attention tolerance of the oracle,
-on 16-bit and FP8 pools, plus the producer, block copy and swap on the larger blocks.
-Every case also runs with 16-token blocks on the same tokens: the block size is a layout
-choice and must not change a result beyond rounding."""
+"""GPU parity tests with the other block sizes PagedAttentionConfig accepts
+(crates/mlx-paged-attn/src/config.rs:40-45; 32 is its default, :128): 32-token and 8-token
+pool blocks.  The KV write bit-exact, decode / verify / chunked-prefill attention within
+the attention tolerance of the oracle, on 16-bit and (32-token blocks) FP8 pools, plus the
+producer, block copy and swap.  One case also runs with 16-token blocks on the same tokens:
+the block size is a layout choice and must not change a result beyond rounding."""
 import numpy as np
 import pytest
 import torch
@@ -17,6 +17,12 @@ from test_gpu_producer import norm_weight, positions_of
 
 pytestmark = pytest.mark.gpu
 BS32 = 32
+SIZES = [8, 32]
+
+
+def pool(n32, bs):
+    """Pool size in blocks of `bs` tokens that holds what n32 32-token blocks hold."""
+    return n32 * 32 // bs
 
 
 def run_case(case, varlen=True, softcap=1.0):
@@ -34,72 +40,78 @@ def run_case(case, varlen=True, softcap=1.0):
 
 @pytest.mark.parametrize("f16", [False, True])
 @pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 2), (16, 1)])
-def test_decode_edge_lengths(cuda_device, G, Hkv, f16):
+@pytest.mark.parametrize("bs", SIZES)
+def test_decode_edge_lengths(cuda_device, G, Hkv, f16, bs):
     # lengths around both the 16-token unit and the 32-token block boundaries
     kv = [1, 15, 16, 17, 31, 32, 33, 47, 48, 49, 64, 255, 256, 257, 1000, 4097]
-    case = Case(kv, [1] * len(kv), G * Hkv, Hkv, 512, seed=131 + G, f16=f16, bs=BS32)
+    case = Case(kv, [1] * len(kv), G * Hkv, Hkv, pool(512, bs), seed=131 + G, f16=f16, bs=bs)
     got, ref = run_case(case, varlen=False)
     check_attention(got, ref, f"decode G={G} f16={f16}")
 
 
-def test_same_tokens_in_16_and_32_token_blocks(cuda_device):
+@pytest.mark.parametrize("bs", SIZES)
+def test_same_tokens_give_the_same_bits_as_16_token_blocks(cuda_device, bs):
     kv, ql = [700, 64, 1029, 300, 6, 2500, 17], [1, 2, 3, 6, 6, 5, 1]
-    c32 = Case(kv, ql, 8, 2, 256, seed=132, bs=BS32)
+    c32 = Case(kv, ql, 8, 2, pool(256, bs), seed=132, bs=bs)
     c16 = Case(kv, ql, 8, 2, 512, seed=132)
     assert (c32.q == c16.q).all() and (c32.k_all == c16.k_all).all()
     got32, ref32 = run_case(c32)
     got16, _ = run_case(c16)
-    check_attention(got32, ref32, "verify widths, 32-token blocks")
-    # the same units are multiplied in the same order: only the split points of long
-    # contexts (and with them the merge order) may differ
-    np.testing.assert_allclose(got32, got16, rtol=0, atol=2e-2)
+    check_attention(got32, ref32, f"verify widths, {bs}-token blocks")
+    # the same units are multiplied in the same order, so the results are the same bits
+    assert (got32 == got16).all()
     got_cap, ref_cap = run_case(c32, softcap=30.0)
-    check_attention(got_cap, ref_cap, "softcap, 32-token blocks")
+    check_attention(got_cap, ref_cap, f"softcap, {bs}-token blocks")
 
 
-def test_long_contexts_are_split_across_ctas(cuda_device):
+@pytest.mark.parametrize("bs", SIZES)
+def test_long_contexts_are_split_across_ctas(cuda_device, bs):
     kv = [20000, 9000, 33, 15000]
-    case = Case(kv, [1] * 4, 32, 8, 2048, seed=133, bs=BS32)
+    case = Case(kv, [1] * 4, 32, 8, pool(2048, bs), seed=133, bs=bs)
     got, ref = run_case(case, varlen=False)
-    check_attention(got, ref, "long decode, 32-token blocks")
+    check_attention(got, ref, f"long decode, {bs}-token blocks")
 
 
-def test_chunked_prefill_runs_on_the_tile_kernel(cuda_device):
+@pytest.mark.parametrize("bs", SIZES)
+def test_chunked_prefill_with_decode_and_verify(cuda_device, bs):
     # chunks that start and end inside blocks and units; a decode token and a verify
-    # sequence in the same call (side-by-side launch)
+    # sequence in the same call (tile kernel side by side with 32-token blocks; chunks in
+    # pieces through the split-KV kernel with 8-token blocks)
     kv = [1500, 300, 77, 2049, 40, 33]
     ql = [700, 300, 50, 1, 3, 33]
-    case = Case(kv, ql, 16, 4, 256, seed=134, bs=BS32)
+    case = Case(kv, ql, 16, 4, pool(256, bs), seed=134, bs=bs)
     launches = pa.load_library().pa_kernel_launch_count()
     got, ref = run_case(case)
-    check_attention(got, ref, "chunked prefill, 32-token blocks")
+    check_attention(got, ref, f"chunked prefill, {bs}-token blocks")
     assert pa.load_library().pa_kernel_launch_count() - launches >= 4  # write, tile, split-KV, merge
     got_cap, ref_cap = run_case(case, softcap=50.0)
-    check_attention(got_cap, ref_cap, "chunked prefill softcap, 32-token blocks")
+    check_attention(got_cap, ref_cap, f"chunked prefill softcap, {bs}-token blocks")
 
 
-def test_prefill_longer_than_the_staged_table(cuda_device):
+@pytest.mark.parametrize("bs", SIZES)
+def test_prefill_longer_than_the_staged_table(cuda_device, bs):
     # more than 2048 units per sequence: ids beyond the staged table are read from memory
-    case = Case([40000], [300], 8, 1, 1280, seed=135, bs=BS32)
+    case = Case([40000], [300], 8, 1, pool(1280, bs), seed=135, bs=bs)
     got, ref = run_case(case)
-    check_attention(got, ref, "40k-token context prefill chunk, 32-token blocks")
+    check_attention(got, ref, f"40k-token context prefill chunk, {bs}-token blocks")
 
 
-def test_out_of_range_block_and_slot_are_reported(cuda_device):
-    case = Case([100, 50], [1, 1], 4, 2, 16, seed=136, bs=BS32)
+@pytest.mark.parametrize("bs", SIZES)
+def test_out_of_range_block_and_slot_are_reported(cuda_device, bs):
+    case = Case([100, 50], [1, 1], 4, 2, pool(16, bs), seed=136, bs=bs)
     dc = DeviceCase(case)
     dc.write()
     torch.cuda.synchronize()
     dc.cache.check_errors()
     bad = dc.slots.clone()
-    bad[0] = case.NB * BS32  # first slot past the pool; NB * 16 would be legal here
+    bad[0] = case.NB * bs  # first slot past the pool
     dc.cache.reshape_and_cache(dc.k_new, dc.v_new, bad, 2, case.Hkv * D, case.Hkv * D)
     torch.cuda.synchronize()
     with pytest.raises(pa.PagedAttnError) as e:
         dc.cache.check_errors()
     assert e.value.status == 4
     ok = dc.slots.clone()
-    ok[0] = case.NB * BS32 - 1
+    ok[0] = case.NB * bs - 1
     dc.cache.reshape_and_cache(dc.k_new, dc.v_new, ok, 2, case.Hkv * D, case.Hkv * D)
     torch.cuda.synchronize()
     dc.cache.check_errors()
@@ -134,8 +146,9 @@ def test_fp8_long_chunk_is_served_in_pieces(cuda_device):
     check_attention(got, ref, "fp8 long chunk, 32-token blocks")
 
 
-def test_producer_writes_32_token_blocks(cuda_device):
-    case = Case([150, 77, 40, 33], [100, 77, 1, 1], 8, 2, 32, seed=139, bs=BS32)
+@pytest.mark.parametrize("bs", SIZES)
+def test_producer_writes_the_blocks(cuda_device, bs):
+    case = Case([150, 77, 40, 33], [100, 77, 1, 1], 8, 2, pool(32, bs), seed=139, bs=bs)
     dc = DeviceCase(case)
     wq, wk = norm_weight(8, False), norm_weight(9, False)
     pos = positions_of(case)
@@ -149,7 +162,7 @@ def test_producer_writes_32_token_blocks(cuda_device):
     k_ref, k_bound = qk_norm_rope_oracle(case.k_new, wk, 1e-6, pos, 1.0e6, D)
     check_rotated(to_bits(q).reshape(case.total_q, case.Hq, D), q_ref, q_bound, False, "rotated queries")
     k_got, v_got = to_bits(dc.k_pool), to_bits(dc.v_pool)
-    blk, off = case.slot_mapping // BS32, case.slot_mapping % BS32
+    blk, off = case.slot_mapping // bs, case.slot_mapping % bs
     rows = np.ascontiguousarray(k_got[blk, :, :, off, :].reshape(case.total_q, case.Hkv, D))
     check_rotated(rows, k_ref, k_bound, False, "rotated keys in the pool")
     k_exp, v_exp = case.k_pool.copy(), case.v_pool.copy()
@@ -160,23 +173,24 @@ def test_producer_writes_32_token_blocks(cuda_device):
     assert (k_got[untouched] == case.k_pool[untouched]).all(), "K pool changed off the slots"
 
 
-def test_copy_and_swap_move_whole_32_token_blocks(cuda_device):
+@pytest.mark.parametrize("bs", SIZES)
+def test_copy_and_swap_move_whole_blocks(cuda_device, bs):
     import ctypes as C
     Hkv, NB = 4, 32
-    k_pool = normal_bf16((NB, Hkv, D // X, BS32, X), 140, 1)
-    v_pool = normal_bf16((NB, Hkv, D, BS32), 140, 2)
+    k_pool = normal_bf16((NB, Hkv, D // X, bs, X), 140, 1)
+    v_pool = normal_bf16((NB, Hkv, D, bs), 140, 2)
     kd, vd = to_dev(k_pool), to_dev(v_pool)
-    cache = pa.PagedCache(BS32, NB, D, Hkv, key_pools=[kd], value_pools=[vd])
+    cache = pa.PagedCache(bs, NB, D, Hkv, key_pools=[kd], value_pools=[vd])
     pairs = np.array([[0, 9], [5, 31], [7, 8]], dtype=np.int64)
     cache.copy_blocks(torch.from_numpy(pairs).cuda(), 3)
     torch.cuda.synchronize()
     cache.check_errors()
-    oracle().oracle_copy_blocks(p(k_pool), p(v_pool), p(pairs), 3, Hkv * D * BS32)
+    oracle().oracle_copy_blocks(p(k_pool), p(v_pool), p(pairs), 3, Hkv * D * bs)
     assert (to_bits(kd) == k_pool).all() and (to_bits(vd) == v_pool).all()
     cpu = cache.create_cpu_cache()
     ids = [3, 31, 0]
     cache.swap_out(ids, cpu)
-    nbytes = Hkv * D * BS32 * 2
+    nbytes = Hkv * D * bs * 2
     for b in ids:
         kp, vp = cpu.block_ptrs(b)
         assert C.string_at(kp, nbytes) == k_pool[b].tobytes()
@@ -188,7 +202,20 @@ def test_copy_and_swap_move_whole_32_token_blocks(cuda_device):
     assert (to_bits(kd) == k_pool).all() and (to_bits(vd) == v_pool).all()
 
 
-def test_block_size_8_is_refused(cuda_device):
+def test_fp8_with_8_token_blocks_is_refused_like_the_reference(cuda_device):
+    # crates/mlx-paged-attn/src/config.rs:71-76, test_fp8_validation (:218-236)
     with pytest.raises(pa.PagedAttnError) as e:
-        pa.PagedCache(8, 16, D, 2)
-    assert e.value.status == 2
+        pa.PagedCache(8, 16, D, 2, fp8=True)
+    assert e.value.status == 1 and "block_size 16 or 32" in str(e.value)
+
+
+def test_long_chunk_on_8_token_blocks_needs_host_lengths(cuda_device):
+    case = Case([200], [100], 8, 2, 32, seed=141, bs=8)
+    dc = DeviceCase(case)
+    dc.write()
+    out = torch.empty((100, 8, D), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(pa.PagedAttnError) as e:
+        dc.cache.varlen(out, dc.q, dc.tables, dc.lens, case.cu_q, 1, 8, case.MB, case.scale, dc.ws,
+                        dc.ws_bytes)
+    assert e.value.status == 1 and "context_lens_host" in str(e.value)
+    torch.cuda.synchronize()

@@ -315,13 +315,14 @@ def test_determinism_and_placement_invariance(cuda_device):
     assert (got_a == got_b).all()
 
 
-def test_tier1_reference_named_entry_points(cuda_device):
+@pytest.mark.parametrize("bs", [16, 32])
+def test_tier1_reference_named_entry_points(cuda_device, bs):
     # create_cache -> reshape_and_cache -> get_*_cache -> forward -> copy_blocks, as
     # crates/mlx-core/src/transformer/paged_attention.rs:85-230 drives them.
     import ctypes as C
     lib = pa.load_library()
-    case = Case([100, 37, 256], [1, 1, 1], 16, 8, 64, seed=12, prefill=False)
-    cfg = pa.PagedAttnConfig(BS, case.NB, D, case.Hkv, 2, 1)
+    case = Case([100, 37, 256], [1, 1, 1], 16, 8, 64, seed=12, prefill=False, bs=bs)
+    cfg = pa.PagedAttnConfig(bs, case.NB, D, case.Hkv, 2, 1)
     cache = lib.mlx_paged_attn_create_cache(C.byref(cfg))
     assert cache
 
@@ -337,22 +338,22 @@ def test_tier1_reference_named_entry_points(cuda_device):
     qa, ta, la = arr(q, 1), arr(tables, 3), arr(lens, 3)
     kc, vc = lib.mlx_paged_attn_get_key_cache(cache, 1), lib.mlx_paged_attn_get_value_cache(cache, 1)
     assert lib.mlx_array_ndim(kc) == 5 and lib.mlx_array_ndim(vc) == 4
-    out = lib.mlx_paged_attn_forward(qa, kc, vc, ta, la, case.scale, BS, int(case.kv_lens.max()))
+    out = lib.mlx_paged_attn_forward(qa, kc, vc, ta, la, case.scale, bs, int(case.kv_lens.max()))
     assert out, pa.last_error()
     shape = (C.c_int64 * 3)()
     lib.mlx_array_shape(out, shape)
     assert list(shape) == [case.S, case.Hq, D]
     got_dev = device_view(lib.pa_array_data(out), (case.S, case.Hq, D)).clone()
-    k_ref = np.zeros((case.NB, case.Hkv, D // X, BS, X), dtype=np.uint16)
-    v_ref = np.zeros((case.NB, case.Hkv, D, BS), dtype=np.uint16)
+    k_ref = np.zeros((case.NB, case.Hkv, D // X, bs, X), dtype=np.uint16)
+    v_ref = np.zeros((case.NB, case.Hkv, D, bs), dtype=np.uint16)
     oracle().oracle_reshape_and_cache(p(case.k_all), p(case.v_all), p(k_ref), p(v_ref),
                                       p(case.slots_all), len(case.slots_all), case.Hkv * D,
-                                      case.Hkv * D, case.Hkv, D, BS, X)
+                                      case.Hkv * D, case.Hkv, D, bs, X)
     check_attention(bf16_to_f32(to_bits(got_dev)), attention_oracle(case, k_ref, v_ref, varlen=False),
                     "tier-1 forward")
     # layer 0 was never written and the pools start zeroed (crates/mlx-sys/src/mlx.cpp:3847)
     k0 = lib.mlx_paged_attn_get_key_cache(cache, 0)
-    assert (device_view(lib.pa_array_data(k0), (case.NB, case.Hkv * D * BS)).view(torch.int16) == 0).all()
+    assert (device_view(lib.pa_array_data(k0), (case.NB, case.Hkv * D * bs)).view(torch.int16) == 0).all()
     for h in (ka, va, sa, qa, ta, la, kc, vc, k0, out):
         lib.mlx_array_delete(h)
     lib.mlx_paged_attn_free_cache(cache)

@@ -169,28 +169,32 @@ def test_numpy_reference_agrees_on_random_case():
     np.testing.assert_allclose(attention_oracle(case, k_pool, v_pool), ref, rtol=0, atol=2e-6)
 
 
-def test_32_token_blocks_against_numpy_reference_and_index_formula():
-    """Block size 32 (the default of PagedAttentionConfig, crates/mlx-paged-attn/src/config.rs:128):
-    slot 50 is block 1, offset 18; attention agrees with the numpy statement."""
-    Hkv, NB = 2, 3
-    k_pool = np.zeros((NB, Hkv, D // X, 32, X), dtype=np.uint16)
-    v_pool = np.zeros((NB, Hkv, D, 32), dtype=np.uint16)
+@pytest.mark.parametrize("bs", [8, 32])
+def test_other_block_sizes_against_numpy_reference_and_index_formula(bs):
+    """Block sizes 8 and 32 (32 is the default of PagedAttentionConfig,
+    crates/mlx-paged-attn/src/config.rs:128): slot 50 is block 50 // bs, offset 50 % bs;
+    attention agrees with the numpy statement."""
+    Hkv, NB = 2, 7
+    k_pool = np.zeros((NB, Hkv, D // X, bs, X), dtype=np.uint16)
+    v_pool = np.zeros((NB, Hkv, D, bs), dtype=np.uint16)
     key = np.arange(1, Hkv * D + 1, dtype=np.uint16).reshape(1, Hkv, D)
     val = (key + 1000).astype(np.uint16)
     write_oracle(k_pool, v_pool, key, val, np.array([50], dtype=np.int64), Hkv)
+    blk, off = 50 // bs, 50 % bs
     for h in range(Hkv):
         for d in (0, 7, 8, 127):
-            assert k_pool[1, h, d // 8, 18, d % 8] == key[0, h, d]
-            assert v_pool[1, h, d, 18] == val[0, h, d]
+            assert k_pool[blk, h, d // 8, off, d % 8] == key[0, h, d]
+            assert v_pool[blk, h, d, off] == val[0, h, d]
     assert np.count_nonzero(k_pool) == Hkv * D and np.count_nonzero(v_pool) == Hkv * D
 
-    case = Case([70, 33, 16, 5, 32, 97], [3, 1, 16, 5, 1, 40], 8, 2, 16, seed=24, bs=32)
+    kv, ql = [70, 33, 16, 5, 32, 97], [3, 1, 16, 5, 1, 40]
+    case = Case(kv, ql, 8, 2, 512 // bs, seed=24, bs=bs)
     k_pool, v_pool = case.pools_after_write()
     ref = numpy_reference.paged_attention(case.q, k_pool, v_pool, case.block_tables, case.kv_lens,
                                           case.cu_q, case.Hq, case.Hkv, case.scale)
     np.testing.assert_allclose(attention_oracle(case, k_pool, v_pool), ref, rtol=0, atol=2e-6)
     # the same tokens through 16-token blocks give the same rows: block size is layout only
-    case16 = Case([70, 33, 16, 5, 32, 97], [3, 1, 16, 5, 1, 40], 8, 2, 32, seed=24)
+    case16 = Case(kv, ql, 8, 2, 32, seed=24)
     k16, v16 = case16.pools_after_write()
     assert (case16.q == case.q).all() and (case16.k_all == case.k_all).all()
     np.testing.assert_allclose(attention_oracle(case16, k16, v16), attention_oracle(case, k_pool, v_pool),
