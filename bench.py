@@ -455,8 +455,10 @@ def main() -> None:
         # ncu capture of one sequence of this workload (profiles/tile_attention_tc_kernel_c4_ncu.md):
         # 61.1 MB of DRAM traffic per sequence per launch, scaled by the sequence count
         roof = {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
-                "frac": achieved / tf_peak, "traffic": int(61.1e6 * S * hkv_l / 8),
-                "traffic_source": "ncu dram bytes of a 1-sequence capture x sequences"}
+                "frac": achieved / tf_peak,
+                "traffic": None if args.fp8 or BS != 16 else int(61.1e6 * S * hkv_l / 8),
+                "traffic_source": None if args.fp8 or BS != 16
+                else "ncu dram bytes of a 1-sequence capture x sequences"}
     else:
         achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
         # ncu capture of a 16-sequence case of this workload

@@ -74,8 +74,8 @@ struct PagedAttnCache {
   int bs_shift = 0;
   std::vector<pa::UnitMaps> unit_maps;
   const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift > 0 ? &unit_maps[layer] : nullptr; }
-  // the tcgen05 tile kernel reads 16-bit pools of 16- or 32-token blocks
-  bool has_tile_kernel() const { return !fp8 && bs_shift >= 0; }
+  // the tcgen05 tile kernel reads pools of 16- or 32-token blocks (16-bit or FP8)
+  bool has_tile_kernel() const { return bs_shift >= 0; }
   unsigned *err_dev = nullptr;
   // pinned, device-mapped copy of the error word, written by the last kernel of an
   // attention call, so that the host-buffer step reads it without a copy of its own
@@ -166,8 +166,10 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->err_host_dev), c->err_host, 0));
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
-  if (!c->fp8 && c->bs_shift >= 0) {  // what the tile kernel reads
-    c->v_maps.resize(c->cfg.num_layers);
+  // the tile kernel fetches V of 16-bit pools through a tensor map (FP8 pools are read with
+  // plain loads: their entries stay zero and unused)
+  c->v_maps.assign(c->cfg.num_layers, pa::TensorMapBlob{});
+  if (!c->fp8 && c->bs_shift >= 0) {
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
                                     (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
@@ -792,8 +794,8 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   std::vector<pa::TileWork> tiles;
   double tile_flops = 0.0, split_bytes = 0.0;  // work estimates, only with host context lengths
   // a chunk too long for the split-KV kernel on a cache the tile kernel does not read
-  // (FP8 pools, 8-token blocks)
-  bool long_fp8 = false;
+  // (8-token blocks)
+  bool in_pieces = false;
   for (int s = 0; s < num_seqs; s++) {
     const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
     if (ql < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing");
@@ -804,7 +806,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
     } else {
       if (!c->has_tile_kernel()) {  // served below as several shorter sequences
-        long_fp8 = true;
+        in_pieces = true;
         continue;
       }
       // Tiles of one (sequence, kv head) are neighbours in launch order so that they
@@ -815,16 +817,16 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       tile_flops += 4.0 * c->cfg.head_size * num_q_heads * ql * (kv - 0.5 * ql);
     }
   }
-  // The tile kernel reads 16-bit pools of 16- or 32-token blocks only.  With an FP8 cache
-  // or 8-token blocks a longer chunk is handed to the split-KV kernel as consecutive pieces of at most 24/G query tokens, each a
+  // The tile kernel reads 16- or 32-token blocks only.  With 8-token blocks a longer chunk
+  // is handed to the split-KV kernel as consecutive pieces of at most 24/G query tokens, each a
   // sequence of its own with the same block-table row and the context length that ends
   // at its last query: the same results (the KV of the chunk's sequence is read once per
   // piece, from L2 mostly), at the price of that re-reading.
   std::vector<int32_t> v_cu, v_ctx, v_row;
-  if (long_fp8) {
+  if (in_pieces) {
     if (!context_lens_host)
       return fail(PA_ERR_INVALID_ARG,
-                  "with an FP8 cache or 8-token blocks, chunks of more than " +
+                  "with 8-token blocks, chunks of more than " +
                       std::to_string(split_cols / G) + " query tokens need context_lens_host");
     const int piece = split_cols / G;
     v_cu.push_back(0);
@@ -846,18 +848,18 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
       }
     }
   }
-  const int num_items = long_fp8 ? (int)v_row.size() : num_seqs;
+  const int num_items = in_pieces ? (int)v_row.size() : num_seqs;
   const bool any_split = have_class[0] || have_class[1] || have_class[2];
   const size_t cu_bytes = ((size_t)(num_items + 1) * 4 + 255) & ~(size_t)255;
-  const size_t vx_bytes = long_fp8 ? (((size_t)num_items * 4 + 255) & ~(size_t)255) : 0;
+  const size_t vx_bytes = in_pieces ? (((size_t)num_items * 4 + 255) & ~(size_t)255) : 0;
   const size_t need = cu_bytes + 2 * vx_bytes + tiles.size() * sizeof(pa::TileWork);
   st = grow(&c->meta, &c->meta_bytes, need);
   if (st != PA_OK) return st;
   char *meta = static_cast<char *>(c->meta);
-  PA_CUDA(cudaMemcpyAsync(meta, long_fp8 ? v_cu.data() : cu_q_lens_host, (size_t)(num_items + 1) * 4,
+  PA_CUDA(cudaMemcpyAsync(meta, in_pieces ? v_cu.data() : cu_q_lens_host, (size_t)(num_items + 1) * 4,
                           cudaMemcpyHostToDevice, stream));
   p.cu_q_lens = reinterpret_cast<const int32_t *>(meta);
-  if (long_fp8) {
+  if (in_pieces) {
     PA_CUDA(cudaMemcpyAsync(meta + cu_bytes, v_ctx.data(), (size_t)num_items * 4,
                             cudaMemcpyHostToDevice, stream));
     PA_CUDA(cudaMemcpyAsync(meta + cu_bytes + vx_bytes, v_row.data(), (size_t)num_items * 4,

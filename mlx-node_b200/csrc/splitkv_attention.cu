@@ -106,29 +106,6 @@ __device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
   return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
 }
 
-// Four cache bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3) holding value / 256,
-// by integer operations only: with the byte in the high half of a 16-bit lane, sign
-// stays at bit 15 and the seven exponent/mantissa bits move down one place, which reads
-// as an f16 with the E4M3 exponent field taken at bias 15 instead of 7 (subnormals
-// included); the factor 2^8 is folded into the scales.  (The conversion instruction
-// cvt.rn.f16x2.e4m3x2 measured about four times slower than this in this kernel.)
-// The cache format (crates/mlx-paged-attn/metal/float8.metal:11-33) reads exponent
-// field 15 as infinity (mantissa 0) or NaN; EXACT restores that by raising the f16
-// exponent field from 15 to 31.  The fast variant is used while the cache is known to
-// hold no such byte.
-template <bool EXACT>
-__device__ __forceinline__ void fp8x4_to_f16(uint32_t w, uint32_t &lo, uint32_t &hi) {
-  const uint32_t xa = __byte_perm(w, 0u, 0x1404u);  // b1 << 24 | b0 << 8
-  const uint32_t xb = __byte_perm(w, 0u, 0x3424u);  // b3 << 24 | b2 << 8
-  lo = ((xa & 0x7F007F00u) >> 1) | (xa & 0x80008000u);
-  hi = ((xb & 0x7F007F00u) >> 1) | (xb & 0x80008000u);
-  if (EXACT) {
-    lo |= ((lo & 0x3C003C00u) + 0x04000400u) & 0x40004000u;
-    hi |= ((hi & 0x3C003C00u) + 0x04000400u) & 0x40004000u;
-  }
-}
-constexpr float kFp8Unbias = 256.f;  // the factor the conversion above leaves out
-
 // D(16x8,f32) += A(16x32,row) * B(32x8,col), both operands E4M3 bytes.  The tensor cores
 // read exponent field 15 as finite values (the OCP variant of the format); every other
 // byte means the same as in the cache format, so this path serves the fast variant only.
@@ -156,9 +133,6 @@ __device__ __forceinline__ float f16hi_to_float(uint32_t h2) {
   float f;
   asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((uint16_t)(h2 >> 16)));
   return f;
-}
-__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
-  return pack2<true>(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 // FP8 path: row r of a 16-token MMA tile holds token fp8_row_token(r) of the block, so
 // that the token pairs a thread gets from one 32-bit piece of a V row (tokens 4t..4t+3)

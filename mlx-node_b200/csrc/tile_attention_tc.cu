@@ -32,6 +32,13 @@
 // overlaps the tensor work of the other.  Online softmax keeps a stale row
 // maximum and rescales O only when the maximum grows by more than 2^8.
 //
+// FP8 (E4M3) pools (template flag FP8): the producers read the cache bytes with plain
+// 16-byte loads, turn them into f16 by the integer conversion of fp8x4_to_f16 (exact
+// variant: exponent field 15 reads as infinity / NaN, as the cache format defines) and
+// store them where the 16-bit copies would have landed; the tensor cores run on f16
+// operands (bf16 queries are converted on the way in, P is packed as f16) and the
+// dequantisation factors ride on the logit scale and on the final normalisation.
+//
 // Every wait is bounded; on expiry the CTA raises the error word, every role
 // leaves its loop, in-flight copies are drained and TMEM is freed.
 #include <cuda.h>
@@ -303,10 +310,18 @@ __device__ __forceinline__ bool wait_bar_at(uint32_t bar, uint32_t parity, volat
 #endif
 }
 
-template <bool CAP, bool F16>
+__device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+// F16: format of q and out (and, without FP8, of the pools).  FP8: the pools hold E4M3 bytes.
+template <bool CAP, bool F16, bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
                          const __grid_constant__ CUtensorMap v_map) {
+  constexpr bool MF16 = F16 || FP8;  // operand format of the MMAs
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -348,7 +363,9 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
     mbar_init(bar(B_QFULL), 128);
     for (int s = 0; s < 2; s++) {
       mbar_init(bar(B_KFULL + s), 128);  // every producer thread, after its pieces landed
-      mbar_init(bar(B_VFULL + s), 2);    // "bytes announced" and "tail of the last block cleared"
+      // 16-bit pools: "bytes announced" and "tail of the last block cleared"; FP8: every
+      // producer thread, after its converted pieces are stored
+      mbar_init(bar(B_VFULL + s), FP8 ? 128 : 2);
       mbar_init(bar(B_KEMPTY + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
       mbar_init(bar(B_SFULL + s), 1);
@@ -395,7 +412,15 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         const elem16 *src =
             have ? p.q + (int64_t)(q0 + w.q_begin + qi) * p.q_stride + (int64_t)(h * G + g) * kHeadSize + c * 8
                  : p.q;
-        cp_async16(q_s + (tile * 2 + (c >> 3)) * kSlab + sw128_off(r, c & 7), src, have ? 16u : 0u);
+        const uint32_t dst = q_s + (tile * 2 + (c >> 3)) * kSlab + sw128_off(r, c & 7);
+        if (FP8 && !F16) {  // bf16 queries become f16 operands
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (have) v = __ldg(reinterpret_cast<const uint4 *>(src));
+          st_shared16(dst, bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z),
+                      bf16x2_to_f16x2(v.w));
+        } else {
+          cp_async16(dst, src, have ? 16u : 0u);
+        }
       }
       cp_async_commit();
       // K tiles: 16-byte cp.async pieces, every thread its share, published with a proxy
@@ -420,6 +445,38 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           }
         }
         cp_async_commit();
+      };
+      // FP8: a K block is 128 pieces of 16 bytes, piece (g, t) = head dimensions 16g..16g+15
+      // of token t, which become the two 16-byte pieces (2g, t) and (2g+1, t) of the tile.
+      auto issue_k_fp8 = [&](int j) {
+        const uint32_t stage = k_s + (j & 1) * kStage;
+        for (int bb = 0; bb < 2; bb++) {
+          const int b = pw * 2 + bb;
+          const int gb = j * 8 + b;
+          const bool have = gb < nblk;
+          const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
+          const uint8_t *src = reinterpret_cast<const uint8_t *>(p.k_pool) +
+                               ((chunk * kChunkElems) << sh) + (gb & sh) * 256;
+          uint4 raw[4];
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            const int e = it * 32 + lane, g = e >> 4, t = e & 15;
+            raw[it] = have ? __ldg(reinterpret_cast<const uint4 *>(src + ((g * 256) << sh) + t * 16))
+                           : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            const int e = it * 32 + lane, g = e >> 4, t = e & 15;
+            uint32_t f[8];
+            fp8x4_to_f16<true>(raw[it].x, f[0], f[1]);
+            fp8x4_to_f16<true>(raw[it].y, f[2], f[3]);
+            fp8x4_to_f16<true>(raw[it].z, f[4], f[5]);
+            fp8x4_to_f16<true>(raw[it].w, f[6], f[7]);
+            const uint32_t dst = stage + (2 * g) * 2048 + b * 256 + t * 16;
+            st_shared16(dst, f[0], f[1], f[2], f[3]);
+            st_shared16(dst + 2048, f[4], f[5], f[6], f[7]);
+          }
+        }
       };
       auto land_k = [&](int j) {  // this thread's pieces of K(j) (and of Q before K(0)) are in
         __syncwarp();
@@ -446,10 +503,11 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         // Published as soon as it has landed (the producers have time to wait here): a
         // tile announced only after the next one could be issued would be held back by the
         // release of that next tile's stage.
-        issue_k(j);
+        if (FP8) issue_k_fp8(j);
+        else issue_k(j);
         {
           PA_T0();
-          cp_async_wait<0>();
+          cp_async_wait<0>();  // FP8: the queries, when they came in through cp.async
           if (lane == 0) PA_T1(10);
         }
         land_k(j);
@@ -457,7 +515,56 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           failed = true;
           break;
         }
-        {
+        if (FP8) {
+          // thread = head dimension d; per block the 16 bytes of row d (16 tokens) become the
+          // row's two 16-byte halves, placed as the 32-byte swizzle of v_block_desc wants
+          // them.  Tokens past the context are cleared on the way (0 * NaN is NaN).
+          const uint32_t vfull = bar(B_VFULL + (j & 1));
+          const int d = pt;
+          const uint32_t sw = (uint32_t)((d >> 2) & 1) << 4;
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            uint4 raw[4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int b = half * 4 + q4, gb = j * 8 + b;
+              raw[q4] = make_uint4(0u, 0u, 0u, 0u);
+              if (b < nb_here) {
+                const size_t chunk = (size_t)block_id(gb) * p.Hkv + h;
+                raw[q4] = __ldg(reinterpret_cast<const uint4 *>(
+                    reinterpret_cast<const uint8_t *>(p.v_pool) + ((chunk * kChunkElems) << sh) +
+                    ((d * 16) << sh) + (gb & sh) * 16));
+                const int valid = kv_len - gb * kBlockSize;  // tokens of this unit inside the context
+                if (valid < kBlockSize) {
+                  uint32_t wv[4] = {raw[q4].x, raw[q4].y, raw[q4].z, raw[q4].w};
+#pragma unroll
+                  for (int wi = 0; wi < 4; wi++) {
+                    uint32_t m = 0u;
+#pragma unroll
+                    for (int bi = 0; bi < 4; bi++)
+                      if (wi * 4 + bi < valid) m |= 0xffu << (8 * bi);
+                    wv[wi] &= m;
+                  }
+                  raw[q4] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+              }
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int b = half * 4 + q4;
+              uint32_t f[8];
+              fp8x4_to_f16<true>(raw[q4].x, f[0], f[1]);
+              fp8x4_to_f16<true>(raw[q4].y, f[2], f[3]);
+              fp8x4_to_f16<true>(raw[q4].z, f[4], f[5]);
+              fp8x4_to_f16<true>(raw[q4].w, f[6], f[7]);
+              const uint32_t dst = v_s + (j & 1) * kStage + b * 4096 + d * 32;
+              st_shared16(dst + sw, f[0], f[1], f[2], f[3]);
+              st_shared16(dst + (sw ^ 16u), f[4], f[5], f[6], f[7]);
+            }
+          }
+          fence_proxy_async();
+          mbar_arrive(vfull);
+        } else {
           const uint32_t vfull = bar(B_VFULL + (j & 1));
           const int tail_b = (have_tail && (last_gb >> 3) == j) ? (last_gb & 7) : -1;
           if (pt == 0) mbar_expect_tx(vfull, (uint32_t)(tail_b >= 0 ? 7 : 8) * kChunkBytes);
@@ -497,7 +604,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
       // (uniform registers feed tcgen05.mma directly); one elected lane issues.
       if (warp == 12) {
-        constexpr uint32_t kIdesc = F16 ? kIdescF16 : kIdescBf16;
+        constexpr uint32_t kIdesc = MF16 ? kIdescF16 : kIdescBf16;
         const bool leader = elect_one();
         auto issue_s = [&](int i, int j) {
           const uint32_t kst = k_s + (j & 1) * kStage;
@@ -565,9 +672,12 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
       const uint32_t s_t = tmem + lane_base + i * 128;
       const uint32_t o_t = tmem + lane_base + 256 + i * 128;
-      const float c = p.scale * kLog2e;
+      // FP8: the converted bytes are value / 2^8; that and the dequantisation factor of the
+      // keys ride on the logit scale
+      const float qk_scale = FP8 ? p.scale * p.k_scale * kFp8Unbias : p.scale;
+      const float c = qk_scale * kLog2e;
       // soft-capping: x -> tanh(x*scale/cap)*cap/scale, so that x*c is the capped logit
-      const float cap_in = p.scale / p.softcap, cap_out = p.softcap / p.scale;
+      const float cap_in = qk_scale / p.softcap, cap_out = p.softcap / qk_scale;
       float m_used = -INFINITY, l = 0.f;
 #ifdef PA_TILE_TIMING
       long long dbg_pass = 0, dbg_store = 0;
@@ -576,9 +686,9 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       auto pass = [&](bool need_mask, int tok0, float &mx, float &sum) {
         const float mc = m_used == -INFINITY ? 0.f : m_used * c;
         if (need_mask)
-          row_pass<CAP, true, F16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
+          row_pass<CAP, true, MF16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
         else
-          row_pass<CAP, false, F16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
+          row_pass<CAP, false, MF16>(s_t, s0, s1, s2, s3, c, mc, lim, tok0, cap_in, cap_out, mx, sum);
       };
 
       for (int j = 0; j < n_tiles && !failed; j++) {
@@ -654,7 +764,8 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       // epilogue: O / l -> bf16 rows
       if (!failed && wait_bar_at(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag, 9)) {
         tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float inv = l > 0.f ? 1.f / l : 0.f;
+        if (FP8) inv *= p.v_scale * kFp8Unbias;
         elem16 *orow = have ? p.out + (int64_t)(q0 + w.q_begin + qi) * p.out_stride +
                                          (int64_t)(h * G + g) * kHeadSize
                                    : nullptr;
@@ -733,10 +844,14 @@ cudaError_t tile_configure() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
   };
-  set(tile_attention_tc_kernel<false, false>);
-  set(tile_attention_tc_kernel<true, false>);
-  set(tile_attention_tc_kernel<false, true>);
-  set(tile_attention_tc_kernel<true, true>);
+  set(tile_attention_tc_kernel<false, false, false>);
+  set(tile_attention_tc_kernel<true, false, false>);
+  set(tile_attention_tc_kernel<false, true, false>);
+  set(tile_attention_tc_kernel<true, true, false>);
+  set(tile_attention_tc_kernel<false, false, true>);
+  set(tile_attention_tc_kernel<true, false, true>);
+  set(tile_attention_tc_kernel<false, true, true>);
+  set(tile_attention_tc_kernel<true, true, true>);
   return e;
 }
 
@@ -772,10 +887,18 @@ cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev,
   if (!v_map) return cudaErrorInvalidValue;
   const CUtensorMap &m = *reinterpret_cast<const CUtensorMap *>(v_map);
   const bool cap = p.softcap != 1.0f, f16 = p.is_f16 != 0;
-  if (cap && f16) tile_attention_tc_kernel<true, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
-  else if (cap) tile_attention_tc_kernel<true, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
-  else if (f16) tile_attention_tc_kernel<false, true><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
-  else tile_attention_tc_kernel<false, false><<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m);
+  auto go = [&](auto kernel) { kernel<<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m); };
+  if (p.is_fp8) {
+    if (cap && f16) go(tile_attention_tc_kernel<true, true, true>);
+    else if (cap) go(tile_attention_tc_kernel<true, false, true>);
+    else if (f16) go(tile_attention_tc_kernel<false, true, true>);
+    else go(tile_attention_tc_kernel<false, false, true>);
+  } else {
+    if (cap && f16) go(tile_attention_tc_kernel<true, true, false>);
+    else if (cap) go(tile_attention_tc_kernel<true, false, false>);
+    else if (f16) go(tile_attention_tc_kernel<false, true, false>);
+    else go(tile_attention_tc_kernel<false, false, false>);
+  }
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

@@ -137,7 +137,7 @@ def test_fp8_pools(cuda_device, f16):
         check_attention(got, ref, f"fp8, 32-token blocks, f16={f16} exact={exact}")
 
 
-def test_fp8_long_chunk_is_served_in_pieces(cuda_device):
+def test_fp8_long_chunk_on_32_token_blocks(cuda_device):
     case = Case([900, 130, 40], [200, 130, 1], 8, 2, 64, seed=138, bs=BS32)
     dc = Fp8DeviceCase(case, 0.5, 0.5, exact=False)
     k_ref, v_ref = dc.write_and_check()

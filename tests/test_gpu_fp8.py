@@ -200,21 +200,34 @@ def test_fp8_overflow_in_a_write_switches_to_exact_decoding(cuda_device):
     check_attention(np.where(fin, got, 0), np.where(fin, ref, 0), "finite part")
 
 
-def test_fp8_long_chunks_run_as_pieces(cuda_device):
-    """The tile kernel reads 16-bit pools only; with an FP8 cache a prefill chunk is served
-    by the split-KV kernel in pieces of 24/G query tokens.  Same results as the oracle on
-    the whole chunk; a decode and an empty sequence ride along."""
-    case = Case([200, 64, 33, 700], [100, 30, 1, 0], 8, 2, 128, seed=86)
-    got, ref = run(case, 0.5, 0.5)
-    check_attention(got, ref, "fp8 chunk in pieces")
-    # the piece boundaries need the context lengths on the host
-    dc = Fp8DeviceCase(case, 0.5, 0.5, exact=False)
-    dc.write_and_check()
-    out = torch.zeros((case.total_q, case.Hq, D), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(pa.PagedAttnError) as e:
-        dc.cache.varlen(out, dc.q, dc.tables, dc.lens, case.cu_q, case.S, case.Hq, case.MB,
-                        case.scale, dc.ws, dc.ws_bytes)
-    assert e.value.status == 1
+@pytest.mark.parametrize("f16", [False, True])
+def test_fp8_long_chunks_run_on_the_tile_kernel(cuda_device, f16):
+    """Prefill chunks over an FP8 cache: the tcgen05 tile kernel converts the cache bytes to
+    f16 on their way into shared memory.  Chunks that start and end inside blocks, contexts
+    that end inside a block (the pool holds NaN codes where nothing was written), a decode
+    and an empty sequence ride along; with and without host context lengths."""
+    case = Case([200, 64, 33, 700, 1500, 129], [100, 30, 1, 0, 600, 129], 8, 2, 256, seed=86, f16=f16)
+    got, ref = run(case, 0.5, 0.25)
+    check_attention(got, ref, f"fp8 chunk on the tile kernel f16={f16}")
+    got_cap, ref_cap = run(case, 0.5, 0.25, softcap=30.0)
+    check_attention(got_cap, ref_cap, f"fp8 chunk on the tile kernel, softcap, f16={f16}")
+    dc = Fp8DeviceCase(case, 0.5, 0.25, exact=False)
+    k_ref, v_ref = dc.write_and_check()
+    out = torch.full((case.total_q, case.Hq, D), float("nan"),
+                     dtype=torch.float16 if f16 else torch.bfloat16, device="cuda")
+    dc.cache.varlen(out, dc.q, dc.tables, dc.lens, case.cu_q, case.S, case.Hq, case.MB,
+                    case.scale, dc.ws, dc.ws_bytes)   # no host lengths: kernels back to back
+    torch.cuda.synchronize()
+    dc.cache.check_errors()
+    check_attention(elems_to_f32(to_bits(out), f16), got, "without host lengths")
+
+
+def test_fp8_tile_kernel_wide_groups_and_long_context(cuda_device):
+    # G = 16 (16 queries per 256-row CTA) and G = 1; a context beyond the staged block table
+    for G, Hkv, kv, ql in ((16, 1, [3000, 500], [40, 500]), (1, 2, [36000, 300], [260, 300])):
+        case = Case(kv, ql, G * Hkv, Hkv, 2400, seed=87 + G)
+        got, ref = run(case, 0.37, 0.6)
+        check_attention(got, ref, f"fp8 tile kernel G={G}")
 
 
 def test_fp8_copy_blocks_and_swap(cuda_device):

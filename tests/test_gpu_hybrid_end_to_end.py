@@ -51,8 +51,8 @@ def test_scheduler_drives_the_kernels(cuda_device, fp8, bs):
     NB = kv_host.total_blocks()
     kv_scale = 1.0 / 16
     if fp8:
-        # prefill chunks of 64 tokens are longer than one split-KV piece (24/G = 6 tokens):
-        # this run also covers the chunk-in-pieces path and its host context lengths
+        # prefill chunks of 64 tokens go to the tile kernel's FP8 path (with 8-token blocks,
+        # further down, to the split-KV kernel in pieces of 24/G = 6 tokens)
         k_pool = torch.zeros(NB, Hkv, D // X8, bs, X8, dtype=torch.uint8, device="cuda")
         v_pool = torch.zeros(NB, Hkv, D, bs, dtype=torch.uint8, device="cuda")
     else:
