@@ -882,14 +882,18 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   int split_ctas = c->num_sms;
   bool side_by_side = false;
   if (!tiles.empty() && any_split && context_lens_host) {
-    const double t_cta = tile_flops / (double)tiles.size() / (0.9e15 / c->num_sms);
+    // (FP8 cache: the tile kernel converts bytes as it goes and sustains about 0.6 PFLOP/s;
+    // the split-KV kernel streams about 30 GB/s per SM, 4.4 TB/s on the whole GPU)
+    const double tile_rate = c->fp8 ? 0.6e15 : 0.9e15;
+    const double sm_bw = c->fp8 ? 30e9 : 70e9, bw_cap = c->fp8 ? 4.4e12 : 6.0e12;
+    const double t_cta = tile_flops / (double)tiles.size() / (tile_rate / c->num_sms);
     const double t_tile_alone = t_cta * (double)((tiles.size() + c->num_sms - 1) / c->num_sms);
-    const double t_split_alone = split_bytes / 6.0e12;
+    const double t_split_alone = split_bytes / bw_cap;
     if (t_tile_alone > 20e-6 && t_split_alone > 20e-6) {
       double best = 1e30;
       int best_tile_sms = 0;
       for (int n2 = 8; n2 <= c->num_sms - 32; n2++) {
-        const double bw = std::min(6.0e12, (c->num_sms - n2) * 70e9);
+        const double bw = std::min(bw_cap, (c->num_sms - n2) * sm_bw);
         const double waves = (double)((tiles.size() + n2 - 1) / n2);
         const double cost = std::max(split_bytes / bw, waves * t_cta);
         if (cost < best - 1e-9) {

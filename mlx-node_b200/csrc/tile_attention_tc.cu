@@ -20,8 +20,8 @@
 //               (256-byte runs placed as [d/8][block][tok][8]); V chunk [d][tok] is
 //               the 32-byte-swizzle K-major order (halves of rows 4..7 swapped).
 //               Runs stay contiguous on both sides of the copy.
-//   warp 12     allocates TMEM; one lane issues every tcgen05.mma (warps 13-15 only
-//               complete the fourth warpgroup)
+//   warp 12     allocates TMEM; one lane issues every tcgen05.mma (warps 13-15 complete
+//               the fourth warpgroup; with an FP8 cache they convert the V tiles)
 //
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16) is
 // written over the first 64 columns of its S and fed back as the A operand of
@@ -32,16 +32,19 @@
 // overlaps the tensor work of the other.  Online softmax keeps a stale row
 // maximum and rescales O only when the maximum grows by more than 2^8.
 //
-// FP8 (E4M3) pools (template flag FP8): the producers read the cache bytes with plain
-// 16-byte loads, turn them into f16 by the integer conversion of fp8x4_to_f16 (exact
-// variant: exponent field 15 reads as infinity / NaN, as the cache format defines) and
-// store them where the 16-bit copies would have landed; the tensor cores run on f16
+// FP8 (E4M3) pools (template flag FP8): the cache bytes of a tile come in by cp.async one
+// tile ahead into a 32 KB staging area, are turned into f16 by the integer conversion of
+// fp8x4_to_f16 (K by the producers, V by warps 13-15; the variant that reads exponent
+// field 15 as infinity / NaN once the cache may hold such a byte) and stored where the
+// 16-bit copies would have landed; the tensor cores run on f16
 // operands (bf16 queries are converted on the way in, P is packed as f16) and the
 // dequantisation factors ride on the logit scale and on the final normalisation.
 //
 // Every wait is bounded; on expiry the CTA raises the error word, every role
 // leaves its loop, in-flight copies are drained and TMEM is freed.
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "pa_common.cuh"
 
@@ -54,9 +57,15 @@ constexpr int kTileTok = 128;          // tokens per KV tile
 constexpr int kSlab = 128 * 128;       // one operand slab: 128 rows x 128 B
 constexpr int kQBytes = 4 * kSlab;     // 2 Q tiles x 2 slabs
 constexpr int kStage = 2 * kSlab;      // one K or V tile
-constexpr int kTblCap = 2048;          // block ids staged per CTA (32768 tokens)
+// Block ids staged per CTA (ids beyond are read from the table in memory): 32768 tokens'
+// worth, or 7168 with an FP8 cache, whose raw bytes take 32 KB of the shared memory.
+template <bool FP8> constexpr int kTblCapOf = FP8 ? 448 : 2048;
+constexpr int kRawTile = 16384;        // FP8: cache bytes of one K or V tile
 constexpr int kNumBars = 16;
-constexpr int kSmemTc = 1024 + kQBytes + 4 * kStage + kTblCap * 4 + kNumBars * 8 + 16;
+template <bool FP8>
+constexpr int kSmemTcOf = 1024 + kQBytes + 4 * kStage + (FP8 ? 2 * kRawTile : 0) + kTblCapOf<FP8> * 4 +
+                          kNumBars * 8 + 16;
+static_assert(kSmemTcOf<true> <= 232448 && kSmemTcOf<false> <= 232448, "shared memory per CTA");
 constexpr int kTcThreads = 16 * 32;  // four warpgroups
 constexpr int kRegsSoftmax = 200, kRegsOther = 56;
 
@@ -316,6 +325,16 @@ __device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t 
                : "memory");
 }
 
+
+__device__ __forceinline__ uint4 ld_shared16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
 // F16: format of q and out (and, without FP8, of the pools).  FP8: the pools hold E4M3 bytes.
 template <bool CAP, bool F16, bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -325,9 +344,13 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+  constexpr int kTblCap = kTblCapOf<FP8>;
+  constexpr int kRawBytes = FP8 ? 2 * kRawTile : 0;
   const uint32_t q_s = base, k_s = base + kQBytes, v_s = k_s + 2 * kStage;
-  int *tbl = reinterpret_cast<int *>(gen + kQBytes + 4 * kStage);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(gen + kQBytes + 4 * kStage + kTblCap * 4);
+  const uint32_t raw_k = v_s + 2 * kStage, raw_v = raw_k + kRawTile;  // FP8 only
+  int *tbl = reinterpret_cast<int *>(gen + kQBytes + 4 * kStage + kRawBytes);
+  uint64_t *bars =
+      reinterpret_cast<uint64_t *>(gen + kQBytes + 4 * kStage + kRawBytes + kTblCap * 4);
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
   auto bar = [&](int i) { return smem_u32(&bars[i]); };
@@ -364,8 +387,8 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
     for (int s = 0; s < 2; s++) {
       mbar_init(bar(B_KFULL + s), 128);  // every producer thread, after its pieces landed
       // 16-bit pools: "bytes announced" and "tail of the last block cleared"; FP8: every
-      // producer thread, after its converted pieces are stored
-      mbar_init(bar(B_VFULL + s), FP8 ? 128 : 2);
+      // thread of warps 13-15, after its converted pieces are stored
+      mbar_init(bar(B_VFULL + s), FP8 ? 96 : 2);
       mbar_init(bar(B_KEMPTY + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
       mbar_init(bar(B_SFULL + s), 1);
@@ -386,6 +409,18 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
   tc_fence_after();
   const uint32_t tmem = *tmem_holder;
   bool failed = false;
+  auto block_id = [&](int b) -> uint32_t {
+    if (b < kTblCap) return (uint32_t)tbl[b];
+    uint32_t id = (uint32_t)table[b >> sh];
+    if (id >= p.num_blocks) {
+      atomicOr(p.err, kErrBlockRange);
+      id = 0;
+    }
+    return id;
+  };
+  // FP8: exponent field 15 of a cache byte means infinity / NaN; the cheaper conversion
+  // serves while the cache is known to hold no such byte
+  const bool fp8_exact = FP8 ? *p.fp8_special != 0u : false;
 
   if (n_tiles > 0) {
     if (warp >= 8 && warp < 12) {
@@ -393,15 +428,6 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       // =========================== producers ========================================
       const int pt = tid - 256;  // 0..127
       const int pw = warp - 8;
-      auto block_id = [&](int b) -> uint32_t {
-        if (b < kTblCap) return (uint32_t)tbl[b];
-        uint32_t id = (uint32_t)table[b >> sh];
-        if (id >= p.num_blocks) {
-          atomicOr(p.err, kErrBlockRange);
-          id = 0;
-        }
-        return id;
-      };
       // Q: 2 tiles x 128 rows x 16 pieces of 16 B
       for (int it = 0; it < 32; it++) {
         const int e = it * 128 + pt;
@@ -448,8 +474,10 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       };
       // FP8: a K block is 128 pieces of 16 bytes, piece (g, t) = head dimensions 16g..16g+15
       // of token t, which become the two 16-byte pieces (2g, t) and (2g+1, t) of the tile.
-      auto issue_k_fp8 = [&](int j) {
-        const uint32_t stage = k_s + (j & 1) * kStage;
+      // The bytes of a tile come in by cp.async one tile ahead into a staging area in which
+      // every thread owns the pieces it fetched (slot-major, 16 bytes per thread), so that
+      // the conversion needs no synchronisation and its loads never wait for memory.
+      auto fetch_k_fp8 = [&](int j) {
         for (int bb = 0; bb < 2; bb++) {
           const int b = pw * 2 + bb;
           const int gb = j * 8 + b;
@@ -457,21 +485,30 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
           const uint8_t *src = reinterpret_cast<const uint8_t *>(p.k_pool) +
                                ((chunk * kChunkElems) << sh) + (gb & sh) * 256;
-          uint4 raw[4];
 #pragma unroll
           for (int it = 0; it < 4; it++) {
             const int e = it * 32 + lane, g = e >> 4, t = e & 15;
-            raw[it] = have ? __ldg(reinterpret_cast<const uint4 *>(src + ((g * 256) << sh) + t * 16))
-                           : make_uint4(0u, 0u, 0u, 0u);
+            cp_async16(raw_k + ((bb * 4 + it) * 128 + pt) * 16, src + ((g * 256) << sh) + t * 16,
+                       have ? 16u : 0u);
           }
+        }
+        cp_async_commit();
+      };
+      auto convert_k_fp8 = [&](int j, auto exact_tag) {
+        constexpr bool EX = decltype(exact_tag)::value;
+        const uint32_t stage = k_s + (j & 1) * kStage;
+#pragma unroll
+        for (int bb = 0; bb < 2; bb++) {
+          const int b = pw * 2 + bb;
 #pragma unroll
           for (int it = 0; it < 4; it++) {
             const int e = it * 32 + lane, g = e >> 4, t = e & 15;
+            const uint4 raw = ld_shared16(raw_k + ((bb * 4 + it) * 128 + pt) * 16);
             uint32_t f[8];
-            fp8x4_to_f16<true>(raw[it].x, f[0], f[1]);
-            fp8x4_to_f16<true>(raw[it].y, f[2], f[3]);
-            fp8x4_to_f16<true>(raw[it].z, f[4], f[5]);
-            fp8x4_to_f16<true>(raw[it].w, f[6], f[7]);
+            fp8x4_to_f16<EX>(raw.x, f[0], f[1]);
+            fp8x4_to_f16<EX>(raw.y, f[2], f[3]);
+            fp8x4_to_f16<EX>(raw.z, f[4], f[5]);
+            fp8x4_to_f16<EX>(raw.w, f[6], f[7]);
             const uint32_t dst = stage + (2 * g) * 2048 + b * 256 + t * 16;
             st_shared16(dst, f[0], f[1], f[2], f[3]);
             st_shared16(dst + 2048, f[4], f[5], f[6], f[7]);
@@ -494,6 +531,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       const int last_valid = kv_len - last_gb * kBlockSize;
       const bool have_tail = last_valid < kBlockSize && last_gb < nblk;
       const int total_chunks = (int)p.num_blocks * p.Hkv;
+      if (FP8) fetch_k_fp8(0);  // the first tile's bytes
       for (int j = 0; j < n_tiles && !failed; j++) {
         const int nb_here = min(8, nblk - j * 8);  // blocks of this tile that exist
         if (j >= 2 && !wait_bar_at(bar(B_KEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
@@ -503,68 +541,26 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         // Published as soon as it has landed (the producers have time to wait here): a
         // tile announced only after the next one could be issued would be held back by the
         // release of that next tile's stage.
-        if (FP8) issue_k_fp8(j);
-        else issue_k(j);
-        {
+        if (FP8) {
+          // the bytes of this tile (and the queries) have been on their way for a tile's time;
+          // once converted, those of the next tile start
+          cp_async_wait<0>();
+          if (fp8_exact) convert_k_fp8(j, std::true_type{});
+          else convert_k_fp8(j, std::false_type{});
+          if (j + 1 < n_tiles) fetch_k_fp8(j + 1);
+        } else {
+          issue_k(j);
           PA_T0();
-          cp_async_wait<0>();  // FP8: the queries, when they came in through cp.async
+          cp_async_wait<0>();
           if (lane == 0) PA_T1(10);
         }
         land_k(j);
+        if (FP8) continue;  // V tiles of an FP8 cache are the work of warps 13-15
         if (j >= 2 && !wait_bar_at(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
           failed = true;
           break;
         }
-        if (FP8) {
-          // thread = head dimension d; per block the 16 bytes of row d (16 tokens) become the
-          // row's two 16-byte halves, placed as the 32-byte swizzle of v_block_desc wants
-          // them.  Tokens past the context are cleared on the way (0 * NaN is NaN).
-          const uint32_t vfull = bar(B_VFULL + (j & 1));
-          const int d = pt;
-          const uint32_t sw = (uint32_t)((d >> 2) & 1) << 4;
-#pragma unroll
-          for (int half = 0; half < 2; half++) {
-            uint4 raw[4];
-#pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) {
-              const int b = half * 4 + q4, gb = j * 8 + b;
-              raw[q4] = make_uint4(0u, 0u, 0u, 0u);
-              if (b < nb_here) {
-                const size_t chunk = (size_t)block_id(gb) * p.Hkv + h;
-                raw[q4] = __ldg(reinterpret_cast<const uint4 *>(
-                    reinterpret_cast<const uint8_t *>(p.v_pool) + ((chunk * kChunkElems) << sh) +
-                    ((d * 16) << sh) + (gb & sh) * 16));
-                const int valid = kv_len - gb * kBlockSize;  // tokens of this unit inside the context
-                if (valid < kBlockSize) {
-                  uint32_t wv[4] = {raw[q4].x, raw[q4].y, raw[q4].z, raw[q4].w};
-#pragma unroll
-                  for (int wi = 0; wi < 4; wi++) {
-                    uint32_t m = 0u;
-#pragma unroll
-                    for (int bi = 0; bi < 4; bi++)
-                      if (wi * 4 + bi < valid) m |= 0xffu << (8 * bi);
-                    wv[wi] &= m;
-                  }
-                  raw[q4] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                }
-              }
-            }
-#pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) {
-              const int b = half * 4 + q4;
-              uint32_t f[8];
-              fp8x4_to_f16<true>(raw[q4].x, f[0], f[1]);
-              fp8x4_to_f16<true>(raw[q4].y, f[2], f[3]);
-              fp8x4_to_f16<true>(raw[q4].z, f[4], f[5]);
-              fp8x4_to_f16<true>(raw[q4].w, f[6], f[7]);
-              const uint32_t dst = v_s + (j & 1) * kStage + b * 4096 + d * 32;
-              st_shared16(dst + sw, f[0], f[1], f[2], f[3]);
-              st_shared16(dst + (sw ^ 16u), f[4], f[5], f[6], f[7]);
-            }
-          }
-          fence_proxy_async();
-          mbar_arrive(vfull);
-        } else {
+        {
           const uint32_t vfull = bar(B_VFULL + (j & 1));
           const int tail_b = (have_tail && (last_gb >> 3) == j) ? (last_gb & 7) : -1;
           if (pt == 0) mbar_expect_tx(vfull, (uint32_t)(tail_b >= 0 ? 7 : 8) * kChunkBytes);
@@ -598,6 +594,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           }
         }
       }
+      if (FP8) cp_async_wait<0>();  // a loop left early may still have bytes on their way
     } else if (warp >= 12) {
       // =========================== MMA issuer ========================================
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
@@ -655,6 +652,73 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
             __syncwarp();
           }
         } while (false);
+      } else if (FP8) {
+        // ===================== V tiles of an FP8 cache (warps 13-15) ====================
+        // A V tile is 1024 pieces of 16 bytes: piece (b, d) = the 16 tokens of head dimension
+        // d in block b, which become the two 16-byte halves of row d of that block, placed as
+        // the 32-byte swizzle of v_block_desc wants them.  The 96 threads take the pieces
+        // round robin; each fetches its pieces by cp.async into slots of its own in the
+        // staging area one tile ahead and converts them when the tile's stage is free.
+        // Tokens past the context are cleared on the way (0 * NaN is NaN).
+        const int vt = tid - 13 * 32;  // 0..95
+        auto fetch_v = [&](int j) {
+          const int nb_here = min(8, nblk - j * 8);
+          for (int i = vt; i < 1024; i += 96) {
+            const int b = i >> 7, d = i & 127, gb = j * 8 + b;
+            const bool have = b < nb_here;
+            const size_t chunk = have ? (size_t)block_id(gb) * p.Hkv + h : 0;
+            cp_async16(raw_v + i * 16,
+                       reinterpret_cast<const uint8_t *>(p.v_pool) + ((chunk * kChunkElems) << sh) +
+                           ((d * 16) << sh) + (gb & sh) * 16,
+                       have ? 16u : 0u);
+          }
+          cp_async_commit();
+        };
+        auto convert_v = [&](int j, auto exact_tag) {
+          constexpr bool EX = decltype(exact_tag)::value;
+          // units of this tile that end inside the context need no clearing
+          const int full_units = (kv_len >> 4) - j * 8;
+          for (int i = vt; i < 1024; i += 96) {
+            const int b = i >> 7, d = i & 127;
+            uint4 raw = ld_shared16(raw_v + i * 16);
+            if (b >= full_units) {
+              const int valid = kv_len - (j * 8 + b) * kBlockSize;  // tokens inside the context
+              uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int wi = 0; wi < 4; wi++) {
+                uint32_t m = 0u;
+#pragma unroll
+                for (int bi = 0; bi < 4; bi++)
+                  if (wi * 4 + bi < valid) m |= 0xffu << (8 * bi);
+                wv[wi] &= m;
+              }
+              raw = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            }
+            uint32_t f[8];
+            fp8x4_to_f16<EX>(raw.x, f[0], f[1]);
+            fp8x4_to_f16<EX>(raw.y, f[2], f[3]);
+            fp8x4_to_f16<EX>(raw.z, f[4], f[5]);
+            fp8x4_to_f16<EX>(raw.w, f[6], f[7]);
+            const uint32_t sw = (uint32_t)((d >> 2) & 1) << 4;
+            const uint32_t dst = v_s + (j & 1) * kStage + b * 4096 + d * 32;
+            st_shared16(dst + sw, f[0], f[1], f[2], f[3]);
+            st_shared16(dst + (sw ^ 16u), f[4], f[5], f[6], f[7]);
+          }
+        };
+        fetch_v(0);
+        for (int j = 0; j < n_tiles && !failed; j++) {
+          if (j >= 2 && !wait_bar_at(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+            failed = true;
+            break;
+          }
+          cp_async_wait<0>();
+          if (fp8_exact) convert_v(j, std::true_type{});
+          else convert_v(j, std::false_type{});
+          if (j + 1 < n_tiles) fetch_v(j + 1);
+          fence_proxy_async();
+          mbar_arrive(bar(B_VFULL + (j & 1)));
+        }
+        cp_async_wait<0>();
       }
     } else {
       // =========================== softmax + epilogue ================================
@@ -840,18 +904,18 @@ int tile_queries_per_cta(int G) { return 2 * kQRows / G; }
 
 cudaError_t tile_configure() {
   cudaError_t e = cudaSuccess;
-  auto set = [&](auto kernel) {
+  auto set = [&](auto kernel, int smem) {
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   };
-  set(tile_attention_tc_kernel<false, false, false>);
-  set(tile_attention_tc_kernel<true, false, false>);
-  set(tile_attention_tc_kernel<false, true, false>);
-  set(tile_attention_tc_kernel<true, true, false>);
-  set(tile_attention_tc_kernel<false, false, true>);
-  set(tile_attention_tc_kernel<true, false, true>);
-  set(tile_attention_tc_kernel<false, true, true>);
-  set(tile_attention_tc_kernel<true, true, true>);
+  set(tile_attention_tc_kernel<false, false, false>, kSmemTcOf<false>);
+  set(tile_attention_tc_kernel<true, false, false>, kSmemTcOf<false>);
+  set(tile_attention_tc_kernel<false, true, false>, kSmemTcOf<false>);
+  set(tile_attention_tc_kernel<true, true, false>, kSmemTcOf<false>);
+  set(tile_attention_tc_kernel<false, false, true>, kSmemTcOf<true>);
+  set(tile_attention_tc_kernel<true, false, true>, kSmemTcOf<true>);
+  set(tile_attention_tc_kernel<false, true, true>, kSmemTcOf<true>);
+  set(tile_attention_tc_kernel<true, true, true>, kSmemTcOf<true>);
   return e;
 }
 
@@ -887,7 +951,8 @@ cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev,
   if (!v_map) return cudaErrorInvalidValue;
   const CUtensorMap &m = *reinterpret_cast<const CUtensorMap *>(v_map);
   const bool cap = p.softcap != 1.0f, f16 = p.is_f16 != 0;
-  auto go = [&](auto kernel) { kernel<<<num_work, kTcThreads, kSmemTc, st>>>(p, work_dev, m); };
+  const int smem = p.is_fp8 ? kSmemTcOf<true> : kSmemTcOf<false>;
+  auto go = [&](auto kernel) { kernel<<<num_work, kTcThreads, smem, st>>>(p, work_dev, m); };
   if (p.is_fp8) {
     if (cap && f16) go(tile_attention_tc_kernel<true, true, true>);
     else if (cap) go(tile_attention_tc_kernel<true, false, true>);
