@@ -155,10 +155,8 @@ pa_status pa_cache_get_config(const PagedAttnCache *cache, PagedAttnConfig *out)
  * 240).  The write stores encode(T(x / scale)) (reshape_and_cache.metal:88-92), the
  * attention reads decode(byte) * scale (paged_attention.metal:569-571, 920-929,
  * 1063-1071) with the per-layer scales below (KvScaleManager::k_scale / v_scale,
- * crates/mlx-paged-attn/src/metal/kv_scale.rs:90-97; default 1).  Decode and
- * multi-token sequences of up to 24 / (query heads per kv head) tokens run in one
- * piece; longer chunks are served in pieces of that many tokens (same results, the
- * chunk's KV read once per piece) and need context_lens_host.                     */
+ * crates/mlx-paged-attn/src/metal/kv_scale.rs:90-97; default 1).  Decode, verify
+ * and prefill chunks are all served, as with a 16-bit cache.                      */
 pa_status pa_cache_create_fp8(const PagedAttnConfig *config, int32_t device,
                               PagedAttnCache **out_cache);
 pa_status pa_cache_wrap_fp8(const PagedAttnConfig *config, int32_t device,
