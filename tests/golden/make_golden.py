@@ -8,7 +8,7 @@ builder.  Stored: the case parameters, a checksum of the inputs, the expected
 pool bits after the write (as a checksum plus a sampled slice) and the expected
 attention output in float32.
 
-Run from the repository root:  python tests/golden/make_golden.py
+Run from the repository root:  python tests/golden/make_golden.py [case names]
 """
 import hashlib
 import os
@@ -23,12 +23,14 @@ import numpy_reference  # noqa: E402
 from pa_testlib import Case  # noqa: E402
 
 CASES = {
-    # name: (kv_lens, q_lens, Hq, Hkv, NB, seed)
+    # name: (kv_lens, q_lens, Hq, Hkv, NB, seed[, tokens per pool block = 16])
     "decode_g2": ([1, 15, 16, 17, 100, 33], [1, 1, 1, 1, 1, 1], 4, 2, 32, 11),
     "decode_g4": ([257, 64, 5, 300], [1, 1, 1, 1], 8, 2, 64, 12),
     "decode_g8": ([40, 129], [1, 1], 8, 1, 16, 13),
     "verify_g4": ([37, 70, 21], [5, 5, 1], 8, 2, 16, 14),
     "prefill_g4": ([96, 50], [64, 50], 4, 1, 16, 15),
+    "mixed_block32": ([1, 31, 32, 33, 100, 75], [1, 1, 1, 3, 1, 40], 8, 2, 16, 16, 32),
+    "mixed_block8": ([1, 7, 8, 9, 100, 75], [1, 1, 1, 3, 1, 40], 8, 2, 64, 17, 8),
 }
 
 
@@ -65,18 +67,21 @@ def digest(*arrays) -> str:
 
 
 def build(name):
-    kv, ql, Hq, Hkv, NB, seed = CASES[name]
-    return Case(kv, ql, Hq, Hkv, NB, seed=seed)
+    kv, ql, Hq, Hkv, NB, seed, *rest = CASES[name]
+    return Case(kv, ql, Hq, Hkv, NB, seed=seed, bs=rest[0] if rest else 16)
 
 
 def main():
+    only = set(sys.argv[1:])  # names to regenerate; none = all
     for name in CASES:
+        if only and name not in only:
+            continue
         case = build(name)
         k_pool, v_pool = case.pools_after_write()
         # pool after the write, by fancy indexing (no shared index arithmetic)
         k_exp = case.k_pool.copy()
         v_exp = case.v_pool.copy()
-        blk, off = case.slots_all // 16, case.slots_all % 16
+        blk, off = case.slots_all // case.bs, case.slots_all % case.bs
         k_exp[blk, :, :, off, :] = case.k_all.reshape(-1, case.Hkv, 16, 8)
         v_exp[blk, :, :, off] = case.v_all
         assert (k_exp == k_pool).all() and (v_exp == v_pool).all(), name
@@ -94,6 +99,8 @@ def main():
             v_pool_block0=v_exp[case.block_tables[0, 0]], out=out, out_softcap30=out_cap)
         print(name, out.shape)
     for name in PRODUCER_CASES:
+        if only and name not in only:
+            continue
         c = build_producer(name)
         out = numpy_reference.qk_norm_rope(c["x"], c["w"], c["eps"], c["pos"], c["base"], c["dims"],
                                            f16=c["f16"]).astype(np.float32)
