@@ -354,6 +354,9 @@ pa_status pa_paged_attention_decode_static(PagedAttnCache *cache, uint32_t layer
  *                       it, a batch that mixes long-query and short-query sequences
  *                       runs its two kernels side by side on SM shares sized by
  *                       their estimated work; without it they run back to back.
+ *                       Required with 8-token blocks when a sequence has more than
+ *                       24 / (query heads per kv head) queries (PA_ERR_INVALID_ARG
+ *                       otherwise): such chunks are served in pieces of that size.
  *   max_context_len     upper bound of context_lens (0 = unknown)              */
 pa_status pa_paged_attention_varlen(PagedAttnCache *cache, uint32_t layer_idx,
                                     void *out, const void *q,

@@ -169,7 +169,7 @@ struct AttnParams {
   int S, Hq, Hkv, G, MB;
   int bs_shift;  // log2(pool block size / 16): 0, 1 (32 tokens) or -1 (8 tokens); MB counts pool blocks
   int is_f16;  // element format: 1 = f16, 0 = bf16
-  int is_fp8;  // pools hold E4M3 bytes (split-KV kernels only); is_f16 is then the q/out format
+  int is_fp8;  // pools hold E4M3 bytes; is_f16 is then the q/out format
   float k_scale, v_scale;  // FP8 dequantisation factors; 1 otherwise
   const unsigned *fp8_special;  // FP8: non-zero once the pools may hold an exponent-15 byte
   int early_trigger;  // split-KV: let the merge grid become resident at once
