@@ -309,6 +309,38 @@ pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
                                     float softcap, void *workspace,
                                     size_t workspace_bytes, void *cuda_stream);
 
+/* One decode step of one layer in ONE launch: the step's new token of every
+ * sequence is written to the pool and attention runs over the cache that
+ * already holds it - the order TransformerBlock::forward_paged keeps with two
+ * calls (crates/mlx-core/src/transformer/block.rs:223-232: update_cache, then
+ * forward).  The warp that attends the last block of a (sequence, kv head)
+ * stores that head's new key and value rows into the pool itself, so no write
+ * kernel runs before the attention kernel and no reduce kernel after it.
+ *   key, value     [num_seqs, num_kv_heads, head_size] in the cache dtype, row
+ *                  strides key_stride / value_stride in elements, device
+ *   slot_mapping   int64 [num_seqs], device: slot of sequence s's new token,
+ *                  which must be position context_lens[s] - 1 of that sequence
+ *                  (what get_slot_mapping_decode returns,
+ *                  crates/mlx-paged-attn/src/paged_kv_cache.rs:539-552); negative
+ *                  = no write.  Any other value is not written and
+ *                  pa_cache_check_errors reports PA_ERR_INVALID_ARG.
+ * The other arguments are those of pa_paged_attention_decode.  The pool bytes
+ * after the call equal those pa_reshape_and_cache would have produced.  On an
+ * FP8 cache, with 8- or 32-token blocks or more than 8 query heads per kv head
+ * the call runs the write kernel and then the attention kernel.
+ *   context_lens (and, for pa_paged_attention_varlen, the query offsets) are read
+ * as soon as the launch is scheduled, which may be before earlier kernels of
+ * the stream have finished when those were launched with programmatic
+ * dependent launch and trigger early: produce them before such a trigger, or
+ * on the host.                                                               */
+pa_status pa_decode_step(PagedAttnCache *cache, uint32_t layer_idx, void *out, const void *q,
+                         const void *key, const void *value, const int64_t *slot_mapping,
+                         const int32_t *block_tables, const int32_t *context_lens,
+                         int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
+                         int64_t q_stride, int64_t out_stride, int64_t key_stride,
+                         int64_t value_stride, float scale, float softcap, void *workspace,
+                         size_t workspace_bytes, void *cuda_stream);
+
 /* Decode attention for callers that cannot allocate device memory.
  * No counterpart in the reference.  Some hosts of this library are handed
  * their buffers by someone else and have no way to ask for more: a plugin
@@ -317,11 +349,14 @@ pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
  * would stall every stream of the process.  For them this entry computes
  * exactly what pa_paged_attention_decode computes, but keeps the split-KV
  * partial results in an array that is part of the library image instead of a
- * caller workspace; it calls no allocator, the CUDA one or any other.
+ * caller workspace; a call that succeeds calls no allocator, the CUDA one or any
+ * other (a refused call builds its error message in a host string).
  *   Limit: the array holds partials for 160 CTAs (one per SM), 4.2 MiB.  It is
  * resident on every GPU this process uses the library on, from load to exit,
  * whether or not this entry is ever called.  On a GPU with more than 160 SMs
- * the call is refused with PA_ERR_UNSUPPORTED and a message saying so.
+ * the call is refused with PA_ERR_UNSUPPORTED and a message saying so.  An FP8
+ * cache runs its narrow kernel on one CTA per SM here instead of two (the array
+ * has slots for 160).
  *   The first call on each device looks up the array's device address (one
  * runtime query, remembered afterwards); make that first call outside any
  * stream capture.
@@ -373,9 +408,12 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *cache, uint32_t layer_idx,
 /* One decode step of one layer from HOST buffers, the order
  * TransformerBlock::forward_paged keeps (crates/mlx-core/src/transformer/
  * block.rs:223-232): write the new tokens' K/V, then attend with context
- * lengths that already count them.  Copies q/k/v/slots/tables/lens to the
- * device, launches both kernels, copies `out` back and synchronises.  Staging
- * buffers are kept in the cache handle and grow on demand.                    */
+ * lengths that already count them.  Brings q/k/v/slots/tables/lens to the
+ * device, runs pa_decode_step, copies `out` back and synchronises.  Staging
+ * buffers are kept in the cache handle and grow on demand.  Everything is
+ * queued on a stream the handle owns, NOT on a stream of the caller: earlier
+ * work on the same pools (a prefill write, copy_blocks, swap_in) must have
+ * completed - be synchronised - before this call.                             */
 pa_status pa_decode_step_host(PagedAttnCache *cache, uint32_t layer_idx,
                               void *out_host, const void *q_host, const void *k_host,
                               const void *v_host, const int64_t *slot_mapping_host,
@@ -383,6 +421,22 @@ pa_status pa_decode_step_host(PagedAttnCache *cache, uint32_t layer_idx,
                               const int32_t *context_lens_host, int32_t num_seqs,
                               int32_t num_q_heads, int32_t max_blocks_per_seq,
                               float scale, float softcap);
+
+/* The same for a mixed batch (decode, verify and prefill-chunk sequences, the
+ * semantics of pa_paged_attention_varlen) from HOST buffers: copies the
+ * total_q = cu_q_lens_host[num_seqs] new tokens' q/k/v and slots, the tables and
+ * the lengths to the device, writes the K/V, attends, copies `out`
+ * [total_q, num_q_heads, head_size] back and synchronises.  Runs on the handle's
+ * own stream like pa_decode_step_host: work the caller queued elsewhere on the
+ * same pools must have completed before either call.                          */
+pa_status pa_varlen_step_host(PagedAttnCache *cache, uint32_t layer_idx, void *out_host,
+                              const void *q_host, const void *k_host, const void *v_host,
+                              const int64_t *slot_mapping_host,
+                              const int32_t *block_tables_host,
+                              const int32_t *context_lens_host,
+                              const int32_t *cu_q_lens_host, int32_t num_seqs,
+                              int32_t num_q_heads, int32_t max_blocks_per_seq, float scale,
+                              float softcap);
 
 /* Number of kernels this library has launched from the calling process
  * (all threads), for launch accounting in benchmarks.                         */

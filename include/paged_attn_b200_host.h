@@ -258,6 +258,167 @@ uint32_t pa_hybrid_num_running(const PaHybridScheduler *s);
  * rejected draft tokens)                                                              */
 pa_status pa_kv_truncate_sequence(PaKvHost *kv, uint32_t seq_id, uint32_t new_num_tokens);
 
+/* ==== The host cache bound to a device cache ========================================
+ * In the reference PagedKVCache is one object: block tables and allocator on the host,
+ * per-layer pools on the device behind its CacheEngineManager.  Here the host side is
+ * PaKvHost and the pools are PagedAttnCache; a binding joins the two so that the
+ * reference's device-touching methods exist with their own argument lists
+ * (sequence ids in, no tables or lengths to build by hand).
+ *
+ * The binding keeps the block tables RESIDENT on the device, one row per live
+ * sequence, and sends per call only the table entries that changed since the last call
+ * (a decode step appends one entry per sequence every block_size steps), the batch's
+ * row indices and its context lengths - one small pinned staging area read by one
+ * launch.  The reference rebuilds and re-uploads the whole [num_seqs,
+ * max_blocks_per_seq] table on every call (paged_kv_cache.rs:1081-1125).
+ * One binding is used by one thread and one stream at a time.                         */
+typedef struct PaKvBinding PaKvBinding;
+pa_status pa_kv_bind(PaKvHost *kv, PagedAttnCache *cache, PaKvBinding **out);
+void pa_kv_unbind(PaKvBinding *b);
+/* PagedKVCache::update (paged_kv_cache.rs:753-870): keys, values [num_tokens,
+ * num_kv_heads, head_size] and slot_mapping int64 [num_tokens], all on the device.     */
+pa_status pa_kv_update(PaKvBinding *b, uint32_t layer_idx, const void *keys, const void *values,
+                       const int64_t *slot_mapping_dev, int64_t num_tokens, void *cuda_stream);
+/* PagedKVCache::update_with_slots (:887-1012): the slot mapping is a host slice.        */
+pa_status pa_kv_update_with_slots(PaKvBinding *b, uint32_t layer_idx, const void *keys,
+                                  const void *values, const int64_t *slot_mapping_host,
+                                  int64_t num_tokens, void *cuda_stream);
+/* PagedKVCache::attention (:1034-1193): decode attention for the sequences `seq_ids`,
+ * context lengths taken from the block tables; q, out [n, num_query_heads, head_size] on
+ * the device.  An id that is not in the cache fails with the reference's message.
+ * FP8 caches take their per-layer scales from the binding's scale manager.              */
+pa_status pa_kv_attention(PaKvBinding *b, uint32_t layer_idx, void *out, const void *queries,
+                          const uint32_t *seq_ids, size_t n, uint32_t num_query_heads, float scale,
+                          void *cuda_stream);
+/* PagedKVCache::attention_with_context (:1205-1347): context lengths given.             */
+pa_status pa_kv_attention_with_context(PaKvBinding *b, uint32_t layer_idx, void *out,
+                                       const void *queries, const uint32_t *seq_ids,
+                                       const uint32_t *context_lens, size_t n,
+                                       uint32_t num_query_heads, float scale, void *cuda_stream);
+/* update_with_slots for the batch's newest tokens followed by attention, as one call
+ * and (where pa_decode_step can) one launch: the slot of sequence i is position
+ * num_tokens - 1 of its table (get_slot_mapping_decode, :539-552); keys, values
+ * [n, num_kv_heads, head_size], q, out [n, num_query_heads, head_size] on the device.   */
+pa_status pa_kv_decode_step(PaKvBinding *b, uint32_t layer_idx, void *out, const void *queries,
+                            const void *keys, const void *values, const uint32_t *seq_ids, size_t n,
+                            uint32_t num_query_heads, float scale, void *cuda_stream);
+/* The same from HOST buffers (pinned buffers are read in place by the ingest launch,
+ * pageable ones are copied first), result copied back to out_host, synchronous.  Runs
+ * on a stream the binding owns: earlier work on the same pools must have completed.     */
+pa_status pa_kv_decode_step_host(PaKvBinding *b, uint32_t layer_idx, void *out_host,
+                                 const void *q_host, const void *k_host, const void *v_host,
+                                 const uint32_t *seq_ids, size_t n, uint32_t num_query_heads,
+                                 float scale);
+/* Counters of the resident tables: block-table entries sent to the device so far, calls
+ * that sent metadata, rows in use.                                                      */
+void pa_kv_binding_stats(const PaKvBinding *b, uint64_t *table_entries_sent, uint64_t *calls,
+                         uint32_t *rows_in_use);
+
+/* ---- KvScaleManager, metal/kv_scale.rs:36-300 -------------------------------------------
+ * alpha < 0 picks the default 0.1; otherwise it is clamped to [0, 1] (with_alpha).       */
+typedef struct PaKvScaleManager PaKvScaleManager;
+typedef struct PaKvScaleStats {
+  uint32_t num_layers_calibrated;
+  float k_scale_min, k_scale_max, k_scale_mean, v_scale_min, v_scale_max, v_scale_mean;
+} PaKvScaleStats;
+PaKvScaleManager *pa_scale_create(uint32_t num_layers, float alpha);
+void pa_scale_destroy(PaKvScaleManager *m);
+uint32_t pa_scale_num_layers(const PaKvScaleManager *m);
+float pa_scale_alpha(const PaKvScaleManager *m);
+void pa_scale_init_default_scales(PaKvScaleManager *m);
+float pa_scale_k(const PaKvScaleManager *m, uint32_t layer_idx);
+float pa_scale_v(const PaKvScaleManager *m, uint32_t layer_idx);
+int32_t pa_scale_is_calibrated(const PaKvScaleManager *m);
+/* calibrate_layer / update_layer_ema on observed maxima of |x| (the host arithmetic)     */
+void pa_scale_calibrate_layer_max(PaKvScaleManager *m, uint32_t layer_idx, float k_max_abs,
+                                  float v_max_abs, float *k_scale, float *v_scale);
+void pa_scale_update_layer_ema_max(PaKvScaleManager *m, uint32_t layer_idx, float k_max_abs,
+                                   float v_max_abs, float *k_scale, float *v_scale);
+/* calibrate_layer / update_layer_ema on device tensors of the cache dtype (any shape,
+ * `count` elements each): max |x| by a reduction kernel, then the above.  dtype 0 = f16,
+ * 1 = bf16.  Synchronises the stream (the reference evaluates the reduction too).        */
+pa_status pa_scale_calibrate_layer(PaKvScaleManager *m, uint32_t layer_idx, const void *keys,
+                                   const void *values, size_t count, int32_t dtype, int32_t ema,
+                                   float *k_scale, float *v_scale, void *cuda_stream);
+void pa_scale_set_scales(PaKvScaleManager *m, uint32_t layer_idx, float k_scale, float v_scale);
+/* get_all_scales / load_scales: num_layers floats each (serialisation)                   */
+void pa_scale_get_all_scales(const PaKvScaleManager *m, float *k_out, float *v_out);
+void pa_scale_load_scales(PaKvScaleManager *m, const float *k, size_t nk, const float *v, size_t nv);
+void pa_scale_reset(PaKvScaleManager *m);
+void pa_scale_stats(const PaKvScaleManager *m, PaKvScaleStats *out);
+/* The manager of a binding whose device cache is FP8 (paged_kv_cache.rs:226-309: the
+ * cache owns one iff use_fp8); NULL otherwise.  Owned by the binding.  Its scales are
+ * handed to the kernels as they are on every update / attention call of the binding,
+ * which is what the reference does (paged_kv_cache.rs:826-834).                          */
+PaKvScaleManager *pa_kv_scale_manager(PaKvBinding *b);
+
+/* ---- PagedAttentionInputMetadata (+ builder), input_metadata.rs:29-278 ------------------- */
+typedef struct PaInputMetadata PaInputMetadata;
+PaInputMetadata *pa_metadata_create(const int32_t *block_tables, size_t num_table_entries,
+                                    const int32_t *context_lens, size_t num_seqs,
+                                    const int64_t *slot_mappings, size_t num_tokens,
+                                    uint32_t max_context_len, int32_t is_prefill,
+                                    uint32_t max_blocks_per_seq);
+PaInputMetadata *pa_metadata_dummy(void);                         /* :88-104 */
+void pa_metadata_destroy(PaInputMetadata *m);
+uint32_t pa_metadata_num_seqs(const PaInputMetadata *m);
+size_t pa_metadata_num_tokens(const PaInputMetadata *m);
+int32_t pa_metadata_is_prefill(const PaInputMetadata *m);
+uint32_t pa_metadata_max_context_len(const PaInputMetadata *m);
+uint32_t pa_metadata_max_blocks_per_seq(const PaInputMetadata *m);
+/* get_metal_buffers (:157-199): device copies of the three arrays on `device`, made on
+ * first use and kept until pa_metadata_invalidate_buffers (:201-206).                    */
+pa_status pa_metadata_device_buffers(PaInputMetadata *m, int32_t device, const int32_t **block_tables,
+                                     const int32_t **context_lens, const int64_t **slot_mappings);
+void pa_metadata_invalidate_buffers(PaInputMetadata *m);
+
+/* ---- PagedAttentionLayer / PagedAttentionLayers, attention_layer.rs:41-478 ---------------
+ * scale, softcap, k_scale, v_scale <= 0 in the parameters mean "default": 1/sqrt(head_size),
+ * 1.0 (off), 1.0, 1.0 (attention_layer.rs:116-124).                                      */
+typedef struct PaLayerParams {
+  uint32_t layer_idx, num_heads, num_kv_heads, head_size;
+  float scale;
+  uint32_t block_size;
+  float softcap;
+  uint32_t use_fp8;
+  float k_scale, v_scale;
+} PaLayerParams;
+typedef struct PaAttentionLayer PaAttentionLayer;
+PaAttentionLayer *pa_layer_create(const PaLayerParams *p);
+PaAttentionLayer *pa_layer_from_cache_config(uint32_t layer_idx, uint32_t num_heads,
+                                             const PaHostConfig *cfg);
+void pa_layer_destroy(PaAttentionLayer *l);
+/* the layer's parameters with the defaults filled in */
+void pa_layer_get(const PaAttentionLayer *l, PaLayerParams *out);
+void pa_layer_set_kv_scales(PaAttentionLayer *l, float k_scale, float v_scale);
+/* PagedAttentionLayer::forward (:217-384): writes the K/V of every token of
+ * metadata.slot_mappings; a prefill batch then returns with *has_output = 0 (the caller
+ * runs dense attention, as the reference's Ok(None)); a decode batch runs paged
+ * attention into `out` and sets *has_output = 1.  queries/out [num_seqs, num_heads,
+ * head_size], keys/values [num_tokens, num_kv_heads, head_size], on the device.          */
+pa_status pa_layer_forward(const PaAttentionLayer *l, PaKvBinding *cache, void *out,
+                           const void *queries, const void *keys, const void *values,
+                           PaInputMetadata *metadata, int32_t *has_output, void *cuda_stream);
+/* forward_decode (:399-416): an error for a prefill batch.                               */
+pa_status pa_layer_forward_decode(const PaAttentionLayer *l, PaKvBinding *cache, void *out,
+                                  const void *queries, const void *keys, const void *values,
+                                  PaInputMetadata *metadata, void *cuda_stream);
+typedef struct PaAttentionLayers PaAttentionLayers;
+PaAttentionLayers *pa_layers_create(uint32_t num_layers, uint32_t num_heads, uint32_t num_kv_heads,
+                                    uint32_t head_size, uint32_t block_size, int32_t use_fp8);
+PaAttentionLayers *pa_layers_from_cache_config(uint32_t num_heads, const PaHostConfig *cfg);
+void pa_layers_destroy(PaAttentionLayers *ls);
+const PaAttentionLayer *pa_layers_get(const PaAttentionLayers *ls, uint32_t layer_idx); /* NULL past the end */
+uint32_t pa_layers_num_layers(const PaAttentionLayers *ls);
+
+/* CacheEngineManager::new (cache_engine.rs:137-216) as one call: validates the host
+ * configuration, sizes the pool with calculate_num_blocks and creates host cache, device
+ * cache (all layers; dtype 0 = f16, 1 = bf16; FP8 if the configuration says so) and the
+ * binding.  The three handles are freed with their own destroy / free / unbind calls,
+ * binding first.                                                                         */
+pa_status pa_kv_create_bound(const PaHostConfig *cfg, int32_t device, uint32_t dtype, PaKvHost **kv_out,
+                             PagedAttnCache **cache_out, PaKvBinding **binding_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,6 +83,8 @@ struct PagedAttnCache {
   // FP8: device word next to the error word, non-zero once a pool may hold a byte with
   // exponent field 15 (infinity / NaN in the cache format)
   unsigned *fp8_special() const { return err_dev + 16; }
+  // arrival counters of the split-KV kernel (pa::AttnParams::sync): zero between launches
+  unsigned *sync_dev = nullptr;
   // scratch owned by the handle: attention workspace for tier 1 / the host step,
   // per-call metadata (cu_q_lens copy, tile work list), host-step staging
   void *ws = nullptr;
@@ -160,6 +162,8 @@ pa_status finish_create(PagedAttnCache *c) {
   c->bs_shift = c->cfg.block_size == 32 ? 1 : (c->cfg.block_size == 8 ? -1 : 0);
   PA_CUDA(cudaMalloc(&c->err_dev, 256));
   PA_CUDA(cudaMemset(c->err_dev, 0, 256));
+  PA_CUDA(cudaMalloc(&c->sync_dev, pa::kSyncWords * sizeof(unsigned)));
+  PA_CUDA(cudaMemset(c->sync_dev, 0, pa::kSyncWords * sizeof(unsigned)));
   PA_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), 64,
                         cudaHostAllocMapped | cudaHostAllocPortable));
   *c->err_host = 0;
@@ -369,6 +373,7 @@ pa_status pa_cache_free(PagedAttnCache *c) {
     for (void *p : c->v) cudaFree(p);
   }
   if (c->err_dev) cudaFree(c->err_dev);
+  if (c->sync_dev) cudaFree(c->sync_dev);
   if (c->err_host) cudaFreeHost(c->err_host);
   if (c->ws) cudaFree(c->ws);
   if (c->meta) cudaFree(c->meta);
@@ -402,8 +407,16 @@ pa_status pa_cache_check_errors(PagedAttnCache *c, void *cuda_stream) {
   PA_CUDA(cudaStreamSynchronize(st));
   if (word == 0) return PA_OK;
   PA_CUDA(cudaMemsetAsync(c->err_dev, 0, sizeof(word), st));
+  // a kernel that gave up may have left arrival counters behind
+  if (word & pa::kErrTimeout)
+    PA_CUDA(cudaMemsetAsync(c->sync_dev, 0, pa::kSyncWords * sizeof(unsigned), st));
   PA_CUDA(cudaStreamSynchronize(st));
+  *c->err_host = 0;
   if (word & pa::kErrTimeout) return fail(PA_ERR_TIMEOUT, "a bounded device-side wait ran out");
+  if (word & pa::kErrStepSlot)
+    return fail(PA_ERR_INVALID_ARG,
+                "decode step: a slot_mapping entry is not position context_len - 1 of its sequence "
+                "(that token was not written)");
   if (word & pa::kErrSlotRange)
     return fail(PA_ERR_OUT_OF_RANGE, "slot_mapping entry beyond num_blocks*block_size (skipped)");
   return fail(PA_ERR_OUT_OF_RANGE, "block id beyond num_blocks (read as block 0)");
@@ -709,15 +722,29 @@ size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {
   return pa::splitkv_workspace_bytes(c->num_sms * (c->fp8 ? 2 : 1));
 }
 
-pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
-                                    const int32_t *block_tables, const int32_t *context_lens,
-                                    const int32_t *cu_q_lens_host,
-                                    const int32_t *context_lens_host, int32_t num_seqs,
-                                    int32_t num_q_heads, int32_t max_blocks_per_seq,
-                                    int64_t q_stride, int64_t out_stride, float scale,
-                                    float softcap, int32_t max_context_len, void *workspace,
-                                    size_t workspace_bytes, void *cuda_stream) {
-  (void)max_context_len;
+}  // extern "C"
+
+namespace {
+// The step's new tokens for a decode call that also writes them (see AttnParams::k_new).
+struct StepWrite {
+  const void *k, *v;
+  const int64_t *slots;
+  int64_t k_stride, v_stride;
+};
+// Whether the split-KV kernel can write the step's tokens itself: 16-bit pools of
+// 16-token blocks and a GQA group that fits the narrow kernel.
+bool can_fuse_write(const PagedAttnCache *c, int num_q_heads) {
+  return !c->fp8 && c->bs_shift == 0 && num_q_heads > 0 &&
+         num_q_heads % (int)c->cfg.num_kv_heads == 0 && num_q_heads / (int)c->cfg.num_kv_heads <= 8;
+}
+
+pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                         const int32_t *block_tables, const int32_t *context_lens,
+                         const int32_t *cu_q_lens_host, const int32_t *context_lens_host,
+                         int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
+                         int64_t q_stride, int64_t out_stride, float scale, float softcap,
+                         void *workspace, size_t workspace_bytes, void *cuda_stream,
+                         const StepWrite *write) {
   pa_status st = check_layer(c, layer);
   if (st != PA_OK) return st;
   if (num_seqs < 0) return fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
@@ -765,6 +792,7 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   p.ws_ctas = (int)std::min<size_t>(workspace_bytes / pa::splitkv_workspace_bytes(1), 1u << 20);
   p.err = c->err_dev;
   p.err_mirror = c->err_host_dev;
+  p.sync = c->sync_dev;
   p.seq_base = 0;
   p.is_f16 = c->cfg.dtype == 0 ? 1 : 0;
   p.is_fp8 = c->fp8 ? 1 : 0;
@@ -776,11 +804,14 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
   if (!cu_q_lens_host) {  // decode: one query per sequence
     p.min_cols = 1;
     p.max_cols = G;
-    int decode_ctas = c->num_sms;
-#ifdef PA_TILE_TIMING  // debug builds: study how bandwidth scales with the CTA count
-    if (const char *e = getenv("PA_DEBUG_SPLIT_CTAS")) decode_ctas = atoi(e);
-#endif
-    PA_CUDA(pa::launch_splitkv_attention(p, decode_ctas, stream, c->unit_map(layer)));
+    if (write) {
+      p.k_new = static_cast<const pa::elem16 *>(write->k);
+      p.v_new = static_cast<const pa::elem16 *>(write->v);
+      p.slot_mapping = write->slots;
+      p.k_new_stride = write->k_stride;
+      p.v_new_stride = write->v_stride;
+    }
+    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream, c->unit_map(layer)));
     return PA_OK;
   }
 
@@ -901,16 +932,6 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
           best_tile_sms = n2;
         }
       }
-#ifdef PA_DEBUG_TUNE  // debug builds: sweep the split by hand
-      if (const char *e = getenv("PA_DEBUG_TILE_SMS")) {
-        best_tile_sms = atoi(e);
-        best = 0.0;
-        if (getenv("PA_DEBUG_VERBOSE")) fprintf(stderr, "tile_sms forced to %d\n", best_tile_sms);
-      } else if (getenv("PA_DEBUG_VERBOSE")) {
-        fprintf(stderr, "model picks tile_sms %d (cost %.1f us, alone %.1f + %.1f us)\n", best_tile_sms,
-                best * 1e6, t_tile_alone * 1e6, t_split_alone * 1e6);
-      }
-#endif
       if (best_tile_sms > 0 && best < t_tile_alone + t_split_alone) {
         split_ctas = c->num_sms - best_tile_sms;
         side_by_side = true;
@@ -941,6 +962,56 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
     PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
   }
   return PA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                                    const int32_t *block_tables, const int32_t *context_lens,
+                                    const int32_t *cu_q_lens_host,
+                                    const int32_t *context_lens_host, int32_t num_seqs,
+                                    int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                    int64_t q_stride, int64_t out_stride, float scale,
+                                    float softcap, int32_t max_context_len, void *workspace,
+                                    size_t workspace_bytes, void *cuda_stream) {
+  (void)max_context_len;
+  return attention_impl(c, layer, out, q, block_tables, context_lens, cu_q_lens_host,
+                        context_lens_host, num_seqs, num_q_heads, max_blocks_per_seq, q_stride,
+                        out_stride, scale, softcap, workspace, workspace_bytes, cuda_stream, nullptr);
+}
+
+pa_status pa_decode_step(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                         const void *key, const void *value, const int64_t *slot_mapping,
+                         const int32_t *block_tables, const int32_t *context_lens,
+                         int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
+                         int64_t q_stride, int64_t out_stride, int64_t key_stride,
+                         int64_t value_stride, float scale, float softcap, void *workspace,
+                         size_t workspace_bytes, void *cuda_stream) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_seqs < 0) return fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
+  if (num_seqs == 0) return PA_OK;
+  if (!key || !value || !slot_mapping) return fail(PA_ERR_INVALID_ARG, "null tensor pointer");
+  const int64_t row = (int64_t)c->cfg.num_kv_heads * c->cfg.head_size;
+  if (key_stride < row || value_stride < row || (key_stride & 7) || (value_stride & 7))
+    return fail(PA_ERR_INVALID_ARG, "key/value stride must be >= num_kv_heads*head_size and a multiple of 8");
+  if (!aligned16(key) || !aligned16(value))
+    return fail(PA_ERR_INVALID_ARG, "key/value must be 16-byte aligned");
+  if (!can_fuse_write(c, num_q_heads)) {
+    // FP8 pools (the write quantises), 8- or 32-token blocks, wide GQA groups: two launches
+    st = pa_reshape_and_cache(c, layer, key, value, slot_mapping, num_seqs, key_stride,
+                              value_stride, cuda_stream);
+    if (st != PA_OK) return st;
+    return attention_impl(c, layer, out, q, block_tables, context_lens, nullptr, nullptr, num_seqs,
+                          num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale, softcap,
+                          workspace, workspace_bytes, cuda_stream, nullptr);
+  }
+  const StepWrite w{key, value, slot_mapping, key_stride, value_stride};
+  return attention_impl(c, layer, out, q, block_tables, context_lens, nullptr, nullptr, num_seqs,
+                        num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale, softcap,
+                        workspace, workspace_bytes, cuda_stream, &w);
 }
 
 pa_status pa_paged_attention_decode(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
@@ -1034,18 +1105,73 @@ pa_status pa_decode_step_host(PagedAttnCache *c, uint32_t layer, void *out_host,
     PA_CUDA(cudaMemcpyAsync(base + o_tb, tables_host, tb_b, cudaMemcpyHostToDevice, s));
     PA_CUDA(cudaMemcpyAsync(base + o_ln, lens_host, ln_b, cudaMemcpyHostToDevice, s));
   }
-  st = pa_reshape_and_cache(c, layer, k_src, v_src, static_cast<const int64_t *>(sl_src), num_seqs,
-                            (int64_t)(Hkv * D), (int64_t)(Hkv * D), s);
-  if (st != PA_OK) return st;
-  st = pa_paged_attention_decode(c, layer, base + o_out, base + o_q,
-                                 reinterpret_cast<const int32_t *>(base + o_tb),
-                                 reinterpret_cast<const int32_t *>(base + o_ln), num_seqs,
-                                 num_q_heads, max_blocks_per_seq, (int64_t)(num_q_heads * D),
-                                 (int64_t)(num_q_heads * D), scale, softcap, c->ws, c->ws_bytes, s);
+  st = pa_decode_step(c, layer, base + o_out, base + o_q, k_src, v_src,
+                      static_cast<const int64_t *>(sl_src),
+                      reinterpret_cast<const int32_t *>(base + o_tb),
+                      reinterpret_cast<const int32_t *>(base + o_ln), num_seqs, num_q_heads,
+                      max_blocks_per_seq, (int64_t)(num_q_heads * D), (int64_t)(num_q_heads * D),
+                      (int64_t)(Hkv * D), (int64_t)(Hkv * D), scale, softcap, c->ws, c->ws_bytes, s);
   if (st != PA_OK) return st;
   PA_CUDA(cudaMemcpyAsync(out_host, base + o_out, q_b, cudaMemcpyDeviceToHost, s));
   PA_CUDA(cudaStreamSynchronize(s));
-  // the merge kernel left a copy of the error word in host-visible memory
+  // the attention kernel left a copy of the error word in host-visible memory
+  if (*reinterpret_cast<volatile unsigned *>(c->err_host) != 0) return pa_cache_check_errors(c, s);
+  return PA_OK;
+}
+
+pa_status pa_varlen_step_host(PagedAttnCache *c, uint32_t layer, void *out_host, const void *q_host,
+                              const void *k_host, const void *v_host, const int64_t *slots_host,
+                              const int32_t *tables_host, const int32_t *lens_host,
+                              const int32_t *cu_q_lens_host, int32_t num_seqs, int32_t num_q_heads,
+                              int32_t max_blocks_per_seq, float scale, float softcap) {
+  pa_status st = check_layer(c, layer);
+  if (st != PA_OK) return st;
+  if (num_seqs <= 0) return num_seqs == 0 ? PA_OK : fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
+  if (!out_host || !q_host || !k_host || !v_host || !slots_host || !tables_host || !lens_host ||
+      !cu_q_lens_host)
+    return fail(PA_ERR_INVALID_ARG, "null host pointer");
+  if (num_q_heads <= 0 || max_blocks_per_seq <= 0) return fail(PA_ERR_INVALID_ARG, "bad sizes");
+  const int64_t T = cu_q_lens_host[num_seqs];
+  if (T < 0) return fail(PA_ERR_INVALID_ARG, "cu_q_lens must be non-decreasing from 0");
+  if (T == 0) return PA_OK;
+  DeviceGuard g(c->device);
+  const size_t D = c->cfg.head_size, Hkv = c->cfg.num_kv_heads, S = (size_t)num_seqs;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  const size_t q_b = (size_t)T * num_q_heads * D * 2, kv_b = (size_t)T * Hkv * D * 2, sl_b = (size_t)T * 8,
+               tb_b = S * (size_t)max_blocks_per_seq * 4, ln_b = S * 4;
+  const size_t o_q = 0, o_k = o_q + up(q_b), o_v = o_k + up(kv_b), o_sl = o_v + up(kv_b),
+               o_tb = o_sl + up(sl_b), o_ln = o_tb + up(tb_b), o_out = o_ln + up(ln_b),
+               total = o_out + up(q_b);
+  st = grow(&c->stage, &c->stage_bytes, total);
+  if (st != PA_OK) return st;
+  st = grow(&c->ws, &c->ws_bytes, pa_attention_workspace_bytes(c));
+  if (st != PA_OK) return st;
+  char *base = static_cast<char *>(c->stage);
+  cudaStream_t s = c->step_stream;
+  // A chunk's inputs are megabytes: the copy engine moves them (a kernel reading pinned
+  // host memory in place is the better route only for the few hundred kilobytes of a
+  // decode step).
+  PA_CUDA(cudaMemcpyAsync(base + o_q, q_host, q_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_k, k_host, kv_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_v, v_host, kv_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_sl, slots_host, sl_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_tb, tables_host, tb_b, cudaMemcpyHostToDevice, s));
+  PA_CUDA(cudaMemcpyAsync(base + o_ln, lens_host, ln_b, cudaMemcpyHostToDevice, s));
+  st = pa_reshape_and_cache(c, layer, base + o_k, base + o_v,
+                            reinterpret_cast<const int64_t *>(base + o_sl), T, (int64_t)(Hkv * D),
+                            (int64_t)(Hkv * D), s);
+  if (st != PA_OK) return st;
+  st = pa_paged_attention_varlen(c, layer, base + o_out, base + o_q,
+                                 reinterpret_cast<const int32_t *>(base + o_tb),
+                                 reinterpret_cast<const int32_t *>(base + o_ln), cu_q_lens_host,
+                                 lens_host, num_seqs, num_q_heads, max_blocks_per_seq,
+                                 (int64_t)(num_q_heads * D), (int64_t)(num_q_heads * D), scale,
+                                 softcap, 0, c->ws, c->ws_bytes, s);
+  if (st != PA_OK) return st;
+  PA_CUDA(cudaMemcpyAsync(out_host, base + o_out, q_b, cudaMemcpyDeviceToHost, s));
+  // every kernel of the call has finished when this copy runs, the tile kernel included
+  PA_CUDA(cudaMemcpyAsync(c->err_host, c->err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
+  PA_CUDA(cudaStreamSynchronize(s));
   if (*reinterpret_cast<volatile unsigned *>(c->err_host) != 0) return pa_cache_check_errors(c, s);
   return PA_OK;
 }

@@ -117,8 +117,14 @@ uint64_t hash_tokens(const uint32_t *tokens, size_t n, uint64_t parent_hash) {
 }
 
 // ---- block tables (crates/mlx-paged-attn/src/block_table.rs) -----------------------------
+void SequenceBlockTable::touch() {
+  static std::atomic<uint64_t> stamp{0};
+  version_ = stamp.fetch_add(1, std::memory_order_relaxed) + 1;
+}
+
 bool SequenceBlockTable::replace_block(size_t i, BlockRef b) {
   if (i >= blocks_.size()) return false;
+  touch();
   blocks_[i] = std::move(b);
   return true;
 }
@@ -927,5 +933,101 @@ std::vector<CompletedSequence> HybridScheduler::get_completed() {
 
 // ---- kv_scale.rs:165-174 -------------------------------------------------------------------------
 float kv_compute_scale(float max_abs) { return max_abs < 1e-12f ? 1.0f : 448.0f / max_abs; }
+
+// ---- kv_scale.rs:36-300 ----------------------------------------------------------------------------
+KvScaleManager::KvScaleManager(uint32_t num_layers, float alpha)
+    : num_layers_(num_layers), alpha_(alpha < 0.f ? 0.f : (alpha > 1.f ? 1.f : alpha)) {}
+
+void KvScaleManager::init_default_scales() {
+  for (uint32_t i = 0; i < num_layers_; i++) k_scales_[i] = v_scales_[i] = 1.0f;
+}
+float KvScaleManager::k_scale(uint32_t layer) const {
+  auto it = k_scales_.find(layer);
+  return it == k_scales_.end() ? 1.0f : it->second;
+}
+float KvScaleManager::v_scale(uint32_t layer) const {
+  auto it = v_scales_.find(layer);
+  return it == v_scales_.end() ? 1.0f : it->second;
+}
+std::pair<float, float> KvScaleManager::calibrate_layer(uint32_t layer, float k_max, float v_max) {
+  const float k = kv_compute_scale(k_max), v = kv_compute_scale(v_max);
+  k_scales_[layer] = k;
+  v_scales_[layer] = v;
+  calibrated_ = true;
+  return {k, v};
+}
+std::pair<float, float> KvScaleManager::update_layer_ema(uint32_t layer, float k_max, float v_max) {
+  // entry(layer).or_insert(observed), then the update runs on that value as well
+  // (kv_scale.rs:167-171)
+  auto kr = k_running_max_.emplace(layer, k_max).first;
+  kr->second = alpha_ * k_max + (1.0f - alpha_) * kr->second;
+  auto vr = v_running_max_.emplace(layer, v_max).first;
+  vr->second = alpha_ * v_max + (1.0f - alpha_) * vr->second;
+  const float k = kv_compute_scale(kr->second), v = kv_compute_scale(vr->second);
+  k_scales_[layer] = k;
+  v_scales_[layer] = v;
+  calibrated_ = true;
+  return {k, v};
+}
+void KvScaleManager::set_scales(uint32_t layer, float k, float v) {
+  k_scales_[layer] = k;
+  v_scales_[layer] = v;
+  calibrated_ = true;
+}
+void KvScaleManager::get_all_scales(std::vector<float> *k, std::vector<float> *v) const {
+  k->assign(num_layers_, 1.0f);
+  v->assign(num_layers_, 1.0f);
+  for (const auto &e : k_scales_) if (e.first < num_layers_) (*k)[e.first] = e.second;
+  for (const auto &e : v_scales_) if (e.first < num_layers_) (*v)[e.first] = e.second;
+}
+void KvScaleManager::load_scales(const float *k, size_t nk, const float *v, size_t nv) {
+  for (size_t i = 0; i < nk; i++) k_scales_[(uint32_t)i] = k[i];
+  for (size_t i = 0; i < nv; i++) v_scales_[(uint32_t)i] = v[i];
+  calibrated_ = true;
+}
+void KvScaleManager::reset() {
+  k_scales_.clear();
+  v_scales_.clear();
+  k_running_max_.clear();
+  v_running_max_.clear();
+  calibrated_ = false;
+}
+KvScaleStats KvScaleManager::stats() const {
+  KvScaleStats s{};
+  s.num_layers_calibrated = (uint32_t)k_scales_.size();
+  auto fold = [](const std::map<uint32_t, float> &m, float *mn, float *mx, float *mean) {
+    *mn = INFINITY;
+    *mx = -INFINITY;
+    float sum = 0.f;
+    for (const auto &e : m) {
+      *mn = std::min(*mn, e.second);
+      *mx = std::max(*mx, e.second);
+      sum += e.second;
+    }
+    *mean = m.empty() ? 0.f : sum / (float)m.size();
+  };
+  fold(k_scales_, &s.k_scale_min, &s.k_scale_max, &s.k_scale_mean);
+  fold(v_scales_, &s.v_scale_min, &s.v_scale_max, &s.v_scale_mean);
+  return s;
+}
+
+// ---- attention_layer.rs:116-161 ----------------------------------------------------------------------
+AttentionLayer::AttentionLayer(const AttentionLayerParams &p)
+    : layer_idx(p.layer_idx), num_heads(p.num_heads), num_kv_heads(p.num_kv_heads), head_size(p.head_size),
+      block_size(p.block_size), scale(p.scale > 0.f ? p.scale : 1.0f / std::sqrt((float)p.head_size)),
+      softcap(p.softcap > 0.f ? p.softcap : 1.0f), k_scale(p.k_scale > 0.f ? p.k_scale : 1.0f),
+      v_scale(p.v_scale > 0.f ? p.v_scale : 1.0f), use_fp8(p.use_fp8) {}
+
+AttentionLayer AttentionLayer::from_cache_config(uint32_t layer_idx, uint32_t num_heads,
+                                                 const PagedAttentionConfig &cfg) {
+  AttentionLayerParams p;
+  p.layer_idx = layer_idx;
+  p.num_heads = num_heads;
+  p.num_kv_heads = cfg.num_kv_heads;
+  p.head_size = cfg.head_size;
+  p.block_size = cfg.block_size;
+  p.use_fp8 = cfg.use_fp8_cache;
+  return AttentionLayer(p);
+}
 
 }  // namespace pa_host

@@ -76,8 +76,15 @@ class SequenceBlockTable {
  public:
   SequenceBlockTable(uint32_t seq_id, uint32_t block_size) : seq_id(seq_id), block_size_(block_size) {}
   uint32_t seq_id;
-  void add_block(BlockRef b) { blocks_.push_back(std::move(b)); }
+  void add_block(BlockRef b) {
+    blocks_.push_back(std::move(b));
+    touch();
+  }
   bool replace_block(size_t i, BlockRef b);
+  // Changes whenever the list of blocks changes (a process-wide stamp, so a table
+  // rebuilt from scratch never repeats an older value): lets a device-side copy of the
+  // row tell "nothing to send" from "compare and send" in O(1).
+  uint64_t version() const { return version_; }
   size_t num_blocks() const { return blocks_.size(); }
   uint32_t num_tokens() const { return num_tokens_; }
   void set_num_tokens(uint32_t n) { num_tokens_ = n; }
@@ -89,9 +96,11 @@ class SequenceBlockTable {
   bool absolute_slot_index(uint32_t token_pos, int64_t *slot) const;
 
  private:
+  void touch();
   std::vector<BlockRef> blocks_;
   uint32_t num_tokens_ = 0;
   uint32_t block_size_;
+  uint64_t version_ = 0;
 };
 
 class BlockTable {
@@ -368,7 +377,61 @@ class HybridScheduler {
   uint32_t block_size_;
 };
 
-// ---- metal/kv_scale.rs (host maths only) ------------------------------------------------------
+// ---- metal/kv_scale.rs -----------------------------------------------------------------------
 float kv_compute_scale(float max_abs);  // 448 / max_abs, 1.0 for an all-zero tensor
+
+struct KvScaleStats {
+  uint32_t num_layers_calibrated;
+  float k_scale_min, k_scale_max, k_scale_mean, v_scale_min, v_scale_max, v_scale_mean;
+};
+
+// Per-layer FP8 scales with one-shot and running (exponential moving average)
+// calibration, crates/mlx-paged-attn/src/metal/kv_scale.rs:36-300.  The tensor
+// reductions (max |x|) are done by the caller (on the device); this class holds the
+// arithmetic and the state, the only checkpointable state of the paged cache
+// (get_all_scales / load_scales, paged_kv_cache.rs:297-309).
+class KvScaleManager {
+ public:
+  explicit KvScaleManager(uint32_t num_layers, float alpha = 0.1f);
+  uint32_t num_layers() const { return num_layers_; }
+  float alpha() const { return alpha_; }
+  void init_default_scales();
+  float k_scale(uint32_t layer) const;
+  float v_scale(uint32_t layer) const;
+  bool is_calibrated() const { return calibrated_; }
+  // scales from the observed maxima of one batch
+  std::pair<float, float> calibrate_layer(uint32_t layer, float k_max_abs, float v_max_abs);
+  // running maxima: m = alpha * observed + (1 - alpha) * m (first observation: m = observed)
+  std::pair<float, float> update_layer_ema(uint32_t layer, float k_max_abs, float v_max_abs);
+  void set_scales(uint32_t layer, float k, float v);
+  void get_all_scales(std::vector<float> *k, std::vector<float> *v) const;
+  void load_scales(const float *k, size_t nk, const float *v, size_t nv);
+  void reset();
+  KvScaleStats stats() const;
+
+ private:
+  std::map<uint32_t, float> k_scales_, v_scales_, k_running_max_, v_running_max_;
+  uint32_t num_layers_;
+  float alpha_;
+  bool calibrated_ = false;
+};
+
+// ---- attention_layer.rs (parameters; the dispatch lives next to the device code) ----------------
+struct AttentionLayerParams {
+  uint32_t layer_idx = 0, num_heads = 0, num_kv_heads = 0, head_size = 0;
+  float scale = 0.f;        // <= 0: 1 / sqrt(head_size)
+  uint32_t block_size = 16;
+  float softcap = 0.f;      // <= 0: 1.0 (off)
+  bool use_fp8 = false;
+  float k_scale = 0.f, v_scale = 0.f;  // <= 0: 1.0
+};
+class AttentionLayer {
+ public:
+  explicit AttentionLayer(const AttentionLayerParams &p);
+  static AttentionLayer from_cache_config(uint32_t layer_idx, uint32_t num_heads, const PagedAttentionConfig &cfg);
+  uint32_t layer_idx, num_heads, num_kv_heads, head_size, block_size;
+  float scale, softcap, k_scale, v_scale;
+  bool use_fp8;
+};
 
 }  // namespace pa_host

@@ -27,6 +27,11 @@ constexpr int kChunkElems = kHeadSize * kBlockSize;      // 2048
 constexpr unsigned kErrBlockRange = 1u;  // block-table entry >= num_blocks
 constexpr unsigned kErrSlotRange = 2u;   // slot >= num_blocks*block_size
 constexpr unsigned kErrTimeout = 4u;     // a bounded wait ran out
+constexpr unsigned kErrStepSlot = 8u;    // fused decode step: a slot is not its sequence's last position
+
+constexpr int kSyncWords = 1024;         // arrival counters of a cache handle (AttnParams::sync)
+constexpr int kSyncDone = 1023;          // index of the finished-CTA counter
+constexpr int kMaxSplitCtas = 1000;      // CTAs of one split-KV launch (each has a counter word)
 
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -180,7 +185,19 @@ struct AttnParams {
   float *ws;      // partial results, two slots per CTA (layout: splitkv_attention.cu)
   int ws_ctas;    // CTAs the workspace has slots for
   unsigned *err;  // error word
-  unsigned *err_mirror;  // null, or a host-visible word the merge kernel copies `err` to
+  unsigned *err_mirror;  // null, or a host-visible word the last CTA to finish copies `err` to
+  // Arrival counters of the cache handle, all zero between launches: word c counts the
+  // CTAs that have stored their partial of the split item whose first piece CTA c holds;
+  // word kSyncDone counts finished CTAs.  The last arriver does the work and clears the word.
+  unsigned *sync;
+  // Decode step in one launch (null = attention only): the new token of every sequence,
+  // [S, Hkv, 128] with these row strides in elements, is written to its pool slot
+  // (slot_mapping[s] must be position context_len - 1 of sequence s, or negative for
+  // "no write") by the warp that attends the sequence's last block.
+  const elem16 *k_new;
+  const elem16 *v_new;
+  const int64_t *slot_mapping;
+  int64_t k_new_stride, v_new_stride;
   int seq_base;   // first sequence this launch covers
   int min_cols;   // a sequence is taken by the split-KV launch iff min_cols <= q_len*G <= max_cols
   int max_cols;

@@ -15,8 +15,18 @@
 // its piece overlaps ("segments").  A segment that covers its whole item writes
 // the final bf16 rows; a segment that starts or ends inside an item writes an
 // unnormalised partial (running max, sum, accumulator) to one of the CTA's two
-// workspace slots, and a small merge kernel combines the partials of each split
-// item in a fixed order (deterministic results).
+// workspace slots and counts itself on the item's arrival counter; the CTA that
+// arrives last combines the item's partials, always in CTA order, so the result
+// does not depend on who was last (deterministic).  There is no second kernel:
+// this replaces the reduce pass paged_attention.metal:1149-1260 as the tail of
+// the attention launch itself.
+//
+// Decode step in one launch (p.k_new set; 16-bit pools of 16-token blocks): the warp
+// that attends the last block of a (sequence, kv head) also stores the step's new
+// token of that head, from the caller's [S, Hkv, 128] rows, into its pool slot and
+// into the copy of the block it has just staged in shared memory, so that the
+// KV write of crates/mlx-core/src/transformer/block.rs:223-232 needs no launch
+// of its own and attention sees the token it must see.
 //
 // Data movement.  Each warp owns a ring of NST stages of 8 KB.  Lane 0 issues two
 // 4 KB bulk async copies (TMA, untiled, this CTA only) per unit, completion
@@ -156,6 +166,57 @@ __device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap *m
       : "memory");
 }
 
+// Combines the partials of one split item, (sequence, kv head), whose pieces lie in
+// CTAs [c_first, c_last], and writes the item's final rows.  Called by all threads
+// of the CTA that arrived last; reads go to L2 (the other CTAs wrote these slots).
+// Thread layout: d = tid & 127 (head dimension), two columns at a time.
+template <int NT, bool F16>
+__device__ __forceinline__ void merge_item(const AttnParams &p, long long W, int num_ctas,
+                                           int c_first, int c_last, int q0, int h, int ncols,
+                                           int tid) {
+  // With fewer units than CTAs some CTAs between c_first and c_last own nothing.
+  auto cta_empty = [&](int c) {
+    return (long long)(c + 1) * W / num_ctas <= (long long)c * W / num_ctas;
+  };
+  const int d = tid & 127;
+  const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
+  for (int col = tid >> 7; col < ncols; col += kThreads / 128) {
+    const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
+    const int lane = gid * 4 + tig;
+    const int o_idx = (((mt * NT + nt) * 4 + upper * 2 + par) * 32) + lane;
+    const int m_idx = (32 * NT + nt * 2 + par) * 32 + lane;
+    const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
+    // partials in CTA order, four at a time so that their loads overlap
+    float mm = -INFINITY, acc = 0.f, lsum = 0.f;
+    for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+      float mj[4], oj[4], lj[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int c = c0 + k;
+        const bool use = c <= c_last && !cta_empty(c);
+        const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
+        mj[k] = use ? __ldcg(slot + m_idx) : -INFINITY;
+        oj[k] = use ? __ldcg(slot + o_idx) : 0.f;
+        lj[k] = use ? __ldcg(slot + l_idx) : 0.f;
+      }
+      const float m_new = fmaxf(fmaxf(fmaxf(mj[0], mj[1]), fmaxf(mj[2], mj[3])), mm);
+      const float keep = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
+      acc *= keep;
+      lsum *= keep;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const float w = mj[k] == -INFINITY ? 0.f : exp2f(mj[k] - m_new);
+        acc += oj[k] * w;
+        lsum += lj[k] * w;
+      }
+      mm = m_new;
+    }
+    const int qj = col / p.G, g = col - qj * p.G;
+    p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
+        to_elem<F16>(lsum > 0.f ? acc / lsum : 0.f);
+  }
+}
+
 constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool block
 
 template <int NT, bool F16, bool FP8, bool B8 = false>
@@ -174,14 +235,17 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kRingBytes + C::kMergeBytes +
                                                 ((C::kPreBytes + 15) / 16) * 16);
 
+  __shared__ int s_last;  // this CTA arrived last at a split item and combines it
+
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: matrix index, row within it
   const int S = p.S, Hkv = p.Hkv, G = p.G;
 
-  // The merge kernel may be scheduled now; it waits for this grid to finish.  Its CTAs
-  // then sit on every SM until this grid ends, holding registers, so the early trigger
-  // is skipped when another kernel is meant to use the SMs this grid leaves free.
+  // The next kernel of the stream may be scheduled now (it orders itself with its own
+  // griddepcontrol.wait).  Its CTAs then sit on the SMs until this grid ends, holding
+  // registers, so the early trigger is skipped when another kernel is meant to use
+  // the SMs this grid leaves free.
   if (p.early_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- per-launch prefix sum of block counts --------------------------------
   for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s);
@@ -210,7 +274,6 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   const long long lo = (long long)blockIdx.x * W / gridDim.x;
   const long long hi = (long long)(blockIdx.x + 1) * W / gridDim.x;
   const int n_local = (int)(hi - lo);
-  if (n_local <= 0) return;
   const int n_w = n_local > warp ? (n_local - warp + kWarps - 1) / kWarps : 0;
 
   // smallest s with Hkv*pre[s+1] > u
@@ -254,6 +317,18 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   // pool (and the workspace and output rows a previous call may still be reading or
   // writing) must not be touched before the predecessor has completed.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Sequences of this launch's width class with nothing to attend get zero rows
+  // (crates/mlx-sys/src/mlx.cpp:4084-4088).
+  for (int s2 = blockIdx.x; s2 < S; s2 += gridDim.x) {
+    if (pre[s2 + 1] != pre[s2]) continue;
+    const int seq = p.seq_base + s2;
+    const int ql = q_len_of(p, seq);
+    if (ql < 1 || ql * G > p.max_cols || ql * G < p.min_cols) continue;
+    const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
+    const int row_elems = p.Hq * kHeadSize;
+    for (int e = tid; e < ql * row_elems; e += kThreads)
+      p.out[(int64_t)(q0 + e / row_elems) * p.out_stride + e % row_elems] = (elem16)0;
+  }
   // FP8: one pass of the main loop is compiled per decoding variant; which one runs is
   // decided by a device word the cache write sets when it produces an exponent-15 byte.
   auto main_loop = [&](auto exact_tag) {
@@ -605,13 +680,58 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           }
         }
     };
-    // Waits for the next unit of this warp; false once a wait has run out.
-    auto wait_unit = [&](int j) {
+    // Decode step in one launch: this warp holds the sequence's last block in ring stage
+    // `st`; the step's new token of this kv head goes to its pool slot and into the staged
+    // copy, which was fetched before the token was in the pool.  Exactly one warp of the
+    // grid handles a given (sequence, kv head, last block), so nobody else reads that slot
+    // during this launch.
+    auto write_new_token = [&](int st) {
+      const int64_t slot = p.slot_mapping[seq];
+      if (slot < 0) return;  // "no write" (crates/.../reshape_and_cache.metal:59-63)
+      const int pos = kv_len - 1, off = pos & (kBlockSize - 1);
+      uint32_t id = (uint32_t)p.block_tables[(long long)seq * p.MB + (pos >> 4)];
+      if (id >= p.num_blocks || slot != (int64_t)id * kBlockSize + off) {
+        if (lane == 0) atomicOr(p.err, kErrStepSlot);
+        return;
+      }
+      const size_t chunk = (size_t)id * Hkv + h;
+      const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunk;
+      uint8_t *kg = const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(p.k_pool)) + chunk * kChunk;
+      uint8_t *vg = const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(p.v_pool)) + chunk * kChunk;
+      if (lane < 16) {  // K: sixteen 16-byte pieces, piece c to [c][off][0..7]
+        const uint4 kk = __ldg(reinterpret_cast<const uint4 *>(
+                                   p.k_new + (int64_t)seq * p.k_new_stride + h * kHeadSize) + lane);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ks + lane * 256 + off * 16),
+                     "r"(kk.x), "r"(kk.y), "r"(kk.z), "r"(kk.w) : "memory");
+        *reinterpret_cast<uint4 *>(kg + lane * 256 + off * 16) = kk;
+      }
+      // V: element d to [d][off]; a lane takes d = 4 lane .. 4 lane + 3
+      const uint2 vv = __ldg(reinterpret_cast<const uint2 *>(
+                                 p.v_new + (int64_t)seq * p.v_new_stride + h * kHeadSize) + lane);
+      const uint16_t e[4] = {(uint16_t)(vv.x & 0xffffu), (uint16_t)(vv.x >> 16),
+                             (uint16_t)(vv.y & 0xffffu), (uint16_t)(vv.y >> 16)};
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int d = 4 * lane + i;
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(vs + d * 32 + off * 2), "h"(e[i]) : "memory");
+        *reinterpret_cast<uint16_t *>(vg + d * 32 + off * 2) = e[i];
+      }
+      // the stage is refilled by a bulk copy later on: order these writes before it
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+    };
+    constexpr bool kCanFuseWrite = NT == 1 && !FP8 && !B8;
+    const bool fuse_write = kCanFuseWrite && p.k_new != nullptr;
+    // Waits for the next unit of this warp (block `blk` of the item); false once a wait
+    // has run out.
+    auto wait_unit = [&](int j, int blk) {
       const bool ok = mbar_wait_bounded(bar_w + (j % NST) * 8, (j / NST) & 1);
       if (!__all_sync(0xffffffffu, ok)) {
         dead = true;
         if (lane == 0) atomicOr(p.err, kErrTimeout);
       }
+      if constexpr (kCanFuseWrite)
+        if (fuse_write && !dead && blk == nb - 1) write_new_token(j % NST);
       return !dead;
     };
     // The warp's units of this segment, software-pipelined: the logits of unit i+1 are
@@ -622,7 +742,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     constexpr bool kPipelined = NST >= 3;
     if constexpr (!kPipelined) {
       for (int k = a + ((warp - a) & (kWarps - 1)); k < a + seglen; k += kWarps) {
-        if (!dead && wait_unit(jc)) {
+        if (!dead && wait_unit(jc, b0 + (k - a))) {
           float s_cur[NT][4];
           s_phase(jc % NST, s_cur);
           finish(jc % NST, b0 + (k - a), s_cur);
@@ -636,13 +756,13 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       const int k_end = a + seglen;
       float s_cur[NT][4];
       bool cur_ok = false;
-      if (k < k_end && !dead && wait_unit(jc)) {
+      if (k < k_end && !dead && wait_unit(jc, b0 + (k - a))) {
         s_phase(jc % NST, s_cur);
         cur_ok = true;
       }
       while (k < k_end) {
         const int kn = k + kWarps;
-        if (cur_ok && kn < k_end && wait_unit(jc + 1)) {
+        if (cur_ok && kn < k_end && wait_unit(jc + 1, b0 + (kn - a))) {
           float s_next[NT][4];
           s_phase((jc + 1) % NST, s_next);
           finish(jc % NST, b0 + (k - a), s_cur);
@@ -705,6 +825,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       __syncthreads();
     }
 
+    const bool partial = b0 > 0 || b1 < nb;
     if (warp == 0) {
 #pragma unroll
       for (int nt = 0; nt < NT; nt++)
@@ -716,7 +837,6 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           v += __shfl_xor_sync(0xffffffffu, v, 16);
           l[nt][c] = v;
         }
-      const bool partial = b0 > 0 || b1 < nb;
       if (partial) {
         float *dst = p.ws + (size_t)(2 * blockIdx.x + (b0 > 0 ? 0 : 1)) * kSlotFloats + lane;
 #pragma unroll
@@ -733,6 +853,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
             dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
             dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
           }
+        __threadfence();  // the partial is visible before this CTA counts itself below
       } else {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
@@ -755,6 +876,28 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       }
     }
 
+    // ---- a split item: count this piece; the last piece to arrive combines them ----
+    if (partial) {
+      const long long U0 = (long long)Hkv * pre[s] + (long long)h * nb, U1 = U0 + nb;
+      const int c_first = (int)(((U0 + 1) * gridDim.x - 1) / W);
+      const int c_last = (int)((U1 * gridDim.x - 1) / W);
+      // Pieces of the item: one per CTA of [c_first, c_last]; with fewer units than CTAs
+      // every unit sits in a CTA of its own and the CTAs in between own nothing.
+      const unsigned pieces = W >= (long long)gridDim.x ? (unsigned)(c_last - c_first + 1) : (unsigned)nb;
+      __syncthreads();
+      if (tid == 0) {
+        // c_first holds the item as its last one, so the word is this item's alone
+        const unsigned arrived = atomicAdd(p.sync + c_first, 1u) + 1u;
+        s_last = arrived == pieces;
+        if (arrived == pieces) atomicExch(p.sync + c_first, 0u);
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        merge_item<NT, F16>(p, W, (int)gridDim.x, c_first, c_last, q0, h, ncols, tid);
+      }
+    }
+
     // ---- next item ---------------------------------------------------------------
     a += seglen;
     b0 = 0;
@@ -765,111 +908,26 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     if (s < S) nb = pre[s + 1] - pre[s];
   }
   };
-  if constexpr (FP8) {
-    if (*p.fp8_special != 0u) main_loop(std::true_type{});
-    else main_loop(std::false_type{});
-  } else {
-    main_loop(std::false_type{});
-  }
-}
-
-// Merge of split items and zero-fill of empty ones.  grid (S, Hkv), block (128, 4):
-// x = head dimension, y = column (query token x head of the group), so every load of a
-// thread is independent of its other loads.  Recomputes the same flat partition as the
-// main kernel: CTA c owns units [c*W/N, (c+1)*W/N); the CTA holding unit u is
-// ((u+1)*N - 1) / W.  Launched as a programmatic dependent of the main kernel: the part
-// above griddepcontrol.wait only reads the call's inputs.
-constexpr int kMergeCols = 4;
-__global__ void __launch_bounds__(128 * kMergeCols)
-splitkv_merge_kernel(const AttnParams p, int num_ctas, int NT) {
-  __shared__ long long red[2][4 * kMergeCols];
-  // a following attention call may set up while this grid runs (it waits before it
-  // touches the workspace or the output)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int s = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-  const int tid = threadIdx.y * 128 + d, nthreads = 128 * kMergeCols;
-  const int seq = p.seq_base + s;
-  long long before = 0, total = 0;
-  for (int i = tid; i < p.S; i += nthreads) {
-    const int nbi = eligible_blocks(p, p.seq_base + i);
-    total += nbi;
-    if (i < s) before += nbi;
-  }
-#pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) {
-    before += __shfl_xor_sync(0xffffffffu, before, o);
-    total += __shfl_xor_sync(0xffffffffu, total, o);
-  }
-  if ((tid & 31) == 0) { red[0][tid >> 5] = before; red[1][tid >> 5] = total; }
-  __syncthreads();
-  before = 0; total = 0;
-#pragma unroll
-  for (int i = 0; i < 4 * kMergeCols; i++) { before += red[0][i]; total += red[1][i]; }
-
-  const int q_len = q_len_of(p, seq);
-  const bool ours = q_len >= 1 && q_len * p.G <= p.max_cols && q_len * p.G >= p.min_cols;
-  const int ncols = q_len * p.G;
-  const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
-  const int nb = ours ? eligible_blocks(p, seq) : 0;
-  const long long W = (long long)p.Hkv * total;
-  const long long U0 = (long long)p.Hkv * before + (long long)h * nb, U1 = U0 + nb;
-  const int c_first = nb ? (int)(((U0 + 1) * num_ctas - 1) / W) : 0;
-  const int c_last = nb ? (int)((U1 * num_ctas - 1) / W) : 0;
-  // everything below depends on what the main kernel wrote
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  // every kernel that can set an error bit in this call has finished by now
-  if (p.err_mirror && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
-    *p.err_mirror = *reinterpret_cast<volatile unsigned *>(p.err);
-  if (!ours) return;
-  if (nb == 0) {  // empty context: zero rows (crates/mlx-sys/src/mlx.cpp:4084-4088)
-    for (int col = threadIdx.y; col < ncols; col += kMergeCols) {
-      const int qj = col / p.G, g = col - qj * p.G;
-      p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
-          (elem16)0;
+  if (n_local > 0) {
+    if constexpr (FP8) {
+      if (*p.fp8_special != 0u) main_loop(std::true_type{});
+      else main_loop(std::false_type{});
+    } else {
+      main_loop(std::false_type{});
     }
-    return;
   }
-  if (c_first == c_last) return;  // written by the main kernel
-
-  // With fewer units than CTAs some CTAs between c_first and c_last own nothing.
-  auto cta_empty = [&](int c) {
-    return (long long)(c + 1) * W / num_ctas <= (long long)c * W / num_ctas;
-  };
-  const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
-  for (int col = threadIdx.y; col < ncols; col += kMergeCols) {
-    const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
-    const int lane = gid * 4 + tig;
-    const int o_idx = (((mt * NT + nt) * 4 + upper * 2 + par) * 32) + lane;
-    const int m_idx = (32 * NT + nt * 2 + par) * 32 + lane;
-    const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
-    // partials in CTA order, four at a time so that their loads overlap
-    float mm = -INFINITY, acc = 0.f, lsum = 0.f;
-    for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-      float mj[4], oj[4], lj[4];
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const int c = c0 + k;
-        const bool use = c <= c_last && !cta_empty(c);
-        const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
-        mj[k] = use ? slot[m_idx] : -INFINITY;
-        oj[k] = use ? slot[o_idx] : 0.f;
-        lj[k] = use ? slot[l_idx] : 0.f;
+  // The last CTA of the grid to get here leaves a copy of the error word where the host
+  // can read it without a copy of its own: every kernel of this stream that can set a
+  // bit in this call has finished by then.
+  if (p.err_mirror) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(p.sync + kSyncDone, 1u) + 1u == gridDim.x) {
+        atomicExch(p.sync + kSyncDone, 0u);
+        *p.err_mirror = *reinterpret_cast<volatile unsigned *>(p.err);
       }
-      const float m_new = fmaxf(fmaxf(fmaxf(mj[0], mj[1]), fmaxf(mj[2], mj[3])), mm);
-      const float keep = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
-      acc *= keep;
-      lsum *= keep;
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const float w = mj[k] == -INFINITY ? 0.f : exp2f(mj[k] - m_new);
-        acc += oj[k] * w;
-        lsum += lj[k] * w;
-      }
-      mm = m_new;
     }
-    const int qj = col / p.G, g = col - qj * p.G;
-    p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
-        to_elem_rt(lsum > 0.f ? acc / lsum : 0.f, p.is_f16 != 0);
   }
 }
 
@@ -1036,6 +1094,7 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
   // as the workspace has partial-result slots for them.
   int num_ctas = num_sms_used;
   if (p_in.is_fp8 && nt <= 1 && 2 * num_sms_used <= p_in.ws_ctas) num_ctas = 2 * num_sms_used;
+  if (num_ctas > kMaxSplitCtas || !p_in.sync) return cudaErrorInvalidValue;
   for (int base = 0; base < p_in.S; base += kMaxSeqsPerLaunch) {
     AttnParams p = p_in;
     p.seq_base = p_in.seq_base + base;
@@ -1044,10 +1103,6 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
     if (nt <= 1) e = launch_nt<1>(p, maps, num_ctas, st);
     else if (nt == 2) e = launch_nt<2>(p, maps, num_ctas, st);
     else e = launch_nt<3>(p, maps, num_ctas, st);
-    if (e != cudaSuccess) return e;
-    e = launch_dependent(splitkv_merge_kernel, dim3((unsigned)p.S, (unsigned)p.Hkv),
-                         dim3(128, kMergeCols), 0, st, p, num_ctas, nt <= 1 ? 1 : (nt == 2 ? 2 : 3));
-    __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

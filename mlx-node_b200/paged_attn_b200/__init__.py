@@ -38,7 +38,7 @@ EXPORTED_SYMBOLS = [
     "pa_paged_attention_decode_static", "pa_cpu_cache_create", "pa_cpu_cache_free",
     "pa_cpu_cache_is_swapped", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
     "pa_swap_in", "pa_swap_block_bytes",
-    "pa_decode_step_host", "pa_kernel_launch_count",
+    "pa_decode_step_host", "pa_kernel_launch_count", "pa_decode_step", "pa_varlen_step_host",
 ]
 
 
@@ -117,6 +117,9 @@ def load_library() -> C.CDLL:
     lib.pa_qk_norm_rope_and_cache.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, f32, vp, f32, u32, vp,
                                               i64, i32, i64, i64, i64, i64, vp]
     lib.pa_decode_step_host.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32]
+    lib.pa_varlen_step_host.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, f32]
+    lib.pa_decode_step.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64,
+                                   i64, f32, f32, vp, sz, vp]
     # tier 1
     lib.mlx_paged_attn_create_cache.argtypes = [C.POINTER(PagedAttnConfig)]
     lib.mlx_paged_attn_create_cache.restype = vp
@@ -279,6 +282,18 @@ class PagedCache:
             num_seqs, num_q_heads, max_blocks_per_seq, q_stride or row, out_stride or row, scale,
             softcap, _ptr(workspace), workspace_bytes, stream))
 
+    def decode_step(self, out, q, key, value, slot_mapping, block_tables, context_lens,
+                    num_seqs: int, num_q_heads: int, max_blocks_per_seq: int, scale: float,
+                    workspace, workspace_bytes: int, softcap: float = 1.0, layer: int = 0,
+                    stream: int = 0) -> None:
+        """KV write of the step's tokens + decode attention in one launch."""
+        row = num_q_heads * self.cfg.head_size
+        kv_row = self.cfg.num_kv_heads * self.cfg.head_size
+        _check(self.lib.pa_decode_step(
+            self.handle, layer, _ptr(out), _ptr(q), _ptr(key), _ptr(value), _ptr(slot_mapping),
+            _ptr(block_tables), _ptr(context_lens), num_seqs, num_q_heads, max_blocks_per_seq,
+            row, row, kv_row, kv_row, scale, softcap, _ptr(workspace), workspace_bytes, stream))
+
     def decode_static(self, out, q, block_tables, context_lens, num_seqs: int, num_q_heads: int,
                       max_blocks_per_seq: int, scale: float, softcap: float = 1.0,
                       q_stride: int | None = None, out_stride: int | None = None, layer: int = 0,
@@ -321,6 +336,16 @@ class PagedCache:
             self.handle, layer, _ptr(out_host), _ptr(q_host), _ptr(k_host), _ptr(v_host),
             _ptr(slots_host), _ptr(tables_host), _ptr(lens_host), num_seqs, num_q_heads,
             max_blocks_per_seq, scale, softcap))
+
+
+    def varlen_step_host(self, out_host, q_host, k_host, v_host, slots_host, tables_host,
+                         lens_host, cu_q_lens_host, num_seqs: int, num_q_heads: int,
+                         max_blocks_per_seq: int, scale: float, softcap: float = 1.0,
+                         layer: int = 0) -> None:
+        _check(self.lib.pa_varlen_step_host(
+            self.handle, layer, _ptr(out_host), _ptr(q_host), _ptr(k_host), _ptr(v_host),
+            _ptr(slots_host), _ptr(tables_host), _ptr(lens_host), _ptr(cu_q_lens_host), num_seqs,
+            num_q_heads, max_blocks_per_seq, scale, softcap))
 
 
 class CpuBlockCache:

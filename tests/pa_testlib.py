@@ -302,25 +302,4 @@ def check_attention(got_f32: np.ndarray, ref_f32: np.ndarray, what: str = "") ->
 
 
 # ---- the five benchmark configurations (lengths only; seeded) ---------------------------
-def config_lengths(name: str, seed: int = 0):
-    """(kv_lens, q_lens, Hq, Hkv, NB) of the named configuration.  kv_lens count the
-    tokens written this step."""
-    rng = np.random.Generator(np.random.PCG64(seed + 1000))
-    if name == "c1":   # Qwen3-0.6B-shaped decode
-        return rng.integers(512, 2049, 8), np.ones(8, int), 16, 8, 1024
-    if name == "c2":   # Qwen3-8B-shaped decode
-        return rng.integers(1024, 8193, 64), np.ones(64, int), 32, 8, 40000
-    if name == "c3":   # Qwen3-32B-shaped decode, lognormal lengths (median 4096, sigma 1)
-        z = rng.standard_normal(128)
-        kv = np.clip(np.rint(np.exp(math.log(4096.0) + z)), 256, 32768).astype(int)
-        return kv, np.ones(128, int), 64, 8, 65536
-    if name == "c4":   # chunked prefill: 8192 cached + 2048 new, causal
-        return np.full(8, 8192 + 2048), np.full(8, 2048), 32, 8, 8192
-    if name == "c5":   # mixed batch: 48 decode + 8 verify (5 queries) + 2 prefill chunks
-        dec = rng.integers(1024, 16385, 48)
-        ver = rng.integers(2048, 8193, 8) + 5
-        pre = np.full(2, 4096 + 1024)
-        kv = np.concatenate([dec, ver, pre])
-        ql = np.concatenate([np.ones(48, int), np.full(8, 5), np.full(2, 1024)])
-        return kv, ql, 32, 8, 60000
-    raise KeyError(name)
+from paged_attn_b200.workloads import config_lengths  # noqa: E402,F401  (tests use it from here)
