@@ -375,26 +375,83 @@ class Workload:
 
     # -- host-buffer leg -----------------------------------------------------------------
     def host_step_fn(self):
-        """(callable, h2d bytes, d2h bytes): one step through the host-buffer entry with
-        pinned host tensors; the call copies in, runs the kernels, copies out, synchronises."""
+        """(callable, h2d-bytes function, d2h bytes): one step from pinned HOST buffers; the
+        call brings the inputs in, runs the kernels, copies the result out, synchronises.
+
+        Decode workloads run a real decode loop through the bound host cache
+        (pa_kv_extend_sequences + pa_kv_decode_step_host): every step the sequences grow by
+        one token, the host cache hands out the slot (and now and then a new block), the
+        block tables stay resident on the device and only new entries travel.  Mixed
+        workloads go through pa_varlen_step_host with the step's tables sent whole."""
         torch = self.torch
         pin = lambda t: t.cpu().pin_memory()
         q_h, k_h, v_h = pin(self.q), pin(self.k_new), pin(self.v_new)
         out_h = torch.empty_like(self.q, device="cpu").pin_memory()
-        slots_h, tables_p, lens_h = pin(self.slots), pin(self.tables), pin(self.lens)
-        h2d = sum(t.numel() * t.element_size() for t in (q_h, k_h, v_h, slots_h, tables_p, lens_h))
+        d2h = int(out_h.numel() * 2)
         c = self.cache
+        self._keep_host = [q_h, k_h, v_h, out_h]
+        bound = self._bound_decode_cache() if self.decode_only else None
+        if bound is not None:
+            host, b, ids = bound
+            sent0 = [b.stats()["table_entries_sent"], 0]
+
+            def fn():
+                host.extend_sequences(ids, 1)
+                b.decode_step_host(out_h, q_h, k_h, v_h, ids, self.hq_l, self.scale)
+                sent0[1] += 1
+
+            def h2d():
+                per_step = (b.stats()["table_entries_sent"] - sent0[0]) / max(sent0[1], 1)
+                return int(q_h.numel() * 2 + k_h.numel() * 2 + v_h.numel() * 2 + 256 + 16 * self.S + 12 * per_step)
+            return fn, h2d, d2h, ("pa_kv_extend_sequences + pa_kv_decode_step_host: decode loop through the "
+                                  "bound host cache, block tables resident on the device")
+        slots_h, tables_p, lens_h = pin(self.slots), pin(self.tables), pin(self.lens)
+        self._keep_host += [slots_h, tables_p, lens_h]
+        n_h2d = sum(t.numel() * t.element_size() for t in (q_h, k_h, v_h, slots_h, tables_p, lens_h))
         if self.decode_only:
             def fn():
                 c.decode_step_host(out_h, q_h, k_h, v_h, slots_h, tables_p, lens_h, self.S, self.hq_l,
                                    self.MB, self.scale)
-        else:
-            h2d += self.cu_q.nbytes
-            def fn():
-                c.varlen_step_host(out_h, q_h, k_h, v_h, slots_h, tables_p, lens_h, self.cu_q, self.S,
-                                   self.hq_l, self.MB, self.scale)
-        self._keep_host = (q_h, k_h, v_h, out_h, slots_h, tables_p, lens_h)
-        return fn, int(h2d), int(out_h.numel() * 2)
+            return fn, (lambda: int(n_h2d)), d2h, "pa_decode_step_host"
+        n_h2d += self.cu_q.nbytes
+
+        def fn():
+            c.varlen_step_host(out_h, q_h, k_h, v_h, slots_h, tables_p, lens_h, self.cu_q, self.S,
+                               self.hq_l, self.MB, self.scale)
+        return fn, (lambda: int(n_h2d)), d2h, "pa_varlen_step_host"
+
+    def _bound_decode_cache(self):
+        """Host cache over this rank's pool with every sequence one token short of the
+        workload's context, the pool refilled at the host allocator's slots."""
+        torch = self.torch
+        from paged_attn_b200.host import BoundCache, PagedKVCacheHost, host_config, seq_id_array
+        block_bytes = 2 * self.hkv_l * D * self.bs * self.eb
+        mb = (self.NB * block_bytes) >> 20
+        if mb < 256:
+            return None  # PagedAttentionConfig::validate wants at least 256 MB
+        max_seq = ((int(self.kv.max()) + 1024 + self.bs - 1) // self.bs) * self.bs
+        cfg = host_config(block_size=self.bs, gpu_memory_mb=mb, head_size=D, num_kv_heads=self.hkv_l,
+                          num_layers=1, use_fp8_cache=int(self.args.fp8), max_seq_len=max_seq)
+        host = PagedKVCacheHost(cfg)
+        assert host.total_blocks() <= self.NB
+        ids = [host.add_sequence(int(n) - 1) for n in self.kv]
+        slots = np.concatenate([np.asarray(host.get_slot_mapping(sid, 0, int(n) - 1), dtype=np.int64)
+                                for sid, n in zip(ids, self.kv)])
+        slots_d = torch.from_numpy(slots).to(self.dev)
+        gen = torch.Generator(device=self.dev)
+        gen.manual_seed(99 + self.rank)
+        step = 1 << 17
+        for i in range(0, len(slots), step):  # refill in pieces to bound the temporaries
+            n = min(step, len(slots) - i)
+            k = torch.randn(n, self.hkv_l, D, generator=gen, device=self.dev).to(torch.bfloat16)
+            v = torch.randn(n, self.hkv_l, D, generator=gen, device=self.dev).to(torch.bfloat16)
+            self.cache.reshape_and_cache(k, v, slots_d[i:i + n], n, self.hkv_l * D, self.hkv_l * D)
+        torch.cuda.synchronize()
+        b = BoundCache(host, self.cache)
+        if self.args.fp8:
+            b.set_layer_scales(0, 1.0 / 32, 1.0 / 32)
+        self._keep_bound = (host, b)
+        return host, b, seq_id_array(ids)
 
     # -- algorithmic work of this rank ---------------------------------------------------
     def attn_bytes(self):
@@ -454,24 +511,38 @@ def time_workload(w, steps, warmup, dist, sample_clocks, e2e=True, extra_step=No
     res = {"ms_per_step": total_ms / steps, "attn_ms": attn_ms, "launches": int(launches),
            "launches_per_step": launches / steps, "clocks": clocks, "soak_steps": soak}
     if e2e:
-        fn, h2d, d2h = w.host_step_fn()
-        for _ in range(3):
-            fn()
-        barrier()
-        n_e2e = max(10, min(steps, 100))
-        t0 = time.perf_counter()
-        for _ in range(n_e2e):
-            fn()
-        barrier()
-        dt = torch.tensor([(time.perf_counter() - t0) / n_e2e], device=w.dev)
-        if dist is not None:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        res["e2e"] = {"value": w.total_q / float(dt.item()), "unit": "tokens/s",
-                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                      "ms_per_step": float(dt.item()) * 1e3, "steps": n_e2e,
-                      "timed": "host wall clock around synchronous calls with pinned host buffers, "
-                               "max over ranks"}
+        res["e2e"] = e2e_leg(w, steps, dist)
     return res
+
+
+def e2e_leg(w, steps, dist):
+    """The step from pinned host buffers through the host-buffer entry, host wall clock
+    around synchronous calls, max over ranks.  Refills the pools (decode workloads), so it
+    runs after everything that checks the device legs' results."""
+    torch = w.torch
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    fn, h2d, d2h, entry = w.host_step_fn()
+    for _ in range(3):
+        fn()
+    barrier()
+    n_e2e = max(10, min(steps, 100))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        fn()
+    barrier()
+    dt = torch.tensor([(time.perf_counter() - t0) / n_e2e], device=w.dev)
+    if dist is not None:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    w.cache.check_errors(w.stream)
+    return {"value": w.total_q / float(dt.item()), "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d(), "d2h_bytes_per_step": d2h,
+            "ms_per_step": float(dt.item()) * 1e3, "steps": n_e2e, "entry": entry,
+            "timed": "host wall clock around synchronous calls with pinned host buffers, max over ranks"}
 
 
 def roofline_of(w, res, peaks, traffic_note=None):
@@ -583,14 +654,16 @@ def main() -> None:
             peer["checked"] = bool(flag.item())
             dist.barrier()
 
-    res = time_workload(w, args.steps, args.warmup, dist, sample_clocks=(rank == 0),
-                        e2e=not args.no_e2e, extra_step=step_fn)
+    res = time_workload(w, args.steps, args.warmup, dist, sample_clocks=(rank == 0), e2e=False,
+                        extra_step=step_fn)
     roof = roofline_of(w, res, peaks)
 
     cpu_base = None
     if (rank == 0 and world == 1 and not args.as_rank_of and w.decode_only and not args.no_cpu_baseline
             and not args.fp8 and not args.seqs):
         cpu_base = cpu_baseline_and_spot_check(w)
+    if not args.no_e2e:
+        res["e2e"] = e2e_leg(w, args.steps, dist)
 
     also = None
     if world == 1 and not args.no_also and not args.as_rank_of and args.workload == "c3" and not args.seqs:

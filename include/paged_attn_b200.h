@@ -182,6 +182,11 @@ pa_status pa_cache_fp8_set_exact_decode(PagedAttnCache *cache, int32_t on);
  * of this cache write instead of trapping (out-of-range block id or slot,
  * a bounded wait that ran out).                                               */
 pa_status pa_cache_check_errors(PagedAttnCache *cache, void *cuda_stream);
+/* The same without a device round trip when nothing is wrong: the attention kernels
+ * leave a copy of the error word in host-visible memory as their last act, and this
+ * call reads that copy.  Valid once the stream the attention call ran on has been
+ * synchronised; falls through to pa_cache_check_errors when the copy is non-zero.   */
+pa_status pa_cache_check_errors_fast(PagedAttnCache *cache, void *cuda_stream);
 
 /* KV block write.  dispatch_reshape_and_cache_raw
  * (crates/mlx-paged-attn/src/metal/reshape_and_cache.rs:177-270) over the
@@ -245,11 +250,19 @@ pa_status pa_copy_blocks(PagedAttnCache *cache, uint32_t layer_idx,
 typedef struct PaCpuBlockCache PaCpuBlockCache;
 PaCpuBlockCache *pa_cpu_cache_create(const PagedAttnCache *cache);
 void pa_cpu_cache_free(PaCpuBlockCache *cpu);
+/* One host cache serves every layer of the device cache: copies are kept per (layer,
+ * block id), so swapping the same block ids out of several layers keeps every layer's
+ * bytes apart (the reference's CpuBlockCache is keyed by block id alone and would
+ * skip the second layer as "already swapped").
+ * is_swapped: some layer of the block has a host copy; num_swapped: such block ids.    */
 int32_t pa_cpu_cache_is_swapped(const PaCpuBlockCache *cpu, uint32_t block_id);
+int32_t pa_cpu_cache_is_swapped_layer(const PaCpuBlockCache *cpu, uint32_t layer_idx,
+                                      uint32_t block_id);
 size_t pa_cpu_cache_num_swapped(const PaCpuBlockCache *cpu);
-/* Host addresses of a swapped block's K and V bytes (borrowed), or PA_ERR_INVALID_ARG. */
-pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t block_id, void **key,
-                                  void **value);
+/* Host addresses of a swapped block's K and V bytes of one layer (borrowed), or
+ * PA_ERR_INVALID_ARG.                                                                  */
+pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t layer_idx,
+                                  uint32_t block_id, void **key, void **value);
 pa_status pa_swap_out(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *block_ids,
                       size_t num_blocks, PaCpuBlockCache *cpu, void *cuda_stream);
 pa_status pa_swap_in(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *block_ids,
@@ -340,6 +353,30 @@ pa_status pa_decode_step(PagedAttnCache *cache, uint32_t layer_idx, void *out, c
                          int64_t q_stride, int64_t out_stride, int64_t key_stride,
                          int64_t value_stride, float scale, float softcap, void *workspace,
                          size_t workspace_bytes, void *cuda_stream);
+
+/* pa_paged_attention_decode / pa_decode_step over a RESIDENT block table: block_tables
+ * is [rows, max_blocks_per_seq] with one row per live sequence, kept on the device
+ * across steps, and seq_rows int32 [num_seqs] (device) names the row of each sequence
+ * of this batch.  The reference has no such form: it rebuilds and re-sends the batch's
+ * table on every call (crates/mlx-paged-attn/src/paged_kv_cache.rs:1081-1125,
+ * crates/mlx-core/src/models/qwen3/model.rs:879-891).  Used by the bound-cache calls of
+ * paged_attn_b200_host.h.                                                         */
+pa_status pa_paged_attention_decode_rows(PagedAttnCache *cache, uint32_t layer_idx, void *out,
+                                         const void *q, const int32_t *block_tables,
+                                         const int32_t *seq_rows, const int32_t *context_lens,
+                                         int32_t num_seqs, int32_t num_q_heads,
+                                         int32_t max_blocks_per_seq, int64_t q_stride,
+                                         int64_t out_stride, float scale, float softcap,
+                                         void *workspace, size_t workspace_bytes,
+                                         void *cuda_stream);
+pa_status pa_decode_step_rows(PagedAttnCache *cache, uint32_t layer_idx, void *out, const void *q,
+                              const void *key, const void *value, const int64_t *slot_mapping,
+                              const int32_t *block_tables, const int32_t *seq_rows,
+                              const int32_t *context_lens, int32_t num_seqs, int32_t num_q_heads,
+                              int32_t max_blocks_per_seq, int64_t q_stride, int64_t out_stride,
+                              int64_t key_stride, int64_t value_stride, float scale,
+                              float softcap, void *workspace, size_t workspace_bytes,
+                              void *cuda_stream);
 
 /* Decode attention for callers that cannot allocate device memory.
  * No counterpart in the reference.  Some hosts of this library are handed

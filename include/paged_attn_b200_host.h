@@ -117,6 +117,9 @@ void pa_kv_destroy(PaKvHost *kv);
 pa_status pa_kv_add_sequence(PaKvHost *kv, uint32_t prompt_len, uint32_t *seq_id);   /* :97-125 */
 pa_status pa_kv_remove_sequence(PaKvHost *kv, uint32_t seq_id);                      /* :127-151 */
 pa_status pa_kv_extend_sequence(PaKvHost *kv, uint32_t seq_id, uint32_t num_new);    /* :458-479 */
+/* extend_sequence for every sequence of a batch, what process_outputs does once per
+ * sampled token (scheduler.rs:354-358), in one call.  Stops at the first failure.       */
+pa_status pa_kv_extend_sequences(PaKvHost *kv, const uint32_t *seq_ids, size_t n, uint32_t num_tokens);
 pa_status pa_kv_fork_sequence(PaKvHost *kv, uint32_t parent, uint32_t *child);       /* :1437-1465 */
 /* handle_cow (:1476-1523): *copied = 0 when the block is not shared; otherwise the
  * caller issues pa_copy_blocks for the (src, dst) pair on every layer.                */
@@ -143,10 +146,13 @@ pa_status pa_kv_get_slot_mapping_batch(const PaKvHost *kv, const uint32_t *seq_i
                                        const uint32_t *input_lens, size_t n, int64_t *out, size_t cap,
                                        size_t *count);
 /* build_input_metadata (:646-704): the three arrays the kernels take, in their device
- * types (int32 tables [n, max_blocks_per_seq], int32 lens [n], int64 slots).          */
+ * types (int32 tables [n, max_blocks_per_seq], int32 lens [n], int64 slots).  The
+ * capacities are in elements; a buffer that is too small is an error, never an
+ * overflow (the table needs n * pa_kv_max_blocks_per_seq(kv) entries).                */
 pa_status pa_kv_build_input_metadata(const PaKvHost *kv, const uint32_t *seq_ids,
                                      const uint32_t *input_lens, const uint8_t *is_prefill, size_t n,
-                                     int32_t *block_tables_out, int32_t *context_lens_out,
+                                     int32_t *block_tables_out, size_t tables_cap,
+                                     int32_t *context_lens_out, size_t lens_cap,
                                      int64_t *slots_out, size_t slots_cap, size_t *num_slots,
                                      uint32_t *max_context_len, int32_t *batch_is_prefill);
 typedef struct PaMemoryStats {
@@ -237,10 +243,13 @@ uint32_t pa_hybrid_batch_tokens(const PaHybridScheduler *s, uint32_t i, uint32_t
 const char *pa_hybrid_batch_request_id(const PaHybridScheduler *s, uint32_t i);
 /* kernel arguments of the current batch: int32 tables [n, max_blocks_per_seq] zero
  * padded, int32 context lens [n] (counting this step's tokens), int32 cu_q_lens [n+1],
- * int64 slots [total_tokens]                                                          */
+ * int64 slots [total_tokens].  Capacities in elements: tables_cap for block_tables,
+ * seqs_cap = sequences context_lens has room for (cu_q_lens then has seqs_cap + 1),
+ * slots_cap for slots; too small is an error, never an overflow.                      */
 pa_status pa_hybrid_batch_metadata(const PaHybridScheduler *s, const PaKvHost *kv, int32_t *block_tables,
-                                   int32_t *context_lens, int32_t *cu_q_lens, int64_t *slots,
-                                   size_t slots_cap, uint32_t *max_context_len);
+                                   size_t tables_cap, int32_t *context_lens, int32_t *cu_q_lens,
+                                   size_t seqs_cap, int64_t *slots, size_t slots_cap,
+                                   uint32_t *max_context_len);
 /* one record per entry with needs_sample: accepted draft tokens and the token sampled
  * after them                                                                          */
 pa_status pa_hybrid_process_outputs(PaHybridScheduler *s, PaKvHost *kv, const uint32_t *seq_ids,
@@ -315,7 +324,7 @@ void pa_kv_binding_stats(const PaKvBinding *b, uint64_t *table_entries_sent, uin
                          uint32_t *rows_in_use);
 
 /* ---- KvScaleManager, metal/kv_scale.rs:36-300 -------------------------------------------
- * alpha < 0 picks the default 0.1; otherwise it is clamped to [0, 1] (with_alpha).       */
+ * alpha is clamped to [0, 1] (with_alpha); KvScaleManager::new uses 0.1.                 */
 typedef struct PaKvScaleManager PaKvScaleManager;
 typedef struct PaKvScaleStats {
   uint32_t num_layers_calibrated;

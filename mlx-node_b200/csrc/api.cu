@@ -588,7 +588,11 @@ struct PaCpuBlockCache {
   static constexpr int kMaxPerLaunch = 4096;
   std::vector<char *> slabs;
   std::vector<char *> free_slots;                    // each slot = K bytes then V bytes
-  std::unordered_map<uint32_t, char *> swapped;      // block id -> slot
+  // (layer, block id) -> slot: one host cache serves every layer of a model, a block id
+  // being the same block in each layer's pool
+  std::unordered_map<uint64_t, char *> swapped;
+  std::unordered_map<uint32_t, uint32_t> layers_of;  // block id -> layers that hold a host copy
+  static uint64_t key(uint32_t layer, uint32_t id) { return ((uint64_t)layer << 32) | id; }
   char *args = nullptr;                              // pinned: ids | host_k ptrs | host_v ptrs
 };
 
@@ -630,12 +634,16 @@ void pa_cpu_cache_free(PaCpuBlockCache *cpu) {
   delete cpu;
 }
 int32_t pa_cpu_cache_is_swapped(const PaCpuBlockCache *cpu, uint32_t id) {
-  return cpu && cpu->swapped.count(id) != 0;
+  return cpu && cpu->layers_of.count(id) != 0;
 }
-size_t pa_cpu_cache_num_swapped(const PaCpuBlockCache *cpu) { return cpu ? cpu->swapped.size() : 0; }
-pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t id, void **key, void **value) {
+int32_t pa_cpu_cache_is_swapped_layer(const PaCpuBlockCache *cpu, uint32_t layer, uint32_t id) {
+  return cpu && cpu->swapped.count(PaCpuBlockCache::key(layer, id)) != 0;
+}
+size_t pa_cpu_cache_num_swapped(const PaCpuBlockCache *cpu) { return cpu ? cpu->layers_of.size() : 0; }
+pa_status pa_cpu_cache_block_ptrs(const PaCpuBlockCache *cpu, uint32_t layer, uint32_t id, void **key,
+                                  void **value) {
   if (!cpu || !key || !value) return fail(PA_ERR_INVALID_ARG, "null argument");
-  auto it = cpu->swapped.find(id);
+  auto it = cpu->swapped.find(PaCpuBlockCache::key(layer, id));
   if (it == cpu->swapped.end())
     return fail(PA_ERR_INVALID_ARG, "Block " + std::to_string(id) + " not found in CPU cache");
   *key = it->second;
@@ -670,7 +678,7 @@ static pa_status swap_impl(PagedAttnCache *c, uint32_t layer, const uint32_t *id
   char **a_v = a_k + kMax;
   if (!to_host)  // every block must have a host copy before anything moves
     for (size_t i = 0; i < n; i++)
-      if (!cpu->swapped.count(ids[i]))
+      if (!cpu->swapped.count(PaCpuBlockCache::key(layer, ids[i])))
         return fail(PA_ERR_INVALID_ARG, "Block " + std::to_string(ids[i]) + " not found in CPU cache");
   for (size_t base = 0; base < n; base += kMax) {
     int m = 0;
@@ -679,12 +687,13 @@ static pa_status swap_impl(PagedAttnCache *c, uint32_t layer, const uint32_t *id
       if (id >= c->cfg.num_blocks) return fail(PA_ERR_OUT_OF_RANGE, "block id beyond num_blocks");
       char *slot = nullptr;
       if (to_host) {
-        if (cpu->swapped.count(id)) continue;  // already swapped out
+        if (cpu->swapped.count(PaCpuBlockCache::key(layer, id))) continue;  // already swapped out
         st = cpu_slot(cpu, &slot);
         if (st != PA_OK) return st;
-        cpu->swapped[id] = slot;
+        cpu->swapped[PaCpuBlockCache::key(layer, id)] = slot;
+        cpu->layers_of[id]++;
       } else {
-        slot = cpu->swapped[id];
+        slot = cpu->swapped[PaCpuBlockCache::key(layer, id)];
       }
       a_ids[m] = id;
       a_k[m] = slot;
@@ -699,10 +708,12 @@ static pa_status swap_impl(PagedAttnCache *c, uint32_t layer, const uint32_t *id
   }
   if (!to_host)
     for (size_t i = 0; i < n; i++) {
-      auto it = cpu->swapped.find(ids[i]);
+      auto it = cpu->swapped.find(PaCpuBlockCache::key(layer, ids[i]));
       if (it != cpu->swapped.end()) {
         cpu->free_slots.push_back(it->second);
         cpu->swapped.erase(it);
+        auto l = cpu->layers_of.find(ids[i]);
+        if (l != cpu->layers_of.end() && --l->second == 0) cpu->layers_of.erase(l);
       }
     }
   return PA_OK;
@@ -744,7 +755,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
                          int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
                          int64_t q_stride, int64_t out_stride, float scale, float softcap,
                          void *workspace, size_t workspace_bytes, void *cuda_stream,
-                         const StepWrite *write) {
+                         const StepWrite *write, const int32_t *seq_rows = nullptr) {
   pa_status st = check_layer(c, layer);
   if (st != PA_OK) return st;
   if (num_seqs < 0) return fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
@@ -804,6 +815,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   if (!cu_q_lens_host) {  // decode: one query per sequence
     p.min_cols = 1;
     p.max_cols = G;
+    p.seq_row = seq_rows;
     if (write) {
       p.k_new = static_cast<const pa::elem16 *>(write->k);
       p.v_new = static_cast<const pa::elem16 *>(write->v);
@@ -982,13 +994,13 @@ pa_status pa_paged_attention_varlen(PagedAttnCache *c, uint32_t layer, void *out
                         out_stride, scale, softcap, workspace, workspace_bytes, cuda_stream, nullptr);
 }
 
-pa_status pa_decode_step(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
-                         const void *key, const void *value, const int64_t *slot_mapping,
-                         const int32_t *block_tables, const int32_t *context_lens,
-                         int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
-                         int64_t q_stride, int64_t out_stride, int64_t key_stride,
-                         int64_t value_stride, float scale, float softcap, void *workspace,
-                         size_t workspace_bytes, void *cuda_stream) {
+static pa_status decode_step_impl(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                                  const void *key, const void *value, const int64_t *slot_mapping,
+                                  const int32_t *block_tables, const int32_t *seq_rows,
+                                  const int32_t *context_lens, int32_t num_seqs, int32_t num_q_heads,
+                                  int32_t max_blocks_per_seq, int64_t q_stride, int64_t out_stride,
+                                  int64_t key_stride, int64_t value_stride, float scale, float softcap,
+                                  void *workspace, size_t workspace_bytes, void *cuda_stream) {
   pa_status st = check_layer(c, layer);
   if (st != PA_OK) return st;
   if (num_seqs < 0) return fail(PA_ERR_INVALID_ARG, "num_seqs < 0");
@@ -1006,12 +1018,55 @@ pa_status pa_decode_step(PagedAttnCache *c, uint32_t layer, void *out, const voi
     if (st != PA_OK) return st;
     return attention_impl(c, layer, out, q, block_tables, context_lens, nullptr, nullptr, num_seqs,
                           num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale, softcap,
-                          workspace, workspace_bytes, cuda_stream, nullptr);
+                          workspace, workspace_bytes, cuda_stream, nullptr, seq_rows);
   }
   const StepWrite w{key, value, slot_mapping, key_stride, value_stride};
   return attention_impl(c, layer, out, q, block_tables, context_lens, nullptr, nullptr, num_seqs,
                         num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale, softcap,
-                        workspace, workspace_bytes, cuda_stream, &w);
+                        workspace, workspace_bytes, cuda_stream, &w, seq_rows);
+}
+
+pa_status pa_decode_step(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                         const void *key, const void *value, const int64_t *slot_mapping,
+                         const int32_t *block_tables, const int32_t *context_lens,
+                         int32_t num_seqs, int32_t num_q_heads, int32_t max_blocks_per_seq,
+                         int64_t q_stride, int64_t out_stride, int64_t key_stride,
+                         int64_t value_stride, float scale, float softcap, void *workspace,
+                         size_t workspace_bytes, void *cuda_stream) {
+  return decode_step_impl(c, layer, out, q, key, value, slot_mapping, block_tables, nullptr, context_lens,
+                          num_seqs, num_q_heads, max_blocks_per_seq, q_stride, out_stride, key_stride,
+                          value_stride, scale, softcap, workspace, workspace_bytes, cuda_stream);
+}
+
+pa_status pa_paged_attention_decode_rows(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                                         const int32_t *block_tables, const int32_t *seq_rows,
+                                         const int32_t *context_lens, int32_t num_seqs,
+                                         int32_t num_q_heads, int32_t max_blocks_per_seq,
+                                         int64_t q_stride, int64_t out_stride, float scale,
+                                         float softcap, void *workspace, size_t workspace_bytes,
+                                         void *cuda_stream) {
+  if (num_seqs > 0 && !seq_rows) return fail(PA_ERR_INVALID_ARG, "seq_rows is null");
+  return attention_impl(c, layer, out, q, block_tables, context_lens, nullptr, nullptr, num_seqs,
+                        num_q_heads, max_blocks_per_seq, q_stride, out_stride, scale, softcap, workspace,
+                        workspace_bytes, cuda_stream, nullptr, seq_rows);
+}
+
+pa_status pa_decode_step_rows(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
+                              const void *key, const void *value, const int64_t *slot_mapping,
+                              const int32_t *block_tables, const int32_t *seq_rows,
+                              const int32_t *context_lens, int32_t num_seqs, int32_t num_q_heads,
+                              int32_t max_blocks_per_seq, int64_t q_stride, int64_t out_stride,
+                              int64_t key_stride, int64_t value_stride, float scale, float softcap,
+                              void *workspace, size_t workspace_bytes, void *cuda_stream) {
+  return decode_step_impl(c, layer, out, q, key, value, slot_mapping, block_tables, seq_rows, context_lens,
+                          num_seqs, num_q_heads, max_blocks_per_seq, q_stride, out_stride, key_stride,
+                          value_stride, scale, softcap, workspace, workspace_bytes, cuda_stream);
+}
+
+pa_status pa_cache_check_errors_fast(PagedAttnCache *c, void *cuda_stream) {
+  if (!c) return fail(PA_ERR_INVALID_ARG, "cache is null");
+  if (*reinterpret_cast<volatile unsigned *>(c->err_host) == 0) return PA_OK;
+  return pa_cache_check_errors(c, cuda_stream);
 }
 
 pa_status pa_paged_attention_decode(PagedAttnCache *c, uint32_t layer, void *out, const void *q,

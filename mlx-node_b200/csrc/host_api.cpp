@@ -14,7 +14,6 @@ using namespace pa_host;
 
 struct PaAllocator { BlockAllocator a; PaAllocator(uint32_t n, uint32_t bs) : a(n, bs) {} };
 struct PaTracker { TokenTracker t; explicit PaTracker(TokenTracker tt) : t(std::move(tt)) {} };
-struct PaKvHost { std::unique_ptr<PagedKVCache> kv; };
 struct PaScheduler {
   ContinuousBatchingScheduler s;
   ScheduledBatch batch;
@@ -224,6 +223,13 @@ pa_status pa_kv_add_sequence(PaKvHost *kv, uint32_t prompt_len, uint32_t *seq_id
 }
 pa_status pa_kv_remove_sequence(PaKvHost *kv, uint32_t seq_id) { KV_CALL(kv->kv->remove_sequence(seq_id, &e)); }
 pa_status pa_kv_extend_sequence(PaKvHost *kv, uint32_t seq_id, uint32_t n) { KV_CALL(kv->kv->extend_sequence(seq_id, n, &e)); }
+pa_status pa_kv_extend_sequences(PaKvHost *kv, const uint32_t *seq_ids, size_t n, uint32_t num_tokens) {
+  if (!kv || (!seq_ids && n)) return err("null argument");
+  std::string e;
+  for (size_t i = 0; i < n; i++)
+    if (!kv->kv->extend_sequence(seq_ids[i], num_tokens, &e)) return err(e);
+  return PA_OK;
+}
 pa_status pa_kv_fork_sequence(PaKvHost *kv, uint32_t parent, uint32_t *child) {
   if (!child) return err("child is null");
   KV_CALL(kv->kv->fork_sequence(parent, child, &e));
@@ -280,13 +286,17 @@ pa_status pa_kv_get_slot_mapping_batch(const PaKvHost *kv, const uint32_t *seq_i
   return PA_OK;
 }
 pa_status pa_kv_build_input_metadata(const PaKvHost *kv, const uint32_t *seq_ids, const uint32_t *input_lens,
-                                     const uint8_t *is_prefill, size_t n, int32_t *tables, int32_t *lens,
-                                     int64_t *slots, size_t slots_cap, size_t *num_slots, uint32_t *max_ctx,
-                                     int32_t *batch_is_prefill) {
+                                     const uint8_t *is_prefill, size_t n, int32_t *tables, size_t tables_cap,
+                                     int32_t *lens, size_t lens_cap, int64_t *slots, size_t slots_cap,
+                                     size_t *num_slots, uint32_t *max_ctx, int32_t *batch_is_prefill) {
   if (!kv || !seq_ids || !tables || !lens || !slots || !num_slots) return err("null argument");
   std::string e;
   InputMetadata m;
   if (!kv->kv->build_input_metadata(seq_ids, input_lens, is_prefill, n, &m, &e)) return err(e);
+  if (m.block_tables.size() > tables_cap)
+    return err("block table buffer too small: need " + std::to_string(m.block_tables.size()) + " entries (" +
+               std::to_string(n) + " x max_blocks_per_seq " + std::to_string(m.max_blocks_per_seq) + ")");
+  if (m.context_lens.size() > lens_cap) return err("context length buffer too small");
   if (m.slot_mappings.size() > slots_cap) return err("slot buffer too small");
   copy_out(m.block_tables, tables, m.block_tables.size());
   copy_out(m.context_lens, lens, m.context_lens.size());
@@ -489,13 +499,16 @@ const char *pa_hybrid_batch_request_id(const PaHybridScheduler *s, uint32_t i) {
   return (s && i < s->batch.entries.size()) ? s->batch.entries[i].request_id.c_str() : "";
 }
 pa_status pa_hybrid_batch_metadata(const PaHybridScheduler *s, const PaKvHost *kv, int32_t *tables,
-                                   int32_t *lens, int32_t *cu_q, int64_t *slots, size_t slots_cap,
-                                   uint32_t *max_ctx) {
+                                   size_t tables_cap, int32_t *lens, int32_t *cu_q, size_t seqs_cap,
+                                   int64_t *slots, size_t slots_cap, uint32_t *max_ctx) {
   if (!s || !kv || !tables || !lens || !cu_q || !slots) return err("null argument");
   InputMetadata m;
   std::vector<int32_t> cu;
   std::string e;
   if (!s->s.build_metadata(*kv->kv, s->batch, &m, &cu, &e)) return err(e);
+  if (m.block_tables.size() > tables_cap)
+    return err("block table buffer too small: need " + std::to_string(m.block_tables.size()) + " entries");
+  if (m.context_lens.size() > seqs_cap) return err("context length / cu_q_lens buffers too small");
   if (m.slot_mappings.size() > slots_cap) return err("slot buffer too small");
   copy_out(m.block_tables, tables, m.block_tables.size());
   copy_out(m.context_lens, lens, m.context_lens.size());

@@ -2,6 +2,8 @@
 #include "host_logic.hpp"
 
 #include <algorithm>
+#include <atomic>
+#include <cmath>
 
 namespace pa_host {
 

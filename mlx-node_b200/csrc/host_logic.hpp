@@ -229,6 +229,8 @@ class PagedKVCache {
     const SequenceBlockTable *t = table_.get(seq_id);
     return t ? t->num_tokens() : 0;
   }
+  // the block table of one sequence, or null
+  const SequenceBlockTable *sequence(uint32_t seq_id) const { return table_.get(seq_id); }
   TokenTracker &tracker() { return tracker_; }
   const TokenTracker &tracker() const { return tracker_; }
   BlockAllocator &allocator() { return alloc_; }
@@ -435,3 +437,16 @@ class AttentionLayer {
 };
 
 }  // namespace pa_host
+
+// Handle types of the C ABI that more than one translation unit opens.
+struct PaKvHost {
+  std::unique_ptr<pa_host::PagedKVCache> kv;
+};
+struct PaKvScaleManager {
+  pa_host::KvScaleManager m;
+  explicit PaKvScaleManager(uint32_t num_layers, float alpha) : m(num_layers, alpha) {}
+};
+struct PaAttentionLayer {
+  pa_host::AttentionLayer l;
+  explicit PaAttentionLayer(const pa_host::AttentionLayer &x) : l(x) {}
+};

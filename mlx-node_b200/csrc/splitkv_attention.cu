@@ -387,6 +387,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   const float sc_log2 = qk_scale * kLog2e;
   const bool use_cap = p.softcap != 1.0f;
 
+  constexpr bool kCanFuseWrite = NT == 1 && !FP8 && !B8;
+  const bool fuse_write = kCanFuseWrite && p.k_new != nullptr;
+
   // ---- walk the segments of [lo, hi) -----------------------------------------
   int s = seq_of(lo);
   int nb = pre[s + 1] - pre[s];
@@ -680,36 +683,47 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           }
         }
     };
-    // Decode step in one launch: this warp holds the sequence's last block in ring stage
-    // `st`; the step's new token of this kv head goes to its pool slot and into the staged
-    // copy, which was fetched before the token was in the pool.  Exactly one warp of the
-    // grid handles a given (sequence, kv head, last block), so nobody else reads that slot
-    // during this launch.
+    // Decode step in one launch: if this segment reaches the item's last block, the warp
+    // that gets that block stores the step's new token of this kv head to its pool slot and
+    // into the staged copy of the block (fetched before the token was in the pool).
+    // Exactly one warp of the grid handles a given (sequence, kv head, last block), so
+    // nobody else reads that slot during this launch.  The token's rows are fetched here,
+    // next to the queries, so that their latency is not paid at the end of the segment.
+    uint4 new_k = make_uint4(0u, 0u, 0u, 0u);
+    uint2 new_v = make_uint2(0u, 0u);
+    int64_t new_slot = -1;
+    uint32_t new_id = 0u;
+    if constexpr (kCanFuseWrite) {
+      if (fuse_write && b1 == nb) {
+        new_slot = p.slot_mapping[seq];
+        const int row = p.seq_row ? p.seq_row[seq] : seq;
+        new_id = (uint32_t)p.block_tables[(long long)row * p.MB + ((kv_len - 1) >> 4)];
+        if (lane < 16)
+          new_k = __ldg(reinterpret_cast<const uint4 *>(
+                            p.k_new + (int64_t)seq * p.k_new_stride + h * kHeadSize) + lane);
+        new_v = __ldg(reinterpret_cast<const uint2 *>(
+                          p.v_new + (int64_t)seq * p.v_new_stride + h * kHeadSize) + lane);
+      }
+    }
     auto write_new_token = [&](int st) {
-      const int64_t slot = p.slot_mapping[seq];
-      if (slot < 0) return;  // "no write" (crates/.../reshape_and_cache.metal:59-63)
-      const int pos = kv_len - 1, off = pos & (kBlockSize - 1);
-      uint32_t id = (uint32_t)p.block_tables[(long long)seq * p.MB + (pos >> 4)];
-      if (id >= p.num_blocks || slot != (int64_t)id * kBlockSize + off) {
+      if (new_slot < 0) return;  // "no write" (crates/.../reshape_and_cache.metal:59-63)
+      const int off = (kv_len - 1) & (kBlockSize - 1);
+      if (new_id >= p.num_blocks || new_slot != (int64_t)new_id * kBlockSize + off) {
         if (lane == 0) atomicOr(p.err, kErrStepSlot);
         return;
       }
-      const size_t chunk = (size_t)id * Hkv + h;
+      const size_t chunk = (size_t)new_id * Hkv + h;
       const uint32_t ks = ring_w + st * kStageBytes, vs = ks + kChunk;
       uint8_t *kg = const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(p.k_pool)) + chunk * kChunk;
       uint8_t *vg = const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(p.v_pool)) + chunk * kChunk;
       if (lane < 16) {  // K: sixteen 16-byte pieces, piece c to [c][off][0..7]
-        const uint4 kk = __ldg(reinterpret_cast<const uint4 *>(
-                                   p.k_new + (int64_t)seq * p.k_new_stride + h * kHeadSize) + lane);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ks + lane * 256 + off * 16),
-                     "r"(kk.x), "r"(kk.y), "r"(kk.z), "r"(kk.w) : "memory");
-        *reinterpret_cast<uint4 *>(kg + lane * 256 + off * 16) = kk;
+                     "r"(new_k.x), "r"(new_k.y), "r"(new_k.z), "r"(new_k.w) : "memory");
+        *reinterpret_cast<uint4 *>(kg + lane * 256 + off * 16) = new_k;
       }
       // V: element d to [d][off]; a lane takes d = 4 lane .. 4 lane + 3
-      const uint2 vv = __ldg(reinterpret_cast<const uint2 *>(
-                                 p.v_new + (int64_t)seq * p.v_new_stride + h * kHeadSize) + lane);
-      const uint16_t e[4] = {(uint16_t)(vv.x & 0xffffu), (uint16_t)(vv.x >> 16),
-                             (uint16_t)(vv.y & 0xffffu), (uint16_t)(vv.y >> 16)};
+      const uint16_t e[4] = {(uint16_t)(new_v.x & 0xffffu), (uint16_t)(new_v.x >> 16),
+                             (uint16_t)(new_v.y & 0xffffu), (uint16_t)(new_v.y >> 16)};
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int d = 4 * lane + i;
@@ -720,8 +734,6 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
     };
-    constexpr bool kCanFuseWrite = NT == 1 && !FP8 && !B8;
-    const bool fuse_write = kCanFuseWrite && p.k_new != nullptr;
     // Waits for the next unit of this warp (block `blk` of the item); false once a wait
     // has run out.
     auto wait_unit = [&](int j, int blk) {

@@ -36,9 +36,10 @@ EXPORTED_SYMBOLS = [
     "pa_gather_heads_peer_store", "pa_gather_heads_wait",
     "pa_attention_workspace_bytes", "pa_paged_attention_decode", "pa_paged_attention_varlen",
     "pa_paged_attention_decode_static", "pa_cpu_cache_create", "pa_cpu_cache_free",
-    "pa_cpu_cache_is_swapped", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
+    "pa_cpu_cache_is_swapped", "pa_cpu_cache_is_swapped_layer", "pa_cpu_cache_num_swapped", "pa_cpu_cache_block_ptrs", "pa_swap_out",
     "pa_swap_in", "pa_swap_block_bytes",
     "pa_decode_step_host", "pa_kernel_launch_count", "pa_decode_step", "pa_varlen_step_host",
+    "pa_cache_check_errors_fast", "pa_paged_attention_decode_rows", "pa_decode_step_rows",
 ]
 
 
@@ -92,6 +93,11 @@ def load_library() -> C.CDLL:
     lib.pa_cache_value_ptr.restype = vp
     lib.pa_cache_get_config.argtypes = [vp, C.POINTER(PagedAttnConfig)]
     lib.pa_cache_check_errors.argtypes = [vp, vp]
+    lib.pa_cache_check_errors_fast.argtypes = [vp, vp]
+    lib.pa_paged_attention_decode_rows.argtypes = [vp, u32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
+                                                   f32, f32, vp, sz, vp]
+    lib.pa_decode_step_rows.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64,
+                                        i64, i64, f32, f32, vp, sz, vp]
     lib.pa_reshape_and_cache.argtypes = [vp, u32, vp, vp, vp, i64, i64, i64, vp]
     lib.pa_copy_blocks.argtypes = [vp, u32, vp, i64, vp]
     lib.pa_attention_workspace_bytes.argtypes = [vp]
@@ -109,7 +115,8 @@ def load_library() -> C.CDLL:
     lib.pa_cpu_cache_is_swapped.argtypes = [vp, u32]
     lib.pa_cpu_cache_num_swapped.argtypes = [vp]
     lib.pa_cpu_cache_num_swapped.restype = sz
-    lib.pa_cpu_cache_block_ptrs.argtypes = [vp, u32, C.POINTER(vp), C.POINTER(vp)]
+    lib.pa_cpu_cache_is_swapped_layer.argtypes = [vp, u32, u32]
+    lib.pa_cpu_cache_block_ptrs.argtypes = [vp, u32, u32, C.POINTER(vp), C.POINTER(vp)]
     lib.pa_swap_out.argtypes = [vp, u32, C.POINTER(u32), sz, vp, vp]
     lib.pa_swap_in.argtypes = [vp, u32, C.POINTER(u32), sz, vp, vp]
     lib.pa_swap_block_bytes.argtypes = [u32, u32, u32, i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
@@ -363,13 +370,15 @@ class CpuBlockCache:
         except Exception:
             pass
 
-    def is_swapped(self, block_id: int) -> bool:
+    def is_swapped(self, block_id: int, layer: int | None = None) -> bool:
+        if layer is not None:
+            return bool(self.lib.pa_cpu_cache_is_swapped_layer(self.handle, layer, block_id))
         return bool(self.lib.pa_cpu_cache_is_swapped(self.handle, block_id))
 
     def num_swapped(self) -> int:
         return int(self.lib.pa_cpu_cache_num_swapped(self.handle))
 
-    def block_ptrs(self, block_id: int):
+    def block_ptrs(self, block_id: int, layer: int = 0):
         k, v = C.c_void_p(), C.c_void_p()
-        _check(self.lib.pa_cpu_cache_block_ptrs(self.handle, block_id, C.byref(k), C.byref(v)))
+        _check(self.lib.pa_cpu_cache_block_ptrs(self.handle, layer, block_id, C.byref(k), C.byref(v)))
         return k.value, v.value

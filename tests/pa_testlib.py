@@ -71,6 +71,8 @@ def oracle() -> C.CDLL:
     lib.oracle_qk_norm_rope.argtypes = [vp, vp, vp, i64, vp, C.c_double, vp, C.c_double, i32, i64,
                                         i32, i32, i32]
     lib.oracle_qk_norm_rope.restype = None
+    lib.oracle_paged_attention_metal.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, i32]
+    lib.oracle_paged_attention_metal.restype = None
     lib.oracle_f32_to_bf16.argtypes = [vp, vp, i64]
     lib.oracle_f32_to_bf16.restype = None
     lib.oracle_bf16_to_f32.argtypes = [vp, vp, i64]
@@ -193,6 +195,17 @@ def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np
                                               case.Hq, case.Hkv, D, k_pool.shape[3], case.MB,
                                               case.Hq * D, case.scale, softcap, int(case.f16))
     return out
+
+
+def attention_oracle_metal(case: Case, k_pool, v_pool, softcap=1.0) -> np.ndarray:
+    """The reference Metal kernels' own arithmetic (oracle/metal_arithmetic.c) on a decode
+    case with 16-token blocks: T-typed output as float32 [S, Hq, D]."""
+    assert (case.q_lens == 1).all() and k_pool.shape[3] == 16
+    out = np.zeros((case.S, case.Hq, D), dtype=np.uint16)
+    oracle().oracle_paged_attention_metal(p(out), p(case.q), p(k_pool), p(v_pool), p(case.block_tables),
+                                          p(case.kv_lens), case.S, case.Hq, case.Hkv, case.MB,
+                                          case.scale, softcap, int(case.f16))
+    return elems_to_f32(out, case.f16)
 
 
 def attention_oracle_rows(rows, q, k_pool, v_pool, block_tables, kv_lens, cu_q, Hq, Hkv, MB, scale,

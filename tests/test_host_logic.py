@@ -4,6 +4,8 @@ crates/mlx-paged-attn/src/{block_allocator,block_table,config,paged_kv_cache,
 scheduler,token_tracker}.rs `mod tests`, and metal/kv_scale.rs for the scale rule."""
 import struct
 
+import numpy as np
+
 import pytest
 
 import paged_attn_b200 as pa
@@ -568,3 +570,153 @@ def test_compute_scale():
     f = lib().pa_kv_compute_scale
     assert abs(f(448.0) - 1.0) < 1e-6 and abs(f(224.0) - 2.0) < 1e-6 and abs(f(896.0) - 0.5) < 1e-6
     assert f(0.0) == 1.0
+
+
+# ---- metal/kv_scale.rs:341-448 (the other seven; compute_scale is above) ------------------------
+from paged_attn_b200.host import (AttentionLayer, AttentionLayers, InputMetadata,  # noqa: E402
+                                  InputMetadataBuilder, KvScaleManager)
+
+
+def test_scale_manager_creation():
+    m = KvScaleManager(28)
+    assert m.num_layers == 28 and not m.is_calibrated()
+    assert m.k_scale(0) == 1.0 and m.v_scale(0) == 1.0
+
+
+def test_default_scales():
+    m = KvScaleManager(4)
+    m.init_default_scales()
+    for i in range(4):
+        assert m.k_scale(i) == 1.0 and m.v_scale(i) == 1.0
+
+
+def test_set_scales():
+    m = KvScaleManager(4)
+    m.set_scales(0, 0.5, 0.25)
+    m.set_scales(1, 2.0, 1.5)
+    assert (m.k_scale(0), m.v_scale(0), m.k_scale(1), m.v_scale(1)) == (0.5, 0.25, 2.0, 1.5)
+    assert m.is_calibrated()
+
+
+def test_serialization():
+    m = KvScaleManager(4)
+    for i, (k, v) in enumerate([(0.5, 0.25), (2.0, 1.5), (1.0, 1.0), (0.8, 0.9)]):
+        m.set_scales(i, k, v)
+    ks, vs = m.get_all_scales()
+    f = lambda xs: [np.float32(x) for x in xs]
+    assert ks == f([0.5, 2.0, 1.0, 0.8]) and vs == f([0.25, 1.5, 1.0, 0.9])
+    m2 = KvScaleManager(4)
+    m2.load_scales(ks, vs)
+    for i in range(4):
+        assert m2.k_scale(i) == m.k_scale(i) and m2.v_scale(i) == m.v_scale(i)
+
+
+def test_scale_stats():
+    m = KvScaleManager(4)
+    for i, (k, v) in enumerate([(0.5, 0.25), (2.0, 1.5), (1.0, 1.0), (0.5, 0.25)]):
+        m.set_scales(i, k, v)
+    s = m.stats()
+    assert s.num_layers_calibrated == 4 and s.k_scale_min == 0.5 and s.k_scale_max == 2.0
+    assert abs(s.k_scale_mean - 1.0) < 1e-6
+
+
+def test_scale_reset():
+    m = KvScaleManager(4)
+    m.set_scales(0, 0.5, 0.25)
+    assert m.is_calibrated()
+    m.reset()
+    assert not m.is_calibrated() and m.k_scale(0) == 1.0
+
+
+def test_with_alpha():
+    assert KvScaleManager.with_alpha(4, 0.5).alpha == 0.5
+    assert KvScaleManager.with_alpha(4, -0.5).alpha == 0.0   # clamped
+    assert KvScaleManager.with_alpha(4, 1.5).alpha == 1.0
+    assert abs(KvScaleManager(4).alpha - 0.1) < 1e-7          # DEFAULT_ALPHA
+
+
+def test_scale_calibration_arithmetic():
+    # kv_scale.rs:108-180: one-shot = 448 / max; running maximum m = a*obs + (1-a)*m,
+    # the first observation seeding m (and then being averaged with itself)
+    m = KvScaleManager.with_alpha(2, 0.5)
+    assert m.calibrate_layer_max(0, 224.0, 896.0) == (2.0, 0.5) and m.is_calibrated()
+    k, v = m.update_layer_ema_max(1, 448.0, 448.0)
+    assert (k, v) == (1.0, 1.0)
+    k, v = m.update_layer_ema_max(1, 896.0, 224.0)       # m_k = 672, m_v = 336
+    assert abs(k - 448.0 / 672.0) < 1e-6 and abs(v - 448.0 / 336.0) < 1e-6
+
+
+# ---- attention_layer.rs:484-546 -----------------------------------------------------------------------
+def test_layer_creation():
+    layer = AttentionLayer(0, 32, 8, 128, block_size=16)
+    assert (layer.layer_idx(), layer.num_heads(), layer.num_kv_heads(), layer.head_size()) == (0, 32, 8, 128)
+    assert abs(layer.scale() - 0.0884) < 0.001
+    p = layer.params()
+    assert p.softcap == 1.0 and p.k_scale == 1.0 and p.v_scale == 1.0 and p.use_fp8 == 0
+
+
+def test_layers_collection():
+    layers = AttentionLayers(28, 32, 8, 128, 16, False)
+    assert layers.num_layers() == 28
+    assert layers.get(0) is not None and layers.get(27) is not None and layers.get(28) is None
+    for i, layer in enumerate(layers):
+        assert layer.layer_idx() == i
+
+
+def test_from_cache_config():
+    cfg = host_config(block_size=32, gpu_memory_mb=4096, head_size=128, num_kv_heads=4, num_layers=28)
+    layer = AttentionLayer.from_cache_config(5, 32, cfg)
+    assert (layer.layer_idx(), layer.num_heads(), layer.num_kv_heads(), layer.head_size()) == (5, 32, 4, 128)
+    layers = AttentionLayers.from_cache_config(32, cfg)
+    assert layers.num_layers() == 28 and layers.get(3).params().block_size == 32
+
+
+# ---- input_metadata.rs:284-321 ------------------------------------------------------------------------
+def test_input_metadata_creation():
+    m = InputMetadata([0, 1, 2, 3], [32, 64], [0, 1, 2], 64, False, 2)
+    assert m.num_seqs() == 2 and m.num_tokens() == 3 and not m.is_prefill() and m.max_context_len == 64
+
+
+def test_builder():
+    m = (InputMetadataBuilder().block_tables([0, 1]).context_lens([16]).slot_mappings([0])
+         .max_context_len(16).is_prefill(True).max_blocks_per_seq(2).build())
+    assert m.num_seqs() == 1 and m.is_prefill()
+
+
+def test_dummy():
+    m = InputMetadata.dummy()
+    assert m.num_seqs() == 1 and m.is_prefill()
+
+
+# ---- cache_engine.rs:222-236 (the host half; the device half is in tests/test_gpu_bound_cache.py) ---------
+def test_cache_engine_manager_host():
+    cfg = host_config(block_size=32, gpu_memory_mb=1024, head_size=128, num_kv_heads=4, num_layers=28)
+    cache = PagedKVCacheHost(cfg)
+    assert cfg.num_layers == 28 and cache.num_free_blocks() > 0
+
+
+# ---- metal/copy_blocks.rs:185-195 ---------------------------------------------------------------------------
+def test_copy_blocks_params():
+    # numel_per_block = num_kv_heads * head_size * block_size; the library's copy moves that
+    # many elements of K and of V per pair (pa_swap_block_bytes reports the same figure in bytes)
+    import ctypes as ct
+    kb, vb = ct.c_uint64(), ct.c_uint64()
+    pa.load_library().pa_swap_block_bytes(4, 128, 16, 0, ct.byref(kb), ct.byref(vb))
+    assert kb.value == 4 * 128 * 16 * 2 and vb.value == 4 * 128 * 16 * 2
+
+
+def test_metadata_buffers_are_bounded():
+    # a caller buffer sized for a narrower table is refused, not overrun
+    cache = PagedKVCacheHost(host_config(block_size=16, gpu_memory_mb=256, num_kv_heads=4, num_layers=28,
+                                         max_seq_len=256))
+    a = cache.add_sequence(40)
+    mb = cache.get_max_blocks_per_seq()
+    import ctypes as ct
+    s = (ct.c_uint32 * 1)(a)
+    l = (ct.c_uint32 * 1)(1)
+    p = (ct.c_uint8 * 1)(0)
+    tables, lens, slots = (ct.c_int32 * (mb - 1))(), (ct.c_int32 * 1)(), (ct.c_int64 * 4)()
+    cnt = ct.c_size_t()
+    rc = lib().pa_kv_build_input_metadata(cache.h, s, l, p, 1, tables, mb - 1, lens, 1, slots, 4, ct.byref(cnt),
+                                          None, None)
+    assert rc == 1
