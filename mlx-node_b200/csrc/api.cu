@@ -69,6 +69,9 @@ struct PagedAttnCache {
   bool fp8 = false;
   std::vector<float> k_scale, v_scale;
   std::vector<pa::TensorMapBlob> v_maps;  // per layer: tensor map of the V pool (16-bit pools)
+  std::vector<pa::TensorMapBlob> k_maps;  // per layer: row view of the K pool (16-bit pools, 16-token blocks)
+  // the tile kernel that fetches K by TMA gather serves 16-bit pools of 16-token blocks
+  bool has_tile64() const { return !fp8 && bs_shift == 0; }
   // log2(block_size / 16): -1, 0 or 1.  32-token blocks: per layer, the maps that fetch
   // one 16-token unit of a chunk for the split-KV kernel
   int bs_shift = 0;
@@ -170,6 +173,7 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->err_host_dev), c->err_host, 0));
   PA_CUDA(pa::splitkv_configure());
   PA_CUDA(pa::tile_configure());
+  PA_CUDA(pa::tile64_configure());
   // the tile kernel fetches V of 16-bit pools through a tensor map (FP8 pools are read with
   // plain loads: their entries stay zero and unused)
   c->v_maps.assign(c->cfg.num_layers, pa::TensorMapBlob{});
@@ -178,6 +182,11 @@ pa_status finish_create(PagedAttnCache *c) {
       PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
                                     (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
                                     (int)c->cfg.block_size));
+  }
+  if (c->has_tile64()) {
+    c->k_maps.assign(c->cfg.num_layers, pa::TensorMapBlob{});
+    for (uint32_t i = 0; i < c->cfg.num_layers; i++)
+      PA_CUDA(pa::tile64_encode_k_map(&c->k_maps[i], c->k[i], (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads));
   }
   if (c->bs_shift > 0) {
     c->unit_maps.resize(c->cfg.num_layers);
@@ -749,6 +758,13 @@ bool can_fuse_write(const PagedAttnCache *c, int num_q_heads) {
          num_q_heads % (int)c->cfg.num_kv_heads == 0 && num_q_heads / (int)c->cfg.num_kv_heads <= 8;
 }
 
+cudaError_t launch_tiles(PagedAttnCache *c, uint32_t layer, const pa::AttnParams &p,
+                         const pa::TileWork *work_dev, int n, cudaStream_t st) {
+  if (c->has_tile64())
+    return pa::launch_tile64_attention(p, work_dev, n, &c->k_maps[layer], &c->v_maps[layer], st);
+  return pa::launch_tile_attention(p, work_dev, n, &c->v_maps[layer], st);
+}
+
 pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const void *q,
                          const int32_t *block_tables, const int32_t *context_lens,
                          const int32_t *cu_q_lens_host, const int32_t *context_lens_host,
@@ -955,7 +971,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     PA_CUDA(cudaEventRecord(c->ev_fork, stream));
     PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
   } else if (!tiles.empty()) {
-    PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), &c->v_maps[layer], stream));
+    PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));
   }
   bool tile_launched = !side_by_side;
   for (int k = 0; k < 3; k++) {
@@ -964,8 +980,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     p.max_cols = 8 * k + 8;
     PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream, c->unit_map(layer)));
     if (!tile_launched) {  // after the first split-KV launch, so that it gets its SMs first
-      PA_CUDA(pa::launch_tile_attention(p, work_dev, (int)tiles.size(), &c->v_maps[layer],
-                                        c->aux_stream));
+      PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), c->aux_stream));
       tile_launched = true;
     }
   }

@@ -382,13 +382,12 @@ cudaError_t launch_peer_wait(const unsigned *my_flags, int world, unsigned epoch
 
 cudaError_t launch_peer_gather(const PeerGather &a, cudaStream_t st) {
   const size_t total = (size_t)a.num_tokens * (a.row_bytes_local / 16) * a.world;
-  if (total) {
-    const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 296);
-    scatter_heads_kernel<<<blocks, 256, 0, st>>>(a);
-    __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
-    return cudaGetLastError();
-  }
-  return cudaSuccess;
+  // An empty step still publishes this rank's flags (one block with nothing to store):
+  // the other ranks wait for every writer's epoch.
+  const unsigned blocks = (unsigned)std::max<size_t>(1, std::min<size_t>((total + 255) / 256, 296));
+  scatter_heads_kernel<<<blocks, 256, 0, st>>>(a);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return cudaGetLastError();
 }
 
 // Swap: one CTA per (block, 4 KB piece), 16 bytes per thread, K then V.  The host side

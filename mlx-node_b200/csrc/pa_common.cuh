@@ -304,6 +304,13 @@ cudaError_t launch_tile_attention(const AttnParams &p, const TileWork *work_dev,
                                   const TensorMapBlob *v_map, cudaStream_t st);
 cudaError_t tile_configure();
 int tile_queries_per_cta(int G);
+// The same for 16-bit pools of 16-token blocks with every KV operand fetched by TMA
+// (tile_attention_tc64.cu); same work list, same rows per CTA.
+cudaError_t tile64_encode_k_map(TensorMapBlob *out, const void *k_pool, uint64_t num_chunks);
+cudaError_t launch_tile64_attention(const AttnParams &p, const TileWork *work_dev, int num_work,
+                                    const TensorMapBlob *k_map, const TensorMapBlob *v_map, cudaStream_t st);
+cudaError_t tile64_configure();
+int tile64_queries_per_cta(int G);
 
 extern unsigned long long g_launch_count;  // host counter of kernel launches
 

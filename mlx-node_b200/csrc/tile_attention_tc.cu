@@ -47,10 +47,13 @@
 #include <type_traits>
 
 #include "pa_common.cuh"
+#include "tile_common.cuh"
 
 namespace pa {
 
 namespace {
+
+using namespace tile;
 
 constexpr int kQRows = 128;            // rows per Q tile
 constexpr int kTileTok = 128;          // tokens per KV tile
@@ -72,175 +75,6 @@ constexpr int kRegsSoftmax = 200, kRegsOther = 56;
 // barrier slots
 enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9,
        B_PREADY = 11, B_PVDONE = 13, B_VTAIL = 15 };
-
-// One V block (128 head dimensions x 16 tokens) through the tensor map of the V pool
-// {16 tokens, 128 rows, chunk}: the 32-byte swizzle of the map lays the rows out as the
-// MMA descriptor of v_block_desc expects them.  This CTA's shared memory only; a chunk
-// index beyond the pool reads as zeros.  y is always 0; x0 is 0, or 16 for the second
-// half of a 32-token pool block (32 bytes into the row).
-__device__ __forceinline__ void tma_load_v_block(uint32_t dst, const CUtensorMap *map, int x0,
-                                                 int chunk, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x0), "r"(0), "r"(chunk), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-// True in exactly one lane of the (fully active) warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.b32 %0, 1, 0, P;\n}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
-      "l"(a), "l"(b), "r"(idesc), "r"(acc)
-      : "memory");
-}
-__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d),
-      "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
-      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-// Wait for outstanding TMEM loads; the registers are named as in/out operands so that
-// no use of them can be scheduled above the wait.
-__device__ __forceinline__ void tmem_wait_ld32(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
-                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
-                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
-                 "+r"(r[31])
-               :
-               : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B
-// apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// K tile, K-major without swizzle: core matrix = 8 tokens x 16 B contiguous (the pool's
-// own [d/8][tok][8] order); 8-token groups 128 B apart (stride byte offset), the two
-// 8-element d-chunks of one K=16 step 2048 B apart (leading byte offset).
-__device__ __forceinline__ uint64_t k_tile_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (128ull << 16) | (8ull << 32) | (1ull << 46);
-}
-// One V block, K-major with 32-byte swizzle: rows = d, 32 B = the block's 16 tokens;
-// 8-row groups 256 B apart.  Layout type 6.
-__device__ __forceinline__ uint64_t v_block_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (16ull << 32) | (1ull << 46) |
-         (6ull << 61);
-}
-// Instruction descriptor: D fp32, A/B bf16 (format 1) or f16 (format 0), both K-major,
-// N = 128, M = 128.
-constexpr uint32_t kIdescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t kIdescF16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-
-// Byte offset of 16-byte unit `u` (0..7) of row `r` inside a 128-row slab.
-__device__ __forceinline__ uint32_t sw128_off(int r, int u) {
-  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((u ^ (r & 7)) << 4));
-}
-
-#ifdef PA_TILE_TIMING
-// Debug builds only: cycles each role spends waiting, summed over CTAs.
-__device__ unsigned long long g_tile_timing[16];
-__device__ unsigned long long g_trace[3 * 2048];
-// event trace of CTA 0 (debug builds): one list per traced warp, plain stores,
-// (clock << 8) | event id; slot 0 = MMA warp, 1 / 2 = first softmax warp of tile 0 / 1
-#define PA_TRACE(slot, id)                                                              \
-  do {                                                                                  \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 2048)                      \
-      g_trace[(slot) * 2048 + tr_n++] = ((unsigned long long)clock64() << 8) | (unsigned)(id); \
-  } while (0)
-#define PA_T0() const long long t_dbg0 = clock64()
-#define PA_T1(slot) atomicAdd(&g_tile_timing[slot], (unsigned long long)(clock64() - t_dbg0))
-#else
-#define PA_T0()
-#define PA_T1(slot)
-#define PA_TRACE(slot, id)
-#endif
-
-// Wait that gives up when the budget runs out or another role has raised the flag.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  int spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > (1ll << 31)) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
 
 // One pass over a row's 128 logits of the current KV tile (thread = row), which the caller
 // holds in registers (fetched from TMEM with four loads in flight at once: one latency
@@ -286,36 +120,6 @@ __device__ __forceinline__ void row_pass(uint32_t s_t, const uint32_t (&s0)[32],
   sum_out = (sma[0] + sma[1]) + (sma[2] + sma[3]);
 }
 
-// Debug builds add the cycles spent in the wait to a per-site counter.
-__device__ __forceinline__ bool wait_bar_at(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                            int site) {
-#ifdef PA_TILE_TIMING
-  const long long t0 = clock64();
-  const bool ok = wait_bar(bar, parity, abort_flag);
-  if ((threadIdx.x & 31) == 0) atomicAdd(&g_tile_timing[site], (unsigned long long)(clock64() - t0));
-  return ok;
-#else
-  (void)site;
-  return wait_bar(bar, parity, abort_flag);
-#endif
-}
-
-__device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
-                                            uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
-               : "memory");
-}
-
-
-__device__ __forceinline__ uint4 ld_shared16(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr)
-               : "memory");
-  return v;
-}
-
 // F16: format of q and out (and, without FP8, of the pools).  FP8: the pools hold E4M3 bytes.
 template <bool CAP, bool F16, bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -337,10 +141,6 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
   auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef PA_TILE_TIMING
-  const long long t_cta0 = clock64();
-  int tr_n = 0;
-#endif
   const TileWork w = work[blockIdx.x];
   const int seq = w.seq, h = w.kv_head, G = p.G;
   const int kv_len = p.context_lens[seq];
@@ -515,7 +315,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       if (FP8) fetch_k_fp8(0);  // the first tile's bytes
       for (int j = 0; j < n_tiles && !failed; j++) {
         const int nb_here = min(8, nblk - j * 8);  // blocks of this tile that exist
-        if (j >= 2 && !wait_bar_at(bar(B_KEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+        if (j >= 2 && !wait_bar(bar(B_KEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag)) {
           failed = true;
           break;
         }
@@ -531,13 +331,11 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           if (j + 1 < n_tiles) fetch_k_fp8(j + 1);
         } else {
           issue_k(j);
-          PA_T0();
           cp_async_wait<0>();
-          if (lane == 0) PA_T1(10);
         }
         land_k(j);
         if (FP8) continue;  // V tiles of an FP8 cache are the work of warps 13-15
-        if (j >= 2 && !wait_bar_at(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+        if (j >= 2 && !wait_bar(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag)) {
           failed = true;
           break;
         }
@@ -559,7 +357,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           }
           if (pw == 1) {  // second arrival: nothing left to clear in this tile
             if (tail_b >= 0) {
-              if (!wait_bar_at(bar(B_VTAIL), 0, abort_flag, 0)) {
+              if (!wait_bar(bar(B_VTAIL), 0, abort_flag)) {
                 failed = true;
                 break;
               }
@@ -606,28 +404,25 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           if (leader) tc_commit(bar(B_PVDONE + i));
         };
         do {
-          if (!wait_bar_at(bar(B_QFULL), 0, abort_flag, 1)) { failed = true; break; }
-          if (!wait_bar_at(bar(B_KFULL + 0), 0, abort_flag, 1)) { failed = true; break; }
+          if (!wait_bar(bar(B_QFULL), 0, abort_flag)) { failed = true; break; }
+          if (!wait_bar(bar(B_KFULL + 0), 0, abort_flag)) { failed = true; break; }
           tc_fence_after();
           issue_s(0, 0);
           issue_s(1, 0);
           if (leader) tc_commit(bar(B_KEMPTY + 0));
           for (int j = 0; j < n_tiles && !failed; j++) {
-            if (!wait_bar_at(bar(B_VFULL + (j & 1)), (j >> 1) & 1, abort_flag, 2)) { failed = true; break; }
+            if (!wait_bar(bar(B_VFULL + (j & 1)), (j >> 1) & 1, abort_flag)) { failed = true; break; }
             const bool more = j + 1 < n_tiles;
-            if (more && !wait_bar_at(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag, 3)) {
+            if (more && !wait_bar(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, abort_flag)) {
               failed = true;
               break;
             }
             for (int i = 0; i < 2; i++) {
-              PA_TRACE(0, 10 + i);
-              if (!wait_bar_at(bar(B_PREADY + i), j & 1, abort_flag, 4 + i)) { failed = true; break; }
-              PA_TRACE(0, 12 + i);
+              if (!wait_bar(bar(B_PREADY + i), j & 1, abort_flag)) { failed = true; break; }
               tc_fence_after();
               issue_pv(i, j);
               if (i == 1 && leader) tc_commit(bar(B_VEMPTY + (j & 1)));
               if (more) issue_s(i, j + 1);
-              PA_TRACE(0, 14 + i);
             }
             if (more && !failed && leader) tc_commit(bar(B_KEMPTY + ((j + 1) & 1)));
             __syncwarp();
@@ -688,7 +483,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         };
         fetch_v(0);
         for (int j = 0; j < n_tiles && !failed; j++) {
-          if (j >= 2 && !wait_bar_at(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 0)) {
+          if (j >= 2 && !wait_bar(bar(B_VEMPTY + (j & 1)), ((j >> 1) - 1) & 1, abort_flag)) {
             failed = true;
             break;
           }
@@ -724,9 +519,6 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       // soft-capping: x -> tanh(x*scale/cap)*cap/scale, so that x*c is the capped logit
       const float cap_in = qk_scale / p.softcap, cap_out = p.softcap / qk_scale;
       float m_used = -INFINITY, l = 0.f;
-#ifdef PA_TILE_TIMING
-      long long dbg_pass = 0, dbg_store = 0;
-#endif
       uint32_t s0[32], s1[32], s2[32], s3[32];  // the row's logits of the current tile
       auto pass = [&](bool need_mask, int tok0, float &mx, float &sum) {
         const float mc = m_used == -INFINITY ? 0.f : m_used * c;
@@ -737,8 +529,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
       };
 
       for (int j = 0; j < n_tiles && !failed; j++) {
-        if (!wait_bar_at(bar(B_SFULL + i), j & 1, abort_flag, 6 + i)) { failed = true; break; }
-        if ((warp & 3) == 0) PA_TRACE(1 + i, 20 + i);
+        if (!wait_bar(bar(B_SFULL + i), j & 1, abort_flag)) { failed = true; break; }
         tc_fence_after();
         const bool need_mask = (j + 1) * kTileTok > warp_min_lim;
         const int tok0 = j * kTileTok;
@@ -751,19 +542,10 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         tmem_wait_ld32(s1);  // already complete: these tie the registers to the wait
         tmem_wait_ld32(s2);
         tmem_wait_ld32(s3);
-        if ((warp & 3) == 0) PA_TRACE(1 + i, 22 + i);
-#ifdef PA_TILE_TIMING
-        const long long t_pass0 = clock64();
-#endif
         // Optimistic pass against the maximum carried from earlier tiles (for the first
         // tile: against 0, result discarded unless the logits happen to be small).  It
         // already writes P; a second pass, from the same registers, overwrites it.
         pass(need_mask, tok0, mx, sum);
-#ifdef PA_TILE_TIMING
-        const long long t_pass1 = clock64();
-        dbg_pass += t_pass1 - t_pass0;
-#endif
-        if ((warp & 3) == 0) PA_TRACE(1 + i, 24 + i);
         // stale-maximum rule: move the reference only when it would grow by > 2^8
         const bool grew = mx > m_used && !((mx - m_used) * c <= 8.f);
         if (__any_sync(0xffffffffu, grew)) {
@@ -774,7 +556,7 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
           }
           if (j > 0) {
             // O_i of the previous tile is complete: its P.V was issued before this S
-            if (!wait_bar_at(bar(B_PVDONE + i), (j - 1) & 1, abort_flag, 8)) { failed = true; break; }
+            if (!wait_bar(bar(B_PVDONE + i), (j - 1) & 1, abort_flag)) { failed = true; break; }
             tc_fence_after();
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
@@ -795,19 +577,9 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + i));
-        if ((warp & 3) == 0) PA_TRACE(1 + i, 26 + i);
-#ifdef PA_TILE_TIMING
-        dbg_store += clock64() - t_pass1;
-#endif
       }
-#ifdef PA_TILE_TIMING
-      if (lane == 0) {
-        atomicAdd(&g_tile_timing[13], (unsigned long long)dbg_pass);
-        atomicAdd(&g_tile_timing[14], (unsigned long long)dbg_store);
-      }
-#endif
       // epilogue: O / l -> bf16 rows
-      if (!failed && wait_bar_at(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag, 9)) {
+      if (!failed && wait_bar(bar(B_PVDONE + i), (n_tiles - 1) & 1, abort_flag)) {
         tc_fence_after();
         float inv = l > 0.f ? 1.f / l : 0.f;
         if (FP8) inv *= p.v_scale * kFp8Unbias;
@@ -847,10 +619,6 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
   }
 
   if (failed) atomicOr(p.err, kErrTimeout);
-#ifdef PA_TILE_TIMING
-  if (tid == 0) atomicAdd(&g_tile_timing[11], (unsigned long long)(clock64() - t_cta0));
-  if (tid == 0) atomicAdd(&g_tile_timing[12], (unsigned long long)n_tiles);
-#endif
   // ---- teardown -------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -862,24 +630,6 @@ tile_attention_tc_kernel(const AttnParams p, const TileWork *__restrict__ work,
 
 }  // namespace
 
-#ifdef PA_TILE_TIMING
-extern "C" int pa_debug_tile_trace(unsigned long long *out, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 3 * 2048);
-  if (e == cudaSuccess && reset) {
-    static unsigned long long z[3 * 2048];
-    e = cudaMemcpyToSymbol(g_trace, z, sizeof(z));
-  }
-  return (int)e;
-}
-extern "C" int pa_debug_tile_timing(unsigned long long *out16, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out16, g_tile_timing, sizeof(unsigned long long) * 16);
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[16] = {0};
-    e = cudaMemcpyToSymbol(g_tile_timing, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
 
 int tile_queries_per_cta(int G) { return 2 * kQRows / G; }
 

@@ -1,11 +1,14 @@
 """The five benchmark configurations at their FULL sizes on the GPU.
 
-A full CPU oracle over these sizes would take hours, so each case is checked by
+Each case is checked by
 (a) the KV write against an independent torch scatter over the whole pool, bit for
     bit, with never-written slots still holding their canary;
-(b) oracle spot checks: the fp64 oracle on a sample of output rows (first / middle /
-    last queries of several sequences, several heads), computed from a compact copy
-    of exactly those sequences' blocks;
+(b) the fp64 oracle: over the WHOLE output for the decode configurations (1-3) and for
+    the decode and verify sequences of the mixed batch (5); for the long chunks
+    (configuration 4 and the prefill part of 5) on the queries either side of every
+    Q-tile edge of the tile kernel (a CTA's two 128-row tiles change every 128 / G
+    queries), which are also the queries whose causal limit crosses a KV-tile edge,
+    all heads;
 (c) size-independent properties: decode entry == varlen entry with one query per
     sequence (bit-identical), run-to-run determinism, and convexity (every output
     lies within the min/max of V over its context for that head dimension is
@@ -21,7 +24,7 @@ import torch
 import paged_attn_b200 as pa
 from gpu_util import to_bits
 from pa_testlib import (BS, CANARY, D, X, attention_oracle_rows, bf16_to_f32, check_attention,
-                        config_lengths)
+                        config_lengths, oracle, p)
 
 pytestmark = pytest.mark.gpu
 
@@ -109,8 +112,9 @@ class FullCase:
         self.cache.check_errors()
         return out
 
-    def spot_check(self, out, seqs, what):
-        """fp64 oracle on rows of the given sequences: queries first/middle/last, 4 heads each."""
+    def check_sequences(self, out, seqs, what, queries_of=None):
+        """fp64 oracle on rows of the given sequences, every head: all their queries, or the
+        queries queries_of(q_len) picks."""
         nblk = (self.kv + BS - 1) // BS
         ids = np.concatenate([self.tables_h[s, :nblk[s]] for s in seqs])
         idt = torch.from_numpy(ids.astype(np.int64)).cuda()
@@ -127,20 +131,38 @@ class FullCase:
         q_c = to_bits(self.q[torch.from_numpy(q_rows).cuda()])
         rows = []
         for i, s in enumerate(seqs):
-            for j in sorted({0, int(ql_c[i]) // 2, int(ql_c[i]) - 1}):
-                for hq in sorted({0, 5 % self.Hq, self.Hq // 2 + 1, self.Hq - 1}):
+            js = range(int(ql_c[i])) if queries_of is None else queries_of(int(ql_c[i]))
+            for j in js:
+                for hq in range(self.Hq):
                     rows.append((i, j, hq))
         ref = attention_oracle_rows(rows, q_c, k_c, v_c, tables_c, lens_c, cu_c, self.Hq, self.Hkv,
                                     self.MB, self.scale)
         out_h = bf16_to_f32(to_bits(out[torch.from_numpy(q_rows).cuda()]))
-        got = np.stack([out_h[cu_c[i] + j, hq] for (i, j, hq) in rows])
-        return check_attention(got, ref, what)
+        idx = np.array([(cu_c[i] + j, hq) for (i, j, hq) in rows])
+        got = out_h[idx[:, 0], idx[:, 1]]
+        stats = check_attention(got, ref, what)
+        stats["rows"] = len(rows)
+        return stats
+
+    def check_whole_decode_output(self, out, what):
+        """The fp64 oracle over every output row of a decode batch, read through the full
+        pools and tables (no sampling)."""
+        k, v = to_bits(self.k_pool), to_bits(self.v_pool)
+        q = to_bits(self.q)
+        ref = np.zeros((self.S, self.Hq, D), dtype=np.float32)
+        lens = np.ascontiguousarray(self.kv.astype(np.int32))
+        oracle().oracle_paged_attention_varlen_dt(p(ref), p(q), p(k), p(v), p(self.tables_h), p(lens), None,
+                                                  self.S, self.Hq, self.Hkv, D, BS, self.MB, self.Hq * D,
+                                                  self.scale, 1.0, 0)
+        stats = check_attention(bf16_to_f32(to_bits(out)), ref, what)
+        stats["rows"] = self.S * self.Hq
+        return stats
 
 
-def pick_sequences(kv, n):
-    order = np.argsort(kv)
-    idx = np.unique(np.concatenate([order[:2], order[-2:], order[np.linspace(0, len(kv) - 1, n).astype(int)]]))
-    return [int(i) for i in idx]
+def tile_edge_queries(G):
+    """Queries on either side of every Q-tile edge (128 rows = 128 / G queries) of a chunk."""
+    step = 128 // G
+    return lambda ql: sorted({j for j in range(ql) if j % step in (0, step - 1)} | {ql - 1})
 
 
 @pytest.mark.parametrize("name", ["c1", "c2", "c3"])
@@ -151,7 +173,7 @@ def test_decode_configuration_full_size(cuda_device, name):
     out = c.attend(varlen=False)
     assert torch.isfinite(out.float()).all()
     assert out.float().abs().max() <= c.v_all.float().abs().max()
-    print(name, c.spot_check(out, pick_sequences(c.kv, 8), name + " full size"))
+    print(name, c.check_whole_decode_output(out, name + " full size, whole output"))
     again = c.attend(varlen=False)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "not deterministic"
     as_varlen = c.attend(varlen=True)
@@ -164,7 +186,7 @@ def test_chunked_prefill_configuration_full_size(cuda_device):
     c.check_pools_against_torch_scatter()
     out = c.attend(varlen=True)
     assert torch.isfinite(out.float()).all()
-    print("c4", c.spot_check(out, [0, 3, 7], "c4 full size"))
+    print("c4", c.check_sequences(out, [0, 3, 7], "c4 full size", tile_edge_queries(c.Hq // c.Hkv)))
     again = c.attend(varlen=True)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "not deterministic"
 
@@ -176,7 +198,7 @@ def test_mixed_configuration_full_size(cuda_device):
     out = c.attend(varlen=True)
     assert torch.isfinite(out.float()).all()
     # decode (0..47), verify (48..55) and prefill (56, 57) sequences
-    seqs = pick_sequences(c.kv[:48], 4) + [48, 51, 55, 56, 57]
-    print("c5", c.spot_check(out, seqs, "c5 full size"))
+    print("c5 decode + verify", c.check_sequences(out, list(range(56)), "c5 decode and verify, whole output"))
+    print("c5 prefill", c.check_sequences(out, [56, 57], "c5 prefill chunks", tile_edge_queries(c.Hq // c.Hkv)))
     again = c.attend(varlen=True)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "not deterministic"

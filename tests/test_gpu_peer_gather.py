@@ -13,13 +13,15 @@ from pa_testlib import BS, D
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world,hl,T", [(2, 4, 64), (4, 2, 33), (8, 1, 5), (1, 8, 7)])
+@pytest.mark.parametrize("world,hl,T", [(2, 4, 64), (4, 2, 33), (8, 1, 5), (1, 8, 7), (2, 4, 0)])
 def test_publish_then_wait_fills_every_buffer(cuda_device, world, hl, T):
     cache = pa.PagedCache(BS, 8, D, 1)
     gen = torch.Generator(device="cuda").manual_seed(5)
     locals_ = [torch.randn(T, hl, D, generator=gen, device="cuda").to(torch.bfloat16)
                for _ in range(world)]
-    fulls = [torch.full((T, world * hl, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    # (T = 0: an empty step moves nothing but still publishes every writer's flag, so the
+    # waits return at once instead of running into their time-out)
+    fulls = [torch.full((max(T, 1), world * hl, D), float("nan"), dtype=torch.bfloat16, device="cuda")[:T]
              for _ in range(world)]
     flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
     for epoch in (1, 2):
