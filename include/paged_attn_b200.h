@@ -339,8 +339,10 @@ pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
  *                  pa_cache_check_errors reports PA_ERR_INVALID_ARG.
  * The other arguments are those of pa_paged_attention_decode.  The pool bytes
  * after the call equal those pa_reshape_and_cache would have produced.  On an
- * FP8 cache, with 8- or 32-token blocks or more than 8 query heads per kv head
- * the call runs the write kernel and then the attention kernel.
+ * FP8 cache, with 8- or 32-token blocks, more than 8 query heads per kv head, or
+ * more than 2 x (SM count) (sequence, kv head) pairs in the batch (the in-kernel
+ * write costs its CTA a few microseconds per pair, a launch of its own about
+ * four in total) the call runs the write kernel and then the attention kernel.
  *   context_lens (and, for pa_paged_attention_varlen, the query offsets) are read
  * as soon as the launch is scheduled, which may be before earlier kernels of
  * the stream have finished when those were launched with programmatic

@@ -753,9 +753,14 @@ struct StepWrite {
 };
 // Whether the split-KV kernel can write the step's tokens itself: 16-bit pools of
 // 16-token blocks and a GQA group that fits the narrow kernel.
-bool can_fuse_write(const PagedAttnCache *c, int num_q_heads) {
+// The fused write sits on the critical path of the CTA that ends a (sequence, kv head) item:
+// measured on B200 about 3 us per item and CTA, against about 4 us for a write launch of
+// its own.  It pays while a CTA ends at most a couple of items (few kv heads per GPU, as
+// under kv-head sharding); beyond that the step runs the write kernel first.
+bool can_fuse_write(const PagedAttnCache *c, int num_q_heads, int num_seqs) {
   return !c->fp8 && c->bs_shift == 0 && num_q_heads > 0 &&
-         num_q_heads % (int)c->cfg.num_kv_heads == 0 && num_q_heads / (int)c->cfg.num_kv_heads <= 8;
+         num_q_heads % (int)c->cfg.num_kv_heads == 0 && num_q_heads / (int)c->cfg.num_kv_heads <= 8 &&
+         (int64_t)num_seqs * c->cfg.num_kv_heads <= 2 * (int64_t)c->num_sms;
 }
 
 cudaError_t launch_tiles(PagedAttnCache *c, uint32_t layer, const pa::AttnParams &p,
@@ -852,6 +857,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
   double tile_flops = 0.0, split_bytes = 0.0;  // work estimates, only with host context lengths
+  double class_bytes[3] = {0.0, 0.0, 0.0};
   // a chunk too long for the split-KV kernel on a cache the tile kernel does not read
   // (8-token blocks)
   bool in_pieces = false;
@@ -863,6 +869,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     if (ql * G <= split_cols) {
       have_class[(ql * G - 1) / 8] = true;
       split_bytes += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
+      class_bytes[(ql * G - 1) / 8] += kv * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
     } else {
       if (!c->has_tile_kernel()) {  // served below as several shorter sequences
         in_pieces = true;
@@ -891,6 +898,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     v_cu.push_back(0);
     have_class[0] = have_class[1] = have_class[2] = false;
     split_bytes = 0.0;
+    class_bytes[0] = class_bytes[1] = class_bytes[2] = 0.0;
     for (int s = 0; s < num_seqs; s++) {
       const int ql = cu_q_lens_host[s + 1] - cu_q_lens_host[s];
       const int kv_len = context_lens_host[s];
@@ -902,6 +910,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
         if (qb > qa) {
           have_class[((qb - qa) * G - 1) / 8] = true;
           split_bytes += (double)v_ctx.back() * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
+          class_bytes[((qb - qa) * G - 1) / 8] += (double)v_ctx.back() * 2.0 * Hkv * c->cfg.head_size * (c->fp8 ? 1.0 : 2.0);
         }
         if (ql == 0) break;
       }
@@ -933,28 +942,35 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
                             cudaMemcpyHostToDevice, stream));
 
   // A batch that holds both kinds of work runs them side by side: the tensor-bound tile
-  // kernel on a second stream, the memory-bound split-KV kernel on fewer CTAs.  The
-  // split is chosen from a small model measured on B200: split-KV streams about 70 GB/s
-  // per SM up to about 6 TB/s in total (100 SMs already saturate HBM); a tile CTA
-  // sustains about 0.9 PFLOP/s / 148 and tile CTAs run in waves over the SMs they get.
-  // Without host context lengths there is no estimate and the two run back to back.
+  // kernel on a second stream, the memory-bound split-KV kernel of the batch's largest
+  // width class on fewer CTAs; the other width classes (a few verify sequences, say) run
+  // first on the whole GPU, so that only two grids ever compete for SMs.  The split is
+  // chosen from a small model measured on B200: split-KV streams about 70 GB/s per SM up
+  // to about 6 TB/s in total (100 SMs already saturate HBM); a tile CTA sustains about
+  // 1.1 PFLOP/s / 148 (0.9 with 32-token blocks) and tile CTAs run in waves over the SMs
+  // they get.  Without host context lengths there is no estimate and the kernels run back
+  // to back.
   int split_ctas = c->num_sms;
   bool side_by_side = false;
+  int main_class = 0;
+  for (int k = 1; k < 3; k++)
+    if (class_bytes[k] > class_bytes[main_class]) main_class = k;
   if (!tiles.empty() && any_split && context_lens_host) {
     // (FP8 cache: the tile kernel converts bytes as it goes and sustains about 0.6 PFLOP/s;
     // the split-KV kernel streams about 30 GB/s per SM, 4.4 TB/s on the whole GPU)
-    const double tile_rate = c->fp8 ? 0.6e15 : 0.9e15;
+    const double tile_rate = c->fp8 ? 0.6e15 : (c->has_tile64() ? 1.1e15 : 0.9e15);
     const double sm_bw = c->fp8 ? 30e9 : 70e9, bw_cap = c->fp8 ? 4.4e12 : 6.0e12;
+    const double main_bytes = class_bytes[main_class];
     const double t_cta = tile_flops / (double)tiles.size() / (tile_rate / c->num_sms);
     const double t_tile_alone = t_cta * (double)((tiles.size() + c->num_sms - 1) / c->num_sms);
-    const double t_split_alone = split_bytes / bw_cap;
+    const double t_split_alone = main_bytes / bw_cap;
     if (t_tile_alone > 20e-6 && t_split_alone > 20e-6) {
       double best = 1e30;
       int best_tile_sms = 0;
       for (int n2 = 8; n2 <= c->num_sms - 32; n2++) {
         const double bw = std::min(bw_cap, (c->num_sms - n2) * sm_bw);
         const double waves = (double)((tiles.size() + n2 - 1) / n2);
-        const double cost = std::max(split_bytes / bw, waves * t_cta);
+        const double cost = std::max(main_bytes / bw, waves * t_cta);
         if (cost < best - 1e-9) {
           best = cost;
           best_tile_sms = n2;
@@ -966,28 +982,34 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
       }
     }
   }
-  if (side_by_side) {
-    p.early_trigger = 0;
-    PA_CUDA(cudaEventRecord(c->ev_fork, stream));
-    PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
-  } else if (!tiles.empty()) {
-    PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));
+  if (!side_by_side) {
+    if (!tiles.empty()) PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));
+    for (int k = 0; k < 3; k++) {
+      if (!have_class[k]) continue;
+      p.min_cols = 8 * k + 1;
+      p.max_cols = 8 * k + 8;
+      PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream, c->unit_map(layer)));
+    }
+    return PA_OK;
   }
-  bool tile_launched = !side_by_side;
-  for (int k = 0; k < 3; k++) {
-    if (!have_class[k]) continue;
+  for (int k = 0; k < 3; k++) {  // the minor width classes, on every SM
+    if (!have_class[k] || k == main_class) continue;
     p.min_cols = 8 * k + 1;
     p.max_cols = 8 * k + 8;
-    PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream, c->unit_map(layer)));
-    if (!tile_launched) {  // after the first split-KV launch, so that it gets its SMs first
-      PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), c->aux_stream));
-      tile_launched = true;
-    }
+    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream, c->unit_map(layer)));
   }
-  if (side_by_side) {
-    PA_CUDA(cudaEventRecord(c->ev_join, c->aux_stream));
-    PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
-  }
+  // the main class first, so that it gets its SMs; the tile CTAs fill the rest and, as
+  // split-KV CTAs finish, theirs too.  No early trigger: dependents parked on the SMs
+  // would hold registers the tile CTAs need.
+  p.early_trigger = 0;
+  p.min_cols = 8 * main_class + 1;
+  p.max_cols = 8 * main_class + 8;
+  PA_CUDA(cudaEventRecord(c->ev_fork, stream));
+  PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
+  PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream, c->unit_map(layer)));
+  PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), c->aux_stream));
+  PA_CUDA(cudaEventRecord(c->ev_join, c->aux_stream));
+  PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
   return PA_OK;
 }
 
@@ -1026,8 +1048,9 @@ static pa_status decode_step_impl(PagedAttnCache *c, uint32_t layer, void *out, 
     return fail(PA_ERR_INVALID_ARG, "key/value stride must be >= num_kv_heads*head_size and a multiple of 8");
   if (!aligned16(key) || !aligned16(value))
     return fail(PA_ERR_INVALID_ARG, "key/value must be 16-byte aligned");
-  if (!can_fuse_write(c, num_q_heads)) {
-    // FP8 pools (the write quantises), 8- or 32-token blocks, wide GQA groups: two launches
+  if (!can_fuse_write(c, num_q_heads, num_seqs)) {
+    // FP8 pools (the write quantises), 8- or 32-token blocks, wide GQA groups, many items
+    // per CTA: two launches
     st = pa_reshape_and_cache(c, layer, key, value, slot_mapping, num_seqs, key_stride,
                               value_stride, cuda_stream);
     if (st != PA_OK) return st;

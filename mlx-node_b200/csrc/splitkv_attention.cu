@@ -219,10 +219,14 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, long long W, int
 
 constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool block
 
-template <int NT, bool F16, bool FP8, bool B8 = false>
+// FUSE: the variant that also writes the step's new tokens (p.k_new).  It is an
+// instantiation of its own because the mere presence of that code cost the plain
+// kernel 1.5 % (measured), and it exists for the narrow 16-bit kernel only.
+template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false>
 __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
+  static_assert(!FUSE || (NT == 1 && !FP8 && !B8), "the fused write exists for the narrow 16-bit kernel");
   using C = Cfg<NT, FP8>;
   constexpr int NST = C::kStages;
   constexpr int kStageBytes = C::kStageBytes;
@@ -387,7 +391,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   const float sc_log2 = qk_scale * kLog2e;
   const bool use_cap = p.softcap != 1.0f;
 
-  constexpr bool kCanFuseWrite = NT == 1 && !FP8 && !B8;
+  constexpr bool kCanFuseWrite = FUSE;
   const bool fuse_write = kCanFuseWrite && p.k_new != nullptr;
 
   // ---- walk the segments of [lo, hi) -----------------------------------------
@@ -974,6 +978,11 @@ cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cud
                                     dim3(kThreads), Cfg<NT>::kSmemBytes, st, p, maps)
                  : launch_dependent(splitkv_kernel<NT, false, false, true>, dim3(num_ctas),
                                     dim3(kThreads), Cfg<NT>::kSmemBytes, st, p, maps);
+  else if (NT == 1 && p.k_new)
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<1, true, false, false, true>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<1>::kSmemBytes, st, p, maps)
+                 : launch_dependent(splitkv_kernel<1, false, false, false, true>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<1>::kSmemBytes, st, p, maps);
   else
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false>, dim3(num_ctas), dim3(kThreads),
                                     Cfg<NT>::kSmemBytes, st, p, maps)
@@ -1025,6 +1034,12 @@ static cudaError_t configure_nt() {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
+  if (e == cudaSuccess && NT == 1)
+    e = cudaFuncSetAttribute(splitkv_kernel<1, false, false, false, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::kSmemBytes);
+  if (e == cudaSuccess && NT == 1)
+    e = cudaFuncSetAttribute(splitkv_kernel<1, true, false, false, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT>::kSmemBytes);
