@@ -496,6 +496,8 @@ def time_workload(w, steps, warmup, dist, sample_clocks, e2e=True, extra_step=No
     t_load0 = time.perf_counter()
     soak = max(warmup, int(600.0 / max(t_one, 1e-3)))  # >= 0.6 s of the same step under the sampler
     soak = min(soak, 20000)
+    if w.args.no_soak:
+        soak = warmup
     for _ in range(soak - warmup):
         step()
     for _ in range(warmup):
@@ -511,8 +513,9 @@ def time_workload(w, steps, warmup, dist, sample_clocks, e2e=True, extra_step=No
     # The attention call timed ALONE, the way the peaks it is held against were measured
     # (best of 10 single launches, CUDA events): after a pause, so that the clocks are those
     # of a burst and not those the power cap settles at under the long loops above.
-    time.sleep(1.5)
-    for _ in range(2):
+    if not w.args.no_soak:
+        time.sleep(1.5)
+    for _ in range(5):
         w.attn_only()
     burst = min(timed(w.attn_only, 1) for _ in range(10))
     res = {"ms_per_step": total_ms / steps, "attn_ms": burst, "attn_ms_sustained": attn_ms,
@@ -553,33 +556,49 @@ def e2e_leg(w, steps, dist):
             "timed": "host wall clock around synchronous calls with pinned host buffers, max over ranks"}
 
 
-def roofline_of(w, res, peaks, traffic_note=None):
-    """achieved = algorithmic bytes (or flops) of one attention call / its duration timed
-    alone (best of 10 single launches), against the measured burst peak; `sustained` gives
-    the same call inside the long loop (clocks under the power cap) against the sustained
-    peak where there is one."""
+# DRAM traffic per algorithmic byte of the attention call, from one profiler capture each on a
+# small case of the same kernel (inputs larger than L2; traffic grows in proportion to the cached
+# tokens, so it is scaled to the full launch by the algorithmic bytes).  The captures are
+# summarised under profiles/.
+TRAFFIC = {
+    "splitkv": (1.010, "dram__bytes_read.sum + dram__bytes_write.sum of splitkv_kernel on the first 24 sequences "
+                       "of configuration 3 (650.0 MB moved for 643.8 MB algorithmic), scaled by algorithmic bytes"),
+    "tile64": (0.808, "dram__bytes_read.sum + dram__bytes_write.sum of tile_attention_tc64_kernel on one sequence "
+                      "of configuration 4 (61.0 MB moved for 75.5 MB algorithmic: the 32 CTAs that share a kv "
+                      "head are served from L2), scaled by the number of sequences"),
+}
+
+
+def roofline_of(w, res, peaks):
+    """achieved = algorithmic bytes (or flops) of one attention call / its average duration
+    in a back-to-back loop of the timed region (CUDA events), against the measured HBM peak
+    or, for the tensor-bound workload, the measured sustained bf16 peak (the loop runs under
+    the power cap like the seconds-long GEMM loop that peak comes from).  `burst` gives the
+    same call timed alone (best of 10 single launches after a pause) against the burst peak."""
     tensor_bound = w.name == "c4"
-    attn_ms, sus_ms = res["attn_ms"], res["attn_ms_sustained"]
+    burst_ms, loop_ms = res["attn_ms"], res["attn_ms_sustained"]
     if tensor_bound:
-        achieved = w.flops() / (attn_ms * 1e-3) / 1e12
-        sus = w.flops() / (sus_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tf"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["tf"], "traffic": None,
-                "sustained": {"kernel_ms": sus_ms, "achieved": sus, "peak": peaks["tf_sustained"],
-                              "frac": sus / peaks["tf_sustained"] if peaks["tf_sustained"] else None},
-                "kernel": "tile_attention_tc64_kernel" if w.bs == 16 and not w.args.fp8 else "tile_attention_tc_kernel"}
+        work, unit, scale = w.flops(), "TFLOP/s", 1e12
+        peak, peak_burst = peaks["tf_sustained"] or peaks["tf"], peaks["tf"]
+        kernel = "tile_attention_tc64_kernel" if w.bs == 16 and not w.args.fp8 else "tile_attention_tc_kernel"
     else:
-        achieved = w.attn_bytes() / (attn_ms * 1e-3) / 1e9
-        sus = w.attn_bytes() / (sus_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm"], "traffic": None,
-                "sustained": {"kernel_ms": sus_ms, "achieved": sus, "peak": peaks["hbm"], "frac": sus / peaks["hbm"]},
-                "kernel": "splitkv_kernel" if w.decode_only else "splitkv_kernel + tile attention kernel"}
-    roof.update({"traffic_source": traffic_note, "peak_source": peaks["kind"], "kernel_ms": attn_ms,
-                 "timing": "best of 10 single attention calls after a 1.5 s pause (CUDA events), as the peak "
-                           "was measured; `sustained` = the same call in a back-to-back loop",
-                 "algorithmic_bytes": w.attn_bytes(), "algorithmic_flops": w.flops(), "per": "rank"})
-    return roof
+        work, unit, scale = w.attn_bytes(), "GB/s", 1e9
+        peak = peak_burst = peaks["hbm"]
+        kernel = "splitkv_kernel" if w.decode_only else "splitkv_kernel + tile attention kernel"
+    achieved = work / (loop_ms * 1e-3) / scale
+    burst = work / (burst_ms * 1e-3) / scale
+    traffic, traffic_note = None, "not captured for this combination of kernels"
+    if w.bs == 16 and not w.args.fp8 and (w.decode_only or tensor_bound):
+        ratio, traffic_note = TRAFFIC["splitkv" if w.decode_only else "tile64"]
+        traffic = int(ratio * w.attn_bytes())
+    return {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak, "unit": unit,
+            "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_note,
+            "peak_source": peaks["kind"] + (", sustained bf16 figure" if tensor_bound and peaks["tf_sustained"] else ""),
+            "kernel": kernel, "kernel_ms": loop_ms,
+            "burst": {"kernel_ms": burst_ms, "achieved": burst, "peak": peak_burst, "frac": burst / peak_burst},
+            "timing": "average of a back-to-back loop of the attention call inside the timed region (CUDA "
+                      "events); `burst` = best of 10 single calls after a 1.5 s pause, as the burst peak was measured",
+            "algorithmic_bytes": w.attn_bytes(), "algorithmic_flops": w.flops(), "per": "rank"}
 
 
 # ---------------------------------------------------------------------------------------
@@ -603,6 +622,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-also", action="store_true", help="headline workload only")
+    ap.add_argument("--no-soak", action="store_true",
+                    help="skip the 0.6 s soak and the pause before the burst timing (profiler captures: few "
+                         "launches before the captured ones)")
     ap.add_argument("--seqs", type=int, default=0, help="use only the first N sequences (small captures)")
     ap.add_argument("--pool-blocks", type=int, default=0, help="override the pool size in blocks")
     ap.add_argument("--block-size", type=int, default=16, choices=[8, 16, 32],
@@ -698,7 +720,7 @@ def main() -> None:
             also[name] = {
                 "workload": workload_config(name, 1, wl.kv, wl.ql, wl.Hq, wl.Hkv, wl.bs)["workload"],
                 "value": wl.total_q / (r["ms_per_step"] * 1e-3), "unit": "tokens/s",
-                "ms_per_step": r["ms_per_step"], "kernel_ms": r["attn_ms"],
+                "ms_per_step": r["ms_per_step"], "kernel_ms": rf["kernel_ms"],
                 "gpu_launches_per_step": r["launches_per_step"], "roofline": rf,
                 "e2e": r.get("e2e"), "clocks": r["clocks"],
             }

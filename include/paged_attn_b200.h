@@ -281,6 +281,8 @@ pa_status pa_swap_in(PagedAttnCache *cache, uint32_t layer_idx, const uint32_t *
  * pa_gather_heads_wait is that wait on its own, for a caller that wants to put work
  * between the two.
  * Use epoch = 1, 2, 3, ... for successive calls; every rank must make the same calls.
+ * A step with num_tokens = 0 moves nothing and still publishes its flag (local_out and the
+ * entries of peer_out may then be null).
  * Before an output buffer is reused as a peer_out target, all ranks must have consumed
  * its previous contents (alternate two buffers, or separate the steps by a barrier). */
 pa_status pa_gather_heads_peer_store(PagedAttnCache *cache, const void *local_out,
@@ -343,11 +345,13 @@ pa_status pa_paged_attention_decode(PagedAttnCache *cache, uint32_t layer_idx,
  * more than 2 x (SM count) (sequence, kv head) pairs in the batch (the in-kernel
  * write costs its CTA a few microseconds per pair, a launch of its own about
  * four in total) the call runs the write kernel and then the attention kernel.
- *   context_lens (and, for pa_paged_attention_varlen, the query offsets) are read
- * as soon as the launch is scheduled, which may be before earlier kernels of
- * the stream have finished when those were launched with programmatic
- * dependent launch and trigger early: produce them before such a trigger, or
- * on the host.                                                               */
+ *   context_lens and block_tables (and, for pa_paged_attention_varlen, the query
+ * offsets) are read as soon as the launch is scheduled, which may be before
+ * earlier kernels of the stream have finished when those were launched with
+ * programmatic dependent launch and trigger early (this library's own write
+ * and attention kernels do; they write none of these): produce them with
+ * ordinary launches or copies, before such a trigger, or on the host.  Queries,
+ * keys, values and the pools are read after the predecessor has completed.    */
 pa_status pa_decode_step(PagedAttnCache *cache, uint32_t layer_idx, void *out, const void *q,
                          const void *key, const void *value, const int64_t *slot_mapping,
                          const int32_t *block_tables, const int32_t *context_lens,

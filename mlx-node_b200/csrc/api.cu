@@ -550,11 +550,13 @@ pa_status pa_gather_heads_peer_store(PagedAttnCache *c, const void *local_out, i
   if (world < 1 || world > pa::kMaxPeers || rank < 0 || rank >= world)
     return fail(PA_ERR_INVALID_ARG, "world must be 1..8 and 0 <= rank < world");
   if (num_tokens < 0 || heads_local <= 0) return fail(PA_ERR_INVALID_ARG, "bad sizes");
-  if (!local_out || !peer_out || !peer_flags) return fail(PA_ERR_INVALID_ARG, "null pointer");
+  // an empty step moves no rows, so its data pointers may be null; the flags are still published
+  const bool empty = num_tokens == 0;
+  if ((!local_out && !empty) || !peer_out || !peer_flags) return fail(PA_ERR_INVALID_ARG, "null pointer");
   pa::PeerGather a{};
   a.local_out = local_out;
   for (int w = 0; w < world; w++) {
-    if (!peer_out[w] || !peer_flags[w] || !aligned16(peer_out[w]))
+    if ((!peer_out[w] && !empty) || !peer_flags[w] || !aligned16(peer_out[w]))
       return fail(PA_ERR_INVALID_ARG, "peer buffers must be non-null and 16-byte aligned");
     a.peer_out[w] = peer_out[w];
     a.peer_flags[w] = peer_flags[w];

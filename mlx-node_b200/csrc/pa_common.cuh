@@ -31,7 +31,7 @@ constexpr unsigned kErrStepSlot = 8u;    // fused decode step: a slot is not its
 
 constexpr int kSyncWords = 1024;         // arrival counters of a cache handle (AttnParams::sync)
 constexpr int kSyncDone = 1023;          // index of the finished-CTA counter
-constexpr int kMaxSplitCtas = 1000;      // CTAs of one split-KV launch (each has a counter word)
+constexpr int kMaxSplitCtas = 320;       // CTAs of one split-KV launch (each has a counter word and a boundary in shared memory)
 
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -199,6 +199,7 @@ struct AttnParams {
   const int64_t *slot_mapping;
   int64_t k_new_stride, v_new_stride;
   int seq_base;   // first sequence this launch covers
+  int item_cost;  // split-KV partition: what starting an item costs a CTA, in units (set by the launcher)
   int min_cols;   // a sequence is taken by the split-KV launch iff min_cols <= q_len*G <= max_cols
   int max_cols;
 };

@@ -100,8 +100,17 @@ struct Cfg {
   static constexpr int kMergeBytes = (kWarps / 2) * kRegs * 32 * 4;
   static constexpr int kPreBytes = (kMaxSeqsPerLaunch + 1) * 4;
   static constexpr int kBarBytes = kWarps * kStages * 8;
-  static constexpr int kSmemBytes = kRingBytes + kMergeBytes + kPreBytes + 12 + kBarBytes;
+  static constexpr int kBndOffset = (kRingBytes + kMergeBytes + kPreBytes + 12 + kBarBytes + 15) / 16 * 16;
+  static constexpr int kBndBytes = (kMaxSplitCtas + 1) * 8;         // first unit of every CTA
+  static constexpr int kCntBytes = (kMaxSeqsPerLaunch + 2) / 2 * 4;  // eligible sequences before each
+  static constexpr int kSmemBytes = kBndOffset + kBndBytes + kCntBytes;
 };
+// What a CTA pays for every item it starts (queries fetched, eight warps combined, a
+// partial stored, possibly a merge), in units of streaming: measured at about 4 us
+// against 0.16 us per 8 KB unit.  The partition charges it, so that a CTA whose range
+// holds many short sequences gets fewer units and all CTAs finish together.
+constexpr int kItemCostUnits = 24;
+constexpr int kItemCostUnitsFp8 = 16;
 constexpr int kSlotFloats = 36 * kMaxNT * 32;  // one workspace slot, sized for the widest kernel
 
 __device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
@@ -169,51 +178,64 @@ __device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap *m
 // Combines the partials of one split item, (sequence, kv head), whose pieces lie in
 // CTAs [c_first, c_last], and writes the item's final rows.  Called by all threads
 // of the CTA that arrived last; reads go to L2 (the other CTAs wrote these slots).
-// Thread layout: d = tid & 127 (head dimension), two columns at a time.
+// Thread layout: d = tid & 127 (head dimension); a thread takes every second column,
+// four of them per pass, and issues all loads of a pass before it uses any (one round
+// trip to L2 per pass instead of one per column).
 template <int NT, bool F16>
-__device__ __forceinline__ void merge_item(const AttnParams &p, long long W, int num_ctas,
-                                           int c_first, int c_last, int q0, int h, int ncols,
-                                           int tid) {
-  // With fewer units than CTAs some CTAs between c_first and c_last own nothing.
-  auto cta_empty = [&](int c) {
-    return (long long)(c + 1) * W / num_ctas <= (long long)c * W / num_ctas;
-  };
+__device__ __forceinline__ void merge_item(const AttnParams &p, const long long *bnd, int c_first,
+                                           int c_last, int q0, int h, int ncols, int tid) {
+  constexpr int CP = 4;  // columns per pass and thread
+  constexpr int PP = 4;  // pieces per pass
   const int d = tid & 127;
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
-  for (int col = tid >> 7; col < ncols; col += kThreads / 128) {
-    const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
-    const int lane = gid * 4 + tig;
-    const int o_idx = (((mt * NT + nt) * 4 + upper * 2 + par) * 32) + lane;
-    const int m_idx = (32 * NT + nt * 2 + par) * 32 + lane;
-    const int l_idx = (34 * NT + nt * 2 + par) * 32 + lane;
-    // partials in CTA order, four at a time so that their loads overlap
-    float mm = -INFINITY, acc = 0.f, lsum = 0.f;
-    for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-      float mj[4], oj[4], lj[4];
+  for (int col0 = tid >> 7; col0 < ncols; col0 += 2 * CP) {
+    float mm[CP], acc[CP], lsum[CP];
 #pragma unroll
-      for (int k = 0; k < 4; k++) {
+    for (int i = 0; i < CP; i++) { mm[i] = -INFINITY; acc[i] = 0.f; lsum[i] = 0.f; }
+    // partials in CTA order
+    for (int c0 = c_first; c0 <= c_last; c0 += PP) {
+      float mj[CP][PP], oj[CP][PP], lj[CP][PP];
+#pragma unroll
+      for (int k = 0; k < PP; k++) {
         const int c = c0 + k;
-        const bool use = c <= c_last && !cta_empty(c);
+        // CTAs between c_first and c_last may own nothing
+        const bool piece = c <= c_last && bnd[c + 1] > bnd[c];
         const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
-        mj[k] = use ? __ldcg(slot + m_idx) : -INFINITY;
-        oj[k] = use ? __ldcg(slot + o_idx) : 0.f;
-        lj[k] = use ? __ldcg(slot + l_idx) : 0.f;
-      }
-      const float m_new = fmaxf(fmaxf(fmaxf(mj[0], mj[1]), fmaxf(mj[2], mj[3])), mm);
-      const float keep = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
-      acc *= keep;
-      lsum *= keep;
 #pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const float w = mj[k] == -INFINITY ? 0.f : exp2f(mj[k] - m_new);
-        acc += oj[k] * w;
-        lsum += lj[k] * w;
+        for (int i = 0; i < CP; i++) {
+          const int col = col0 + 2 * i;
+          const bool use = piece && col < ncols;
+          const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
+          const int lane = gid * 4 + tig;
+          mj[i][k] = use ? __ldcg(slot + (32 * NT + nt * 2 + par) * 32 + lane) : -INFINITY;
+          oj[i][k] = use ? __ldcg(slot + ((mt * NT + nt) * 4 + upper * 2 + par) * 32 + lane) : 0.f;
+          lj[i][k] = use ? __ldcg(slot + (34 * NT + nt * 2 + par) * 32 + lane) : 0.f;
+        }
       }
-      mm = m_new;
+#pragma unroll
+      for (int i = 0; i < CP; i++) {
+        const float m_new = fmaxf(fmaxf(fmaxf(mj[i][0], mj[i][1]), fmaxf(mj[i][2], mj[i][3])), mm[i]);
+        const float keep = mm[i] == -INFINITY ? 0.f : exp2f(mm[i] - m_new);
+        acc[i] *= keep;
+        lsum[i] *= keep;
+#pragma unroll
+        for (int k = 0; k < PP; k++) {
+          const float w = mj[i][k] == -INFINITY ? 0.f : exp2f(mj[i][k] - m_new);
+          acc[i] += oj[i][k] * w;
+          lsum[i] += lj[i][k] * w;
+        }
+        mm[i] = m_new;
+      }
     }
-    const int qj = col / p.G, g = col - qj * p.G;
-    p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
-        to_elem<F16>(lsum > 0.f ? acc / lsum : 0.f);
+#pragma unroll
+    for (int i = 0; i < CP; i++) {
+      const int col = col0 + 2 * i;
+      if (col < ncols) {
+        const int qj = col / p.G, g = col - qj * p.G;
+        p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
+            to_elem<F16>(lsum[i] > 0.f ? acc[i] / lsum[i] : 0.f);
+      }
+    }
   }
 }
 
@@ -238,6 +260,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   int *pre = reinterpret_cast<int *>(smem + C::kRingBytes + C::kMergeBytes);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kRingBytes + C::kMergeBytes +
                                                 ((C::kPreBytes + 15) / 16) * 16);
+  long long *bnd = reinterpret_cast<long long *>(smem + C::kBndOffset);
+  uint16_t *cnt = reinterpret_cast<uint16_t *>(smem + C::kBndOffset + C::kBndBytes);
 
   __shared__ int s_last;  // this CTA arrived last at a split item and combines it
 
@@ -260,23 +284,67 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   }
   __syncthreads();
   if (warp == 0) {
-    int running = 0;
+    int running = 0, running_n = 0;
+    if (lane == 0) cnt[0] = 0;
     for (int base = 0; base < S; base += 32) {
       int v = (base + lane < S) ? pre[base + lane + 1] : 0;
+      const unsigned have = __ballot_sync(0xffffffffu, v > 0);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int n = __shfl_up_sync(0xffffffffu, v, o);
         if (lane >= o) v += n;
       }
-      if (base + lane < S) pre[base + lane + 1] = running + v;
+      if (base + lane < S) {
+        pre[base + lane + 1] = running + v;
+        cnt[base + lane + 1] = (uint16_t)(running_n + __popc(have & (0xffffffffu >> (31 - lane))));
+      }
       running += __shfl_sync(0xffffffffu, v, 31);
+      running_n += __popc(have);
     }
   }
   __syncthreads();
 
+  // ---- the partition: bnd[c] = first unit of CTA c ------------------------------
+  // Equal shares of units + item_cost per item: in that weighted order an item is
+  // item_cost slots of padding followed by its units, CTA c starts at share c of the
+  // weighted total, and a start inside the padding moves to the item's first unit.
   const long long W = (long long)Hkv * pre[S];
-  const long long lo = (long long)blockIdx.x * W / gridDim.x;
-  const long long hi = (long long)(blockIdx.x + 1) * W / gridDim.x;
+  {
+    const int K = p.item_cost;
+    const long long Wt = W + (long long)Hkv * K * cnt[S];
+    for (int c = tid; c <= (int)gridDim.x; c += kThreads) {
+      long long f;
+      if (c == (int)gridDim.x) {
+        f = W;
+      } else if (K <= 0) {
+        f = (long long)c * W / gridDim.x;
+      } else {
+        const long long t = (long long)c * Wt / gridDim.x;
+        int a = 0, b = S - 1;  // smallest s whose weighted range ends beyond t
+        while (a < b) {
+          const int mid = (a + b) >> 1;
+          if ((long long)Hkv * (pre[mid + 1] + (long long)K * cnt[mid + 1]) > t) b = mid; else a = mid + 1;
+        }
+        const int nb_a = pre[a + 1] - pre[a];
+        const long long r = t - (long long)Hkv * (pre[a] + (long long)K * cnt[a]);
+        const long long hh = r / (nb_a + K), off = r - hh * (nb_a + K);
+        f = (long long)Hkv * pre[a] + hh * nb_a + (off > K ? off - K : 0);
+      }
+      bnd[c] = f;
+    }
+  }
+  __syncthreads();
+  const long long lo = bnd[blockIdx.x];
+  const long long hi = bnd[blockIdx.x + 1];
+  // the CTA whose range holds unit u
+  auto cta_of = [&](long long u) {
+    int a = 0, b = (int)gridDim.x - 1;
+    while (a < b) {
+      const int mid = (a + b + 1) >> 1;
+      if (bnd[mid] <= u) a = mid; else b = mid - 1;
+    }
+    return a;
+  };
   const int n_local = (int)(hi - lo);
   const int n_w = n_local > warp ? (n_local - warp + kWarps - 1) / kWarps : 0;
 
@@ -292,9 +360,16 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   // Pool chunk index (block id * Hkv + kv head) of this warp's j-th unit; with 32-token
   // blocks, twice that plus the unit's place in the chunk.
   // B8: the argument is 2 * j + (0: first, 1: second pool block of the unit).
-  auto lookup = [&](int jj) -> uint32_t {
+  // In two halves, so that the table reads of several look-ups can be in flight together:
+  // locate() finds the table entry, resolve() turns what was read there into the chunk.
+  struct Loc {
+    const int32_t *entry;  // null: no table entry to read (see `fixed`)
+    uint32_t fixed;        // the result then: 0 (no such unit) or kNoBlock
+    int h, b;
+  };
+  auto locate = [&](int jj) -> Loc {
     const int j = B8 ? jj >> 1 : jj;
-    if (j >= n_w) return 0u;
+    if (j >= n_w) return Loc{nullptr, 0u, 0, 0};
     const long long u = lo + warp + (long long)kWarps * j;
     const int s = seq_of(u);
     const int r = (int)(u - (long long)Hkv * pre[s]);
@@ -304,18 +379,36 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     int col;  // block-table column
     if (B8) {
       col = 2 * b + (jj & 1);
-      if (col * 8 >= p.context_lens[p.seq_base + s]) return kNoBlock;
+      if (col * 8 >= p.context_lens[p.seq_base + s]) return Loc{nullptr, kNoBlock, h, b};
     } else {
       col = b >> p.bs_shift;
     }
-    uint32_t id = (uint32_t)p.block_tables[(long long)row * p.MB + col];
+    return Loc{p.block_tables + (long long)row * p.MB + col, 0u, h, b};
+  };
+  auto resolve = [&](const Loc &at, int32_t raw) -> uint32_t {
+    if (!at.entry) return at.fixed;
+    uint32_t id = (uint32_t)raw;
     if (id >= p.num_blocks) {
       atomicOr(p.err, kErrBlockRange);
       id = 0;
     }
-    const uint32_t chunk = id * (uint32_t)Hkv + (uint32_t)h;
-    return (!B8 && p.bs_shift) ? 2u * chunk + (uint32_t)(b & 1) : chunk;
+    const uint32_t chunk = id * (uint32_t)Hkv + (uint32_t)at.h;
+    return (!B8 && p.bs_shift) ? 2u * chunk + (uint32_t)(at.b & 1) : chunk;
   };
+  auto lookup = [&](int jj) -> uint32_t {
+    const Loc at = locate(jj);
+    return resolve(at, at.entry ? *at.entry : 0);
+  };
+  // The first two batches of look-ups, both reads in flight together.  Like the context
+  // lengths above, the block tables are read before the wait below.
+  uint32_t first_ids, second_ids;
+  {
+    const Loc a0 = locate(lane), a1 = locate(32 + lane);
+    const int32_t r0 = a0.entry ? *a0.entry : 0;
+    const int32_t r1 = a1.entry ? *a1.entry : 0;
+    first_ids = resolve(a0, r0);
+    second_ids = resolve(a1, r1);
+  }
 
   // This grid may have started while the KV write before it was still running: the
   // pool (and the workspace and output rows a previous call may still be reading or
@@ -339,7 +432,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     constexpr bool EXACT = decltype(exact_tag)::value;
   const uint32_t ring_w = smem_u32(ring) + warp * NST * kStageBytes;
   const uint32_t bar_w = smem_u32(&bars[warp * NST]);
-  uint32_t cur_ids = lookup(lane), nxt_ids = lookup(32 + lane);
+  uint32_t cur_ids = first_ids, nxt_ids = second_ids;
   int ji = 0;  // units issued by this warp
   constexpr int kBatch = B8 ? 16 : 32;  // units per lookup
   auto issue = [&]() {  // whole warp calls; lane 0 issues unit ji
@@ -381,7 +474,11 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     }
     ji++;
   };
-  for (int j = 0; j < NST && j < n_w; j++) issue();
+  // 16-bit pools: the first copies are issued inside the first segment below, right
+  // behind its query loads (see there); FP8 converts its queries as they arrive, so
+  // there the copies go first.
+  if constexpr (FP8)
+    for (int j = 0; j < NST && j < n_w; j++) issue();
 
   int jc = 0;          // units consumed by this warp
   bool dead = false;   // a wait ran out: stop touching data, keep the barriers balanced
@@ -492,11 +589,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
 #pragma unroll
         for (int j = 0; j < 8; j++) qf[nt][j][0] = qf[nt][j][1] = 0u;
       }
+      if (QK8) {
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        const int cc = nt * 8 + 2 * tig + c;
-        lim[nt][c] = cc < ncols ? kv_len - q_len + cc / G + 1 : 0;
-        if (QK8) {
+        for (int c = 0; c < 2; c++) {
           // the exponent of column 2tig+c sits with the threads whose gid is that column;
           // in the fast variant the K bytes are taken at face value (no 2^8 left out)
           const int e = __shfl_sync(0xffffffffu, q_exp, (2 * tig + c) * 4);
@@ -504,6 +599,21 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         }
       }
     }
+    // First segment: the ring starts here, behind the query loads issued above and before
+    // anything waits for them or for the context length.  Issued the other way round,
+    // those few loads queue behind the first ~28 MB of bulk copies of the whole grid
+    // (measured: 3 us instead of 1).
+    if constexpr (!FP8) {
+      if (a == 0)
+        for (int j = 0; j < NST && j < n_w; j++) issue();
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        const int cc = nt * 8 + 2 * tig + c;
+        lim[nt][c] = cc < ncols ? kv_len - q_len + cc / G + 1 : 0;
+      }
     const int min_lim = kv_len - q_len + 1;
 
     float o[8][NT][4];
@@ -797,49 +907,58 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       }
     }
 
-    // ---- combine the eight warps' partials (fixed tree order) -----------------
-    for (int half = kWarps / 2; half >= 1; half >>= 1) {
-      if (warp >= half && warp < 2 * half) {
-        float *dst = merge_buf + (warp - half) * (C::kRegs * 32) + lane;
+    // ---- combine the eight warps' partials (fixed order) -----------------------
+    // Warps 4-7 hand theirs to warps 0-3 through four slots; warps 1-3 then put their
+    // sums back into the slot they have just read (a lane reads and writes its own
+    // column only) and warp 0 adds them in order: three barriers per item.
+    auto put = [&](int slot) {
+      float *dst = merge_buf + slot * (C::kRegs * 32) + lane;
 #pragma unroll
-        for (int mt = 0; mt < 8; mt++)
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) dst[((mt * NT + nt) * 4 + i) * 32] = o[mt][nt][i];
+      for (int mt = 0; mt < 8; mt++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-          for (int c = 0; c < 2; c++) {
-            dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
-            dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
-          }
-      }
-      __syncthreads();
-      if (warp < half) {
-        const float *src = merge_buf + warp * (C::kRegs * 32) + lane;
+          for (int i = 0; i < 4; i++) dst[((mt * NT + nt) * 4 + i) * 32] = o[mt][nt][i];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          float wa[2], wb[2];
+      for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-          for (int c = 0; c < 2; c++) {
-            const float mb = src[(32 * NT + nt * 2 + c) * 32];
-            const float lb = src[(34 * NT + nt * 2 + c) * 32];
-            const float mm = fmaxf(m[nt][c], mb);
-            wa[c] = m[nt][c] == -INFINITY ? 0.f : fast_exp2(m[nt][c] - mm);
-            wb[c] = mb == -INFINITY ? 0.f : fast_exp2(mb - mm);
-            m[nt][c] = mm;
-            l[nt][c] = l[nt][c] * wa[c] + lb * wb[c];
-          }
-#pragma unroll
-          for (int mt = 0; mt < 8; mt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-              o[mt][nt][i] = o[mt][nt][i] * wa[i & 1] + src[((mt * NT + nt) * 4 + i) * 32] * wb[i & 1];
+        for (int c = 0; c < 2; c++) {
+          dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
+          dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
         }
+    };
+    auto take = [&](int slot) {
+      const float *src = merge_buf + slot * (C::kRegs * 32) + lane;
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        float wa[2], wb[2];
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const float mb = src[(32 * NT + nt * 2 + c) * 32];
+          const float lb = src[(34 * NT + nt * 2 + c) * 32];
+          const float mm = fmaxf(m[nt][c], mb);
+          wa[c] = m[nt][c] == -INFINITY ? 0.f : fast_exp2(m[nt][c] - mm);
+          wb[c] = mb == -INFINITY ? 0.f : fast_exp2(mb - mm);
+          m[nt][c] = mm;
+          l[nt][c] = l[nt][c] * wa[c] + lb * wb[c];
+        }
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++)
+            o[mt][nt][i] = o[mt][nt][i] * wa[i & 1] + src[((mt * NT + nt) * 4 + i) * 32] * wb[i & 1];
       }
-      __syncthreads();
+    };
+    if (warp >= kWarps / 2) put(warp - kWarps / 2);
+    __syncthreads();
+    if (warp < kWarps / 2) take(warp);
+    if (warp >= 1 && warp < kWarps / 2) put(warp);
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int w2 = 1; w2 < kWarps / 2; w2++) take(w2);
     }
+    __syncthreads();
 
     const bool partial = b0 > 0 || b1 < nb;
     if (warp == 0) {
@@ -895,13 +1014,12 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     // ---- a split item: count this piece; the last piece to arrive combines them ----
     if (partial) {
       const long long U0 = (long long)Hkv * pre[s] + (long long)h * nb, U1 = U0 + nb;
-      const int c_first = (int)(((U0 + 1) * gridDim.x - 1) / W);
-      const int c_last = (int)((U1 * gridDim.x - 1) / W);
-      // Pieces of the item: one per CTA of [c_first, c_last]; with fewer units than CTAs
-      // every unit sits in a CTA of its own and the CTAs in between own nothing.
-      const unsigned pieces = W >= (long long)gridDim.x ? (unsigned)(c_last - c_first + 1) : (unsigned)nb;
+      const int c_first = cta_of(U0), c_last = cta_of(U1 - 1);
       __syncthreads();
       if (tid == 0) {
+        // Pieces of the item: one per CTA of [c_first, c_last] that owns anything.
+        unsigned pieces = 0;
+        for (int c = c_first; c <= c_last; c++) pieces += bnd[c + 1] > bnd[c] ? 1u : 0u;
         // c_first holds the item as its last one, so the word is this item's alone
         const unsigned arrived = atomicAdd(p.sync + c_first, 1u) + 1u;
         s_last = arrived == pieces;
@@ -910,7 +1028,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       __syncthreads();
       if (s_last) {
         __threadfence();
-        merge_item<NT, F16>(p, W, (int)gridDim.x, c_first, c_last, q0, h, ncols, tid);
+        merge_item<NT, F16>(p, bnd, c_first, c_last, q0, h, ncols, tid);
       }
     }
 
@@ -1126,6 +1244,7 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
     AttnParams p = p_in;
     p.seq_base = p_in.seq_base + base;
     p.S = min(kMaxSeqsPerLaunch, p_in.S - base);
+    p.item_cost = p.is_fp8 ? kItemCostUnitsFp8 : kItemCostUnits;
     cudaError_t e;
     if (nt <= 1) e = launch_nt<1>(p, maps, num_ctas, st);
     else if (nt == 2) e = launch_nt<2>(p, maps, num_ctas, st);
