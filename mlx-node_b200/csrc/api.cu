@@ -99,7 +99,9 @@ struct PagedAttnCache {
   cudaStream_t step_stream = nullptr;
   // second stream and fork/join events for calls that run two kernels side by side
   cudaStream_t aux_stream = nullptr;
+  cudaStream_t lane_stream[2] = {nullptr, nullptr};
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaEvent_t ev_lane[2] = {nullptr, nullptr};
 };
 
 struct mlx_array {
@@ -199,6 +201,10 @@ pa_status finish_create(PagedAttnCache *c) {
   PA_CUDA(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
   PA_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
   PA_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+  for (int i = 0; i < 2; i++) {
+    PA_CUDA(cudaStreamCreateWithFlags(&c->lane_stream[i], cudaStreamNonBlocking));
+    PA_CUDA(cudaEventCreateWithFlags(&c->ev_lane[i], cudaEventDisableTiming));
+  }
   return PA_OK;
 }
 
@@ -391,6 +397,10 @@ pa_status pa_cache_free(PagedAttnCache *c) {
   if (c->aux_stream) cudaStreamDestroy(c->aux_stream);
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
+  for (int i = 0; i < 2; i++) {
+    if (c->lane_stream[i]) cudaStreamDestroy(c->lane_stream[i]);
+    if (c->ev_lane[i]) cudaEventDestroy(c->ev_lane[i]);
+  }
   delete c;
   return PA_OK;
 }
@@ -943,48 +953,50 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     PA_CUDA(cudaMemcpyAsync(work_dev, tiles.data(), tiles.size() * sizeof(pa::TileWork),
                             cudaMemcpyHostToDevice, stream));
 
-  // A batch that holds both kinds of work runs them side by side: the tensor-bound tile
-  // kernel on a second stream, the memory-bound split-KV kernel of the batch's largest
-  // width class on fewer CTAs; the other width classes (a few verify sequences, say) run
-  // first on the whole GPU, so that only two grids ever compete for SMs.  The split is
-  // chosen from a small model measured on B200: split-KV streams about 70 GB/s per SM up
-  // to about 6 TB/s in total (100 SMs already saturate HBM); a tile CTA sustains about
-  // 1.1 PFLOP/s / 148 (0.9 with 32-token blocks) and tile CTAs run in waves over the SMs
-  // they get.  Without host context lengths there is no estimate and the kernels run back
-  // to back.
-  int split_ctas = c->num_sms;
-  bool side_by_side = false;
-  int main_class = 0;
-  for (int k = 1; k < 3; k++)
-    if (class_bytes[k] > class_bytes[main_class]) main_class = k;
-  if (!tiles.empty() && any_split && context_lens_host) {
-    // (FP8 cache: the tile kernel converts bytes as it goes and sustains about 0.6 PFLOP/s;
-    // the split-KV kernel streams about 30 GB/s per SM, 4.4 TB/s on the whole GPU)
-    const double tile_rate = c->fp8 ? 0.6e15 : (c->has_tile64() ? 1.1e15 : 0.9e15);
-    const double sm_bw = c->fp8 ? 30e9 : 70e9, bw_cap = c->fp8 ? 4.4e12 : 6.0e12;
-    const double main_bytes = class_bytes[main_class];
-    const double t_cta = tile_flops / (double)tiles.size() / (tile_rate / c->num_sms);
-    const double t_tile_alone = t_cta * (double)((tiles.size() + c->num_sms - 1) / c->num_sms);
-    const double t_split_alone = main_bytes / bw_cap;
-    if (t_tile_alone > 20e-6 && t_split_alone > 20e-6) {
-      double best = 1e30;
-      int best_tile_sms = 0;
-      for (int n2 = 8; n2 <= c->num_sms - 32; n2++) {
-        const double bw = std::min(bw_cap, (c->num_sms - n2) * sm_bw);
-        const double waves = (double)((tiles.size() + n2 - 1) / n2);
-        const double cost = std::max(main_bytes / bw, waves * t_cta);
-        if (cost < best - 1e-9) {
-          best = cost;
-          best_tile_sms = n2;
+  // A batch that holds several kinds of work runs them side by side, each kernel on a
+  // share of the SMs and on a stream of its own: the tensor-bound tile kernel and one
+  // memory-bound split-KV launch per width class present (each launch "lane" keeps its
+  // partial slots and counters apart from the others').  Run one after the other, every
+  // kernel would pay its start-up and tail on the whole GPU and a few verify sequences
+  // would hold 148 SMs for tens of microseconds.  The shares come from a small model
+  // measured on B200: the narrow split-KV kernel streams about 70 GB/s per SM up to about
+  // 6 TB/s in total (100 SMs already saturate HBM); the wider ones (two and three column
+  // tiles: more tensor work per unit, a two-stage ring) a half and two fifths of that per
+  // SM; a tile CTA sustains about 1.1 PFLOP/s / 148 (0.9 with 32-token blocks) and tile
+  // CTAs run in waves over the SMs they get.  Without host context lengths there is no
+  // estimate and the kernels run back to back.
+  int n_classes = 0;
+  for (int k = 0; k < 3; k++) n_classes += have_class[k] ? 1 : 0;
+  const double class_weight[3] = {1.0, 2.0, 2.5};
+  double eff_bytes = 0.0;  // bytes in units of the narrow kernel's per-SM rate
+  for (int k = 0; k < 3; k++) eff_bytes += class_bytes[k] * class_weight[k];
+  // (FP8 cache: the tile kernel converts bytes as it goes and sustains about 0.6 PFLOP/s;
+  // the split-KV kernel streams about 30 GB/s per SM, 4.4 TB/s on the whole GPU)
+  const double tile_rate = c->fp8 ? 0.6e15 : (c->has_tile64() ? 1.1e15 : 0.9e15);
+  const double sm_bw = c->fp8 ? 30e9 : 70e9, bw_cap = c->fp8 ? 4.4e12 : 6.0e12;
+  int tile_sms = 0;
+  bool concurrent = false;
+  if (context_lens_host && any_split && eff_bytes / bw_cap > 20e-6) {
+    if (!tiles.empty()) {
+      const double t_cta = tile_flops / (double)tiles.size() / (tile_rate / c->num_sms);
+      const double t_tile_alone = t_cta * (double)((tiles.size() + c->num_sms - 1) / c->num_sms);
+      if (t_tile_alone > 20e-6) {
+        double best = 1e30;
+        for (int n2 = 8; n2 <= c->num_sms - 32; n2++) {
+          const double bw = std::min(bw_cap, (c->num_sms - n2) * sm_bw);
+          const double waves = (double)((tiles.size() + n2 - 1) / n2);
+          const double cost = std::max(eff_bytes / bw, waves * t_cta);
+          if (cost < best - 1e-9) {
+            best = cost;
+            tile_sms = n2;
+          }
         }
-      }
-      if (best_tile_sms > 0 && best < t_tile_alone + t_split_alone) {
-        split_ctas = c->num_sms - best_tile_sms;
-        side_by_side = true;
+        if (best >= t_tile_alone + eff_bytes / bw_cap) tile_sms = 0;
       }
     }
+    concurrent = tile_sms > 0 || n_classes > 1;
   }
-  if (!side_by_side) {
+  if (!concurrent) {
     if (!tiles.empty()) PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));
     for (int k = 0; k < 3; k++) {
       if (!have_class[k]) continue;
@@ -994,24 +1006,57 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
     }
     return PA_OK;
   }
-  for (int k = 0; k < 3; k++) {  // the minor width classes, on every SM
-    if (!have_class[k] || k == main_class) continue;
+  // SMs of the split-KV classes, in proportion to their weighted bytes, four at least
+  const int split_sms = c->num_sms - tile_sms;
+  int share[3] = {0, 0, 0};
+  {
+    int given = 0, largest = 0;
+    for (int k = 0; k < 3; k++) {
+      if (!have_class[k]) continue;
+      share[k] = std::max(4, (int)(split_sms * class_bytes[k] * class_weight[k] / eff_bytes));
+      given += share[k];
+      if (class_bytes[k] * class_weight[k] > class_bytes[largest] * class_weight[largest] || !have_class[largest])
+        largest = k;
+    }
+    share[largest] += split_sms - given;  // rounding, and what the minimum shares took
+    if (share[largest] < 4) {             // cannot happen with 148 SMs and three classes; stay safe
+      share[largest] = 4;
+    }
+  }
+  // No early trigger: dependents parked on the SMs would hold registers and shared memory
+  // the other kernels' CTAs need.
+  p.early_trigger = 0;
+  PA_CUDA(cudaEventRecord(c->ev_fork, stream));
+  // the largest class on the caller's stream, first, so that it gets its SMs; then the
+  // other classes; the tile CTAs fill the rest and, as split-KV CTAs finish, theirs too
+  int order[3] = {0, 1, 2};
+  std::sort(order, order + 3, [&](int x, int y) { return share[x] > share[y]; });
+  int lane = 0, cta_base = 0;
+  for (int i = 0; i < 3; i++) {
+    const int k = order[i];
+    if (!have_class[k]) continue;
+    cudaStream_t ls = lane == 0 ? stream : c->lane_stream[lane - 1];
+    if (lane > 0) PA_CUDA(cudaStreamWaitEvent(ls, c->ev_fork, 0));
     p.min_cols = 8 * k + 1;
     p.max_cols = 8 * k + 8;
-    PA_CUDA(pa::launch_splitkv_attention(p, c->num_sms, stream, c->unit_map(layer)));
+    p.lane = lane;
+    p.cta_base = cta_base;
+    PA_CUDA(pa::launch_splitkv_attention(p, share[k], ls, c->unit_map(layer)));
+    if (lane > 0) {
+      PA_CUDA(cudaEventRecord(c->ev_lane[lane - 1], ls));
+      PA_CUDA(cudaStreamWaitEvent(stream, c->ev_lane[lane - 1], 0));
+    }
+    cta_base += (c->fp8 && k == 0) ? 2 * share[k] : share[k];  // the narrow FP8 kernel runs two CTAs per SM
+    lane++;
   }
-  // the main class first, so that it gets its SMs; the tile CTAs fill the rest and, as
-  // split-KV CTAs finish, theirs too.  No early trigger: dependents parked on the SMs
-  // would hold registers the tile CTAs need.
-  p.early_trigger = 0;
-  p.min_cols = 8 * main_class + 1;
-  p.max_cols = 8 * main_class + 8;
-  PA_CUDA(cudaEventRecord(c->ev_fork, stream));
-  PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
-  PA_CUDA(pa::launch_splitkv_attention(p, split_ctas, stream, c->unit_map(layer)));
-  PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), c->aux_stream));
-  PA_CUDA(cudaEventRecord(c->ev_join, c->aux_stream));
-  PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
+  if (tile_sms > 0) {
+    PA_CUDA(cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
+    PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), c->aux_stream));
+    PA_CUDA(cudaEventRecord(c->ev_join, c->aux_stream));
+    PA_CUDA(cudaStreamWaitEvent(stream, c->ev_join, 0));
+  } else if (!tiles.empty()) {
+    PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));
+  }
   return PA_OK;
 }
 

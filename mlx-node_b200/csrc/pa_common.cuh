@@ -30,7 +30,8 @@ constexpr unsigned kErrTimeout = 4u;     // a bounded wait ran out
 constexpr unsigned kErrStepSlot = 8u;    // fused decode step: a slot is not its sequence's last position
 
 constexpr int kSyncWords = 1024;         // arrival counters of a cache handle (AttnParams::sync)
-constexpr int kSyncDone = 1023;          // index of the finished-CTA counter
+constexpr int kSyncDone = 1023;          // index of the finished-CTA counter (launch lane 0; lane i uses kSyncDone - i)
+constexpr int kMaxLanes = 3;             // split-KV launches of one call that may run at the same time
 constexpr int kMaxSplitCtas = 320;       // CTAs of one split-KV launch (each has a counter word and a boundary in shared memory)
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -80,6 +81,21 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// The same with an L2 eviction policy for the lines it brings in (see l2_evict_first).
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void *src, uint32_t bytes,
+                                              uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1], %2, [%3], %4;" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+// Policy "evict these lines first": for data that is read once and not again soon.
+__device__ __forceinline__ uint64_t l2_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
 
 // ---- warp-level tensor-core pieces ------------------------------------------
@@ -199,6 +215,10 @@ struct AttnParams {
   const int64_t *slot_mapping;
   int64_t k_new_stride, v_new_stride;
   int seq_base;   // first sequence this launch covers
+  // Several split-KV launches of one call may run at the same time (one per width class):
+  // launch lane i keeps its partial slots and arrival counters from CTA index cta_base on
+  // and counts its finished CTAs on word kSyncDone - lane.
+  int cta_base, lane;
   int item_cost;  // split-KV partition: what starting an item costs a CTA, in units (set by the launcher)
   int min_cols;   // a sequence is taken by the split-KV launch iff min_cols <= q_len*G <= max_cols
   int max_cols;

@@ -200,7 +200,7 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, const long long 
         const int c = c0 + k;
         // CTAs between c_first and c_last may own nothing
         const bool piece = c <= c_last && bnd[c + 1] > bnd[c];
-        const float *slot = p.ws + (size_t)(2 * c + (c == c_first ? 1 : 0)) * kSlotFloats;
+        const float *slot = p.ws + (size_t)(2 * (p.cta_base + c) + (c == c_first ? 1 : 0)) * kSlotFloats;
 #pragma unroll
         for (int i = 0; i < CP; i++) {
           const int col = col0 + 2 * i;
@@ -435,6 +435,13 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   uint32_t cur_ids = first_ids, nxt_ids = second_ids;
   int ji = 0;  // units issued by this warp
   constexpr int kBatch = B8 ? 16 : 32;  // units per lookup
+  // A launch that reads more than L2 holds reads every chunk once: its lines are marked
+  // "evict first", so that they do not push out what is reused - the queries and partials
+  // of this grid and, in a mixed batch, the KV tiles the tile kernel's CTAs share.  A
+  // small batch (everything fits in L2) keeps the default: the next layer's or step's
+  // call may find its blocks still there.
+  const bool stream_once = W * (long long)kStageBytes > (96ll << 20);
+  const uint64_t evict_first = l2_evict_first();
   auto issue = [&]() {  // whole warp calls; lane 0 issues unit ji
     if ((ji & (kBatch - 1)) == 0 && ji > 0) {
       cur_ids = nxt_ids;
@@ -464,6 +471,12 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         mbar_expect_tx(bar, kStageBytes);
         tma_load_unit(dst, &maps.k, unit * (FP8 ? 256 : 128), ch, bar);
         tma_load_unit(dst + kChunk, &maps.v, unit * 16, ch, bar);
+      } else if (stream_once) {
+        mbar_expect_tx(bar, kStageBytes);
+        bulk_g2s_hint(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk,
+                      kChunk, bar, evict_first);
+        bulk_g2s_hint(dst + kChunk, reinterpret_cast<const uint8_t *>(p.v_pool) + (size_t)chunk * kChunk,
+                      kChunk, bar, evict_first);
       } else {
         mbar_expect_tx(bar, kStageBytes);
         bulk_g2s(dst, reinterpret_cast<const uint8_t *>(p.k_pool) + (size_t)chunk * kChunk, kChunk,
@@ -973,7 +986,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           l[nt][c] = v;
         }
       if (partial) {
-        float *dst = p.ws + (size_t)(2 * blockIdx.x + (b0 > 0 ? 0 : 1)) * kSlotFloats + lane;
+        float *dst = p.ws + (size_t)(2 * (p.cta_base + blockIdx.x) + (b0 > 0 ? 0 : 1)) * kSlotFloats + lane;
 #pragma unroll
         for (int mt = 0; mt < 8; mt++)
 #pragma unroll
@@ -1021,9 +1034,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         unsigned pieces = 0;
         for (int c = c_first; c <= c_last; c++) pieces += bnd[c + 1] > bnd[c] ? 1u : 0u;
         // c_first holds the item as its last one, so the word is this item's alone
-        const unsigned arrived = atomicAdd(p.sync + c_first, 1u) + 1u;
+        const unsigned arrived = atomicAdd(p.sync + p.cta_base + c_first, 1u) + 1u;
         s_last = arrived == pieces;
-        if (arrived == pieces) atomicExch(p.sync + c_first, 0u);
+        if (arrived == pieces) atomicExch(p.sync + p.cta_base + c_first, 0u);
       }
       __syncthreads();
       if (s_last) {
@@ -1057,8 +1070,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     __syncthreads();
     if (tid == 0) {
       __threadfence();
-      if (atomicAdd(p.sync + kSyncDone, 1u) + 1u == gridDim.x) {
-        atomicExch(p.sync + kSyncDone, 0u);
+      if (atomicAdd(p.sync + kSyncDone - p.lane, 1u) + 1u == gridDim.x) {
+        atomicExch(p.sync + kSyncDone - p.lane, 0u);
         *p.err_mirror = *reinterpret_cast<volatile unsigned *>(p.err);
       }
     }
@@ -1238,8 +1251,11 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
   // CTAs: one per SM the caller grants, two for the variant built to share an SM, as far
   // as the workspace has partial-result slots for them.
   int num_ctas = num_sms_used;
-  if (p_in.is_fp8 && nt <= 1 && 2 * num_sms_used <= p_in.ws_ctas) num_ctas = 2 * num_sms_used;
-  if (num_ctas > kMaxSplitCtas || !p_in.sync) return cudaErrorInvalidValue;
+  if (p_in.is_fp8 && nt <= 1 && p_in.cta_base + 2 * num_sms_used <= p_in.ws_ctas) num_ctas = 2 * num_sms_used;
+  if (num_ctas < 1 || num_ctas > kMaxSplitCtas || !p_in.sync || p_in.cta_base < 0 ||
+      p_in.cta_base + num_ctas > p_in.ws_ctas || p_in.cta_base + num_ctas > kSyncDone - kMaxLanes ||
+      p_in.lane < 0 || p_in.lane >= kMaxLanes)
+    return cudaErrorInvalidValue;
   for (int base = 0; base < p_in.S; base += kMaxSeqsPerLaunch) {
     AttnParams p = p_in;
     p.seq_base = p_in.seq_base + base;
