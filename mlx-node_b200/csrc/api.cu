@@ -71,14 +71,14 @@ struct PagedAttnCache {
   std::vector<pa::TensorMapBlob> v_maps;  // per layer: tensor map of the V pool (16-bit pools)
   std::vector<pa::TensorMapBlob> k_maps;  // per layer: row view of the K pool (16-bit pools, 16-token blocks)
   // the tile kernel that fetches K by TMA gather serves 16-bit pools of 16-token blocks
-  bool has_tile64() const { return !fp8 && bs_shift == 0; }
+  bool has_tile64() const { return !fp8 && bs_shift == 0 && cfg.head_size == (uint32_t)pa::kHeadSize; }
   // log2(block_size / 16): -1, 0 or 1.  32-token blocks: per layer, the maps that fetch
   // one 16-token unit of a chunk for the split-KV kernel
   int bs_shift = 0;
   std::vector<pa::UnitMaps> unit_maps;
   const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift > 0 ? &unit_maps[layer] : nullptr; }
   // the tcgen05 tile kernel reads pools of 16- or 32-token blocks (16-bit or FP8)
-  bool has_tile_kernel() const { return bs_shift >= 0; }
+  bool has_tile_kernel() const { return bs_shift >= 0 && cfg.head_size == (uint32_t)pa::kHeadSize; }
   unsigned *err_dev = nullptr;
   // pinned, device-mapped copy of the error word, written by the last kernel of an
   // attention call, so that the host-buffer step reads it without a copy of its own
@@ -142,8 +142,10 @@ pa_status validate_config(const PagedAttnConfig *c) {
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
   if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
-  if (c->head_size != pa::kHeadSize)
-    return fail(PA_ERR_UNSUPPORTED, "only head_size 128 is built");
+  if (c->head_size != 64 && c->head_size != pa::kHeadSize && c->head_size != 256)
+    return fail(PA_ERR_UNSUPPORTED, "head sizes 64, 128 and 256 are built");
+  if (c->head_size != pa::kHeadSize && c->block_size != 16)
+    return fail(PA_ERR_UNSUPPORTED, "head sizes 64 and 256 are built for 16-token blocks");
   // with 32-token blocks a unit is addressed as 2 * (block * heads + head) + half in 32 bits
   if (c->block_size == 32 && (uint64_t)c->num_blocks * c->num_kv_heads >= (1ull << 31))
     return fail(PA_ERR_INVALID_ARG, "num_blocks * num_kv_heads must be below 2^31 with block_size 32");
@@ -179,7 +181,7 @@ pa_status finish_create(PagedAttnCache *c) {
   // the tile kernel fetches V of 16-bit pools through a tensor map (FP8 pools are read with
   // plain loads: their entries stay zero and unused)
   c->v_maps.assign(c->cfg.num_layers, pa::TensorMapBlob{});
-  if (!c->fp8 && c->bs_shift >= 0) {
+  if (!c->fp8 && c->has_tile_kernel()) {
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::tile_encode_v_map(&c->v_maps[i], c->v[i],
                                     (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads,
@@ -304,6 +306,8 @@ static pa_status cache_create_impl(const PagedAttnConfig *config, int32_t device
   if (st != PA_OK) return st;
   if (fp8 && config->block_size == 8)  // crates/mlx-paged-attn/src/config.rs:71-76
     return fail(PA_ERR_INVALID_ARG, "FP8 cache requires block_size 16 or 32 for optimal alignment.");
+  if (fp8 && config->head_size != (uint32_t)pa::kHeadSize)
+    return fail(PA_ERR_UNSUPPORTED, "the FP8 cache is built for head size 128");
   DeviceGuard g(device);
   if (!g.ok) return fail(PA_ERR_CUDA, "cannot select device");
   PagedAttnCache *c = new (std::nothrow) PagedAttnCache();
@@ -351,6 +355,8 @@ static pa_status cache_wrap_impl(const PagedAttnConfig *config, int32_t device, 
   if (st != PA_OK) return st;
   if (fp8 && config->block_size == 8)  // crates/mlx-paged-attn/src/config.rs:71-76
     return fail(PA_ERR_INVALID_ARG, "FP8 cache requires block_size 16 or 32 for optimal alignment.");
+  if (fp8 && config->head_size != (uint32_t)pa::kHeadSize)
+    return fail(PA_ERR_UNSUPPORTED, "the FP8 cache is built for head size 128");
   if (!key_ptrs || !value_ptrs) return fail(PA_ERR_INVALID_ARG, "pool pointer arrays are null");
   for (uint32_t i = 0; i < config->num_layers; i++) {
     if (!key_ptrs[i] || !value_ptrs[i]) return fail(PA_ERR_INVALID_ARG, "a pool pointer is null");
@@ -469,7 +475,8 @@ pa_status pa_reshape_and_cache(PagedAttnCache *c, uint32_t layer, const void *ke
       static_cast<const pa::elem16 *>(key), static_cast<const pa::elem16 *>(value),
       static_cast<pa::elem16 *>(c->k[layer]), static_cast<pa::elem16 *>(c->v[layer]),
       slot_mapping, num_tokens, key_stride, value_stride, (int)c->cfg.num_kv_heads,
-      c->cfg.num_blocks, c->bs_shift, c->err_dev, static_cast<cudaStream_t>(cuda_stream)));
+      c->cfg.num_blocks, c->bs_shift, c->err_dev, static_cast<cudaStream_t>(cuda_stream),
+      (int)c->cfg.head_size));
   return PA_OK;
 }
 
@@ -488,6 +495,8 @@ pa_status pa_qk_norm_rope_and_cache(PagedAttnCache *c, uint32_t layer, void *q_o
   if (!q_out || !q || !k || !v || !positions || !slot_mapping)
     return fail(PA_ERR_INVALID_ARG, "null tensor pointer");
   const int Hkv = (int)c->cfg.num_kv_heads, D = (int)c->cfg.head_size;
+  if (D != pa::kHeadSize)
+    return fail(PA_ERR_UNSUPPORTED, "the fused norm + rotary + write launch is built for head size 128");
   if (num_q_heads <= 0 || num_q_heads % Hkv)
     return fail(PA_ERR_INVALID_ARG, "num_q_heads must be a positive multiple of num_kv_heads");
   if (rope_dims > (uint32_t)D || (rope_dims & 1))
@@ -770,7 +779,7 @@ struct StepWrite {
 // its own.  It pays while a CTA ends at most a couple of items (few kv heads per GPU, as
 // under kv-head sharding); beyond that the step runs the write kernel first.
 bool can_fuse_write(const PagedAttnCache *c, int num_q_heads, int num_seqs) {
-  return !c->fp8 && c->bs_shift == 0 && num_q_heads > 0 &&
+  return !c->fp8 && c->bs_shift == 0 && c->cfg.head_size == (uint32_t)pa::kHeadSize && num_q_heads > 0 &&
          num_q_heads % (int)c->cfg.num_kv_heads == 0 && num_q_heads / (int)c->cfg.num_kv_heads <= 8 &&
          (int64_t)num_seqs * c->cfg.num_kv_heads <= 2 * (int64_t)c->num_sms;
 }
@@ -799,8 +808,8 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   if (num_q_heads <= 0 || num_q_heads % Hkv != 0)
     return fail(PA_ERR_INVALID_ARG, "num_q_heads must be a positive multiple of num_kv_heads");
   const int G = num_q_heads / Hkv;
-  if (G > pa::splitkv_max_cols() || (128 % G) != 0)
-    return fail(PA_ERR_UNSUPPORTED, "query heads per kv head must be 1, 2, 4, 8 or 16");
+  if (G > pa::splitkv_max_cols_for((int)c->cfg.head_size) || (128 % G) != 0)
+    return fail(PA_ERR_UNSUPPORTED, "query heads per kv head must be 1, 2, 4, 8 or 16 (up to 8 with head size 256)");
   if (max_blocks_per_seq <= 0) return fail(PA_ERR_INVALID_ARG, "max_blocks_per_seq must be > 0");
   const int64_t row = (int64_t)num_q_heads * c->cfg.head_size;
   if (q_stride < row || out_stride < row || (q_stride & 7) || (out_stride & 7))
@@ -826,6 +835,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   p.Hkv = Hkv;
   p.G = G;
   p.MB = max_blocks_per_seq;
+  p.head_size = (int)c->cfg.head_size;
   p.bs_shift = c->bs_shift;
   p.num_blocks = c->cfg.num_blocks;
   p.q_stride = q_stride;
@@ -864,7 +874,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   // up to 24 columns -> split-KV kernel, one launch per 8-column width class so that
   // plain decode sequences run in the narrow, deepest-pipelined variant even when the
   // batch also holds multi-token (verify) sequences; more -> tile kernel.
-  const int split_cols = pa::splitkv_max_cols();
+  const int split_cols = pa::splitkv_max_cols_for((int)c->cfg.head_size);
   const int tile_q = pa::tile_queries_per_cta(G);
   bool have_class[3] = {false, false, false};
   std::vector<pa::TileWork> tiles;
@@ -904,7 +914,7 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   if (in_pieces) {
     if (!context_lens_host)
       return fail(PA_ERR_INVALID_ARG,
-                  "with 8-token blocks, chunks of more than " +
+                  "with 8-token blocks or a head size other than 128, chunks of more than " +
                       std::to_string(split_cols / G) + " query tokens need context_lens_host");
     const int piece = split_cols / G;
     v_cu.push_back(0);

@@ -20,6 +20,7 @@ unsigned long long g_launch_count = 0;
 constexpr int kTokPerCta = 16;
 constexpr int kVPad = 2;  // bf16 elements of row padding: 65-word rows, conflict-free
 
+template <int HD>
 __global__ void __launch_bounds__(256)
 reshape_and_cache_kernel(const elem16 *__restrict__ key,
                          const elem16 *__restrict__ value,
@@ -27,8 +28,9 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
                          const int64_t *__restrict__ slot_mapping, int64_t num_tokens,
                          int64_t key_stride, int64_t value_stride, int Hkv, uint32_t num_blocks,
                          int bs_shift, unsigned *err) {
-  __shared__ uint4 k_s[kTokPerCta][kHeadSize / 8];                 // 16 x 256 B
-  __shared__ __align__(16) uint16_t v_s[kTokPerCta][kHeadSize + kVPad];
+  constexpr int kPieces = HD / 8;  // 16-byte pieces of one token's row of one head
+  __shared__ uint4 k_s[kTokPerCta][kPieces];
+  __shared__ __align__(16) uint16_t v_s[kTokPerCta][HD + kVPad];
   __shared__ int64_t slot_s[kTokPerCta];
 
   // the attention kernel that follows may set up (it reads no pool data before its
@@ -51,14 +53,14 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
     }
     slot_s[tid] = s;
   }
-  // Stage: 16 tokens x 16 pieces of 16 B for K and for V; thread -> (token, piece).
-  {
-    const int tok = tid >> 4, piece = tid & 15;
+  // Stage: 16 tokens x HD/8 pieces of 16 B for K and for V; thread -> (token, piece).
+  for (int i = tid; i < kTokPerCta * kPieces; i += 256) {
+    const int tok = i / kPieces, piece = i % kPieces;
     if (t0 + tok < num_tokens) {
       const uint4 kv = *reinterpret_cast<const uint4 *>(key + (t0 + tok) * key_stride +
-                                                        (int64_t)h * kHeadSize + piece * 8);
+                                                        (int64_t)h * HD + piece * 8);
       const uint4 vv = *reinterpret_cast<const uint4 *>(value + (t0 + tok) * value_stride +
-                                                        (int64_t)h * kHeadSize + piece * 8);
+                                                        (int64_t)h * HD + piece * 8);
       k_s[tok][piece] = kv;
       uint32_t *vd = reinterpret_cast<uint32_t *>(&v_s[tok][piece * 8]);
       vd[0] = vv.x; vd[1] = vv.y; vd[2] = vv.z; vd[3] = vv.w;
@@ -67,26 +69,25 @@ reshape_and_cache_kernel(const elem16 *__restrict__ key,
   __syncthreads();
 
   // K: piece c of token `tok` goes to chunk offset c*BS*8 + off*8 (elements).
-  {
-    const int tok = tid & 15, c = tid >> 4;
+  for (int i = tid; i < kTokPerCta * kPieces; i += 256) {
+    const int tok = i & 15, c = i >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
       const int64_t blk = slot >> bs_log;
       const int off = (int)(slot & (bs - 1));
-      elem16 *dst = k_pool + (((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) + c * (bs * 8) +
-                           off * 8;
+      elem16 *dst = k_pool + (((blk * Hkv + h) * (int64_t)HD) << bs_log) + c * (bs * 8) + off * 8;
       *reinterpret_cast<uint4 *>(dst) = k_s[tok][c];
     }
   }
   // V: element d of token `tok` goes to chunk offset d*BS + off.
-  for (int e = tid; e < kTokPerCta * kHeadSize; e += 256) {
+  for (int e = tid; e < kTokPerCta * HD; e += 256) {
     const int tok = e & 15, d = e >> 4;
     const int64_t slot = slot_s[tok];
     if (slot >= 0) {
       const int64_t blk = slot >> bs_log;
       const int off = (int)(slot & (bs - 1));
-      reinterpret_cast<uint16_t *>(v_pool)[(((blk * Hkv + h) * (int64_t)kHeadSize) << bs_log) +
-                                           d * bs + off] = v_s[tok][d];
+      reinterpret_cast<uint16_t *>(v_pool)[(((blk * Hkv + h) * (int64_t)HD) << bs_log) + d * bs + off] =
+          v_s[tok][d];
     }
   }
 }
@@ -96,14 +97,19 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
                                      uint32_t num_blocks, int bs_shift, unsigned *err,
-                                     cudaStream_t st) {
+                                     cudaStream_t st, int head_size) {
   if (num_tokens <= 0) return cudaSuccess;
   const int64_t groups = (num_tokens + kTokPerCta - 1) / kTokPerCta;
   // grid.x is 31-bit; a write of more than 2^31*16 tokens is not a real call.
   dim3 grid((unsigned)groups, (unsigned)Hkv);
-  reshape_and_cache_kernel<<<grid, 256, 0, st>>>(key, value, k_pool, v_pool, slot_mapping,
-                                                 num_tokens, key_stride, value_stride, Hkv,
-                                                 num_blocks, bs_shift, err);
+  auto go = [&](auto kernel) {
+    kernel<<<grid, 256, 0, st>>>(key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride,
+                                 value_stride, Hkv, num_blocks, bs_shift, err);
+  };
+  if (head_size == kHeadSize) go(reshape_and_cache_kernel<kHeadSize>);
+  else if (head_size == 64) go(reshape_and_cache_kernel<64>);
+  else if (head_size == 256) go(reshape_and_cache_kernel<256>);
+  else return cudaErrorInvalidValue;
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

@@ -188,6 +188,7 @@ struct AttnParams {
   const int32_t *seq_row;       // null, or [S]: block-table row of each sequence (when a long
                                 // chunk is served as several shorter sequences)
   int S, Hq, Hkv, G, MB;
+  int head_size;  // 128; 64 and 256 for 16-bit pools with 16-token blocks (split-KV kernel only)
   int bs_shift;  // log2(pool block size / 16): 0, 1 (32 tokens) or -1 (8 tokens); MB counts pool blocks
   int is_f16;  // element format: 1 = f16, 0 = bf16
   int is_fp8;  // pools hold E4M3 bytes; is_f16 is then the q/out format
@@ -253,7 +254,7 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
                                      const int64_t *slot_mapping, int64_t num_tokens,
                                      int64_t key_stride, int64_t value_stride, int Hkv,
                                      uint32_t num_blocks, int bs_shift, unsigned *err,
-                                     cudaStream_t st);
+                                     cudaStream_t st, int head_size = kHeadSize);
 cudaError_t launch_reshape_and_cache_fp8(const elem16 *key, const elem16 *value, uint8_t *k_pool,
                                          uint8_t *v_pool, const int64_t *slot_mapping,
                                          int64_t num_tokens, int64_t key_stride,
@@ -308,6 +309,7 @@ cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStre
                                      const UnitMaps *maps = nullptr);
 size_t splitkv_workspace_bytes(int num_ctas);
 int splitkv_max_cols();
+int splitkv_max_cols_for(int head_size);
 cudaError_t splitkv_configure();  // opt-in shared memory sizes, once per device
 // Library-resident scratch for callers that cannot allocate (see splitkv_attention.cu).
 int splitkv_static_max_ctas();

@@ -86,16 +86,23 @@ constexpr int kMaxNT = 3;  // up to 24 columns per item
 
 // FP8: an E4M3 cache, one byte per element; a unit is a 2 KB K chunk laid out
 // [D/16][BS][16] plus a 2 KB V chunk [D][BS], and the ring holds twice as many stages.
-template <int NT, bool FP8 = false>
+template <int NT, bool FP8 = false, int HD = kHeadSize>
 struct Cfg {
-  static constexpr int kChunk = FP8 ? kChunkBytes / 2 : kChunkBytes;  // bytes of one K or V chunk
+  static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes built: 64, 128, 256");
+  static constexpr int kSteps = HD / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
+  static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize;  // bytes of one K or V chunk
   static constexpr int kStageBytes = 2 * kChunk;
   // The narrow FP8 variant runs two CTAs per SM (its per-unit work is latency-bound, so
   // it wants 16 warps per SM; 128 registers per thread allow it): two 4 KB stages per
   // warp there, otherwise the ring keeps its byte size and holds twice as many stages.
   static constexpr int kCtasPerSm = (FP8 && NT == 1) ? 2 : 1;
-  static constexpr int kStages = kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1);
-  static constexpr int kRegs = 36 * NT;  // per thread: 32NT accumulators, 2NT maxima, 2NT sums
+  // Head size 64 halves the stage, so the ring holds twice as many; head size 256 doubles it
+  // and the 227 KB of an SM hold one 16 KB stage per warp (the eight warps then overlap
+  // each other's copies instead of each its own).
+  static constexpr int kStages = HD == 256 ? 1
+                                 : (kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1)) * (HD == 64 ? 2 : 1);
+  static constexpr int kAcc = 4 * kSteps;      // O^T accumulators per thread and column tile
+  static constexpr int kRegs = (kAcc + 4) * NT;  // per thread: accumulators, 2NT maxima, 2NT sums
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
   static constexpr int kMergeBytes = (kWarps / 2) * kRegs * 32 * 4;
   static constexpr int kPreBytes = (kMaxSeqsPerLaunch + 1) * 4;
@@ -112,6 +119,8 @@ struct Cfg {
 constexpr int kItemCostUnits = 24;
 constexpr int kItemCostUnitsFp8 = 16;
 constexpr int kSlotFloats = 36 * kMaxNT * 32;  // one workspace slot, sized for the widest kernel
+static_assert(Cfg<1, false, 256>::kRegs * 32 <= kSlotFloats && Cfg<3, false, 64>::kRegs * 32 <= kSlotFloats,
+              "a partial of every kernel variant fits a workspace slot");
 
 __device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
   return p.cu_q_lens ? p.cu_q_lens[seq + 1] - p.cu_q_lens[seq] : 1;
@@ -178,17 +187,19 @@ __device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap *m
 // Combines the partials of one split item, (sequence, kv head), whose pieces lie in
 // CTAs [c_first, c_last], and writes the item's final rows.  Called by all threads
 // of the CTA that arrived last; reads go to L2 (the other CTAs wrote these slots).
-// Thread layout: d = tid & 127 (head dimension); a thread takes every second column,
-// four of them per pass, and issues all loads of a pass before it uses any (one round
-// trip to L2 per pass instead of one per column).
-template <int NT, bool F16>
+// Thread layout: d = tid mod HD (head dimension); a thread takes every (256 / HD)-th
+// column, four of them per pass, and issues all loads of a pass before it uses any (one
+// round trip to L2 per pass instead of one per column).
+template <int NT, bool F16, int HD>
 __device__ __forceinline__ void merge_item(const AttnParams &p, const long long *bnd, int c_first,
                                            int c_last, int q0, int h, int ncols, int tid) {
   constexpr int CP = 4;  // columns per pass and thread
   constexpr int PP = 4;  // pieces per pass
-  const int d = tid & 127;
+  constexpr int CS = kThreads / HD;  // column stride of a thread
+  constexpr int kAcc = 4 * (HD / 16);
+  const int d = tid % HD;
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
-  for (int col0 = tid >> 7; col0 < ncols; col0 += 2 * CP) {
+  for (int col0 = tid / HD; col0 < ncols; col0 += CS * CP) {
     float mm[CP], acc[CP], lsum[CP];
 #pragma unroll
     for (int i = 0; i < CP; i++) { mm[i] = -INFINITY; acc[i] = 0.f; lsum[i] = 0.f; }
@@ -203,13 +214,13 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, const long long 
         const float *slot = p.ws + (size_t)(2 * (p.cta_base + c) + (c == c_first ? 1 : 0)) * kSlotFloats;
 #pragma unroll
         for (int i = 0; i < CP; i++) {
-          const int col = col0 + 2 * i;
+          const int col = col0 + CS * i;
           const bool use = piece && col < ncols;
           const int nt = col >> 3, tig = (col & 7) >> 1, par = col & 1;
           const int lane = gid * 4 + tig;
-          mj[i][k] = use ? __ldcg(slot + (32 * NT + nt * 2 + par) * 32 + lane) : -INFINITY;
+          mj[i][k] = use ? __ldcg(slot + (kAcc * NT + nt * 2 + par) * 32 + lane) : -INFINITY;
           oj[i][k] = use ? __ldcg(slot + ((mt * NT + nt) * 4 + upper * 2 + par) * 32 + lane) : 0.f;
-          lj[i][k] = use ? __ldcg(slot + (34 * NT + nt * 2 + par) * 32 + lane) : 0.f;
+          lj[i][k] = use ? __ldcg(slot + ((kAcc + 2) * NT + nt * 2 + par) * 32 + lane) : 0.f;
         }
       }
 #pragma unroll
@@ -229,10 +240,10 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, const long long 
     }
 #pragma unroll
     for (int i = 0; i < CP; i++) {
-      const int col = col0 + 2 * i;
+      const int col = col0 + CS * i;
       if (col < ncols) {
         const int qj = col / p.G, g = col - qj * p.G;
-        p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * kHeadSize + d] =
+        p.out[(int64_t)(q0 + qj) * p.out_stride + (int64_t)(h * p.G + g) * HD + d] =
             to_elem<F16>(lsum[i] > 0.f ? acc[i] / lsum[i] : 0.f);
       }
     }
@@ -244,12 +255,16 @@ constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool b
 // FUSE: the variant that also writes the step's new tokens (p.k_new).  It is an
 // instantiation of its own because the mere presence of that code cost the plain
 // kernel 1.5 % (measured), and it exists for the narrow 16-bit kernel only.
-template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false>
+template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false, int HD = kHeadSize>
 __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
   static_assert(!FUSE || (NT == 1 && !FP8 && !B8), "the fused write exists for the narrow 16-bit kernel");
-  using C = Cfg<NT, FP8>;
+  static_assert(HD == kHeadSize || (!FP8 && !B8 && !FUSE), "other head sizes: 16-bit pools, 16-token blocks");
+  using C = Cfg<NT, FP8, HD>;
+  constexpr int KS = C::kSteps;          // 16-wide steps of the head dimension / 16-row tiles of O^T
+  constexpr int KSA = KS < 8 ? 8 : KS;   // array extent (the FP8 code, head size 128 only, indexes 8)
+  constexpr int kAcc = C::kAcc;
   constexpr int NST = C::kStages;
   constexpr int kStageBytes = C::kStageBytes;
   constexpr int kChunk = C::kChunk;
@@ -422,7 +437,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     const int ql = q_len_of(p, seq);
     if (ql < 1 || ql * G > p.max_cols || ql * G < p.min_cols) continue;
     const int q0 = p.cu_q_lens ? p.cu_q_lens[seq] : seq;
-    const int row_elems = p.Hq * kHeadSize;
+    const int row_elems = p.Hq * HD;
     for (int e = tid; e < ql * row_elems; e += kThreads)
       p.out[(int64_t)(q0 + e / row_elems) * p.out_stride + e % row_elems] = (elem16)0;
   }
@@ -531,7 +546,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     // qf[.][0..3] hold hi and qf[.][4..7] lo of the four 32-wide steps, and the power of
     // two comes back out in the column's logit scale.
     constexpr bool QK8 = FP8 && !EXACT;
-    uint32_t qf[NT][8][2];
+    uint32_t qf[NT][KSA][2];
     int lim[NT][2];  // keys visible to columns nt*8 + 2tig + {0,1}
     float col_lin[NT][2];  // S accumulator -> logit, for columns nt*8 + 2tig + {0,1}
 #pragma unroll
@@ -545,7 +560,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         const bool have_col = col < ncols;
         const int qj = have_col ? col / G : 0, g = have_col ? col - qj * G : 0;
         const uint32_t *qp = reinterpret_cast<const uint32_t *>(
-            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
+            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * HD);
         float qv[8][4];
         float amax = 0.f;
 #pragma unroll
@@ -584,9 +599,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       } else if (col < ncols) {
         const int qj = col / G, g = col - qj * G;
         const uint32_t *qp = reinterpret_cast<const uint32_t *>(
-            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * kHeadSize);
+            p.q + (int64_t)(q0 + qj) * p.q_stride + (int64_t)(h * G + g) * HD);
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+        for (int j = 0; j < KS; j++) {
           if (FP8) {
             // k-slots {2tig, 2tig+1, 2tig+8, 2tig+9} of step j carry d = 16j + 4tig .. +3,
             // the four bytes a thread gets from one 16-byte K row piece
@@ -600,7 +615,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; j++) qf[nt][j][0] = qf[nt][j][1] = 0u;
+        for (int j = 0; j < KS; j++) qf[nt][j][0] = qf[nt][j][1] = 0u;
       }
       if (QK8) {
 #pragma unroll
@@ -629,14 +644,14 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       }
     const int min_lim = kv_len - q_len + 1;
 
-    float o[8][NT][4];
+    float o[KSA][NT][4];
     float m[NT][2], l[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
       m[nt][0] = m[nt][1] = -INFINITY;
       l[nt][0] = l[nt][1] = 0.f;
 #pragma unroll
-      for (int mt = 0; mt < 8; mt++)
+      for (int mt = 0; mt < KS; mt++)
 #pragma unroll
         for (int i = 0; i < 4; i++) o[mt][nt][i] = 0.f;
     }
@@ -691,7 +706,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
+          for (int j = 0; j < KS; j++) {
             uint32_t af[4];
             // B8: tokens 0-7 and 8-15 sit in the two 2 KB sub-chunks, rows of 8 tokens
             if (B8) ldmatrix_x4(af, ks + (mi & 1) * 2048 + (2 * j + (mi >> 1)) * 128 + mr * 16);
@@ -796,7 +811,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           }
         } else {
 #pragma unroll
-          for (int mt = 0; mt < 8; mt++) {
+          for (int mt = 0; mt < KS; mt++) {
             uint32_t vf[4];
             if (B8) ldmatrix_x4(vf, vs + (mi >> 1) * 2048 + (16 * mt + (mi & 1) * 8 + mr) * 16);
             else ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
@@ -827,9 +842,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         new_id = (uint32_t)p.block_tables[(long long)row * p.MB + ((kv_len - 1) >> 4)];
         if (lane < 16)
           new_k = __ldg(reinterpret_cast<const uint4 *>(
-                            p.k_new + (int64_t)seq * p.k_new_stride + h * kHeadSize) + lane);
+                            p.k_new + (int64_t)seq * p.k_new_stride + h * HD) + lane);
         new_v = __ldg(reinterpret_cast<const uint2 *>(
-                          p.v_new + (int64_t)seq * p.v_new_stride + h * kHeadSize) + lane);
+                          p.v_new + (int64_t)seq * p.v_new_stride + h * HD) + lane);
       }
     }
     auto write_new_token = [&](int st) {
@@ -927,7 +942,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     auto put = [&](int slot) {
       float *dst = merge_buf + slot * (C::kRegs * 32) + lane;
 #pragma unroll
-      for (int mt = 0; mt < 8; mt++)
+      for (int mt = 0; mt < KS; mt++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -936,8 +951,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       for (int nt = 0; nt < NT; nt++)
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-          dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
-          dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
+          dst[(kAcc * NT + nt * 2 + c) * 32] = m[nt][c];
+          dst[((kAcc + 2) * NT + nt * 2 + c) * 32] = l[nt][c];
         }
     };
     auto take = [&](int slot) {
@@ -947,8 +962,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         float wa[2], wb[2];
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-          const float mb = src[(32 * NT + nt * 2 + c) * 32];
-          const float lb = src[(34 * NT + nt * 2 + c) * 32];
+          const float mb = src[(kAcc * NT + nt * 2 + c) * 32];
+          const float lb = src[((kAcc + 2) * NT + nt * 2 + c) * 32];
           const float mm = fmaxf(m[nt][c], mb);
           wa[c] = m[nt][c] == -INFINITY ? 0.f : fast_exp2(m[nt][c] - mm);
           wb[c] = mb == -INFINITY ? 0.f : fast_exp2(mb - mm);
@@ -956,7 +971,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           l[nt][c] = l[nt][c] * wa[c] + lb * wb[c];
         }
 #pragma unroll
-        for (int mt = 0; mt < 8; mt++)
+        for (int mt = 0; mt < KS; mt++)
 #pragma unroll
           for (int i = 0; i < 4; i++)
             o[mt][nt][i] = o[mt][nt][i] * wa[i & 1] + src[((mt * NT + nt) * 4 + i) * 32] * wb[i & 1];
@@ -988,7 +1003,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       if (partial) {
         float *dst = p.ws + (size_t)(2 * (p.cta_base + blockIdx.x) + (b0 > 0 ? 0 : 1)) * kSlotFloats + lane;
 #pragma unroll
-        for (int mt = 0; mt < 8; mt++)
+        for (int mt = 0; mt < KS; mt++)
 #pragma unroll
           for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -998,8 +1013,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
           for (int c = 0; c < 2; c++) {
-            dst[(32 * NT + nt * 2 + c) * 32] = m[nt][c];
-            dst[(34 * NT + nt * 2 + c) * 32] = l[nt][c];
+            dst[(kAcc * NT + nt * 2 + c) * 32] = m[nt][c];
+            dst[((kAcc + 2) * NT + nt * 2 + c) * 32] = l[nt][c];
           }
         __threadfence();  // the partial is visible before this CTA counts itself below
       } else {
@@ -1013,9 +1028,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
               float inv = l[nt][c] > 0.f ? 1.f / l[nt][c] : 0.f;
               if (FP8) inv *= v_unscale;
               elem16 *op = p.out + (int64_t)(q0 + qj) * p.out_stride +
-                                  (int64_t)(h * G + g) * kHeadSize;
+                                  (int64_t)(h * G + g) * HD;
 #pragma unroll
-              for (int mt = 0; mt < 8; mt++) {
+              for (int mt = 0; mt < KS; mt++) {
                 op[16 * mt + gid] = to_elem<F16>(o[mt][nt][c] * inv);
                 op[16 * mt + gid + 8] = to_elem<F16>(o[mt][nt][c + 2] * inv);
               }
@@ -1041,7 +1056,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       __syncthreads();
       if (s_last) {
         __threadfence();
-        merge_item<NT, F16>(p, bnd, c_first, c_last, q0, h, ncols, tid);
+        merge_item<NT, F16, HD>(p, bnd, c_first, c_last, q0, h, ncols, tid);
       }
     }
 
@@ -1096,8 +1111,25 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Head sizes 64 and 256: 16-bit pools with 16-token blocks, attention only.
+template <int NT, int HD>
+cudaError_t launch_hd(const AttnParams &p, const KvMaps &maps, int num_ctas, cudaStream_t st) {
+  const cudaError_t e =
+      p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, false, false, HD>, dim3(num_ctas),
+                                  dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps)
+               : launch_dependent(splitkv_kernel<NT, false, false, false, false, HD>, dim3(num_ctas),
+                                  dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps);
+  __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
+  return e;
+}
+
 template <int NT>
 cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cudaStream_t st) {
+  if (p.head_size == 64) return launch_hd<NT, 64>(p, maps, num_ctas, st);
+  if (p.head_size == 256) {
+    if constexpr (NT == 1) return launch_hd<1, 256>(p, maps, num_ctas, st);
+    else return cudaErrorInvalidValue;  // wider items are cut into pieces of 8 columns by the caller
+  }
   cudaError_t e;
   if (p.is_fp8)
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, true>, dim3(num_ctas), dim3(kThreads),
@@ -1153,6 +1185,8 @@ cudaError_t splitkv_static_scratch(int device, float **out) {
 }
 
 int splitkv_max_cols() { return 8 * kMaxNT; }
+// Head size 256 leaves registers for one 8-column tile only.
+int splitkv_max_cols_for(int head_size) { return head_size == 256 ? 8 : 8 * kMaxNT; }
 
 size_t splitkv_workspace_bytes(int num_ctas) {
   return (size_t)num_ctas * 2 * kSlotFloats * sizeof(float);
@@ -1183,6 +1217,18 @@ static cudaError_t configure_nt() {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, true, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, true>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, 64>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, 64>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, 64>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, 64>::kSmemBytes);
+  if (e == cudaSuccess && NT == 1)
+    e = cudaFuncSetAttribute(splitkv_kernel<1, false, false, false, false, 256>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, false, 256>::kSmemBytes);
+  if (e == cudaSuccess && NT == 1)
+    e = cudaFuncSetAttribute(splitkv_kernel<1, true, false, false, false, 256>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, false, 256>::kSmemBytes);
   return e;
 }
 
@@ -1243,6 +1289,10 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
                                      const UnitMaps *unit_maps) {
   if (p_in.bs_shift > 0 && !unit_maps) return cudaErrorInvalidValue;
   if (p_in.bs_shift < 0 && p_in.is_fp8) return cudaErrorInvalidValue;
+  if (p_in.head_size != kHeadSize &&
+      ((p_in.head_size != 64 && p_in.head_size != 256) || p_in.is_fp8 || p_in.bs_shift != 0 || p_in.k_new ||
+       p_in.max_cols > splitkv_max_cols_for(p_in.head_size)))
+    return cudaErrorInvalidValue;
   KvMaps maps;
   if (unit_maps) memcpy(&maps, unit_maps, sizeof(maps));
   else memset(&maps, 0, sizeof(maps));

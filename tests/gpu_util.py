@@ -35,7 +35,8 @@ class DeviceCase:
         f16 = getattr(case, "f16", False)
         self.k_pool = to_dev(case.k_pool if k_pool is None else k_pool, f16)
         self.v_pool = to_dev(case.v_pool if v_pool is None else v_pool, f16)
-        self.cache = pa.PagedCache(getattr(case, "bs", BS), case.NB, D, case.Hkv, dtype=0 if f16 else 1,
+        self.D = getattr(case, "D", D)
+        self.cache = pa.PagedCache(getattr(case, "bs", BS), case.NB, self.D, case.Hkv, dtype=0 if f16 else 1,
                                    key_pools=[self.k_pool], value_pools=[self.v_pool])
         self.q = to_dev(case.q, f16)
         self.k_new = to_dev(case.k_new, f16)
@@ -51,12 +52,12 @@ class DeviceCase:
     def write(self):
         c = self.case
         self.cache.reshape_and_cache(self.k_new, self.v_new, self.slots, len(c.slot_mapping),
-                                     c.Hkv * D, c.Hkv * D)
+                                     c.Hkv * self.D, c.Hkv * self.D)
 
     def attend(self, varlen=True, softcap=1.0, host_lens=True):
         c = self.case
         f16 = getattr(c, "f16", False)
-        out = torch.full((max(c.total_q, 1), c.Hq, D), float("nan"),
+        out = torch.full((max(c.total_q, 1), c.Hq, self.D), float("nan"),
                          dtype=torch.float16 if f16 else torch.bfloat16, device="cuda")
         if varlen:
             self.cache.varlen(out, self.q, self.tables, self.lens, c.cu_q, c.S, c.Hq, c.MB,

@@ -12,6 +12,7 @@ from pa_testlib import D, X, elems_to_f32
 
 def gather_sequence(k_pool, v_pool, table_row, kv_len, f16=False):
     BS = v_pool.shape[3]  # tokens per pool block
+    D = v_pool.shape[2]   # head size
     nb = (kv_len + BS - 1) // BS
     blocks = table_row[:nb]
     k = k_pool[blocks]                                  # [nb, Hkv, D/X, BS, X]

@@ -122,9 +122,11 @@ class Case:
     step's new tokens and queries held apart for the code under test."""
 
     def __init__(self, kv_lens, q_lens, Hq, Hkv, NB, seed=0, mb_extra=0, prefill=True, f16=False,
-                 bs=BS):
+                 bs=BS, head_size=D):
         self.f16 = f16
         self.bs = bs  # tokens per pool block (16 or 32)
+        self.D = head_size  # the module constant D (128) unless a test says otherwise
+        D_ = head_size
         self.S = len(kv_lens)
         self.Hq, self.Hkv, self.NB = Hq, Hkv, NB
         self.G = Hq // Hkv
@@ -144,15 +146,15 @@ class Case:
         for s in range(self.S):
             self.block_tables[s, :nblk[s]] = perm[pos:pos + nblk[s]]
             pos += nblk[s]
-        self.scale = 1.0 / math.sqrt(D)
+        self.scale = 1.0 / math.sqrt(D_)
         # tensors
         gen = normal_f16 if f16 else normal_bf16
-        self.q = gen((self.total_q, Hq, D), seed, 1)
+        self.q = gen((self.total_q, Hq, D_), seed, 1)
         tot_kv = int(self.kv_lens.sum())
         self.cu_kv = np.zeros(self.S + 1, dtype=np.int32)
         self.cu_kv[1:] = np.cumsum(self.kv_lens)
-        self.k_all = gen((tot_kv, Hkv, D), seed, 2)  # every token of every sequence
-        self.v_all = gen((tot_kv, Hkv, D), seed, 3)
+        self.k_all = gen((tot_kv, Hkv, D_), seed, 2)  # every token of every sequence
+        self.v_all = gen((tot_kv, Hkv, D_), seed, 3)
         slots_all = np.empty(tot_kv, dtype=np.int64)
         is_new = np.zeros(tot_kv, dtype=bool)
         for s in range(self.S):
@@ -164,8 +166,8 @@ class Case:
         self.k_new = np.ascontiguousarray(self.k_all[is_new])
         self.v_new = np.ascontiguousarray(self.v_all[is_new])
         self.slot_mapping = np.ascontiguousarray(slots_all[is_new])
-        self.k_pool = np.full((NB, Hkv, D // X, bs, X), CANARY, dtype=np.uint16)
-        self.v_pool = np.full((NB, Hkv, D, bs), CANARY, dtype=np.uint16)
+        self.k_pool = np.full((NB, Hkv, D_ // X, bs, X), CANARY, dtype=np.uint16)
+        self.v_pool = np.full((NB, Hkv, D_, bs), CANARY, dtype=np.uint16)
         if prefill:
             old = ~is_new
             write_oracle(self.k_pool, self.v_pool, np.ascontiguousarray(self.k_all[old]),
@@ -182,18 +184,20 @@ def write_oracle(k_pool, v_pool, key, value, slots, Hkv, key_stride=None, value_
     n = len(slots)
     if n == 0:
         return
+    hd = v_pool.shape[2]  # head size
     oracle().oracle_reshape_and_cache(p(key), p(value), p(k_pool), p(v_pool), p(slots), n,
-                                      key_stride or Hkv * D, value_stride or Hkv * D, Hkv, D,
+                                      key_stride or Hkv * hd, value_stride or Hkv * hd, Hkv, hd,
                                       k_pool.shape[3], X)
 
 
 def attention_oracle(case: Case, k_pool, v_pool, softcap=1.0, varlen=True) -> np.ndarray:
-    out = np.zeros((case.total_q, case.Hq, D), dtype=np.float32)
+    hd = v_pool.shape[2]  # head size
+    out = np.zeros((case.total_q, case.Hq, hd), dtype=np.float32)
     cu = p(case.cu_q) if varlen else None
     oracle().oracle_paged_attention_varlen_dt(p(out), p(case.q), p(k_pool), p(v_pool),
                                               p(case.block_tables), p(case.kv_lens), cu, case.S,
-                                              case.Hq, case.Hkv, D, k_pool.shape[3], case.MB,
-                                              case.Hq * D, case.scale, softcap, int(case.f16))
+                                              case.Hq, case.Hkv, hd, k_pool.shape[3], case.MB,
+                                              case.Hq * hd, case.scale, softcap, int(case.f16))
     return out
 
 
@@ -293,8 +297,9 @@ def check_attention(got_f32: np.ndarray, ref_f32: np.ndarray, what: str = "") ->
     short contexts (outputs ~0.3) with long ones (outputs ~0.01): a global floor
     would be loose for the long rows and meaningless for the short ones, and a
     pure relative test would be dominated by elements that happen to be near 0."""
-    got = got_f32.astype(np.float64).reshape(-1, D)
-    ref = ref_f32.astype(np.float64).reshape(-1, D)
+    hd = ref_f32.shape[-1] if ref_f32.ndim > 1 else D  # a row = the outputs of one (query, head)
+    got = got_f32.astype(np.float64).reshape(-1, hd)
+    ref = ref_f32.astype(np.float64).reshape(-1, hd)
     assert got.shape == ref.shape
     assert np.isfinite(got).all(), f"{what}: non-finite values in the output"
     if ref.size == 0:

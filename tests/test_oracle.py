@@ -201,6 +201,33 @@ def test_other_block_sizes_against_numpy_reference_and_index_formula(bs):
                                rtol=0, atol=1e-6)
 
 
+@pytest.mark.parametrize("hd", [64, 256])
+def test_other_head_sizes_against_numpy_reference_and_index_formula(hd):
+    """Head sizes 64 and 256 (two of those PagedAttentionConfig accepts,
+    crates/mlx-paged-attn/src/config.rs:47-50): element (h, d) of the token in slot 50 lands at
+    K[3, h, d//8, 2, d%8] and V[3, h, d, 2]; attention agrees with the numpy statement."""
+    Hkv, NB = 2, 5
+    k_pool = np.zeros((NB, Hkv, hd // X, BS, X), dtype=np.uint16)
+    v_pool = np.zeros((NB, Hkv, hd, BS), dtype=np.uint16)
+    key = np.arange(1, Hkv * hd + 1, dtype=np.uint16).reshape(1, Hkv, hd)
+    val = (key + 1000).astype(np.uint16)
+    write_oracle(k_pool, v_pool, key, val, np.array([50], dtype=np.int64), Hkv)
+    for h in range(Hkv):
+        for d in (0, 7, 8, hd - 1):
+            assert k_pool[3, h, d // 8, 2, d % 8] == key[0, h, d]
+            assert v_pool[3, h, d, 2] == val[0, h, d]
+    assert np.count_nonzero(k_pool) == Hkv * hd and np.count_nonzero(v_pool) == Hkv * hd
+    for f16 in (False, True):
+        case = Case([70, 33, 16, 5, 32, 97], [3, 1, 16, 5, 1, 40], 8, 2, 32, seed=25, f16=f16, head_size=hd)
+        assert case.q.shape[-1] == hd and abs(case.scale - hd ** -0.5) < 1e-12
+        k_pool, v_pool = case.pools_after_write()
+        ref = numpy_reference.paged_attention(case.q, k_pool, v_pool, case.block_tables, case.kv_lens,
+                                              case.cu_q, case.Hq, case.Hkv, case.scale, f16=f16)
+        got = attention_oracle(case, k_pool, v_pool)
+        assert got.shape == (case.total_q, 8, hd)
+        np.testing.assert_allclose(got, ref, rtol=0, atol=2e-6)
+
+
 def test_f16_inputs_against_numpy_reference():
     case = Case([70, 33, 16, 5], [3, 1, 16, 5], 8, 2, 16, seed=23, f16=True)
     k_pool, v_pool = case.pools_after_write()
