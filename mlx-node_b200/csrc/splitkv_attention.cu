@@ -86,20 +86,22 @@ constexpr int kMaxNT = 3;  // up to 24 columns per item
 
 // FP8: an E4M3 cache, one byte per element; a unit is a 2 KB K chunk laid out
 // [D/16][BS][16] plus a 2 KB V chunk [D][BS], and the ring holds twice as many stages.
-template <int NT, bool FP8 = false, int HD = kHeadSize>
+// SUB: 16-token sub-units a warp takes from one stage (2 = a whole 32-token pool block).
+template <int NT, bool FP8 = false, int HD = kHeadSize, int SUB = 1>
 struct Cfg {
   static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes built: 64, 128, 256");
+  static_assert(SUB == 1 || (SUB == 2 && HD == kHeadSize && !FP8), "whole 32-token blocks: 16-bit pools, head size 128");
   static constexpr int kSteps = HD / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
-  static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize;  // bytes of one K or V chunk
+  static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize * SUB;  // bytes of one K or V chunk
   static constexpr int kStageBytes = 2 * kChunk;
   // The narrow FP8 variant runs two CTAs per SM (its per-unit work is latency-bound, so
   // it wants 16 warps per SM; 128 registers per thread allow it): two 4 KB stages per
   // warp there, otherwise the ring keeps its byte size and holds twice as many stages.
   static constexpr int kCtasPerSm = (FP8 && NT == 1) ? 2 : 1;
-  // Head size 64 halves the stage, so the ring holds twice as many; head size 256 doubles it
-  // and the 227 KB of an SM hold one 16 KB stage per warp (the eight warps then overlap
-  // each other's copies instead of each its own).
-  static constexpr int kStages = HD == 256 ? 1
+  // Head size 64 halves the stage, so the ring holds twice as many; head size 256 and whole
+  // 32-token blocks double it and the 227 KB of an SM hold one 16 KB stage per warp (the
+  // eight warps then overlap each other's copies instead of each its own).
+  static constexpr int kStages = (HD == 256 || SUB == 2) ? 1
                                  : (kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1)) * (HD == 64 ? 2 : 1);
   static constexpr int kAcc = 4 * kSteps;      // O^T accumulators per thread and column tile
   static constexpr int kRegs = (kAcc + 4) * NT;  // per thread: accumulators, 2NT maxima, 2NT sums
@@ -127,11 +129,11 @@ __device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
 }
 // Blocks of a sequence this kernel family handles (0 if the sequence belongs to
 // the tile kernel or has nothing to attend).
-__device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq) {
+__device__ __forceinline__ int eligible_blocks(const AttnParams &p, int seq, int unit_tokens = kBlockSize) {
   const int ql = q_len_of(p, seq);
   if (ql < 1 || ql * p.G > p.max_cols || ql * p.G < p.min_cols) return 0;
   const int ctx = p.context_lens[seq];
-  return ctx > 0 ? (ctx + kBlockSize - 1) / kBlockSize : 0;
+  return ctx > 0 ? (ctx + unit_tokens - 1) / unit_tokens : 0;
 }
 
 // D(16x8,f32) += A(16x32,row) * B(32x8,col), both operands E4M3 bytes.  The tensor cores
@@ -255,13 +257,18 @@ constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool b
 // FUSE: the variant that also writes the step's new tokens (p.k_new).  It is an
 // instantiation of its own because the mere presence of that code cost the plain
 // kernel 1.5 % (measured), and it exists for the narrow 16-bit kernel only.
-template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false, int HD = kHeadSize>
+// B32: pools of 32-token blocks, 16-bit, head size 128: a unit is a whole block, fetched as one
+// contiguous 8 KB copy per operand, and the warp takes its two 16-token halves one after the
+// other from the same stage (the interleave of the halves is an ldmatrix address term).
+template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false, int HD = kHeadSize, bool B32 = false>
 __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
   static_assert(!FUSE || (NT == 1 && !FP8 && !B8), "the fused write exists for the narrow 16-bit kernel");
   static_assert(HD == kHeadSize || (!FP8 && !B8 && !FUSE), "other head sizes: 16-bit pools, 16-token blocks");
-  using C = Cfg<NT, FP8, HD>;
+  static_assert(!B32 || (!FP8 && !B8 && !FUSE && HD == kHeadSize), "whole 32-token blocks: 16-bit pools, head size 128");
+  constexpr int SUB = B32 ? 2 : 1;       // 16-token sub-units per unit
+  using C = Cfg<NT, FP8, HD, SUB>;
   constexpr int KS = C::kSteps;          // 16-wide steps of the head dimension / 16-row tiles of O^T
   constexpr int KSA = KS < 8 ? 8 : KS;   // array extent (the FP8 code, head size 128 only, indexes 8)
   constexpr int kAcc = C::kAcc;
@@ -291,7 +298,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   // the SMs this grid leaves free.
   if (p.early_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- per-launch prefix sum of block counts --------------------------------
-  for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s);
+  for (int s = tid; s < S; s += kThreads) pre[s + 1] = eligible_blocks(p, p.seq_base + s, kBlockSize * SUB);
   if (tid == 0) pre[0] = 0;
   if (lane == 0) {
     for (int st = 0; st < NST; st++) mbar_init(smem_u32(&bars[warp * NST + st]), 1);
@@ -396,7 +403,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       col = 2 * b + (jj & 1);
       if (col * 8 >= p.context_lens[p.seq_base + s]) return Loc{nullptr, kNoBlock, h, b};
     } else {
-      col = b >> p.bs_shift;
+      col = B32 ? b : b >> p.bs_shift;
     }
     return Loc{p.block_tables + (long long)row * p.MB + col, 0u, h, b};
   };
@@ -408,7 +415,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
       id = 0;
     }
     const uint32_t chunk = id * (uint32_t)Hkv + (uint32_t)at.h;
-    return (!B8 && p.bs_shift) ? 2u * chunk + (uint32_t)(at.b & 1) : chunk;
+    return (!B8 && !B32 && p.bs_shift) ? 2u * chunk + (uint32_t)(at.b & 1) : chunk;
   };
   auto lookup = [&](int jj) -> uint32_t {
     const Loc at = locate(jj);
@@ -480,7 +487,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           bulk_g2s(dst + kChunk / 2, kp + (size_t)chunk_b * (kChunk / 2), kChunk / 2, bar);
           bulk_g2s(dst + kChunk + kChunk / 2, vp + (size_t)chunk_b * (kChunk / 2), kChunk / 2, bar);
         }
-      } else if (p.bs_shift) {
+      } else if (!B32 && p.bs_shift) {
         // elements of a K row per unit: 16 tokens x 8 (16-bit) or x 16 (bytes); of a V row: 16
         const int unit = (int)(chunk & 1u), ch = (int)(chunk >> 1);
         mbar_expect_tx(bar, kStageBytes);
@@ -657,7 +664,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     }
 
     // S^T = K.Q^T of the unit in ring stage `st`
-    auto s_phase = [&](int st, float (&sacc)[NT][4]) {
+    auto s_phase = [&](int st, float (&sacc)[NT][4], int sub = 0) {
         const uint32_t ks = ring_w + st * kStageBytes;
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
@@ -709,7 +716,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
           for (int j = 0; j < KS; j++) {
             uint32_t af[4];
             // B8: tokens 0-7 and 8-15 sit in the two 2 KB sub-chunks, rows of 8 tokens
+            // B32: a K row holds 32 tokens (512 B), the sub-unit's 16 at offset sub * 256
             if (B8) ldmatrix_x4(af, ks + (mi & 1) * 2048 + (2 * j + (mi >> 1)) * 128 + mr * 16);
+            else if (B32) ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 512 + sub * 256 + ((mi & 1) * 8 + mr) * 16);
             else ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
@@ -717,7 +726,8 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
         }
     };
     // softmax of the unit's logits and O^T += V^T.P^T, V from ring stage `st`
-    auto finish = [&](int st, int blk, float (&sacc)[NT][4]) {
+    // (blk counts 16-token sub-units of the item)
+    auto finish = [&](int st, int blk, float (&sacc)[NT][4], int sub = 0) {
         const uint32_t vs = ring_w + st * kStageBytes + kChunk;
         const int tok0 = blk * kBlockSize + (FP8 ? fp8_row_token(gid) : gid);
         const int tok1 = FP8 ? tok0 + 2 : tok0 + 8;
@@ -813,7 +823,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
 #pragma unroll
           for (int mt = 0; mt < KS; mt++) {
             uint32_t vf[4];
+            // B32: a V row holds 32 tokens (64 B), the sub-unit's 16 at offset sub * 32
             if (B8) ldmatrix_x4(vf, vs + (mi >> 1) * 2048 + (16 * mt + (mi & 1) * 8 + mr) * 16);
+            else if (B32) ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 64 + sub * 32 + (mi >> 1) * 16);
             else ldmatrix_x4(vf, vs + (16 * mt + (mi & 1) * 8 + mr) * 32 + (mi >> 1) * 16);
             vf[0] &= vmask[0]; vf[1] &= vmask[0]; vf[2] &= vmask[1]; vf[3] &= vmask[1];
 #pragma unroll
@@ -897,9 +909,14 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     if constexpr (!kPipelined) {
       for (int k = a + ((warp - a) & (kWarps - 1)); k < a + seglen; k += kWarps) {
         if (!dead && wait_unit(jc, b0 + (k - a))) {
-          float s_cur[NT][4];
-          s_phase(jc % NST, s_cur);
-          finish(jc % NST, b0 + (k - a), s_cur);
+#pragma unroll
+          for (int sub = 0; sub < SUB; sub++) {
+            const int blk16 = (b0 + (k - a)) * SUB + sub;
+            if (sub > 0 && blk16 * kBlockSize >= kv_len) break;  // the block's second half is empty
+            float s_cur[NT][4];
+            s_phase(jc % NST, s_cur, sub);
+            finish(jc % NST, blk16, s_cur, sub);
+          }
         }
         __syncwarp();
         jc++;
@@ -1131,7 +1148,14 @@ cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cud
     else return cudaErrorInvalidValue;  // wider items are cut into pieces of 8 columns by the caller
   }
   cudaError_t e;
-  if (p.is_fp8)
+  if (p.bs_shift > 0 && !p.is_fp8)  // 16-bit pools of 32-token blocks: whole blocks per stage
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, false, false, kHeadSize, true>,
+                                    dim3(num_ctas), dim3(kThreads),
+                                    Cfg<NT, false, kHeadSize, 2>::kSmemBytes, st, p, maps)
+                 : launch_dependent(splitkv_kernel<NT, false, false, false, false, kHeadSize, true>,
+                                    dim3(num_ctas), dim3(kThreads),
+                                    Cfg<NT, false, kHeadSize, 2>::kSmemBytes, st, p, maps);
+  else if (p.is_fp8)
     e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, true>, dim3(num_ctas), dim3(kThreads),
                                     Cfg<NT, true>::kSmemBytes, st, p, maps)
                  : launch_dependent(splitkv_kernel<NT, false, true>, dim3(num_ctas),
@@ -1229,6 +1253,14 @@ static cudaError_t configure_nt() {
   if (e == cudaSuccess && NT == 1)
     e = cudaFuncSetAttribute(splitkv_kernel<1, true, false, false, false, 256>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, false, 256>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, kHeadSize, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg<NT, false, kHeadSize, 2>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, kHeadSize, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg<NT, false, kHeadSize, 2>::kSmemBytes);
   return e;
 }
 
@@ -1310,7 +1342,7 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
     AttnParams p = p_in;
     p.seq_base = p_in.seq_base + base;
     p.S = min(kMaxSeqsPerLaunch, p_in.S - base);
-    p.item_cost = p.is_fp8 ? kItemCostUnitsFp8 : kItemCostUnits;
+    p.item_cost = p.is_fp8 ? kItemCostUnitsFp8 : (p.bs_shift > 0 ? kItemCostUnits / 2 : kItemCostUnits);
     cudaError_t e;
     if (nt <= 1) e = launch_nt<1>(p, maps, num_ctas, st);
     else if (nt == 2) e = launch_nt<2>(p, maps, num_ctas, st);
