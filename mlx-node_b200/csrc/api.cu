@@ -1004,7 +1004,9 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
         if (best >= t_tile_alone + eff_bytes / bw_cap) tile_sms = 0;
       }
     }
-    concurrent = tile_sms > 0 || n_classes > 1;
+    // (width classes side by side without tiles: measured a gain on 16-bit pools only; the
+    // FP8 kernels are latency-bound per SM and lose on a share of the SMs)
+    concurrent = tile_sms > 0 || (n_classes > 1 && !c->fp8);
   }
   if (!concurrent) {
     if (!tiles.empty()) PA_CUDA(launch_tiles(c, layer, p, work_dev, (int)tiles.size(), stream));

@@ -224,6 +224,23 @@ def test_mixed_batch_reduced(cuda_device):
     assert (dc.attend(host_lens=True) == got).all()
 
 
+def test_all_width_classes_and_a_chunk_side_by_side(cuda_device):
+    """Decode (4 columns), 3-token verify (12), 5-token verify (20) and a prefill chunk, long
+    enough that the call runs its three split-KV launches and the tile kernel at the same
+    time, each split-KV launch on its own range of partial slots and counters."""
+    kv = [9000, 6000, 500, 7000, 2500, 8000, 1200, 3000 + 512]
+    ql = [1, 1, 1, 3, 3, 5, 5, 512]
+    case = Case(kv, ql, 32, 8, 2400, seed=9)
+    got, ref = run_case(case)
+    print("classes", check_attention(got, ref, "three width classes + chunk"))
+    dc = DeviceCase(case)
+    dc.write()
+    assert (dc.attend() == got).all()          # same shares, same partitions: same bits
+    # and with a soft cap (the tile kernel's other variant)
+    got_cap, ref_cap = run_case(case, softcap=30.0)
+    check_attention(got_cap, ref_cap, "three width classes + chunk, soft cap")
+
+
 def test_prefill_chunk_reduced(cuda_device):
     # config-4-shaped: cached prefix + causal chunk, including a chunk that is not a
     # multiple of the tile and a prefix that is not a multiple of the block
