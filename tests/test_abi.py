@@ -36,7 +36,10 @@ def test_no_torch_or_oracle_in_the_library():
     # The shipped library must not depend on the oracle or on a tensor library.
     import subprocess
     out = subprocess.run(["ldd", pa.LIB_PATH], capture_output=True, text=True).stdout
-    assert "liboracle" not in out and "torch" not in out and "c10" not in out
+    # library names only: the load addresses ldd prints are random hex and may spell anything
+    names = " ".join(line.split("(0x")[0] for line in out.splitlines())
+    assert names.strip()
+    assert "liboracle" not in names and "torch" not in names and "c10" not in names
 
 
 def test_version_and_error_string():
