@@ -106,10 +106,17 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
     kernel<<<grid, 256, 0, st>>>(key, value, k_pool, v_pool, slot_mapping, num_tokens, key_stride,
                                  value_stride, Hkv, num_blocks, bs_shift, err);
   };
-  if (head_size == kHeadSize) go(reshape_and_cache_kernel<kHeadSize>);
-  else if (head_size == 64) go(reshape_and_cache_kernel<64>);
-  else if (head_size == 256) go(reshape_and_cache_kernel<256>);
-  else return cudaErrorInvalidValue;
+  switch (head_size) {
+    case 32: go(reshape_and_cache_kernel<32>); break;
+    case 64: go(reshape_and_cache_kernel<64>); break;
+    case 80: go(reshape_and_cache_kernel<80>); break;
+    case 96: go(reshape_and_cache_kernel<96>); break;
+    case 112: go(reshape_and_cache_kernel<112>); break;
+    case kHeadSize: go(reshape_and_cache_kernel<kHeadSize>); break;
+    case 192: go(reshape_and_cache_kernel<192>); break;
+    case 256: go(reshape_and_cache_kernel<256>); break;
+    default: return cudaErrorInvalidValue;
+  }
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return cudaGetLastError();
 }

@@ -89,7 +89,7 @@ constexpr int kMaxNT = 3;  // up to 24 columns per item
 // SUB: 16-token sub-units a warp takes from one stage (2 = a whole 32-token pool block).
 template <int NT, bool FP8 = false, int HD = kHeadSize, int SUB = 1>
 struct Cfg {
-  static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes built: 64, 128, 256");
+  static_assert(HD % 16 == 0 && HD >= 32 && HD <= 256, "head sizes built: multiples of 16 from 32 to 256");
   static_assert(SUB == 1 || (SUB == 2 && HD == kHeadSize && !FP8), "whole 32-token blocks: 16-bit pools, head size 128");
   static constexpr int kSteps = HD / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
   static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize * SUB;  // bytes of one K or V chunk
@@ -98,11 +98,12 @@ struct Cfg {
   // it wants 16 warps per SM; 128 registers per thread allow it): two 4 KB stages per
   // warp there, otherwise the ring keeps its byte size and holds twice as many stages.
   static constexpr int kCtasPerSm = (FP8 && NT == 1) ? 2 : 1;
-  // Head size 64 halves the stage, so the ring holds twice as many; head size 256 and whole
-  // 32-token blocks double it and the 227 KB of an SM hold one 16 KB stage per warp (the
-  // eight warps then overlap each other's copies instead of each its own).
-  static constexpr int kStages = (HD == 256 || SUB == 2) ? 1
-                                 : (kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1)) * (HD == 64 ? 2 : 1);
+  // Head sizes up to 64 halve the stage (or more), so the ring holds twice as many; head
+  // sizes from 192 and whole 32-token blocks make it 12 or 16 KB and the 227 KB of an SM
+  // hold one stage per warp (the eight warps then overlap each other's copies instead of
+  // each its own).
+  static constexpr int kStages = (HD >= 192 || SUB == 2) ? 1
+                                 : (kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1)) * (HD <= 64 ? 2 : 1);
   static constexpr int kAcc = 4 * kSteps;      // O^T accumulators per thread and column tile
   static constexpr int kRegs = (kAcc + 4) * NT;  // per thread: accumulators, 2NT maxima, 2NT sums
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
@@ -121,7 +122,8 @@ struct Cfg {
 constexpr int kItemCostUnits = 24;
 constexpr int kItemCostUnitsFp8 = 16;
 constexpr int kSlotFloats = 36 * kMaxNT * 32;  // one workspace slot, sized for the widest kernel
-static_assert(Cfg<1, false, 256>::kRegs * 32 <= kSlotFloats && Cfg<3, false, 64>::kRegs * 32 <= kSlotFloats,
+static_assert(Cfg<1, false, 256>::kRegs * 32 <= kSlotFloats && Cfg<2, false, 192>::kRegs * 32 <= kSlotFloats &&
+                  Cfg<3, false, 112>::kRegs * 32 <= kSlotFloats,
               "a partial of every kernel variant fits a workspace slot");
 
 __device__ __forceinline__ int q_len_of(const AttnParams &p, int seq) {
@@ -199,6 +201,7 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, const long long 
   constexpr int PP = 4;  // pieces per pass
   constexpr int CS = kThreads / HD;  // column stride of a thread
   constexpr int kAcc = 4 * (HD / 16);
+  if (tid >= CS * HD) return;        // head sizes that do not divide the block leave some threads out
   const int d = tid % HD;
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
   for (int col0 = tid / HD; col0 < ncols; col0 += CS * CP) {
@@ -1142,10 +1145,20 @@ cudaError_t launch_hd(const AttnParams &p, const KvMaps &maps, int num_ctas, cud
 
 template <int NT>
 cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cudaStream_t st) {
-  if (p.head_size == 64) return launch_hd<NT, 64>(p, maps, num_ctas, st);
-  if (p.head_size == 256) {
-    if constexpr (NT == 1) return launch_hd<1, 256>(p, maps, num_ctas, st);
-    else return cudaErrorInvalidValue;  // wider items are cut into pieces of 8 columns by the caller
+  switch (p.head_size) {
+    case kHeadSize: break;
+    case 32: return launch_hd<NT, 32>(p, maps, num_ctas, st);
+    case 64: return launch_hd<NT, 64>(p, maps, num_ctas, st);
+    case 80: return launch_hd<NT, 80>(p, maps, num_ctas, st);
+    case 96: return launch_hd<NT, 96>(p, maps, num_ctas, st);
+    case 112: return launch_hd<NT, 112>(p, maps, num_ctas, st);
+    case 192:  // wider items are cut into pieces by the caller (splitkv_max_cols_for)
+      if constexpr (NT <= 2) return launch_hd<NT, 192>(p, maps, num_ctas, st);
+      else return cudaErrorInvalidValue;
+    case 256:
+      if constexpr (NT == 1) return launch_hd<1, 256>(p, maps, num_ctas, st);
+      else return cudaErrorInvalidValue;
+    default: return cudaErrorInvalidValue;
   }
   cudaError_t e;
   if (p.bs_shift > 0 && !p.is_fp8)  // 16-bit pools of 32-token blocks: whole blocks per stage
@@ -1209,8 +1222,8 @@ cudaError_t splitkv_static_scratch(int device, float **out) {
 }
 
 int splitkv_max_cols() { return 8 * kMaxNT; }
-// Head size 256 leaves registers for one 8-column tile only.
-int splitkv_max_cols_for(int head_size) { return head_size == 256 ? 8 : 8 * kMaxNT; }
+// Head size 256 leaves registers for one 8-column tile only, 192 for two.
+int splitkv_max_cols_for(int head_size) { return head_size == 256 ? 8 : head_size == 192 ? 16 : 8 * kMaxNT; }
 
 size_t splitkv_workspace_bytes(int num_ctas) {
   return (size_t)num_ctas * 2 * kSlotFloats * sizeof(float);
@@ -1241,18 +1254,22 @@ static cudaError_t configure_nt() {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, true, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, true>::kSmemBytes);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, 64>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, 64>::kSmemBytes);
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, 64>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, 64>::kSmemBytes);
-  if (e == cudaSuccess && NT == 1)
-    e = cudaFuncSetAttribute(splitkv_kernel<1, false, false, false, false, 256>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, false, 256>::kSmemBytes);
-  if (e == cudaSuccess && NT == 1)
-    e = cudaFuncSetAttribute(splitkv_kernel<1, true, false, false, false, 256>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1, false, 256>::kSmemBytes);
+  auto head = [&](auto hd_tag) {
+    constexpr int HD = decltype(hd_tag)::value;
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, HD>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, HD>::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, HD>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, HD>::kSmemBytes);
+  };
+  head(std::integral_constant<int, 32>{});
+  head(std::integral_constant<int, 64>{});
+  head(std::integral_constant<int, 80>{});
+  head(std::integral_constant<int, 96>{});
+  head(std::integral_constant<int, 112>{});
+  if constexpr (NT <= 2) head(std::integral_constant<int, 192>{});
+  if constexpr (NT == 1) head(std::integral_constant<int, 256>{});
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, kHeadSize, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1321,9 +1338,9 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
                                      const UnitMaps *unit_maps) {
   if (p_in.bs_shift > 0 && !unit_maps) return cudaErrorInvalidValue;
   if (p_in.bs_shift < 0 && p_in.is_fp8) return cudaErrorInvalidValue;
+  // (launch_nt refuses a head size that is not built)
   if (p_in.head_size != kHeadSize &&
-      ((p_in.head_size != 64 && p_in.head_size != 256) || p_in.is_fp8 || p_in.bs_shift != 0 || p_in.k_new ||
-       p_in.max_cols > splitkv_max_cols_for(p_in.head_size)))
+      (p_in.is_fp8 || p_in.bs_shift != 0 || p_in.k_new || p_in.max_cols > splitkv_max_cols_for(p_in.head_size)))
     return cudaErrorInvalidValue;
   KvMaps maps;
   if (unit_maps) memcpy(&maps, unit_maps, sizeof(maps));

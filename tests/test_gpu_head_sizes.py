@@ -1,11 +1,13 @@
-"""Head sizes 64 and 256 (crates/mlx-paged-attn/src/config.rs:47-50 accepts 32 ... 256; 64, 128
-and 256 are built): KV write bit-exact, decode and multi-token attention against the oracle.
+"""Head sizes other than 128 (crates/mlx-paged-attn/src/config.rs:47-50 accepts 32, 64, 80, 96,
+112, 120, 128, 192, 256; all but 120 are built): KV write bit-exact, decode and multi-token
+attention against the oracle.
 
 What the library does with them: the write kernel and the split-KV kernel are compiled per
 head size (16-bit pools, 16-token blocks); the tcgen05 tile kernel, the FP8 cache, the fused
 norm + rotary + write launch and the other block sizes are head-size-128 code and are refused
-for 64 / 256 with PA_ERR_UNSUPPORTED.  Chunks too wide for the split-KV kernel (more than 24
-columns, 8 with head size 256) are served as consecutive pieces, as with 8-token blocks."""
+for the other sizes with PA_ERR_UNSUPPORTED.  Chunks too wide for the split-KV kernel (more
+than 24 columns; 16 with head size 192, 8 with 256) are served as consecutive pieces, as with
+8-token blocks."""
 import numpy as np
 import pytest
 import torch
@@ -32,7 +34,10 @@ def run_case(case, varlen=True, softcap=1.0):
     return got, ref
 
 
-@pytest.mark.parametrize("hd", [64, 256])
+OTHER_SIZES = [32, 64, 80, 96, 112, 192, 256]
+
+
+@pytest.mark.parametrize("hd", OTHER_SIZES)
 @pytest.mark.parametrize("f16", [False, True])
 @pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 4)])
 def test_decode(cuda_device, hd, f16, G, Hkv):
@@ -53,11 +58,11 @@ def test_decode(cuda_device, hd, f16, G, Hkv):
     check_attention(got_cap, ref_cap, f"decode with soft cap, head size {hd}")
 
 
-@pytest.mark.parametrize("hd", [64, 256])
+@pytest.mark.parametrize("hd", OTHER_SIZES)
 def test_verify_and_chunks_in_one_call(cuda_device, hd):
-    # decode + 5-token verify (20 columns) + prefill chunks: head size 64 takes the verify
-    # sequences in the wide split-KV variant, 256 cuts them into pieces of 2 tokens; the
-    # chunks go through the split-KV kernel in pieces for both
+    # decode + 5-token verify (20 columns) + prefill chunks: head sizes up to 112 take the
+    # verify sequences in the wide split-KV variant, 192 and 256 cut them into pieces of 4 and
+    # 2 tokens; the chunks go through the split-KV kernel in pieces for all of them
     kv = [1500, 3333, 16, 2053, 4101, 700, 300 + 77, 512 + 300]
     ql = [1, 1, 1, 5, 5, 5, 77, 300]
     case = Case(kv, ql, 32, 8, 1024, seed=70 + hd, head_size=hd)
@@ -69,17 +74,17 @@ def test_verify_and_chunks_in_one_call(cuda_device, hd):
     assert (dc.attend() == got).all()
 
 
-@pytest.mark.parametrize("hd", [64, 256])
+@pytest.mark.parametrize("hd", OTHER_SIZES)
 def test_config2_shape_reduced(cuda_device, hd):
     # configuration-2-shaped decode (32 query / 8 kv heads), 12 sequences, whole output
     rng = np.random.Generator(np.random.PCG64(hd))
     kv = rng.integers(1024, 8193, 12)
-    case = Case(kv, np.ones(12, int), 32, 8, 4096, seed=80 + hd, head_size=hd)
+    case = Case(kv, np.ones(12, int), 32, 8, 6200, seed=80 + hd, head_size=hd)
     got, ref = run_case(case, varlen=False)
     print(hd, check_attention(got, ref, f"configuration 2 reduced, head size {hd}"))
 
 
-@pytest.mark.parametrize("hd", [64, 256])
+@pytest.mark.parametrize("hd", OTHER_SIZES)
 def test_decode_step_runs_write_then_attention(cuda_device, hd):
     # the one-call decode step exists for every head size; the in-kernel write is
     # head-size-128 code, so here it is the write kernel followed by the attention kernel
@@ -98,15 +103,14 @@ def test_decode_step_runs_write_then_attention(cuda_device, hd):
 
 
 def test_what_is_refused(cuda_device):
-    # head sizes the reference accepts and this library does not build
-    for hd in (32, 80, 96, 112, 120, 192):
-        with pytest.raises(pa.PagedAttnError) as e:
-            pa.PagedCache(BS, 8, hd, 2)
-        assert e.value.status == UNSUPPORTED
+    # the one head size the reference accepts and this library does not build
+    with pytest.raises(pa.PagedAttnError) as e:
+        pa.PagedCache(BS, 8, 120, 2)
+    assert e.value.status == UNSUPPORTED
     with pytest.raises(pa.PagedAttnError) as e:   # not one of the reference's either
         pa.PagedCache(BS, 8, 100, 2)
     assert e.value.status == INVALID_ARG
-    for hd in (64, 256):
+    for hd in OTHER_SIZES:
         for bs in (8, 32):
             with pytest.raises(pa.PagedAttnError) as e:
                 pa.PagedCache(bs, 8, hd, 2)
