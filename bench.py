@@ -629,7 +629,7 @@ def main() -> None:
     ap.add_argument("--pool-blocks", type=int, default=0, help="override the pool size in blocks")
     ap.add_argument("--block-size", type=int, default=16, choices=[8, 16, 32],
                     help="tokens per pool block (the configurations are quoted on 16)")
-    ap.add_argument("--head-size", type=int, default=128, choices=[32, 64, 80, 96, 112, 128, 192, 256],
+    ap.add_argument("--head-size", type=int, default=128, choices=[32, 64, 80, 96, 112, 120, 128, 192, 256],
                     help="head size of the decode workloads (other than 128: 16-bit pools, 16-token blocks)")
     ap.add_argument("--as-rank-of", type=int, default=0, metavar="N",
                     help="on one GPU, run the share of rank 0 of an N-way kv-head split "

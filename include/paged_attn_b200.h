@@ -43,7 +43,7 @@ typedef int32_t pa_status;
 enum {
   PA_OK = 0,
   PA_ERR_INVALID_ARG = 1,  /* null pointer, bad size/stride/alignment          */
-  PA_ERR_UNSUPPORTED = 2,  /* f32 / head size / block size not built           */
+  PA_ERR_UNSUPPORTED = 2,  /* f32, or a combination of head size, block size and FP8 that is not built */
   PA_ERR_OOM = 3,          /* device allocation failed                         */
   PA_ERR_OUT_OF_RANGE = 4, /* a block id or slot outside the pool was seen     */
   PA_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out               */
@@ -61,14 +61,14 @@ int32_t pa_version(void);
 /* Same six u32 fields as the reference (crates/mlx-sys/src/lib.rs:690-705,
  * crates/mlx-sys/src/mlx.cpp:3796-3803). dtype: 0 f16, 1 bf16, 2 f32.
  * Built: head_size 128 with every block size the reference accepts (8, 16, 32;
- * crates/mlx-paged-attn/src/config.rs:40-45) and dtype 0 or 1; head_size 32,
- * 64, 80, 96, 112, 192 and 256 with block_size 16, dtype 0 or 1, no FP8 cache
- * (KV write, decode and multi-token attention; chunks of more than 24 / G query
- * tokens - 16 / G with head size 192, 8 / G with 256 - are served in pieces and
- * need context_lens_host, the fused producer launch is refused, pa_decode_step
- * runs its two kernels).  Head size 120, the last of config.rs:47-50, and dtype
- * 2 return PA_ERR_UNSUPPORTED.  An FP8 cache needs block_size 16 or 32, as in
- * the reference (config.rs:71-76).                                             */
+ * crates/mlx-paged-attn/src/config.rs:40-45) and dtype 0 or 1; the other head
+ * sizes of config.rs:47-50 (32, 64, 80, 96, 112, 120, 192, 256) with block_size
+ * 16, dtype 0 or 1, no FP8 cache (KV write, decode and multi-token attention;
+ * chunks of more than 24 / G query tokens - 16 / G with head size 192, 8 / G with
+ * 256 - are served in pieces and need context_lens_host, the fused producer
+ * launch is refused, pa_decode_step runs its two kernels).  dtype 2 returns
+ * PA_ERR_UNSUPPORTED.  An FP8 cache needs block_size 16 or 32, as in the
+ * reference (config.rs:71-76).                                                 */
 typedef struct PagedAttnConfig {
   uint32_t block_size;
   uint32_t num_blocks;

@@ -142,8 +142,6 @@ pa_status validate_config(const PagedAttnConfig *c) {
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
   if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
-  if (c->head_size % 16 != 0)  // i.e. 120, the one size of the reference's list whose rows are not whole MMA steps
-    return fail(PA_ERR_UNSUPPORTED, "head size 120 is not built (32, 64, 80, 96, 112, 128, 192 and 256 are)");
   if (c->head_size != pa::kHeadSize && c->block_size != 16)
     return fail(PA_ERR_UNSUPPORTED, "head sizes other than 128 are built for 16-token blocks");
   // with 32-token blocks a unit is addressed as 2 * (block * heads + head) + half in 32 bits

@@ -112,6 +112,7 @@ cudaError_t launch_reshape_and_cache(const elem16 *key, const elem16 *value,
     case 80: go(reshape_and_cache_kernel<80>); break;
     case 96: go(reshape_and_cache_kernel<96>); break;
     case 112: go(reshape_and_cache_kernel<112>); break;
+    case 120: go(reshape_and_cache_kernel<120>); break;
     case kHeadSize: go(reshape_and_cache_kernel<kHeadSize>); break;
     case 192: go(reshape_and_cache_kernel<192>); break;
     case 256: go(reshape_and_cache_kernel<256>); break;

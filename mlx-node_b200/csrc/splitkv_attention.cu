@@ -89,9 +89,11 @@ constexpr int kMaxNT = 3;  // up to 24 columns per item
 // SUB: 16-token sub-units a warp takes from one stage (2 = a whole 32-token pool block).
 template <int NT, bool FP8 = false, int HD = kHeadSize, int SUB = 1>
 struct Cfg {
-  static_assert(HD % 16 == 0 && HD >= 32 && HD <= 256, "head sizes built: multiples of 16 from 32 to 256");
+  // (a head size that is a multiple of 8 only - 120 - runs with its last 16-wide step half
+  // empty: the missing eight dimensions are zeros in Q and in the K fragments and are never stored)
+  static_assert(HD % 8 == 0 && HD >= 32 && HD <= 256, "head sizes built: multiples of 8 from 32 to 256");
   static_assert(SUB == 1 || (SUB == 2 && HD == kHeadSize && !FP8), "whole 32-token blocks: 16-bit pools, head size 128");
-  static constexpr int kSteps = HD / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
+  static constexpr int kSteps = (HD + 15) / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
   static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize * SUB;  // bytes of one K or V chunk
   static constexpr int kStageBytes = 2 * kChunk;
   // The narrow FP8 variant runs two CTAs per SM (its per-unit work is latency-bound, so
@@ -200,7 +202,7 @@ __device__ __forceinline__ void merge_item(const AttnParams &p, const long long 
   constexpr int CP = 4;  // columns per pass and thread
   constexpr int PP = 4;  // pieces per pass
   constexpr int CS = kThreads / HD;  // column stride of a thread
-  constexpr int kAcc = 4 * (HD / 16);
+  constexpr int kAcc = 4 * ((HD + 15) / 16);
   if (tid >= CS * HD) return;        // head sizes that do not divide the block leave some threads out
   const int d = tid % HD;
   const int mt = d >> 4, gid = d & 7, upper = (d >> 3) & 1;
@@ -620,7 +622,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
             qf[nt][j][1] = F16 ? w.y : bf16x2_to_f16x2(w.y);
           } else {
             qf[nt][j][0] = __ldg(qp + 8 * j + tig);
-            qf[nt][j][1] = __ldg(qp + 8 * j + 4 + tig);
+            qf[nt][j][1] = (HD % 16 != 0 && j == KS - 1) ? 0u : __ldg(qp + 8 * j + 4 + tig);
           }
         }
       } else {
@@ -723,6 +725,9 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
             if (B8) ldmatrix_x4(af, ks + (mi & 1) * 2048 + (2 * j + (mi >> 1)) * 128 + mr * 16);
             else if (B32) ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 512 + sub * 256 + ((mi & 1) * 8 + mr) * 16);
             else ldmatrix_x4(af, ks + (2 * j + (mi >> 1)) * 256 + ((mi & 1) * 8 + mr) * 16);
+            // the K chunk has no second row for a half-empty last step: what was read there
+            // belongs to the V chunk and 0 * NaN is NaN
+            if (HD % 16 != 0 && j == KS - 1) af[2] = af[3] = 0u;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) mma_16816<MF16>(sacc[nt], af, qf[nt][j][0], qf[nt][j][1]);
           }
@@ -1052,7 +1057,7 @@ splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
 #pragma unroll
               for (int mt = 0; mt < KS; mt++) {
                 op[16 * mt + gid] = to_elem<F16>(o[mt][nt][c] * inv);
-                op[16 * mt + gid + 8] = to_elem<F16>(o[mt][nt][c + 2] * inv);
+                if (HD % 16 == 0 || mt < KS - 1) op[16 * mt + gid + 8] = to_elem<F16>(o[mt][nt][c + 2] * inv);
               }
             }
           }
@@ -1152,6 +1157,7 @@ cudaError_t launch_nt(const AttnParams &p, const KvMaps &maps, int num_ctas, cud
     case 80: return launch_hd<NT, 80>(p, maps, num_ctas, st);
     case 96: return launch_hd<NT, 96>(p, maps, num_ctas, st);
     case 112: return launch_hd<NT, 112>(p, maps, num_ctas, st);
+    case 120: return launch_hd<NT, 120>(p, maps, num_ctas, st);
     case 192:  // wider items are cut into pieces by the caller (splitkv_max_cols_for)
       if constexpr (NT <= 2) return launch_hd<NT, 192>(p, maps, num_ctas, st);
       else return cudaErrorInvalidValue;
@@ -1268,6 +1274,7 @@ static cudaError_t configure_nt() {
   head(std::integral_constant<int, 80>{});
   head(std::integral_constant<int, 96>{});
   head(std::integral_constant<int, 112>{});
+  head(std::integral_constant<int, 120>{});
   if constexpr (NT <= 2) head(std::integral_constant<int, 192>{});
   if constexpr (NT == 1) head(std::integral_constant<int, 256>{});
   if (e == cudaSuccess)

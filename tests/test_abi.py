@@ -54,7 +54,6 @@ def test_version_and_error_string():
     ("num_blocks", 0, 1),
     ("dtype", 7, 1),
     ("dtype", 2, 2),            # f32 accepted by the reference, not built here
-    ("head_size", 120, 2),      # accepted by the reference (config.rs:47-50); the only one of its sizes not built
 ])
 def test_config_validation_needs_no_device(field, value, status):
     lib = pa.load_library()

@@ -201,7 +201,7 @@ def test_other_block_sizes_against_numpy_reference_and_index_formula(bs):
                                rtol=0, atol=1e-6)
 
 
-@pytest.mark.parametrize("hd", [32, 64, 80, 96, 112, 192, 256])
+@pytest.mark.parametrize("hd", [32, 64, 80, 96, 112, 120, 192, 256])
 def test_other_head_sizes_against_numpy_reference_and_index_formula(hd):
     """The other head sizes that are built (of those PagedAttentionConfig accepts,
     crates/mlx-paged-attn/src/config.rs:47-50): element (h, d) of the token in slot 50 lands at
