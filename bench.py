@@ -3,8 +3,10 @@
 
 A step is one pass of the path over one synthetic batch: the KV block write of
 the step's new tokens (reshape_and_cache) followed by paged attention over the
-block-table cache, the order one transformer layer runs them.  For decode
-batches both happen in one launch (pa_decode_step).
+block-table cache, the order one transformer layer runs them.  Decode batches
+go through one call (pa_decode_step): one launch while a rank holds at most
+2 x SMs (sequence, kv head) pairs - the attention kernel writes the tokens
+itself - and the write kernel chained to the attention kernel otherwise.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3]
   python bench.py --impl reference ...      # the CPU path, timed on the host cores

@@ -539,7 +539,11 @@ pa_status pa_kv_decode_step_host(PaKvBinding *b, uint32_t layer, void *out_host,
   const void *src[3] = {mapped(q_host), mapped(k_host), mapped(v_host)};
   void *dst[3] = {io + o_q, io + o_k, io + o_v};
   const size_t bytes[3] = {q_b, kv_b, kv_b};
-  const bool zero_copy = src[0] && src[1] && src[2];
+  // Small batches: the ingest launch reads the three arrays itself (one launch instead of
+  // three copies, about 10 us for 0.3 MB).  Large ones go through the copy engine, which
+  // moves a few megabytes at the full PCIe rate where SM loads from host memory reach about
+  // two thirds of it (measured: 2.6 MB in 72 us against 47 us).
+  const bool zero_copy = src[0] && src[1] && src[2] && q_b + 2 * kv_b <= ((size_t)512 << 10);
   if (!zero_copy) {
     KV_CUDA(cudaMemcpyAsync(io + o_q, q_host, q_b, cudaMemcpyHostToDevice, st));
     KV_CUDA(cudaMemcpyAsync(io + o_k, k_host, kv_b, cudaMemcpyHostToDevice, st));

@@ -238,7 +238,10 @@ class BlockAllocator:
         self.h = lib().pa_alloc_create(num_blocks, block_size)
 
     def __del__(self):
-        lib().pa_alloc_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            lib().pa_alloc_destroy(self.h)
+        except Exception:
+            pass
 
     def allocate(self):
         r = lib().pa_alloc_allocate(self.h)
@@ -297,7 +300,10 @@ class TokenTracker(_TrackerOps):
         self.h = lib().pa_tracker_create(block_size, int(enabled))
 
     def __del__(self):
-        lib().pa_tracker_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            lib().pa_tracker_destroy(self.h)
+        except Exception:
+            pass
 
     def is_enabled(self): return bool(lib().pa_tracker_is_enabled(self.h))
 
@@ -327,8 +333,11 @@ class PagedKVCacheHost(_TrackerOps):
         _check(lib().pa_kv_create(C.byref(cfg), C.byref(self.h)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().pa_kv_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            if getattr(self, "h", None):
+                lib().pa_kv_destroy(self.h)
+        except Exception:
+            pass
 
     def add_sequence(self, prompt_len):
         sid = u32()
@@ -450,7 +459,10 @@ class Scheduler:
         self.h = lib().pa_sched_create(block_size, C.byref(c) if c is not None else None)
 
     def __del__(self):
-        lib().pa_sched_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            lib().pa_sched_destroy(self.h)
+        except Exception:
+            pass
 
     def add_request(self, request_id, prompt_tokens, max_new_tokens, priority=0):
         a, n = _arr(prompt_tokens)
@@ -526,7 +538,10 @@ class HybridScheduler:
         self.h = lib().pa_hybrid_create(block_size, C.byref(c))
 
     def __del__(self):
-        lib().pa_hybrid_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            lib().pa_hybrid_destroy(self.h)
+        except Exception:
+            pass
 
     def add_request(self, request_id, prompt_tokens, max_new_tokens, priority=0):
         a, n = _arr(prompt_tokens)
@@ -610,8 +625,11 @@ class KvScaleManager:
         return cls(num_layers, alpha)
 
     def __del__(self):
-        if getattr(self, "_own", False) and self.h:
-            lib().pa_scale_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            if getattr(self, "_own", False) and self.h:
+                lib().pa_scale_destroy(self.h)
+        except Exception:
+            pass
 
     @property
     def num_layers(self): return int(lib().pa_scale_num_layers(self.h))
@@ -682,8 +700,11 @@ class InputMetadata:
         return cls(None, None, None, 0, False, 0, handle=lib().pa_metadata_dummy())
 
     def __del__(self):
-        if self.h:
-            lib().pa_metadata_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            if self.h:
+                lib().pa_metadata_destroy(self.h)
+        except Exception:
+            pass
 
     def num_seqs(self): return int(lib().pa_metadata_num_seqs(self.h))
     def num_tokens(self): return int(lib().pa_metadata_num_tokens(self.h))
@@ -739,8 +760,11 @@ class AttentionLayer:
         return cls(handle=lib().pa_layer_from_cache_config(layer_idx, num_heads, C.byref(cfg)))
 
     def __del__(self):
-        if self._owner is None and self.h:
-            lib().pa_layer_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            if self._owner is None and self.h:
+                lib().pa_layer_destroy(self.h)
+        except Exception:
+            pass
 
     def params(self):
         p = PaLayerParams()
@@ -778,8 +802,11 @@ class AttentionLayers:
         return cls(0, 0, 0, 0, 0, False, handle=lib().pa_layers_from_cache_config(num_heads, C.byref(cfg)))
 
     def __del__(self):
-        if self.h:
-            lib().pa_layers_destroy(self.h)
+        try:  # at interpreter shutdown the module's globals may already be gone
+            if self.h:
+                lib().pa_layers_destroy(self.h)
+        except Exception:
+            pass
 
     def num_layers(self): return int(lib().pa_layers_num_layers(self.h))
 
