@@ -757,8 +757,8 @@ pa_status pa_swap_in(PagedAttnCache *c, uint32_t layer, const uint32_t *ids, siz
 
 size_t pa_attention_workspace_bytes(const PagedAttnCache *c) {
   if (!c) return 0;
-  // an FP8 cache may run its narrow kernel with two CTAs per SM
-  return pa::splitkv_workspace_bytes(c->num_sms * (c->fp8 ? 2 : 1));
+  // an FP8 cache and one with small heads may run the narrow kernel with two CTAs per SM
+  return pa::splitkv_workspace_bytes(c->num_sms * pa::splitkv_narrow_ctas_per_sm((int)c->cfg.head_size, c->fp8));
 }
 
 }  // extern "C"
@@ -1056,7 +1056,8 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
       PA_CUDA(cudaEventRecord(c->ev_lane[lane - 1], ls));
       PA_CUDA(cudaStreamWaitEvent(stream, c->ev_lane[lane - 1], 0));
     }
-    cta_base += (c->fp8 && k == 0) ? 2 * share[k] : share[k];  // the narrow FP8 kernel runs two CTAs per SM
+    // (the narrow kernel may run two CTAs per SM)
+    cta_base += (k == 0 ? pa::splitkv_narrow_ctas_per_sm((int)c->cfg.head_size, c->fp8) : 1) * share[k];
     lane++;
   }
   if (tile_sms > 0) {

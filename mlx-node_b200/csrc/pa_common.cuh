@@ -309,6 +309,8 @@ cudaError_t launch_splitkv_attention(const AttnParams &p, int num_ctas, cudaStre
                                      const UnitMaps *maps = nullptr);
 size_t splitkv_workspace_bytes(int num_ctas);
 int splitkv_max_cols();
+// CTAs per SM of the narrow (8-column) kernel: 2 on an FP8 cache and on small heads
+int splitkv_narrow_ctas_per_sm(int head_size, bool fp8);
 int splitkv_max_cols_for(int head_size);
 cudaError_t splitkv_configure();  // opt-in shared memory sizes, once per device
 // Library-resident scratch for callers that cannot allocate (see splitkv_attention.cu).

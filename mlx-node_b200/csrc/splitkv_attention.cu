@@ -86,6 +86,7 @@ constexpr int kMaxNT = 3;  // up to 24 columns per item
 
 // FP8: an E4M3 cache, one byte per element; a unit is a 2 KB K chunk laid out
 // [D/16][BS][16] plus a 2 KB V chunk [D][BS], and the ring holds twice as many stages.
+constexpr int kTwoCtaMaxHead = 80;  // largest head size whose narrow kernel runs two CTAs per SM
 // SUB: 16-token sub-units a warp takes from one stage (2 = a whole 32-token pool block).
 template <int NT, bool FP8 = false, int HD = kHeadSize, int SUB = 1>
 struct Cfg {
@@ -99,13 +100,18 @@ struct Cfg {
   // The narrow FP8 variant runs two CTAs per SM (its per-unit work is latency-bound, so
   // it wants 16 warps per SM; 128 registers per thread allow it): two 4 KB stages per
   // warp there, otherwise the ring keeps its byte size and holds twice as many stages.
-  static constexpr int kCtasPerSm = (FP8 && NT == 1) ? 2 : 1;
+  // The narrow kernel on head sizes up to 80 shares an SM as well: a unit is 5 KB or less, so
+  // the per-unit latency chain weighs as in the FP8 case (measured on configuration 2 / 3
+  // shapes: head 64 0.84 / 0.87 of the HBM peak with one CTA per SM, 0.94 / 0.99 with two;
+  // head 32 0.48 -> 0.72 / 0.80).  From 96 on, two CTAs' rings no longer fit an SM.
+  static constexpr int kCtasPerSm = (NT == 1 && SUB == 1 && (FP8 || HD <= kTwoCtaMaxHead)) ? 2 : 1;
   // Head sizes up to 64 halve the stage (or more), so the ring holds twice as many; head
   // sizes from 192 and whole 32-token blocks make it 12 or 16 KB and the 227 KB of an SM
   // hold one stage per warp (the eight warps then overlap each other's copies instead of
   // each its own).
   static constexpr int kStages = (HD >= 192 || SUB == 2) ? 1
-                                 : (kCtasPerSm == 2 ? 2 : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1)) * (HD <= 64 ? 2 : 1);
+                                 : kCtasPerSm == 2 ? (HD <= 32 ? 4 : 2)
+                                                   : (NT == 1 ? 3 : 2) * (FP8 ? 2 : 1) * (HD <= 64 ? 2 : 1);
   static constexpr int kAcc = 4 * kSteps;      // O^T accumulators per thread and column tile
   static constexpr int kRegs = (kAcc + 4) * NT;  // per thread: accumulators, 2NT maxima, 2NT sums
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
@@ -266,7 +272,7 @@ constexpr uint32_t kNoBlock = 0xffffffffu;  // B8: the unit has no second pool b
 // contiguous 8 KB copy per operand, and the warp takes its two 16-token halves one after the
 // other from the same stage (the interleave of the halves is an ldmatrix address term).
 template <int NT, bool F16, bool FP8, bool B8 = false, bool FUSE = false, int HD = kHeadSize, bool B32 = false>
-__global__ void __launch_bounds__(kThreads, Cfg<NT, FP8>::kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, Cfg<NT, FP8, HD, B32 ? 2 : 1>::kCtasPerSm)
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
   static_assert(!FUSE || (NT == 1 && !FP8 && !B8), "the fused write exists for the narrow 16-bit kernel");
@@ -1228,6 +1234,7 @@ cudaError_t splitkv_static_scratch(int device, float **out) {
 }
 
 int splitkv_max_cols() { return 8 * kMaxNT; }
+int splitkv_narrow_ctas_per_sm(int head_size, bool fp8) { return (fp8 || head_size <= kTwoCtaMaxHead) ? 2 : 1; }
 // Head size 256 leaves registers for one 8-column tile only, 192 for two.
 int splitkv_max_cols_for(int head_size) { return head_size == 256 ? 8 : head_size == 192 ? 16 : 8 * kMaxNT; }
 
@@ -1357,7 +1364,9 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
   // CTAs: one per SM the caller grants, two for the variant built to share an SM, as far
   // as the workspace has partial-result slots for them.
   int num_ctas = num_sms_used;
-  if (p_in.is_fp8 && nt <= 1 && p_in.cta_base + 2 * num_sms_used <= p_in.ws_ctas) num_ctas = 2 * num_sms_used;
+  if ((p_in.is_fp8 || p_in.head_size <= kTwoCtaMaxHead) && nt <= 1 &&
+      p_in.cta_base + 2 * num_sms_used <= p_in.ws_ctas)
+    num_ctas = 2 * num_sms_used;
   if (num_ctas < 1 || num_ctas > kMaxSplitCtas || !p_in.sync || p_in.cta_base < 0 ||
       p_in.cta_base + num_ctas > p_in.ws_ctas || p_in.cta_base + num_ctas > kSyncDone - kMaxLanes ||
       p_in.lane < 0 || p_in.lane >= kMaxLanes)
