@@ -303,8 +303,11 @@ pa_status pa_gather_heads_wait(PagedAttnCache *cache, const uint32_t *my_flags, 
 void pa_swap_block_bytes(uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                          int32_t use_fp8, uint64_t *key_bytes, uint64_t *value_bytes);
 
-/* Scratch the attention calls need, for any batch on this cache's device
- * (it depends only on the device's SM count and the head size).               */
+/* Scratch the attention calls need, for any batch on this cache's device (it
+ * depends only on the device's SM count, the head size and whether the cache is
+ * FP8: partial-result slots for one CTA per SM, two where the decode kernel shares
+ * an SM - FP8 caches and head sizes up to 80).  A call given less, but at least the
+ * slots of one CTA per SM, still runs, on fewer CTAs.                           */
 size_t pa_attention_workspace_bytes(const PagedAttnCache *cache);
 
 /* Single-token decode attention: one query per sequence, all query heads of a

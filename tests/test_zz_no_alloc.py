@@ -77,3 +77,20 @@ def test_static_scratch_entry_on_an_fp8_cache(cuda_device):
         cache.check_errors()
         check_attention(bf16_to_f32(to_bits(got)), ref, f"static entry, FP8 cache, call {call}")
         check_attention(bf16_to_f32(to_bits(want)), ref, f"workspace entry, FP8 cache, call {call}")
+
+
+def test_static_scratch_entry_with_small_heads(cuda_device):
+    """Head size 64: the workspace entry runs its narrow kernel on two CTAs per SM, this entry
+    on one (the scratch has slots for one per SM): another partition of the same work, the
+    same parity bound, twice in a row on the shared scratch."""
+    case = Case([9000, 300, 4100, 17, 2500, 12000], [1] * 6, 32, 8, 2048, seed=104, head_size=64)
+    dc = DeviceCase(case)
+    dc.write()
+    k_ref, v_ref = case.pools_after_write()
+    ref = attention_oracle(case, k_ref, v_ref, varlen=False)
+    for call in range(2):
+        got = torch.full((case.S, case.Hq, 64), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dc.cache.decode_static(got, dc.q, dc.tables, dc.lens, case.S, case.Hq, case.MB, case.scale)
+        torch.cuda.synchronize()
+        dc.cache.check_errors()
+        check_attention(bf16_to_f32(to_bits(got)), ref, f"static entry, head size 64, call {call}")
