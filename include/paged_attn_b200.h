@@ -316,6 +316,8 @@ size_t pa_attention_workspace_bytes(const PagedAttnCache *cache);
  * paged_attention.rs:954-991; kernels crates/mlx-paged-attn/metal/attention/
  * paged_attention.metal:760-1260) and mlx_paged_attn_forward
  * (crates/mlx-sys/src/mlx.cpp:4041-4162).
+ *   num_q_heads   a multiple of the cache's num_kv_heads, at most 24 times it (16 with
+ *                 head size 192, 8 with 256; else PA_ERR_UNSUPPORTED)
  *   out, q        [num_seqs, num_q_heads, head_size] in the cache dtype; row strides
  *                 q_stride / out_stride in elements
  *   block_tables  int32 [num_seqs, max_blocks_per_seq], device

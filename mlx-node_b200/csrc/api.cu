@@ -806,8 +806,11 @@ pa_status attention_impl(PagedAttnCache *c, uint32_t layer, void *out, const voi
   if (num_q_heads <= 0 || num_q_heads % Hkv != 0)
     return fail(PA_ERR_INVALID_ARG, "num_q_heads must be a positive multiple of num_kv_heads");
   const int G = num_q_heads / Hkv;
-  if (G > pa::splitkv_max_cols_for((int)c->cfg.head_size) || (128 % G) != 0)
-    return fail(PA_ERR_UNSUPPORTED, "query heads per kv head must be 1, 2, 4, 8 or 16 (up to 8 with head size 256)");
+  // any group size whose columns fit the widest split-KV kernel: 24 (16 with head size 192, 8
+  // with 256); rows and columns are (query token, head of the group) pairs by plain division
+  if (G > pa::splitkv_max_cols_for((int)c->cfg.head_size))
+    return fail(PA_ERR_UNSUPPORTED, "more query heads per kv head than the kernels take: 24 (16 with head size "
+                                    "192, 8 with head size 256)");
   if (max_blocks_per_seq <= 0) return fail(PA_ERR_INVALID_ARG, "max_blocks_per_seq must be > 0");
   const int64_t row = (int64_t)num_q_heads * c->cfg.head_size;
   if (q_stride < row || out_stride < row || (q_stride & 7) || (out_stride & 7))

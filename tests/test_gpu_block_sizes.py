@@ -39,7 +39,7 @@ def run_case(case, varlen=True, softcap=1.0):
 
 
 @pytest.mark.parametrize("f16", [False, True])
-@pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 2), (16, 1)])
+@pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 2), (16, 1), (5, 8), (6, 2)])
 @pytest.mark.parametrize("bs", SIZES)
 def test_decode_edge_lengths(cuda_device, G, Hkv, f16, bs):
     # lengths around both the 16-token unit and the 32-token block boundaries

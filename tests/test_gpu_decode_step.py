@@ -25,7 +25,7 @@ def fused_step(dc, case, slots=None):
 
 
 @pytest.mark.parametrize("G,Hkv,f16", [(1, 2, False), (4, 8, False), (8, 8, False), (8, 1, False),
-                                       (4, 8, True)])
+                                       (4, 8, True), (5, 8, False), (7, 4, True), (3, 2, False)])
 def test_fused_step_pool_bit_exact_and_attention_parity(cuda_device, G, Hkv, f16):
     # contexts 1, block edges +-1, several long ones that are split across CTAs
     kv = [1, 15, 16, 17, 31, 32, 33, 255, 256, 257, 1000, 4097, 9000, 12001, 5, 700]

@@ -84,7 +84,7 @@ def run(case, ks, vs, varlen=True, softcap=1.0, exact=False):
 
 
 @pytest.mark.parametrize("f16", [False, True])
-@pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 2), (16, 1)])
+@pytest.mark.parametrize("G,Hkv", [(1, 2), (4, 8), (8, 2), (16, 1), (5, 8), (7, 4), (12, 2)])
 def test_fp8_decode_edge_lengths(cuda_device, G, Hkv, f16):
     kv = [1, 15, 16, 17, 31, 32, 33, 255, 256, 257, 1000, 4097]
     case = Case(kv, [1] * len(kv), G * Hkv, Hkv, 512, seed=81 + G, f16=f16)

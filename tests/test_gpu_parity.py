@@ -42,8 +42,12 @@ def test_golden_cases(cuda_device, name):
     check_attention(got_cap, g["out_softcap30"], name + " softcap vs golden")
 
 
-@pytest.mark.parametrize("G,Hkv", [(1, 2), (2, 8), (4, 8), (8, 8), (16, 1)])
+@pytest.mark.parametrize("G,Hkv", [(1, 2), (2, 8), (4, 8), (8, 8), (16, 1),
+                                   (3, 4), (5, 8), (6, 2), (7, 4), (12, 2), (24, 1)])
 def test_decode_edge_lengths(cuda_device, G, Hkv):
+    # (group sizes that are not powers of two too: 40 query / 8 kv heads and 28 / 4 are shapes
+    # of the Qwen family, 12 / 2 is the one the reference's parameter test uses,
+    # crates/mlx-paged-attn/src/metal/paged_attention.rs:998-1016)
     # context 1, one block exactly, k*BS +- 1, a long one, and an empty sequence
     kv = [1, 15, 16, 17, 31, 32, 33, 0, 255, 256, 257, 1000, 4097]
     ql = [1 if n > 0 else 0 for n in kv]
@@ -239,6 +243,20 @@ def test_all_width_classes_and_a_chunk_side_by_side(cuda_device):
     # and with a soft cap (the tile kernel's other variant)
     got_cap, ref_cap = run_case(case, softcap=30.0)
     check_attention(got_cap, ref_cap, "three width classes + chunk, soft cap")
+
+
+@pytest.mark.parametrize("G,Hkv,fp8", [(5, 8, False), (7, 4, False), (6, 2, False), (3, 4, False)])
+def test_mixed_batch_with_odd_group_sizes(cuda_device, G, Hkv, fp8):
+    """Decode, verify and prefill chunks in one call with 5, 7, 6 and 3 query heads per kv
+    head: columns and tile rows are (query token, head) pairs by plain division, so a
+    query's heads may straddle column tiles and the two 128-row halves of a tile CTA."""
+    kv = [1500, 3333, 16, 2053, 4101, 700, 300 + 77, 512 + 300, 9000]
+    ql = [1, 1, 1, 2, 4, 5, 77, 300, 1]
+    case = Case(kv, ql, G * Hkv, Hkv, 1600, seed=40 + G)
+    got, ref = run_case(case)
+    print("G", G, check_attention(got, ref, f"mixed batch, {G} query heads per kv head"))
+    got_cap, ref_cap = run_case(case, softcap=30.0)
+    check_attention(got_cap, ref_cap, f"mixed batch with soft cap, {G} query heads per kv head")
 
 
 def test_prefill_chunk_reduced(cuda_device):
