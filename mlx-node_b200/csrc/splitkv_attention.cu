@@ -10,9 +10,13 @@
 // Work decomposition.  A unit is one (sequence, kv head, 16-token block): a 4 KB
 // K chunk plus a 4 KB V chunk, each contiguous in the pool.  Units are numbered
 // item-major (item = sequence*Hkv + kv head, then block index) and the flat range
-// [0, W) is cut into gridDim.x equal pieces, one persistent CTA per SM each, so
-// that ragged context lengths balance to within one unit.  A CTA walks the items
-// its piece overlaps ("segments").  A segment that covers its whole item writes
+// [0, W) is cut into gridDim.x pieces of equal COST, one persistent CTA per SM each:
+// cost = units + item_cost per item start (starting an item costs a CTA about 4 us of
+// query loads, warp combine, partial store and merge during which its ring idles), so
+// that a CTA whose range holds many short sequences gets fewer units and all CTAs
+// finish together.  The boundaries of all pieces are computed once per CTA into shared
+// memory (bnd[]); which CTAs hold pieces of an item is read from that table.  A CTA
+// walks the items its piece overlaps ("segments").  A segment that covers its whole item writes
 // the final bf16 rows; a segment that starts or ends inside an item writes an
 // unnormalised partial (running max, sum, accumulator) to one of the CTA's two
 // workspace slots and counts itself on the item's arrival counter; the CTA that
@@ -49,11 +53,13 @@
 // computed next to the softmax and P.V of the current one, so that the two dependency
 // chains (ldmatrix -> MMA chain, and max -> exp2 -> movmatrix -> MMA) overlap.
 //
-// 32-token pool blocks (p.bs_shift = 1): the unit stays 16 tokens.  A (block, kv head)
-// chunk then holds two units interleaved row by row, and a unit comes in through two
-// tensor-map copies (a [D/8] x 256 B box of the K chunk, a [D] x 32 B box of the V chunk)
-// that land in the ring stage in exactly the layout of a 16-token chunk; everything after
-// the copy is the same code.
+// 32-token pool blocks (p.bs_shift = 1).  16-bit pools (template flag B32): a unit is a
+// whole block, one contiguous 8 KB bulk copy per operand into a 16 KB stage (one stage per
+// warp), and the warp takes the block's two 16-token halves one after the other from it;
+// the halves interleave row by row in the chunk, which is an ldmatrix address term.  FP8
+// pools: the unit stays 16 tokens and comes in through two tensor-map copies (a [D/16] x
+// 256 B box of the K chunk, a [D] x 16 B box of the V chunk) that land in the ring stage
+// in exactly the layout of a 16-token chunk; everything after the copy is the same code.
 //
 // 8-token pool blocks (p.bs_shift = -1, template flag B8; 16-bit pools): a unit is two pool
 // blocks with ids of their own, four 2 KB bulk copies into the stage (K of the first block,
@@ -61,6 +67,14 @@
 // token half from the 2 KB sub-chunk instead of from the row.  Block ids are looked up 16
 // units at a time, lane 2i and 2i+1 holding the two blocks of unit i; a last unit of eight
 // tokens or fewer has no second block and copies half the bytes.
+//
+// Head sizes other than 128 (template parameter HD, 16-bit pools of 16-token blocks): chunks
+// of 32 * HD bytes, ceil(HD / 16) steps of the head dimension and as many row tiles of O^T
+// (120 runs with its last step half empty); up to head size 80 the narrow kernel runs two
+// CTAs per SM, from 192 on the ring is one stage per warp.
+//
+// Several launches of one call may run at the same time, one per width class of a mixed
+// batch ("lanes"): each keeps its partial slots and arrival counters from cta_base on.
 //
 // FP8 (E4M3) pools: the same kernel on 2 KB chunks.  K.Q^T runs on the FP8 tensor-core
 // path straight from the cache bytes (queries split into two E4M3 numbers) unless the
