@@ -63,7 +63,8 @@ int32_t pa_version(void);
  * Built: head_size 128 with every block size the reference accepts (8, 16, 32;
  * crates/mlx-paged-attn/src/config.rs:40-45) and dtype 0 or 1; the other head
  * sizes of config.rs:47-50 (32, 64, 80, 96, 112, 120, 192, 256) with block_size
- * 16, dtype 0 or 1, no FP8 cache (KV write, decode and multi-token attention;
+ * 16 - and, up to head size 120, with the reference's default block_size 32 -
+ * dtype 0 or 1, no FP8 cache (KV write, decode and multi-token attention;
  * chunks of more than 24 / G query tokens - 16 / G with head size 192, 8 / G with
  * 256 - are served in pieces and need context_lens_host, the fused producer
  * launch is refused, pa_decode_step runs its two kernels).  dtype 2 returns

@@ -76,7 +76,9 @@ struct PagedAttnCache {
   // one 16-token unit of a chunk for the split-KV kernel
   int bs_shift = 0;
   std::vector<pa::UnitMaps> unit_maps;
-  const pa::UnitMaps *unit_map(uint32_t layer) const { return bs_shift > 0 ? &unit_maps[layer] : nullptr; }
+  const pa::UnitMaps *unit_map(uint32_t layer) const {
+    return bs_shift > 0 && !unit_maps.empty() ? &unit_maps[layer] : nullptr;
+  }
   // the tcgen05 tile kernel reads pools of 16- or 32-token blocks (16-bit or FP8)
   bool has_tile_kernel() const { return bs_shift >= 0 && cfg.head_size == (uint32_t)pa::kHeadSize; }
   unsigned *err_dev = nullptr;
@@ -142,8 +144,9 @@ pa_status validate_config(const PagedAttnConfig *c) {
     return fail(PA_ERR_INVALID_ARG, "num_blocks, num_kv_heads and num_layers must be > 0");
   if (c->dtype > 2) return fail(PA_ERR_INVALID_ARG, "dtype must be 0 (f16), 1 (bf16) or 2 (f32)");
   if (c->dtype == 2) return fail(PA_ERR_UNSUPPORTED, "dtype 2 (f32) is not built; use 0 (f16) or 1 (bf16)");
-  if (c->head_size != pa::kHeadSize && c->block_size != 16)
-    return fail(PA_ERR_UNSUPPORTED, "head sizes other than 128 are built for 16-token blocks");
+  if (c->head_size != pa::kHeadSize && (c->block_size == 8 || (c->block_size == 32 && c->head_size > pa::kHeadSize)))
+    return fail(PA_ERR_UNSUPPORTED, "head sizes other than 128 are built for 16-token blocks and, up to 128, "
+                                    "for 32-token blocks");
   // with 32-token blocks a unit is addressed as 2 * (block * heads + head) + half in 32 bits
   if (c->block_size == 32 && (uint64_t)c->num_blocks * c->num_kv_heads >= (1ull << 31))
     return fail(PA_ERR_INVALID_ARG, "num_blocks * num_kv_heads must be below 2^31 with block_size 32");
@@ -190,7 +193,7 @@ pa_status finish_create(PagedAttnCache *c) {
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::tile64_encode_k_map(&c->k_maps[i], c->k[i], (uint64_t)c->cfg.num_blocks * c->cfg.num_kv_heads));
   }
-  if (c->bs_shift > 0) {
+  if (c->bs_shift > 0 && c->cfg.head_size == (uint32_t)pa::kHeadSize) {
     c->unit_maps.resize(c->cfg.num_layers);
     for (uint32_t i = 0; i < c->cfg.num_layers; i++)
       PA_CUDA(pa::encode_unit_maps(&c->unit_maps[i], c->k[i], c->v[i],

@@ -107,7 +107,8 @@ struct Cfg {
   // (a head size that is a multiple of 8 only - 120 - runs with its last 16-wide step half
   // empty: the missing eight dimensions are zeros in Q and in the K fragments and are never stored)
   static_assert(HD % 8 == 0 && HD >= 32 && HD <= 256, "head sizes built: multiples of 8 from 32 to 256");
-  static_assert(SUB == 1 || (SUB == 2 && HD == kHeadSize && !FP8), "whole 32-token blocks: 16-bit pools, head size 128");
+  static_assert(SUB == 1 || (SUB == 2 && HD <= kHeadSize && !FP8),
+                "whole 32-token blocks: 16-bit pools, head sizes up to 128 (a stage is 64 * HD bytes)");
   static constexpr int kSteps = (HD + 15) / 16;  // 16-wide steps of the head dimension (K.Q^T) = 16-row tiles of O^T
   static constexpr int kChunk = (FP8 ? kChunkBytes / 2 : kChunkBytes) * HD / kHeadSize * SUB;  // bytes of one K or V chunk
   static constexpr int kStageBytes = 2 * kChunk;
@@ -290,8 +291,8 @@ __global__ void __launch_bounds__(kThreads, Cfg<NT, FP8, HD, B32 ? 2 : 1>::kCtas
 splitkv_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
   static_assert(!(FP8 && B8), "8-token blocks exist for 16-bit pools only");
   static_assert(!FUSE || (NT == 1 && !FP8 && !B8), "the fused write exists for the narrow 16-bit kernel");
-  static_assert(HD == kHeadSize || (!FP8 && !B8 && !FUSE), "other head sizes: 16-bit pools, 16-token blocks");
-  static_assert(!B32 || (!FP8 && !B8 && !FUSE && HD == kHeadSize), "whole 32-token blocks: 16-bit pools, head size 128");
+  static_assert(HD == kHeadSize || (!FP8 && !B8 && !FUSE), "other head sizes: 16-bit pools, 16- or 32-token blocks");
+  static_assert(!B32 || (!FP8 && !B8 && !FUSE && HD <= kHeadSize), "whole 32-token blocks: 16-bit pools, head sizes up to 128");
   constexpr int SUB = B32 ? 2 : 1;       // 16-token sub-units per unit
   using C = Cfg<NT, FP8, HD, SUB>;
   constexpr int KS = C::kSteps;          // 16-wide steps of the head dimension / 16-row tiles of O^T
@@ -1159,11 +1160,21 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 // Head sizes 64 and 256: 16-bit pools with 16-token blocks, attention only.
 template <int NT, int HD>
 cudaError_t launch_hd(const AttnParams &p, const KvMaps &maps, int num_ctas, cudaStream_t st) {
-  const cudaError_t e =
-      p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, false, false, HD>, dim3(num_ctas),
-                                  dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps)
-               : launch_dependent(splitkv_kernel<NT, false, false, false, false, HD>, dim3(num_ctas),
-                                  dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps);
+  cudaError_t e;
+  if (p.bs_shift > 0) {  // 32-token blocks: whole blocks per stage, head sizes up to 128
+    if constexpr (HD <= kHeadSize)
+      e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, false, false, HD, true>, dim3(num_ctas),
+                                      dim3(kThreads), Cfg<NT, false, HD, 2>::kSmemBytes, st, p, maps)
+                   : launch_dependent(splitkv_kernel<NT, false, false, false, false, HD, true>, dim3(num_ctas),
+                                      dim3(kThreads), Cfg<NT, false, HD, 2>::kSmemBytes, st, p, maps);
+    else
+      return cudaErrorInvalidValue;
+  } else {
+    e = p.is_f16 ? launch_dependent(splitkv_kernel<NT, true, false, false, false, HD>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps)
+                 : launch_dependent(splitkv_kernel<NT, false, false, false, false, HD>, dim3(num_ctas),
+                                    dim3(kThreads), Cfg<NT, false, HD>::kSmemBytes, st, p, maps);
+  }
   __atomic_fetch_add(&g_launch_count, 1ull, __ATOMIC_RELAXED);
   return e;
 }
@@ -1289,6 +1300,14 @@ static cudaError_t configure_nt() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, HD>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, HD>::kSmemBytes);
+    if constexpr (HD <= kHeadSize) {
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(splitkv_kernel<NT, false, false, false, false, HD, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, HD, 2>::kSmemBytes);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(splitkv_kernel<NT, true, false, false, false, HD, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NT, false, HD, 2>::kSmemBytes);
+    }
   };
   head(std::integral_constant<int, 32>{});
   head(std::integral_constant<int, 64>{});
@@ -1364,11 +1383,12 @@ cudaError_t encode_unit_maps(UnitMaps *out, const void *k_pool, const void *v_po
 
 cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, cudaStream_t st,
                                      const UnitMaps *unit_maps) {
-  if (p_in.bs_shift > 0 && !unit_maps) return cudaErrorInvalidValue;
+  if (p_in.bs_shift > 0 && p_in.is_fp8 && !unit_maps) return cudaErrorInvalidValue;
   if (p_in.bs_shift < 0 && p_in.is_fp8) return cudaErrorInvalidValue;
   // (launch_nt refuses a head size that is not built)
   if (p_in.head_size != kHeadSize &&
-      (p_in.is_fp8 || p_in.bs_shift != 0 || p_in.k_new || p_in.max_cols > splitkv_max_cols_for(p_in.head_size)))
+      (p_in.is_fp8 || p_in.bs_shift < 0 || (p_in.bs_shift > 0 && p_in.head_size > kHeadSize) || p_in.k_new ||
+       p_in.max_cols > splitkv_max_cols_for(p_in.head_size)))
     return cudaErrorInvalidValue;
   KvMaps maps;
   if (unit_maps) memcpy(&maps, unit_maps, sizeof(maps));
@@ -1378,7 +1398,7 @@ cudaError_t launch_splitkv_attention(const AttnParams &p_in, int num_sms_used, c
   // CTAs: one per SM the caller grants, two for the variant built to share an SM, as far
   // as the workspace has partial-result slots for them.
   int num_ctas = num_sms_used;
-  if ((p_in.is_fp8 || p_in.head_size <= kTwoCtaMaxHead) && nt <= 1 &&
+  if ((p_in.is_fp8 || (p_in.head_size <= kTwoCtaMaxHead && p_in.bs_shift == 0)) && nt <= 1 &&
       p_in.cta_base + 2 * num_sms_used <= p_in.ws_ctas)
     num_ctas = 2 * num_sms_used;
   if (num_ctas < 1 || num_ctas > kMaxSplitCtas || !p_in.sync || p_in.cta_base < 0 ||

@@ -3,9 +3,9 @@
 against the oracle.
 
 What the library does with them: the write kernel and the split-KV kernel are compiled per
-head size (16-bit pools, 16-token blocks); the tcgen05 tile kernel, the FP8 cache, the fused
-norm + rotary + write launch and the other block sizes are head-size-128 code and are refused
-for the other sizes with PA_ERR_UNSUPPORTED.  Chunks too wide for the split-KV kernel (more
+head size (16-bit pools; 16-token blocks, and 32-token blocks up to head size 128); the tcgen05
+tile kernel, the FP8 cache, the fused norm + rotary + write launch and 8-token blocks are
+head-size-128 code and are refused for the other sizes with PA_ERR_UNSUPPORTED.  Chunks too wide for the split-KV kernel (more
 than 24 columns; 16 with head size 192, 8 with 256) are served as consecutive pieces, as with
 8-token blocks."""
 import numpy as np
@@ -102,12 +102,29 @@ def test_decode_step_runs_write_then_attention(cuda_device, hd):
                     f"decode step, head size {hd}")
 
 
+@pytest.mark.parametrize("hd", [h for h in OTHER_SIZES if h <= 128])
+def test_32_token_blocks(cuda_device, hd):
+    """The reference's default block size (crates/mlx-paged-attn/src/config.rs:128) with the
+    head sizes up to 128: a warp takes a whole 32-token block from one stage."""
+    kv = [1, 15, 16, 17, 31, 32, 33, 47, 48, 49, 64, 255, 256, 257, 1000, 4097, 9000]
+    case = Case(kv, [1] * len(kv), 32, 8, 600, seed=95 + hd, head_size=hd, bs=32)
+    got, ref = run_case(case, varlen=False)
+    print(hd, check_attention(got, ref, f"decode, 32-token blocks, head size {hd}"))
+    # verify widths and a chunk (served in pieces) in one call
+    kv2, ql2 = [700, 64, 1029, 300, 2500, 17, 300 + 40], [1, 2, 3, 6, 5, 1, 40]
+    case2 = Case(kv2, ql2, 8, 2, 200, seed=96 + hd, head_size=hd, bs=32)
+    got2, ref2 = run_case(case2)
+    check_attention(got2, ref2, f"verify widths and a chunk, 32-token blocks, head size {hd}")
+
+
 def test_what_is_refused(cuda_device):
     with pytest.raises(pa.PagedAttnError) as e:   # not one of the reference's either
         pa.PagedCache(BS, 8, 100, 2)
     assert e.value.status == INVALID_ARG
     for hd in OTHER_SIZES:
         for bs in (8, 32):
+            if bs == 32 and hd <= 128:
+                continue   # built: test_32_token_blocks
             with pytest.raises(pa.PagedAttnError) as e:
                 pa.PagedCache(bs, 8, hd, 2)
             assert e.value.status == UNSUPPORTED
