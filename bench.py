@@ -540,10 +540,10 @@ def e2e_leg(w, steps, dist):
         torch.cuda.synchronize()
 
     fn, h2d, d2h, entry = w.host_step_fn()
-    for _ in range(3):
+    for _ in range(5):
         fn()
     barrier()
-    n_e2e = max(10, min(steps, 100))
+    n_e2e = max(50 if w.decode_only else 10, min(steps, 100))  # enough calls for a steady figure
     t0 = time.perf_counter()
     for _ in range(n_e2e):
         fn()
