@@ -23,7 +23,7 @@ import numpy_reference  # noqa: E402
 from pa_testlib import Case  # noqa: E402
 
 CASES = {
-    # name: (kv_lens, q_lens, Hq, Hkv, NB, seed[, tokens per pool block = 16])
+    # name: (kv_lens, q_lens, Hq, Hkv, NB, seed[, tokens per pool block = 16[, head size = 128]])
     "decode_g2": ([1, 15, 16, 17, 100, 33], [1, 1, 1, 1, 1, 1], 4, 2, 32, 11),
     "decode_g4": ([257, 64, 5, 300], [1, 1, 1, 1], 8, 2, 64, 12),
     "decode_g8": ([40, 129], [1, 1], 8, 1, 16, 13),
@@ -31,6 +31,10 @@ CASES = {
     "prefill_g4": ([96, 50], [64, 50], 4, 1, 16, 15),
     "mixed_block32": ([1, 31, 32, 33, 100, 75], [1, 1, 1, 3, 1, 40], 8, 2, 16, 16, 32),
     "mixed_block8": ([1, 7, 8, 9, 100, 75], [1, 1, 1, 3, 1, 40], 8, 2, 64, 17, 8),
+    # ... [, head size = 128]: other head sizes and group sizes that are not powers of two
+    "decode_g5_head64": ([1, 16, 17, 300, 45], [1, 1, 1, 1, 1], 10, 2, 32, 18, 16, 64),
+    "mixed_g3_head256": ([33, 70, 21, 90], [1, 2, 1, 30], 6, 2, 16, 19, 16, 256),
+    "decode_g7_head120": ([5, 129, 64], [1, 1, 1], 7, 1, 16, 20, 16, 120),
 }
 
 
@@ -68,7 +72,8 @@ def digest(*arrays) -> str:
 
 def build(name):
     kv, ql, Hq, Hkv, NB, seed, *rest = CASES[name]
-    return Case(kv, ql, Hq, Hkv, NB, seed=seed, bs=rest[0] if rest else 16)
+    return Case(kv, ql, Hq, Hkv, NB, seed=seed, bs=rest[0] if rest else 16,
+                head_size=rest[1] if len(rest) > 1 else 128)
 
 
 def main():
@@ -82,7 +87,7 @@ def main():
         k_exp = case.k_pool.copy()
         v_exp = case.v_pool.copy()
         blk, off = case.slots_all // case.bs, case.slots_all % case.bs
-        k_exp[blk, :, :, off, :] = case.k_all.reshape(-1, case.Hkv, 16, 8)
+        k_exp[blk, :, :, off, :] = case.k_all.reshape(-1, case.Hkv, case.D // 8, 8)
         v_exp[blk, :, :, off] = case.v_all
         assert (k_exp == k_pool).all() and (v_exp == v_pool).all(), name
         out = numpy_reference.paged_attention(case.q, k_exp, v_exp, case.block_tables,

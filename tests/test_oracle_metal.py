@@ -34,7 +34,8 @@ def distance(case, softcap=1.0):
     return float(rel), float(np.abs(exact - metal).max())
 
 
-DECODE_FIXTURES = [n for n in sorted(make_golden.CASES) if n.startswith("decode")]
+# (the restatement follows the Metal kernel at its head-size-128 template constants)
+DECODE_FIXTURES = [n for n in sorted(make_golden.CASES) if n.startswith("decode") and "head" not in n]
 
 
 @pytest.mark.parametrize("name", DECODE_FIXTURES)
