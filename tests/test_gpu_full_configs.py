@@ -159,12 +159,6 @@ class FullCase:
         return stats
 
 
-def tile_edge_queries(G):
-    """Queries on either side of every Q-tile edge (128 rows = 128 / G queries) of a chunk."""
-    step = 128 // G
-    return lambda ql: sorted({j for j in range(ql) if j % step in (0, step - 1)} | {ql - 1})
-
-
 @pytest.mark.parametrize("name", ["c1", "c2", "c3"])
 def test_decode_configuration_full_size(cuda_device, name):
     c = FullCase(name)
@@ -180,13 +174,18 @@ def test_decode_configuration_full_size(cuda_device, name):
     assert torch.equal(out.view(torch.int16), as_varlen.view(torch.int16)), "decode != varlen(q_len=1)"
 
 
-def test_chunked_prefill_configuration_full_size(cuda_device):
+@pytest.mark.parametrize("half", [0, 1])
+def test_chunked_prefill_configuration_full_size(cuda_device, half):
+    """Configuration 4 at full size, every output row against the fp64 oracle: four of the
+    eight sequences per test (8192 queries x 32 heads x ~9200 keys each is about 25 s of host
+    arithmetic, well inside the per-test limit)."""
     c = FullCase("c4")
     c.write_all()
     c.check_pools_against_torch_scatter()
     out = c.attend(varlen=True)
     assert torch.isfinite(out.float()).all()
-    print("c4", c.check_sequences(out, [0, 3, 7], "c4 full size", tile_edge_queries(c.Hq // c.Hkv)))
+    for pair in ([0, 1], [2, 3]) if half == 0 else ([4, 5], [6, 7]):
+        print("c4", pair, c.check_sequences(out, pair, f"c4 full size, whole output, sequences {pair}"))
     again = c.attend(varlen=True)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "not deterministic"
 
@@ -199,6 +198,6 @@ def test_mixed_configuration_full_size(cuda_device):
     assert torch.isfinite(out.float()).all()
     # decode (0..47), verify (48..55) and prefill (56, 57) sequences
     print("c5 decode + verify", c.check_sequences(out, list(range(56)), "c5 decode and verify, whole output"))
-    print("c5 prefill", c.check_sequences(out, [56, 57], "c5 prefill chunks", tile_edge_queries(c.Hq // c.Hkv)))
+    print("c5 prefill", c.check_sequences(out, [56, 57], "c5 prefill chunks, whole output"))
     again = c.attend(varlen=True)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "not deterministic"
